@@ -1,0 +1,74 @@
+"""Seeded synthetic inputs for the parity configurations (test infrastructure only).
+
+The reference has no dataset: every test and perf input is `np.random` data
+(test_li_triton.py:30-36, test_sfa_triton.py:47-85, perf_sfa_triton.py:35-62).  The
+generators below follow that recipe: one RandomState per case, fp32 normal draws in the
+order the reference tests draw them, rounded to the io dtype so that the CUDA kernels
+and the oracle see identical values.
+"""
+import numpy as np
+
+from .li_oracle import round_bf16
+
+
+def round_io(x, dtype):
+    if dtype == "fp16":
+        return x.astype(np.float16).astype(np.float32)
+    return round_bf16(x.astype(np.float32))
+
+
+def li_inputs(seed, B, S1, S2, N1, N2, D, dtype="bf16", w_scale=None):
+    """q, k, w drawn in that order (test_li_triton.py:32-35); w stays fp32."""
+    rng = np.random.RandomState(seed)
+    q = round_io(rng.randn(B, S1, N1, D).astype(np.float32), dtype)
+    k = round_io(rng.randn(B, S2, N2, D).astype(np.float32), dtype)
+    w_scale = (1.0 / np.sqrt(N1)) if w_scale is None else w_scale
+    w = (rng.randn(B, S1, N1).astype(np.float32) * np.float32(w_scale)).astype(np.float32)
+    return q, k, w
+
+
+def sparse_indices(seed, B, S1, S2, count, block=1, sparse_mode=3, act_q=None, act_k=None):
+    """Front-packed ascending distinct block ids inside each row's causal window, -1 padded
+    (the contract of test_sfa_triton.py:63-85)."""
+    rng = np.random.RandomState(seed)
+    si = np.full((B, S1, 1, count), -1, dtype=np.int32)
+    for b in range(B):
+        aq = S1 if act_q is None else int(act_q[b])
+        ak = S2 if act_k is None else int(act_k[b])
+        for s1 in range(aq):
+            thr = ak if sparse_mode == 0 else ak - aq + s1 + 1
+            if thr <= 0:
+                continue
+            nblk = int(np.ceil(thr / block))
+            n = min(count, nblk)
+            si[b, s1, 0, :n] = np.sort(rng.permutation(nblk)[:n]).astype(np.int32)
+    return si
+
+
+def sfa_inputs(seed, B, S1, S2, N1, D=512, Dr=64, dtype="bf16"):
+    """q, k, v (drawn, unused), q_rope, k_rope in the reference's order (test_sfa_triton.py:54-58)."""
+    rng = np.random.RandomState(seed)
+
+    def draw(*shape):
+        return round_io(rng.randn(*shape).astype(np.float32), dtype)
+
+    q = draw(B, S1, N1, D)
+    k = draw(B, S2, 1, D)
+    draw(B, S2, 1, D)  # value: drawn to keep the stream aligned, ignored by the operator
+    qr = draw(B, S1, N1, Dr)
+    kr = draw(B, S2, 1, Dr)
+    return q, k, qr, kr
+
+
+# The two CPU-sized configurations of the benchmark specification.
+def config1():
+    """LI, seed 0, B=1, S1=S2=512, N1=8, N2=1, D=128, bf16, fp32 w ~ N(0,1)/sqrt(N1), k=64, mode 3."""
+    q, k, w = li_inputs(0, 1, 512, 512, 8, 1, 128, "bf16")
+    return dict(q=q, k=k, w=w, sparse_count=64, sparse_mode=3)
+
+
+def config2():
+    """SFA, seed 1, B=1, S1=256, S2=1024, N1=16, D=512, Dr=64, k=256 token-wise, mode 3."""
+    q, k, qr, kr = sfa_inputs(1, 1, 256, 1024, 16)
+    si = sparse_indices(1001, 1, 256, 1024, 256)
+    return dict(q=q, k=k, qr=qr, kr=kr, idx=si, scale=1.0 / np.sqrt(576.0), sparse_mode=3)

@@ -1,0 +1,75 @@
+"""Generate tests/golden/*.npz from the UNMODIFIED reference goldens.
+
+Run in a container that has the reference checkout:
+    python tests/golden/make_golden.py /path/to/reference
+It imports lightning_indexer_numpy.lightning_indexer_golden_bsnd and
+sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd from that checkout, runs
+them on the seeded inputs of tests/golden/cases.py and stores only the outputs (inputs are
+regenerated from the seeds).  For cases with `rows_every` only the listed rows are kept.
+The stored arrays pin the numpy restatement under oracle/ (tests/test_oracle_golden.py).
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from tests.golden.cases import LI_CASES, SFA_CASES, case_rows, li_case_inputs, sfa_case_inputs  # noqa: E402
+
+
+def main(ref_dir):
+    sys.path.insert(0, ref_dir)
+    import lightning_indexer_numpy as ref_li
+    import sparse_flash_attention_numpy as ref_sfa
+
+    for name in LI_CASES:
+        q, k, w, act_q, act_k, c = li_case_inputs(name)
+        out = {}
+        for tag, patch in (("io", False), ("fp32", True)):
+            # "fp32" ranks un-rounded scores: the reference golden with its score
+            # quantisation switched off (what the device path's fp32 top-k ranks).
+            saved = ref_li._quantize
+            if patch:
+                ref_li._quantize = lambda x, value_dtype: x
+            try:
+                idx, val = ref_li.lightning_indexer_golden_bsnd(
+                    q, k, w, act_q, act_k, sparse_count=c["k"], sparse_mode=c["mode"],
+                    return_value=True, value_dtype=c["dtype"])
+            finally:
+                ref_li._quantize = saved
+            rows = case_rows(c, act_q)
+            sel = np.asarray(rows, dtype=np.int64).reshape(-1, 2)
+            out[f"idx_{tag}"] = idx[sel[:, 0], sel[:, 1]]
+            out[f"val_{tag}"] = val[sel[:, 0], sel[:, 1]]
+            out["rows"] = sel
+            if "rows_every" not in c:
+                # untouched rows (s1 >= act_q) must stay -1 / 0 in the full output
+                assert (idx[~_row_mask(idx.shape, sel)] == -1).all()
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+        print(name, {k_: v.shape for k_, v in out.items()})
+
+    for name in SFA_CASES:
+        q, k, qr, kr, idx, act_q, act_k, scale, c = sfa_case_inputs(name)
+        dt = ref_sfa.BF16 if c["dtype"] == "bf16" else np.float16
+        o, smax, ssum = ref_sfa.sparse_flash_attention_golden_bsnd(
+            q, k, k, idx, qr, kr, scale, act_q, act_k, sparse_block_size=c["block"],
+            sparse_mode=c["mode"], return_softmax_lse=True, dtype=dt)
+        rows = case_rows(c, act_q)
+        sel = np.asarray(rows, dtype=np.int64).reshape(-1, 2)
+        np.savez_compressed(
+            os.path.join(HERE, name + ".npz"), rows=sel,
+            out=o[sel[:, 0], sel[:, 1]].astype(np.float16 if c["dtype"] == "fp16" else np.float32),
+            smax=smax[sel[:, 0], 0, sel[:, 1]], ssum=ssum[sel[:, 0], 0, sel[:, 1]])
+        print(name, o.shape, len(rows))
+
+
+def _row_mask(shape, sel):
+    m = np.zeros(shape[:2], dtype=bool)
+    m[sel[:, 0], sel[:, 1]] = True
+    return m
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
