@@ -1,0 +1,449 @@
+"""Benchmark of the DSA forward hot path: lightning_indexer (score + top-k) feeding
+sparse_flash_attention forward, at S=8K, topk=2048.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
+
+One step = one pass of the hot path over one synthetic batch:
+  * indexer:   B=1, S1=S2=8192, 64 heads, D=128, bf16, fp32 weights, sparse_count=2048, mode 3
+  * attention: TND, sequence lengths 8192/4096/2048/1024 (15360 tokens), 128 heads, D=512+64,
+               bf16, top-k 2048 token-wise, mode 3, indices taken from an indexer run over the
+               same token layout (done once, outside the timed region), softmax stats returned.
+`value` is attention forward TFLOP/s over all ranks (valid query-key pairs x 128 heads x
+2*(576+512) flop); the indexer's query-tokens/s (score + top-k) is reported beside it.  Every
+rank works on its own seeded batch (weak scaling, no collective on the data path); the timed
+region is bracketed by a barrier and a device synchronise, timed with CUDA events on the launch
+stream, max over ranks.  `e2e` repeats the step through the public Python operators with
+pinned HOST buffers: host->device copies of every input and device->host copies of every result
+are inside its timed region.
+
+`--impl reference` times the CPU implementation of the same path (the numpy restatement of the
+reference goldens under oracle/, run over all host cores) on a bounded sample of the same
+workload and prints the same JSON line with "impl": "reference".
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "SFA-fwd TFLOP/s at S=8K, topk=2048 (LI+top-k query-tokens/s beside it)"
+UNIT = "TFLOP/s"
+SEQ_LENS = [8192, 4096, 2048, 1024]
+TOPK = 2048
+LI_S, LI_HEADS, LI_D = 8192, 64, 128
+SFA_HEADS, SFA_D, SFA_DR = 128, 512, 64
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def sfa_flops(lens=SEQ_LENS, topk=TOPK, heads=SFA_HEADS, d=SFA_D, dr=SFA_DR):
+    """2 flop per multiply-add over valid (token, key) pairs: QK^T over d+dr, PV over d."""
+    pairs = sum(sum(min(topk, s + 1) for s in range(L)) for L in lens)
+    return float(pairs) * heads * 2.0 * (d + dr + d), pairs
+
+
+def li_flops(S=LI_S, heads=LI_HEADS, d=LI_D):
+    pairs = S * (S + 1) // 2
+    return float(pairs) * heads * 2.0 * d, pairs
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def make_gpu_batch(torch, seed, lens, quick):
+    """Synthetic batch resident in HBM: N(0,1) bf16 activations, fp32 weights N(0,1)/8."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    bf = torch.bfloat16
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    S = lens[0]
+    T = sum(lens)
+    b = {}
+    b["li_q"] = rn(1, S, LI_HEADS, LI_D).to(bf)
+    b["li_k"] = rn(1, S, 1, LI_D).to(bf)
+    b["li_w"] = rn(1, S, LI_HEADS) / 8
+    # indexer inputs over the attention batch's token layout (only used to make the indices)
+    iq = rn(T, LI_HEADS, LI_D).to(bf)
+    ik = rn(T, 1, LI_D).to(bf)
+    iw = rn(T, LI_HEADS) / 8
+    b["q"] = torch.empty(T, SFA_HEADS, SFA_D, dtype=bf, device="cuda")
+    for i in range(0, T, 2048):  # chunked: keeps the fp32 staging buffer small
+        b["q"][i:i + 2048] = rn(min(2048, T - i), SFA_HEADS, SFA_D).to(bf)
+    b["qr"] = rn(T, SFA_HEADS, SFA_DR).to(bf)
+    b["k"] = rn(T, 1, SFA_D).to(bf)
+    b["kr"] = rn(T, 1, SFA_DR).to(bf)
+    cu = np.cumsum(lens).tolist()
+    b["cu"] = cu
+    from dsa_triton_ascend_b200 import lightning_indexer_triton
+    idx, _ = lightning_indexer_triton(iq, ik, iw, actual_seq_lengths_query=cu, actual_seq_lengths_key=cu,
+                                      layout_query="TND", layout_key="TND", sparse_count=TOPK, sparse_mode=3)
+    b["idx"] = idx.contiguous()
+    del iq, ik, iw
+    torch.cuda.synchronize()
+    return b
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
+    from dsa_triton_ascend_b200 import _cabi
+    import dsa_triton_ascend_b200.lightning_indexer as li_mod
+
+    lens = [L // 8 for L in SEQ_LENS] if args.quick else SEQ_LENS
+    topk = TOPK // 8 if args.quick else TOPK
+    globals()["TOPK"] = topk
+    batch = make_gpu_batch(torch, 1000 + rank, lens, args.quick)
+    S, T = lens[0], sum(lens)
+    scale = 1.0 / np.sqrt(SFA_D + SFA_DR)
+    flops_sfa, _ = sfa_flops(lens, topk)
+    flops_li, _ = li_flops(S)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def li_step():
+        return lightning_indexer_triton(batch["li_q"], batch["li_k"], batch["li_w"], sparse_count=topk, sparse_mode=3)
+
+    def sfa_step():
+        return sparse_flash_attention_triton(
+            batch["q"], batch["k"], batch["k"], batch["idx"], scale_value=scale,
+            actual_seq_lengths_query=batch["cu"], actual_seq_lengths_kv=batch["cu"],
+            query_rope=batch["qr"], key_rope=batch["kr"], layout_query="TND", layout_kv="TND",
+            sparse_mode=3, return_softmax_lse=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        li_step()
+        sfa_step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    t_wall = time.perf_counter()
+    for s in range(args.steps):
+        flush.fill_(s & 0xFF)  # evict L2 between timed iterations
+        ev[s][0].record()
+        li_step()
+        ev[s][1].record()
+        sfa_step()
+        ev[s][2].record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    clocks = sampler.stop()
+    li_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    sfa_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+
+    # score / top-k split of the indexer (same inputs, phases launched separately)
+    p, keep, _, _, _ = li_mod._build_params(batch["li_q"], batch["li_k"], batch["li_w"], None, None, None,
+                                            "BSND", "BSND", topk, 3, False)
+    import ctypes
+    nbytes = ctypes.c_size_t(0)
+    _cabi.check(_cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)), "li")
+    ws = torch.empty(nbytes.value, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    tensor_li = bool(_cabi.lib.dsa_li_uses_tensor_path(ctypes.byref(p)))
+    phase_ms = {}
+    for name, ph in (("score", _cabi.PHASE_SCORE), ("topk", _cabi.PHASE_TOPK)):
+        p.phases = ph
+        times = []
+        for i in range(args.warmup + args.steps):
+            flush.fill_(i & 0xFF)
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _cabi.check(_cabi.lib.dsa_li_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), stream), "li")
+            b_.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(a.elapsed_time(b_))
+        phase_ms[name] = float(np.mean(times))
+    del keep
+
+    # end to end through the public operators with pinned host buffers
+    host_in = {k: v.cpu().pin_memory() for k, v in batch.items() if hasattr(v, "cpu")}
+    out_h = torch.empty(batch["q"].shape, dtype=torch.bfloat16).pin_memory()
+    st_h = torch.empty((2, 1, T, SFA_HEADS), dtype=torch.float32).pin_memory()
+    idx_h = torch.empty((1, S, 1, topk), dtype=torch.int32).pin_memory()
+    h2d = sum(host_in[k].numel() * host_in[k].element_size() for k in host_in)
+    d2h = out_h.numel() * 2 + st_h.numel() * 4 + idx_h.numel() * 4
+
+    def e2e_step():
+        d = {k: v.cuda(non_blocking=True) for k, v in host_in.items()}
+        i_, _ = lightning_indexer_triton(d["li_q"], d["li_k"], d["li_w"], sparse_count=topk, sparse_mode=3)
+        idx_h.copy_(i_, non_blocking=True)
+        o, m, s_ = sparse_flash_attention_triton(
+            d["q"], d["k"], d["k"], d["idx"], scale_value=scale, actual_seq_lengths_query=batch["cu"],
+            actual_seq_lengths_kv=batch["cu"], query_rope=d["qr"], key_rope=d["kr"], layout_query="TND",
+            layout_kv="TND", sparse_mode=3, return_softmax_lse=True)
+        out_h.copy_(o, non_blocking=True)
+        st_h[0].copy_(m, non_blocking=True)
+        st_h[1].copy_(s_, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b_.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b_) / e2e_steps
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    li_ms, sfa_ms, e2e_ms = reduce_max(li_ms), reduce_max(sfa_ms), reduce_max(e2e_ms)
+    pk = peaks()
+    sfa_tf = flops_sfa / (sfa_ms * 1e-3) / 1e12
+    tensor_sfa = bool(getattr(run_gpu, "_sfa_tensor", False))
+    line = {
+        "metric": METRIC, "value": sfa_tf * world, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": li_ms + sfa_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "LI B=1 S=%d N1=64 D=128 k=%d + SFA TND lens=%s N1=128 D=512+64 topk=%d, mode 3"
+                               % (S, topk, lens, topk),
+                   "l2": "256 MiB buffer written between timed iterations; inputs (q 1.9 GiB) exceed L2",
+                   "quick": bool(args.quick)},
+        "li_topk_qtok_per_s": S / (li_ms * 1e-3) * world,
+        "li_ms": li_ms, "li_score_ms": phase_ms["score"], "li_topk_ms": phase_ms["topk"],
+        "li_score_tflops": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
+        "sfa_ms": sfa_ms, "sfa_tflops_per_gpu": sfa_tf,
+        "li_tensor_path": tensor_li,
+        "roofline": {"bound": "tensor", "achieved": sfa_tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": sfa_tf / pk["bf16_tflops"], "traffic": None, "kernel": "sfa_fwd",
+                     "peak_source": pk["source"] + " (burst bf16 GEMM)"},
+        "roofline_li_score": {"bound": "tensor", "achieved": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
+                              "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                              "frac": flops_li / (phase_ms["score"] * 1e-3) / 1e12 / pk["bf16_tflops"]},
+        "e2e": {"value": flops_sfa / (e2e_ms * 1e-3) / 1e12 * world, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "li_topk_qtok_per_s": S / (e2e_ms * 1e-3) * world},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks, "wall_s": t_wall,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_reference(sample_s=args.cpu_seconds, procs=1, lens=lens, topk=topk)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle (numpy restatement of the reference goldens) on a bounded sample
+# ----------------------------------------------------------------------------------------------
+def _one_blas_thread():
+    try:
+        from threadpoolctl import threadpool_limits
+        return threadpool_limits(limits=1)
+    except Exception:  # pragma: no cover
+        import contextlib
+        return contextlib.nullcontext()
+
+
+def _cpu_sfa_rows(args):
+    """Oracle attention for query tokens at positions `tokens` of one L-token sequence.  Each token
+    is one oracle call with S1=1, act_q=1, act_k=pos+1, which gives the causal threshold pos+1."""
+    seed, tokens, L, topk = args
+    from oracle import sparse_flash_attention_oracle
+    from oracle.inputs import round_io
+    rng = np.random.RandomState(seed)
+    k = round_io(rng.randn(1, L, 1, SFA_D).astype(np.float32), "bf16")
+    kr = round_io(rng.randn(1, L, 1, SFA_DR).astype(np.float32), "bf16")
+    work = []
+    for s in tokens:
+        q = round_io(rng.randn(1, 1, SFA_HEADS, SFA_D).astype(np.float32), "bf16")
+        qr = round_io(rng.randn(1, 1, SFA_HEADS, SFA_DR).astype(np.float32), "bf16")
+        n = min(topk, s + 1)
+        idx = np.full((1, 1, 1, topk), -1, np.int32)
+        idx[0, 0, 0, :n] = np.sort(rng.choice(s + 1, n, replace=False))
+        work.append((s, q, qr, idx, n))
+    pairs = 0
+    with _one_blas_thread():
+        t = time.perf_counter()
+        for s, q, qr, idx, n in work:
+            sparse_flash_attention_oracle(q, k, idx, qr, kr, 1.0 / np.sqrt(576.0), [1], [s + 1], sparse_mode=3,
+                                          dtype="bf16")
+            pairs += n
+        t = time.perf_counter() - t
+    return t, pairs
+
+
+def _cpu_li_rows(args):
+    """Oracle indexer (score, mask, round, rank) for query rows at positions `rows` (one call per row
+    with S1=1, act_q=1, act_k=pos+1)."""
+    seed, rows, S, topk = args
+    from oracle import lightning_indexer_oracle
+    from oracle.inputs import round_io
+    rng = np.random.RandomState(seed)
+    k = round_io(rng.randn(1, S, 1, LI_D).astype(np.float32), "bf16")
+    work = []
+    for s in rows:
+        q = round_io(rng.randn(1, 1, LI_HEADS, LI_D).astype(np.float32), "bf16")
+        w = (rng.randn(1, 1, LI_HEADS) / 8).astype(np.float32)
+        work.append((s, q, w))
+    with _one_blas_thread():
+        t = time.perf_counter()
+        for s, q, w in work:
+            lightning_indexer_oracle(q, k, w, [1], [s + 1], sparse_count=topk, sparse_mode=3)
+        t = time.perf_counter() - t
+    return t, sum(s + 1 for s in rows)
+
+
+def cpu_reference(sample_s=12.0, procs=None, lens=SEQ_LENS, topk=TOPK):
+    """Times the CPU implementation on evenly spaced rows of the same workload and scales by the
+    work measure (valid query-key pairs).  `procs` worker processes, one BLAS thread each."""
+    import multiprocessing as mp
+    procs = procs or len(os.sched_getaffinity(0))
+    L = lens[0]
+    # a short calibration decides how many rows fit the time budget
+    t0, p0 = _cpu_sfa_rows((11, [L - 1], L, topk))
+    n_sfa = max(procs, int(sample_s * 0.7 / max(t0, 1e-3)) * procs)
+    tok = np.unique(np.linspace(0, L - 1, n_sfa).astype(int)).tolist()
+    t1, p1 = _cpu_li_rows((12, [L - 1], L, topk))
+    n_li = max(procs, int(sample_s * 0.3 / max(t1, 1e-3)) * procs)
+    rows = np.unique(np.linspace(0, L - 1, n_li).astype(int)).tolist()
+    ctx = mp.get_context("fork")
+    t = time.perf_counter()
+    with ctx.Pool(procs) as pool:
+        r_sfa = pool.map(_cpu_sfa_rows, [(100 + i, tok[i::procs], L, topk) for i in range(procs)])
+        t_sfa = time.perf_counter() - t
+        t = time.perf_counter()
+        r_li = pool.map(_cpu_li_rows, [(12, rows[i::procs], L, topk) for i in range(procs)])
+        t_li = time.perf_counter() - t
+    # input generation inside the workers is excluded: use the slowest worker's compute time
+    t_sfa_c = max(r[0] for r in r_sfa)
+    t_li_c = max(r[0] for r in r_li)
+    pairs_sfa = sum(r[1] for r in r_sfa)
+    pairs_li = sum(r[1] for r in r_li)
+    sfa_tf = pairs_sfa * SFA_HEADS * 2.0 * (SFA_D + SFA_DR + SFA_D) / t_sfa_c / 1e12
+    _, li_pairs_full = li_flops(L)
+    li_qtok = L / (t_li_c * li_pairs_full / pairs_li)
+    return {"value": sfa_tf, "unit": UNIT, "cores": procs, "kind": "port",
+            "sample": "%d attention tokens (evenly spaced positions of an %d-token sequence, all 128 heads, "
+                      "top-%d) and %d indexer rows; scaled by valid query-key pairs" % (len(tok), L, topk, len(rows)),
+            "li_topk_qtok_per_s": li_qtok, "sfa_seconds": t_sfa_c, "li_seconds": t_li_c,
+            "wall_seconds": t_sfa + t_li}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    lens = [L // 8 for L in SEQ_LENS] if args.quick else SEQ_LENS
+    topk = TOPK // 8 if args.quick else TOPK
+    vals, last = [], None
+    for _ in range(max(1, min(args.steps, 3))):
+        last = cpu_reference(sample_s=args.cpu_seconds, lens=lens, topk=topk)
+        vals.append(last["value"])
+    v = float(np.mean(vals))
+    flops, _ = sfa_flops(lens, topk)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": int(args.gpus),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": flops / (v * 1e12) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "LI B=1 S=%d N1=64 D=128 k=%d + SFA TND lens=%s N1=128 D=512+64 topk=%d, mode 3"
+                               % (lens[0], topk, lens, topk), "quick": bool(args.quick)},
+        "li_topk_qtok_per_s": last["li_topk_qtok_per_s"],
+        "cpu_baseline": dict(last, value=v),
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--quick", action="store_true", help="1/8-size workload (debugging only; not a bench value)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,14 @@
+"""B200-native (sm_100a) DeepSeek-Sparse-Attention forward hot path.
+
+Public API = the two operators of WhFanatic/dsa_triton_ascend with unchanged signatures:
+`lightning_indexer_triton` / `LightningIndexerTriton` and `sparse_flash_attention_triton` /
+`SparseFlashAttentionTriton`.  Both are thin wrappers over the C-ABI CUDA library built from
+`dsa_triton_ascend_b200/csrc` (declared in `include/dsa_b200.h`).
+"""
+from .lightning_indexer import LightningIndexerTriton, lightning_indexer_triton  # noqa: F401
+from .sparse_flash_attention import SparseFlashAttentionTriton, sparse_flash_attention_triton  # noqa: F401
+
+__all__ = [
+    "lightning_indexer_triton", "LightningIndexerTriton",
+    "sparse_flash_attention_triton", "SparseFlashAttentionTriton",
+]

@@ -1,0 +1,59 @@
+"""Host-side helpers shared by the two operator wrappers: dtype/length handling, workspace
+and stream plumbing.  torch is used for device memory and streams only."""
+import torch
+
+from . import _cabi
+
+INT64_MAX = 9223372036854775807
+
+_DTYPES = {torch.bfloat16: _cabi.DTYPE_BF16, torch.float16: _cabi.DTYPE_FP16, torch.float32: _cabi.DTYPE_FP32}
+
+
+def dtype_code(t, allowed, what):
+    code = _DTYPES.get(t.dtype)
+    if code is None or t.dtype not in allowed:
+        raise ValueError(f"{what} dtype {t.dtype} is not supported")
+    return code
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("dsa_triton_ascend_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def seq_tensor(lengths, device):
+    """None / list / tuple / tensor -> (int32 device tensor or None, host list or None)."""
+    if lengths is None:
+        return None, None
+    if isinstance(lengths, (list, tuple)):
+        host = [int(v) for v in lengths]
+        return torch.tensor(host, dtype=torch.int32, device=device), host
+    if isinstance(lengths, torch.Tensor):
+        host = lengths.tolist() if not lengths.is_cuda else None
+        return lengths.to(device=device, dtype=torch.int32).contiguous(), host
+    raise ValueError("actual_seq_lengths must be None, a list/tuple or an int32 tensor")
+
+
+def max_len_from_cumulative(host, fallback):
+    """Largest per-sequence length of a cumulative list (upper bound `fallback` when unknown)."""
+    if not host:
+        return fallback
+    prev, best = 0, 0
+    for v in host:
+        best = max(best, v - prev)
+        prev = v
+    return best
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def workspace(nbytes, device):
+    # torch's caching allocator returns 512-byte aligned blocks; the library wants 256.
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def current_stream(device):
+    return torch.cuda.current_stream(device).cuda_stream

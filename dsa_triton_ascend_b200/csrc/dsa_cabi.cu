@@ -1,0 +1,241 @@
+// C ABI of the library (declared in include/dsa_b200.h): argument validation, kernel choice,
+// workspace layout and launches.  Host code only decides and enqueues; it never synchronises
+// (except dsa_read_device_status) and never allocates device memory.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dsa_b200.h"
+#include "dsa_common.cuh"
+#include "li_score_simt.cuh"
+#include "li_topk.cuh"
+#include "sfa_fwd_simt.cuh"
+
+namespace dsa {
+
+constexpr size_t kWorkspaceHeader = 256;  // bytes reserved at the start of every workspace (status word)
+
+static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+static int li_validate(const DsaLiParams* p) {
+  if (p == nullptr) return DSA_ERR_NULL;
+  if (p->struct_size != sizeof(DsaLiParams)) return DSA_ERR_STRUCT;
+  if (!p->query || !p->key || !p->weights || !p->out_indices) return DSA_ERR_NULL;
+  if (p->layout_q != DSA_LAYOUT_BSND && p->layout_q != DSA_LAYOUT_TND) return DSA_ERR_VALUE;
+  if (p->layout_k < DSA_LAYOUT_BSND || p->layout_k > DSA_LAYOUT_PA_BSND) return DSA_ERR_VALUE;
+  if (p->dtype_qk != DSA_DTYPE_BF16 && p->dtype_qk != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
+  if (p->dtype_w < DSA_DTYPE_BF16 || p->dtype_w > DSA_DTYPE_FP32) return DSA_ERR_VALUE;
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 0 || p->n1 < 1 || p->n2 < 1 || p->d < 1) return DSA_ERR_VALUE;
+  if (p->n1 % p->n2 != 0) return DSA_ERR_VALUE;  // lightning_indexer_triton.py:524-525
+  if (p->d % 8 != 0) return DSA_ERR_VALUE;
+  if (p->sparse_mode != 0 && p->sparse_mode != 3) return DSA_ERR_VALUE;
+  if (p->rank_mode != DSA_RANK_IO_DTYPE && p->rank_mode != DSA_RANK_FP32) return DSA_ERR_VALUE;
+  if (p->sparse_count < 1) return DSA_ERR_VALUE;
+  if (p->sparse_count > kTopkMaxCount) return DSA_ERR_TOO_LARGE;
+  if (p->s2 >= (1 << 24)) return DSA_ERR_TOO_LARGE;
+  if (p->layout_q == DSA_LAYOUT_TND && (!p->seq_q || !p->seq_q_cumulative)) return DSA_ERR_VALUE;
+  if (p->layout_k == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
+  if (p->layout_k == DSA_LAYOUT_PA_BSND && (!p->block_table || p->block_size < 1 || p->max_blocks < 1 || !p->seq_k))
+    return DSA_ERR_VALUE;
+  if (p->phases < 1 || p->phases > DSA_PHASE_ALL) return DSA_ERR_VALUE;
+  if (p->kernel < DSA_KERNEL_AUTO || p->kernel > DSA_KERNEL_TENSOR) return DSA_ERR_VALUE;
+  return DSA_OK;
+}
+
+static inline int64_t li_rows(const DsaLiParams* p) {
+  return p->layout_q == DSA_LAYOUT_TND ? (int64_t)p->s1 : (int64_t)p->batch * p->s1;
+}
+static inline int64_t li_score_ld(const DsaLiParams* p) { return round_up(p->s2 > 0 ? p->s2 : 1, 4); }
+
+static LiDev li_dev(const DsaLiParams* p) {
+  LiDev d;
+  d.seq.seq_q = p->seq_q; d.seq.seq_k = p->seq_k; d.seq.block_table = p->block_table;
+  d.seq.layout_q = p->layout_q; d.seq.layout_k = p->layout_k;
+  d.seq.seq_q_cum = p->seq_q_cumulative; d.seq.seq_k_cum = p->seq_k_cumulative;
+  d.seq.batch = p->batch; d.seq.s1 = p->s1; d.seq.s2 = p->s2;
+  d.seq.block_size = p->block_size; d.seq.max_blocks = p->max_blocks;
+  d.seq.sparse_mode = p->sparse_mode;
+  d.query = p->query; d.key = p->key; d.weights = p->weights;
+  d.out_indices = p->out_indices; d.out_values = p->out_values;
+  d.dtype_w = p->dtype_w; d.n1 = p->n1; d.n2 = p->n2; d.d = p->d;
+  d.rows = (int32_t)li_rows(p);
+  d.sparse_count = p->sparse_count; d.rank_mode = p->rank_mode; d.return_value = p->return_value;
+  return d;
+}
+
+template <typename T>
+static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st) {
+  LiDev d = li_dev(p);
+  const int64_t ld = li_score_ld(p);
+  const int64_t rown = (int64_t)d.rows * p->n2;
+  if (rown == 0) return DSA_OK;
+  if (p->phases & DSA_PHASE_SCORE) {
+    if (p->s2 > 0) {
+      dim3 grid((unsigned)rown, (unsigned)((p->s2 + kSimtKeys - 1) / kSimtKeys), 1);
+      li_score_simt_kernel<T><<<grid, kSimtKeys, 0, st>>>(d, scores, ld);
+      if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    }
+  }
+  if (p->phases & DSA_PHASE_TOPK) {
+    int32_t cap = 1;
+    while (cap < p->sparse_count) cap <<= 1;
+    const size_t smem = (size_t)cap * 8 + (size_t)kTopkKeyCache * 4;
+    cudaError_t e;
+    if (p->rank_mode == DSA_RANK_IO_DTYPE) {
+      e = cudaFuncSetAttribute(li_topk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return DSA_ERR_CUDA;
+      li_topk_kernel<T, true><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+    } else {
+      e = cudaFuncSetAttribute(li_topk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return DSA_ERR_CUDA;
+      li_topk_kernel<T, false><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+    }
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  }
+  return DSA_OK;
+}
+
+static int sfa_validate(const DsaSfaParams* p) {
+  if (p == nullptr) return DSA_ERR_NULL;
+  if (p->struct_size != sizeof(DsaSfaParams)) return DSA_ERR_STRUCT;
+  if (!p->query || !p->query_rope || !p->key || !p->key_rope || !p->sparse_indices || !p->out) return DSA_ERR_NULL;
+  if (p->return_lse && (!p->softmax_max || !p->softmax_sum)) return DSA_ERR_NULL;
+  if (p->layout_q != DSA_LAYOUT_BSND && p->layout_q != DSA_LAYOUT_TND) return DSA_ERR_VALUE;
+  if (p->layout_kv < DSA_LAYOUT_BSND || p->layout_kv > DSA_LAYOUT_PA_BSND) return DSA_ERR_VALUE;
+  if (p->dtype != DSA_DTYPE_BF16 && p->dtype != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
+  // shape guards of sparse_flash_attention_triton.py:1391-1398 (head count relaxed to any n1 >= 1)
+  if (p->d != 128 && p->d != 256 && p->d != 512) return DSA_ERR_VALUE;
+  if (p->d_rope != 64) return DSA_ERR_VALUE;
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 0 || p->n1 < 1) return DSA_ERR_VALUE;
+  if (p->sparse_mode != 0 && p->sparse_mode != 3) return DSA_ERR_VALUE;
+  const int bs = p->sparse_block_size;
+  if (bs < 1 || bs > 128 || (bs & (bs - 1)) != 0) return DSA_ERR_VALUE;  // :1349-1351
+  if (p->sparse_count < 1) return DSA_ERR_VALUE;
+  if (p->layout_q == DSA_LAYOUT_TND && (!p->seq_q || !p->seq_q_cumulative)) return DSA_ERR_VALUE;
+  if (p->layout_kv == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
+  if (p->layout_kv == DSA_LAYOUT_PA_BSND && (!p->block_table || p->block_size < 1 || p->max_blocks < 1 || !p->seq_k))
+    return DSA_ERR_VALUE;
+  if (p->kernel < DSA_KERNEL_AUTO || p->kernel > DSA_KERNEL_TENSOR) return DSA_ERR_VALUE;
+  return DSA_OK;
+}
+
+static SfaDev sfa_dev(const DsaSfaParams* p) {
+  SfaDev d;
+  d.seq.seq_q = p->seq_q; d.seq.seq_k = p->seq_k; d.seq.block_table = p->block_table;
+  d.seq.layout_q = p->layout_q; d.seq.layout_k = p->layout_kv;
+  d.seq.seq_q_cum = p->seq_q_cumulative; d.seq.seq_k_cum = p->seq_k_cumulative;
+  d.seq.batch = p->batch; d.seq.s1 = p->s1; d.seq.s2 = p->s2;
+  d.seq.block_size = p->block_size; d.seq.max_blocks = p->max_blocks;
+  d.seq.sparse_mode = p->sparse_mode;
+  d.query = p->query; d.query_rope = p->query_rope; d.key = p->key; d.key_rope = p->key_rope;
+  d.sparse_indices = p->sparse_indices;
+  d.out = p->out; d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
+  d.rows = p->layout_q == DSA_LAYOUT_TND ? p->s1 : p->batch * p->s1;
+  d.n1 = p->n1; d.d = p->d; d.d_rope = p->d_rope;
+  d.sparse_count = p->sparse_count; d.sparse_block_size = p->sparse_block_size;
+  d.return_lse = p->return_lse;
+  d.scale = p->scale;
+  return d;
+}
+
+template <typename T>
+static int sfa_launch_simt(const DsaSfaParams* p, cudaStream_t st) {
+  SfaDev d = sfa_dev(p);
+  if (d.rows == 0) return DSA_OK;
+  const size_t smem = (size_t)(kSfaSimtHeads + kSfaSimtKeys) * (p->d + p->d_rope + kSfaSimtPad) * sizeof(T);
+  if (cudaFuncSetAttribute(sfa_fwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return DSA_ERR_CUDA;
+  const unsigned gy = (unsigned)((p->n1 + kSfaSimtHeads - 1) / kSfaSimtHeads);
+  dim3 grid((unsigned)d.rows, gy, 1);
+  sfa_fwd_simt_kernel<T><<<grid, kSfaSimtThreads, smem, st>>>(d);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  return DSA_OK;
+}
+
+}  // namespace dsa
+
+using namespace dsa;
+
+extern "C" {
+
+int dsa_abi_version(void) { return 1; }
+
+const char* dsa_status_string(int status) {
+  switch (status) {
+    case DSA_OK: return "ok";
+    case DSA_ERR_NULL: return "a required pointer is NULL";
+    case DSA_ERR_STRUCT: return "struct_size does not match the library (ABI mismatch)";
+    case DSA_ERR_VALUE: return "argument outside the supported set";
+    case DSA_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+    case DSA_ERR_UNSUPPORTED: return "requested kernel variant cannot run this shape";
+    case DSA_ERR_CUDA: return "a CUDA runtime call failed";
+    case DSA_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+    case DSA_ERR_TOO_LARGE: return "size beyond a fixed maximum of the library";
+    default: return "unknown status";
+  }
+}
+
+int dsa_li_uses_tensor_path(const DsaLiParams* p) {
+  if (li_validate(p) != DSA_OK) return 0;
+  return 0;
+}
+
+int dsa_sfa_uses_tensor_path(const DsaSfaParams* p) {
+  if (sfa_validate(p) != DSA_OK) return 0;
+  return 0;
+}
+
+int dsa_li_workspace_bytes(const DsaLiParams* p, size_t* out_bytes) {
+  int st = li_validate(p);
+  if (st != DSA_OK) return st;
+  if (!out_bytes) return DSA_ERR_NULL;
+  const int64_t rown = li_rows(p) * p->n2;
+  *out_bytes = kWorkspaceHeader + (size_t)round_up(rown * li_score_ld(p) * 4, 256);
+  return DSA_OK;
+}
+
+int dsa_li_forward(const DsaLiParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = li_validate(p);
+  if (st != DSA_OK) return st;
+  size_t need = 0;
+  dsa_li_workspace_bytes(p, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  if (p->kernel == DSA_KERNEL_TENSOR && !dsa_li_uses_tensor_path(p)) return DSA_ERR_UNSUPPORTED;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  float* scores = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
+  if (p->dtype_qk == DSA_DTYPE_BF16) return li_launch<__nv_bfloat16>(p, scores, cs);
+  return li_launch<__half>(p, scores, cs);
+}
+
+int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes) {
+  int st = sfa_validate(p);
+  if (st != DSA_OK) return st;
+  if (!out_bytes) return DSA_ERR_NULL;
+  *out_bytes = kWorkspaceHeader;
+  return DSA_OK;
+}
+
+int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = sfa_validate(p);
+  if (st != DSA_OK) return st;
+  size_t need = 0;
+  dsa_sfa_workspace_bytes(p, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  if (p->kernel == DSA_KERNEL_TENSOR && !dsa_sfa_uses_tensor_path(p)) return DSA_ERR_UNSUPPORTED;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  if (p->dtype == DSA_DTYPE_BF16) return sfa_launch_simt<__nv_bfloat16>(p, cs);
+  return sfa_launch_simt<__half>(p, cs);
+}
+
+int dsa_read_device_status(const void* workspace, void* stream) {
+  if (!workspace) return DSA_ERR_NULL;
+  int32_t word = 0;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  if (cudaStreamSynchronize(cs) != cudaSuccess) return DSA_ERR_CUDA;
+  return word == 0 ? DSA_OK : DSA_ERR_DEVICE_WAIT;
+}
+
+}  // extern "C"

@@ -1,0 +1,248 @@
+// Portable (CUDA-core) sparse flash attention forward: any head count, D in {128,256,512},
+// all layouts, token-wise and block-wise indices.  Same math as _sfa_kernel's chunked path
+// (sparse_flash_attention_triton.py:461-604): rows gathered by index, invalid slots masked to
+// -inf, online softmax with fp32 statistics, probabilities rounded to the io dtype before the
+// second product (:520), value = key[..., :D].
+#pragma once
+
+#include "dsa_common.cuh"
+
+namespace dsa {
+
+struct SfaDev {
+  SeqDesc seq;
+  const void* query;
+  const void* query_rope;
+  const void* key;
+  const void* key_rope;
+  const int32_t* sparse_indices;
+  void* out;
+  float* softmax_max;
+  float* softmax_sum;
+  int32_t rows, n1, d, d_rope;
+  int32_t sparse_count, sparse_block_size, return_lse;
+  float scale;
+};
+
+constexpr int kSfaSimtHeads = 16;   // heads per block
+constexpr int kSfaSimtKeys = 32;    // gathered keys per step
+constexpr int kSfaSimtThreads = 256;
+constexpr int kSfaSimtPad = 8;      // elements of row padding (keeps 16-byte loads conflict free)
+
+// Validity and physical row of slot j of a query row (sparse_flash_attention_triton.py:465,
+// 1036-1051): returns the logical token or -1.
+__device__ __forceinline__ int32_t sfa_slot_token(const SfaDev& p, const RowInfo& ri, const int32_t* idx_row,
+                                                  int32_t j) {
+  const int32_t bs = p.sparse_block_size;
+  const int32_t id = idx_row[j / bs];
+  if (id < 0) return -1;
+  const int64_t tok = (int64_t)id * bs + (j % bs);
+  if (tok >= ri.threshold || tok >= ri.act_k) return -1;
+  if (p.seq.layout_k != DSA_LAYOUT_PA_BSND && tok >= p.seq.s2) return -1;
+  return (int32_t)tok;
+}
+
+// grid = (rows, ceil(n1 / 16)); block = 256 threads.
+// dynamic smem: (16 + 32) * (d + d_rope + pad) elements of T.
+template <typename T>
+__global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p) {
+  extern __shared__ __align__(16) unsigned char sfa_smem[];
+  const int32_t dq = p.d + p.d_rope;
+  const int32_t stride = dq + kSfaSimtPad;
+  T* qs = reinterpret_cast<T*>(sfa_smem);
+  T* ks = qs + kSfaSimtHeads * stride;
+  __shared__ float ps[kSfaSimtHeads][kSfaSimtKeys];
+  __shared__ float alpha_s[kSfaSimtHeads];
+  __shared__ float l_s[kSfaSimtHeads];
+  __shared__ float m_s[kSfaSimtHeads];
+  __shared__ int32_t tok_s[kSfaSimtKeys];
+  __shared__ int64_t krow_s[kSfaSimtKeys];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t row = blockIdx.x;
+  const int32_t h0 = blockIdx.y * kSfaSimtHeads;
+  const RowInfo ri = row_info(p.seq, row);
+  const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
+
+  // accumulator mapping: head = tid / 16, columns 2*(tid%16) + 32*j (+1)
+  const int ah = tid >> 4, ac = (tid & 15) * 2;
+  float acc[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+
+  T* outp = (T*)p.out + ((int64_t)row * p.n1 + h0) * p.d;
+  if (!row_active) {
+    for (int i = tid; i < kSfaSimtHeads * p.d; i += kSfaSimtThreads) {
+      int h = i / p.d;
+      if (h0 + h < p.n1) outp[i] = from_f32<T>(0.f);
+    }
+    if (p.return_lse && tid < kSfaSimtHeads && h0 + tid < p.n1) {
+      p.softmax_max[(int64_t)row * p.n1 + h0 + tid] = 0.f;
+      p.softmax_sum[(int64_t)row * p.n1 + h0 + tid] = 0.f;
+    }
+    return;
+  }
+
+  // stage the head chunk of q (nope | rope) into shared memory, zero for heads past n1
+  {
+    const T* qn = (const T*)p.query + (int64_t)row * p.n1 * p.d;
+    const T* qr = (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope;
+    for (int i = tid; i < kSfaSimtHeads * dq; i += kSfaSimtThreads) {
+      int h = i / dq, c = i - h * dq;
+      T v = from_f32<T>(0.f);
+      if (h0 + h < p.n1) v = c < p.d ? qn[(int64_t)(h0 + h) * p.d + c] : qr[(int64_t)(h0 + h) * p.d_rope + (c - p.d)];
+      qs[h * stride + c] = v;
+    }
+  }
+  if (tid < kSfaSimtHeads) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+  __syncthreads();
+
+  const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.sparse_count;
+  const int32_t slots = p.sparse_count * p.sparse_block_size;
+  const T* kn = (const T*)p.key;
+  const T* kr = (const T*)p.key_rope;
+
+  // Up to 128 valid slots the softmax is normalised before the probabilities are rounded, which is the
+  // order of the golden and of the reference's single-block path (:419-436): pass 0 finds max and
+  // sum, pass 1 accumulates.  Longer rows use the online form in one pass.
+  __shared__ int32_t nvalid_s;
+  if (tid == 0) nvalid_s = 0;
+  __syncthreads();
+  {
+    int32_t part = 0;
+    for (int32_t j = tid; j < slots; j += kSfaSimtThreads) part += sfa_slot_token(p, ri, idx_row, j) >= 0;
+    if (part) atomicAdd(&nvalid_s, part);
+  }
+  __syncthreads();
+  const bool two_pass = nvalid_s <= 128;
+  const int npass = two_pass ? 2 : 1;
+  for (int pass = 0; pass < npass; ++pass)
+  for (int32_t j0 = 0; j0 < slots; j0 += kSfaSimtKeys) {
+    int any = 0;
+    if (tid < kSfaSimtKeys) {
+      int32_t j = j0 + tid;
+      int32_t tok = j < slots ? sfa_slot_token(p, ri, idx_row, j) : -1;
+      tok_s[tid] = tok;
+      krow_s[tid] = tok >= 0 ? key_row(p.seq, ri, tok) : -1;
+      any = tok >= 0;
+    }
+    if (!__syncthreads_or(any)) continue;
+
+    // gather the rows (16-byte chunks; absent paged blocks read as zeros, like the un-paged cache)
+    {
+      const int cn = p.d / 8, cr = p.d_rope / 8, ct = cn + cr;
+      for (int i = tid; i < kSfaSimtKeys * ct; i += kSfaSimtThreads) {
+        int k = i / ct, c = i - k * ct;
+        int64_t kr_ = krow_s[k];
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (kr_ >= 0) {
+          v = c < cn ? reinterpret_cast<const uint4*>(kn + kr_ * p.d)[c]
+                     : reinterpret_cast<const uint4*>(kr + kr_ * p.d_rope)[c - cn];
+        }
+        *reinterpret_cast<uint4*>(&ks[k * stride + c * 8]) = v;
+      }
+    }
+    __syncthreads();
+
+    // scores: thread -> key = lane, heads warp and warp + 8
+    {
+      float s0 = 0.f, s1 = 0.f;
+      const uint4* kp = reinterpret_cast<const uint4*>(&ks[lane * stride]);
+      const uint4* q0 = reinterpret_cast<const uint4*>(&qs[warp * stride]);
+      const uint4* q1 = reinterpret_cast<const uint4*>(&qs[(warp + 8) * stride]);
+      for (int c = 0; c < dq / 8; ++c) {
+        uint4 kv = kp[c], a = q0[c], b = q1[c];
+        const T* kk = reinterpret_cast<const T*>(&kv);
+        const T* aa = reinterpret_cast<const T*>(&a);
+        const T* bb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float kf = to_f32<T>(kk[e]);
+          s0 = fmaf(kf, to_f32<T>(aa[e]), s0);
+          s1 = fmaf(kf, to_f32<T>(bb[e]), s1);
+        }
+      }
+      const bool valid = tok_s[lane] >= 0;
+      s0 = valid ? s0 * p.scale : -INFINITY;
+      s1 = valid ? s1 * p.scale : -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int h = warp + half * 8;
+        float sv = half ? s1 : s0;
+        float mx = sv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_old = m_s[h];
+        if (two_pass && pass == 1) {
+          const float l = l_s[h];
+          const float pv = (valid && l > 0.f) ? expf(sv - m_old) / l : 0.f;
+          ps[h][lane] = round_io<T>(pv);
+          if (lane == 0) alpha_s[h] = 1.f;
+          continue;
+        }
+        const float m_new = fmaxf(m_old, mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        float pv = valid ? expf(sv - m_safe) : 0.f;
+        float sum = pv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        ps[h][lane] = round_io<T>(pv);
+        __syncwarp();
+        if (lane == 0) {
+          const float a = m_old == -INFINITY ? 0.f : expf(m_old - m_safe);
+          alpha_s[h] = a;
+          l_s[h] = l_s[h] * a + sum;
+          m_s[h] = m_new;
+        }
+      }
+    }
+    __syncthreads();
+
+    // accumulate: acc = acc * alpha + P . V   (skipped in the statistics pass)
+    if (!(two_pass && pass == 0)) {
+      const float a = alpha_s[ah];
+      const int nj = p.d / 32;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < nj) { acc[2 * j] *= a; acc[2 * j + 1] *= a; }
+      }
+      for (int k = 0; k < kSfaSimtKeys; ++k) {
+        const float pk = ps[ah][k];
+        if (pk == 0.f) continue;
+        const T* vr = &ks[k * stride + ac];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j < nj) {
+            acc[2 * j] = fmaf(pk, to_f32<T>(vr[32 * j]), acc[2 * j]);
+            acc[2 * j + 1] = fmaf(pk, to_f32<T>(vr[32 * j + 1]), acc[2 * j + 1]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // epilogue
+  {
+    const float l = l_s[ah];
+    const float inv = two_pass ? 1.f : (l > 0.f ? 1.f / l : 0.f);
+    const int nj = p.d / 32;
+    if (h0 + ah < p.n1) {
+      T* o = outp + (int64_t)ah * p.d + ac;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < nj) {
+          o[32 * j] = from_f32<T>(acc[2 * j] * inv);
+          o[32 * j + 1] = from_f32<T>(acc[2 * j + 1] * inv);
+        }
+      }
+    }
+    if (p.return_lse && tid < kSfaSimtHeads && h0 + tid < p.n1) {
+      const float lt = l_s[tid];
+      p.softmax_max[(int64_t)row * p.n1 + h0 + tid] = lt > 0.f ? m_s[tid] : 0.f;
+      p.softmax_sum[(int64_t)row * p.n1 + h0 + tid] = lt > 0.f ? lt : 0.f;
+    }
+  }
+}
+
+}  // namespace dsa

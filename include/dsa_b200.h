@@ -1,0 +1,152 @@
+/*
+ * dsa_b200.h - C ABI of the B200 (sm_100a) DeepSeek-Sparse-Attention forward kernels.
+ *
+ * The library replaces the device side of two operators of WhFanatic/dsa_triton_ascend:
+ *   lightning_indexer       (score kernel + top-k)   lightning_indexer_triton.py:466-554
+ *   sparse_flash_attention  (forward)                sparse_flash_attention_triton.py:1295-1455
+ * The reference reaches its kernels through `ms.ops._ms_pyfunc` cores that take typed
+ * tensors plus scalars, write into caller-allocated buffers and report nothing from the
+ * device (lightning_indexer_triton.py:386-417, sparse_flash_attention_triton.py:1160-1289).
+ * This ABI keeps that contract: plain pointers and sizes, the caller owns every buffer
+ * (inputs, outputs, workspace), calls are enqueued on the given CUDA stream and return
+ * without synchronising.  All functions return 0 on success and a negative DSA_ERR_*
+ * code otherwise; none throws, exits or allocates device memory (except the entry point
+ * explicitly documented to own static device scratch).
+ */
+#ifndef DSA_B200_H_
+#define DSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define DSA_OK 0
+#define DSA_ERR_NULL (-1)         /* a required pointer is NULL                      */
+#define DSA_ERR_STRUCT (-2)       /* struct_size does not match this library          */
+#define DSA_ERR_VALUE (-3)        /* argument outside the supported set (ValueError)  */
+#define DSA_ERR_WORKSPACE (-4)    /* workspace too small or misaligned                */
+#define DSA_ERR_UNSUPPORTED (-5)  /* requested kernel variant cannot run this shape   */
+#define DSA_ERR_CUDA (-6)         /* a CUDA runtime call failed (launch, attribute)   */
+#define DSA_ERR_DEVICE_WAIT (-7)  /* a bounded device-side wait ran out (status word) */
+#define DSA_ERR_TOO_LARGE (-8)    /* size beyond a documented fixed maximum           */
+
+/* enums (plain ints in the structs) */
+#define DSA_LAYOUT_BSND 0
+#define DSA_LAYOUT_TND 1
+#define DSA_LAYOUT_PA_BSND 2
+
+#define DSA_DTYPE_BF16 0
+#define DSA_DTYPE_FP16 1
+#define DSA_DTYPE_FP32 2
+
+#define DSA_RANK_IO_DTYPE 0 /* rank scores rounded to the q/k dtype (numpy golden)       */
+#define DSA_RANK_FP32 1     /* rank raw fp32 scores (what the reference device path does) */
+
+#define DSA_KERNEL_AUTO 0     /* tensor-core path when the shape is eligible, else portable */
+#define DSA_KERNEL_PORTABLE 1 /* CUDA-core kernels, any shape                               */
+#define DSA_KERNEL_TENSOR 2   /* tcgen05 path; DSA_ERR_UNSUPPORTED when not eligible        */
+
+#define DSA_PHASE_SCORE 1
+#define DSA_PHASE_TOPK 2
+#define DSA_PHASE_ALL 3
+
+/*
+ * lightning_indexer.  Replaces _lightning_indexer_score_core + _stable_topk
+ * (lightning_indexer_triton.py:386-417, 343-361) and the TND copy loops (:294-340).
+ *
+ *   score[row, n2, s2] = sum_{g in group n2} relu(Q[row, g, :] . K[s2, n2, :]) * W[row, g]
+ * masked to the row's visible prefix, then the `sparse_count` best keys are emitted in
+ * (score descending, position ascending) order; unused slots hold index -1 / value 0.
+ *
+ * Row numbering: BSND row = b * s1 + position, TND row = token.  Positions written to
+ * out_indices are local to the row's own sequence (batch-local), as in the reference.
+ */
+typedef struct DsaLiParams {
+  uint32_t struct_size; /* sizeof(DsaLiParams) */
+  int32_t kernel;       /* DSA_KERNEL_*  */
+  const void* query;    /* BSND [batch, s1, n1, d] | TND [s1(=T1), n1, d]                    */
+  const void* key;      /* BSND [batch, s2, n2, d] | TND [T2, n2, d] | PA [blocks, block_size, n2, d] */
+  const void* weights;  /* [rows, n1], dtype_w                                                */
+  const int32_t* seq_q; /* [batch] lengths, or cumulative ends when seq_q_cumulative; NULL = s1 */
+  const int32_t* seq_k; /* [batch] lengths, or cumulative ends when seq_k_cumulative; NULL = s2 */
+  const int32_t* block_table; /* PA only: [batch, max_blocks], -1 = no block                  */
+  int32_t* out_indices; /* [rows, n2, sparse_count]                                           */
+  void* out_values;     /* [rows, n2, sparse_count] in dtype_qk; may be NULL if !return_value */
+  int32_t layout_q;     /* DSA_LAYOUT_BSND | DSA_LAYOUT_TND                                    */
+  int32_t layout_k;     /* DSA_LAYOUT_*                                                        */
+  int32_t dtype_qk;     /* DSA_DTYPE_BF16 | DSA_DTYPE_FP16                                     */
+  int32_t dtype_w;      /* DSA_DTYPE_BF16 | FP16 | FP32                                        */
+  int32_t seq_q_cumulative;
+  int32_t seq_k_cumulative;
+  int32_t batch;
+  int32_t s1;           /* BSND: S1; TND: total query tokens T1                                */
+  int32_t s2;           /* BSND: S2; TND/PA: upper bound of any sequence's key length          */
+  int32_t n1, n2, d;
+  int32_t block_size, max_blocks; /* PA only */
+  int32_t sparse_count;
+  int32_t sparse_mode;  /* 0 full, 3 rightDownCausal */
+  int32_t rank_mode;    /* DSA_RANK_* */
+  int32_t return_value;
+  int32_t phases;       /* DSA_PHASE_*; score-only and top-k-only share the workspace scores  */
+} DsaLiParams;
+
+/*
+ * sparse_flash_attention forward, MLA-absorb (value = key[..., :d]), one KV head.
+ * Replaces _sfa_core and its three kernels (sparse_flash_attention_triton.py:1160-1289,
+ * 324-962), the layout copy loops (:975-1033) and _expand_block_indices (:1036-1051).
+ *
+ * A slot j of a row selects token  idx[j / sparse_block_size] * sparse_block_size +
+ * j % sparse_block_size; it takes part when idx != -1, token < threshold and token <
+ * act_k, with threshold = act_k (mode 0) or act_k - act_q + position + 1 (mode 3)
+ * (sparse_flash_attention_triton.py:392-398,465).  Rows without any valid slot produce
+ * zeros in all three outputs.
+ */
+typedef struct DsaSfaParams {
+  uint32_t struct_size; /* sizeof(DsaSfaParams) */
+  int32_t kernel;       /* DSA_KERNEL_* */
+  const void* query;      /* [rows, n1, d]        */
+  const void* query_rope; /* [rows, n1, d_rope]   */
+  const void* key;        /* BSND [batch, s2, 1, d] | TND [T2, 1, d] | PA [blocks, block_size, 1, d] */
+  const void* key_rope;   /* same with d_rope     */
+  const int32_t* sparse_indices; /* [rows, 1, sparse_count] */
+  const int32_t* seq_q;
+  const int32_t* seq_k;
+  const int32_t* block_table;
+  void* out;              /* [rows, n1, d], dtype */
+  float* softmax_max;     /* [rows, n1] (BSND view [batch,1,s1,n1], TND view [1,T1,n1]); NULL if !return_lse */
+  float* softmax_sum;
+  int32_t layout_q, layout_kv, dtype;
+  int32_t seq_q_cumulative, seq_k_cumulative;
+  int32_t batch, s1, s2, n1, d, d_rope;
+  int32_t block_size, max_blocks;
+  int32_t sparse_count, sparse_block_size, sparse_mode, return_lse;
+  float scale;
+} DsaSfaParams;
+
+/* Workspace size for dsa_li_forward (fp32 score rows + a status word). 256-byte aligned use. */
+int dsa_li_workspace_bytes(const DsaLiParams* p, size_t* out_bytes);
+/* Enqueue the indexer on `stream` (a cudaStream_t passed as void*). */
+int dsa_li_forward(const DsaLiParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes);
+int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Static description of a status code. */
+const char* dsa_status_string(int status);
+/* Synchronises `stream` and returns the device status word stored at the start of a
+ * workspace: DSA_OK, or DSA_ERR_DEVICE_WAIT when a bounded in-kernel wait gave up. */
+int dsa_read_device_status(const void* workspace, void* stream);
+/* 1 when dsa_*_forward would take the tcgen05 path for these parameters, else 0. */
+int dsa_li_uses_tensor_path(const DsaLiParams* p);
+int dsa_sfa_uses_tensor_path(const DsaSfaParams* p);
+/* ABI version of this header. */
+int dsa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_B200_H_ */

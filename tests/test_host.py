@@ -1,0 +1,145 @@
+"""CPU-only checks of the host side: library loads and exports the declared C ABI, struct layouts
+match the header, argument guards raise like the reference wrappers, row sharding is exact."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "dsa_b200.h")
+
+
+def test_library_exports_every_declared_symbol():
+    from dsa_triton_ascend_b200 import _cabi
+    text = open(HEADER).read()
+    declared = set(re.findall(r"\b(dsa_[a-z0-9_]+)\s*\(", text))
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(_cabi.lib, name), f"{name} is declared in include/dsa_b200.h but not exported"
+    assert set(_cabi.EXPORTS) <= declared
+    assert _cabi.lib.dsa_abi_version() >= 1
+    assert _cabi.status_string(0) == "ok" and "NULL" in _cabi.status_string(-1)
+
+
+def test_ctypes_structs_match_the_c_header():
+    from dsa_triton_ascend_b200 import _cabi
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu\\n",' \
+          'sizeof(DsaLiParams),sizeof(DsaSfaParams),offsetof(DsaLiParams,phases),' \
+          'offsetof(DsaSfaParams,scale),offsetof(DsaLiParams,out_indices));return 0;}\n'
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "t.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "t")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        li, sfa, off_ph, off_sc, off_oi = map(int, subprocess.check_output([exe]).split())
+    assert li == ctypes.sizeof(_cabi.DsaLiParams) and sfa == ctypes.sizeof(_cabi.DsaSfaParams)
+    assert off_ph == _cabi.DsaLiParams.phases.offset
+    assert off_sc == _cabi.DsaSfaParams.scale.offset
+    assert off_oi == _cabi.DsaLiParams.out_indices.offset
+
+
+def test_abi_rejects_bad_arguments_without_a_gpu():
+    from dsa_triton_ascend_b200 import _cabi
+    n = ctypes.c_size_t(0)
+    p = _cabi.DsaLiParams()
+    assert _cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -2  # struct_size 0
+    p.struct_size = ctypes.sizeof(p)
+    assert _cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -1  # NULL pointers
+    p.query = p.key = p.weights = p.out_indices = 256
+    p.batch, p.s1, p.s2, p.n1, p.n2, p.d = 1, 8, 64, 8, 3, 128
+    p.sparse_count, p.sparse_mode, p.phases = 16, 3, 3
+    assert _cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -3  # n1 % n2
+    p.n2 = 1
+    assert _cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    assert n.value >= 8 * 64 * 4
+    p.sparse_count = 1 << 20
+    assert _cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -8
+    p.sparse_count = 16
+    # forward refuses a missing / misaligned workspace before touching the device
+    assert _cabi.lib.dsa_li_forward(ctypes.byref(p), None, 0, None) == -4
+    s = _cabi.DsaSfaParams()
+    s.struct_size = ctypes.sizeof(s)
+    s.query = s.query_rope = s.key = s.key_rope = s.sparse_indices = s.out = 256
+    s.batch, s.s1, s.s2, s.n1, s.d, s.d_rope = 1, 4, 64, 8, 192, 64
+    s.sparse_count, s.sparse_block_size, s.sparse_mode = 16, 1, 3
+    assert _cabi.lib.dsa_sfa_workspace_bytes(ctypes.byref(s), ctypes.byref(n)) == -3  # D not in {128,256,512}
+    s.d, s.sparse_block_size = 512, 3
+    assert _cabi.lib.dsa_sfa_workspace_bytes(ctypes.byref(s), ctypes.byref(n)) == -3
+    s.sparse_block_size = 4
+    assert _cabi.lib.dsa_sfa_workspace_bytes(ctypes.byref(s), ctypes.byref(n)) == 0
+
+
+def _sfa_args(D=512, Dr=64, N1=8, N2=1):
+    bf = torch.bfloat16
+    q = torch.zeros(1, 4, N1, D, dtype=bf)
+    k = torch.zeros(1, 32, N2, D, dtype=bf)
+    qr = torch.zeros(1, 4, N1, Dr, dtype=bf)
+    kr = torch.zeros(1, 32, N2, Dr, dtype=bf)
+    si = torch.zeros(1, 4, 1, 8, dtype=torch.int32)
+    return q, k, qr, kr, si
+
+
+@pytest.mark.parametrize("kw", [
+    dict(attention_mode=1), dict(pre_tokens=5), dict(next_tokens=0), dict(sparse_mode=2),
+    dict(sparse_block_size=3), dict(sparse_block_size=256), dict(sparse_block_size=0),
+    dict(layout_kv="PA_BSND"),
+])
+def test_sfa_guards_raise_value_error_like_the_reference(kw):
+    """sparse_flash_attention_triton.py:1341-1351,1377-1378."""
+    from dsa_triton_ascend_b200 import sparse_flash_attention_triton
+    q, k, qr, kr, si = _sfa_args()
+    with pytest.raises(ValueError):
+        sparse_flash_attention_triton(q, k, k, si, query_rope=qr, key_rope=kr, **kw)
+
+
+def test_sfa_shape_guards_raise_value_error():
+    """sparse_flash_attention_triton.py:1391-1398 and the missing-rope guard (:1347-1348)."""
+    from dsa_triton_ascend_b200 import sparse_flash_attention_triton
+    q, k, qr, kr, si = _sfa_args()
+    with pytest.raises(ValueError):
+        sparse_flash_attention_triton(q, k, k, si, query_rope=None, key_rope=kr)
+    q, k, qr, kr, si = _sfa_args(D=192)
+    with pytest.raises(ValueError):
+        sparse_flash_attention_triton(q, k, k, si, query_rope=qr, key_rope=kr)
+    q, k, qr, kr, si = _sfa_args(Dr=32)
+    with pytest.raises(ValueError):
+        sparse_flash_attention_triton(q, k, k, si, query_rope=qr, key_rope=kr)
+    q, k, qr, kr, si = _sfa_args(N2=2)
+    with pytest.raises(ValueError):
+        sparse_flash_attention_triton(q, k, k, si, query_rope=qr, key_rope=kr)
+
+
+def test_li_guards_raise_value_error_like_the_reference():
+    """lightning_indexer_triton.py:501-502 (block_table without a paged layout), :524-525."""
+    from dsa_triton_ascend_b200 import LightningIndexerTriton, lightning_indexer_triton
+    bf = torch.bfloat16
+    q = torch.zeros(1, 4, 8, 128, dtype=bf)
+    k = torch.zeros(1, 16, 1, 128, dtype=bf)
+    w = torch.zeros(1, 4, 8)
+    with pytest.raises(ValueError):
+        lightning_indexer_triton(q, k, w, block_table=torch.zeros(1, 1, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        lightning_indexer_triton(q, torch.zeros(1, 16, 3, 128, dtype=bf), w)
+    with pytest.raises(ValueError):
+        lightning_indexer_triton(q, k, w, sparse_mode=1)
+    with pytest.raises(ValueError):
+        lightning_indexer_triton(q[0], k, w, layout_query="TND")  # TND needs cumulative lengths
+    cell = LightningIndexerTriton(sparse_count=4)
+    assert cell.sparse_mode == 3 and cell.layout_query == "BSND" and not cell.return_value
+    with pytest.raises(RuntimeError):  # CPU tensors: there is no CPU path
+        cell(q, k, w)
+
+
+def test_product_package_never_imports_the_oracle():
+    code = "import sys, dsa_triton_ascend_b200; assert not any(m == 'oracle' or m.startswith('oracle.') " \
+           "for m in sys.modules), 'oracle imported by the product package'"
+    subprocess.check_call([sys.executable, "-c", code], cwd=ROOT)
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "dsa_triton_ascend_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                assert "oracle" not in open(os.path.join(dirpath, f)).read().replace("numpy golden", ""), f
