@@ -1,6 +1,6 @@
 """Build libdsa_b200.so in-tree with nvcc for sm_100a.
 
-    python -m dsa_triton_ascend_b200.csrc.build [--verbose]
+    python dsa_triton_ascend_b200/csrc/build.py [--verbose]
 
 The library has no dependency besides the CUDA runtime (statically linked by nvcc's default
 cudart=static) and the driver API entry point it resolves at run time.
