@@ -1,7 +1,7 @@
 """ctypes binding of libdsa_b200.so (the C ABI declared in include/dsa_b200.h).
 
 There is no fallback: importing this module fails loudly when the CUDA library has not been
-built (`python -m dsa_triton_ascend_b200.csrc.build`).
+built (`python dsa_triton_ascend_b200/csrc/build.py`).
 """
 import ctypes
 import os
@@ -59,13 +59,14 @@ EXPORTS = (
     "dsa_abi_version", "dsa_status_string", "dsa_read_device_status",
     "dsa_li_workspace_bytes", "dsa_li_forward", "dsa_li_uses_tensor_path",
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
+    "dsa_li_forward_static", "dsa_li_static_scratch_bytes",
 )
 
 
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m dsa_triton_ascend_b200.csrc.build` "
+            f"{LIB_PATH} is missing: build it with `python dsa_triton_ascend_b200/csrc/build.py` "
             "(nvcc, sm_100a). There is no CPU or eager fallback.")
     lib = _c.CDLL(LIB_PATH)
     lib.dsa_abi_version.restype = _c.c_int
@@ -82,6 +83,9 @@ def _load():
         f = getattr(lib, f"dsa_{name}_uses_tensor_path")
         f.argtypes = [_c.POINTER(ptype)]
         f.restype = _c.c_int
+    lib.dsa_li_forward_static.argtypes = [_c.POINTER(DsaLiParams), _c.c_void_p]
+    lib.dsa_li_forward_static.restype = _c.c_int
+    lib.dsa_li_static_scratch_bytes.restype = _c.c_size_t
     return lib
 
 

@@ -229,6 +229,48 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
   return sfa_launch_simt<__half>(p, cs);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Indexer entry point for callers that cannot hand over a workspace and must not allocate.
+// The fp32 score rows live in a fixed array inside the library image instead.
+// ---------------------------------------------------------------------------------------------
+#define DSA_LI_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_li_static_scratch[kWorkspaceHeader + DSA_LI_STATIC_SCRATCH_BYTES];
+
+// Device address of the array, resolved once per device.  In host code the array's name is only
+// a handle for the runtime, never a pointer a kernel may use.
+static void* g_li_static_ptr[64] = {nullptr};
+
+static int li_static_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
+  void* ptr = __atomic_load_n(&g_li_static_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    if (cudaGetSymbolAddress(&ptr, g_li_static_scratch) != cudaSuccess || ptr == nullptr) return DSA_ERR_CUDA;
+    __atomic_store_n(&g_li_static_ptr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return DSA_OK;
+}
+
+size_t dsa_li_static_scratch_bytes(void) { return (size_t)DSA_LI_STATIC_SCRATCH_BYTES; }
+
+int dsa_li_forward_static(const DsaLiParams* p, void* stream) {
+  int st = li_validate(p);
+  if (st != DSA_OK) return st;
+  const int64_t score_bytes = li_rows(p) * p->n2 * li_score_ld(p) * 4;
+  if (score_bytes > (int64_t)DSA_LI_STATIC_SCRATCH_BYTES) return DSA_ERR_TOO_LARGE;
+  if (p->kernel == DSA_KERNEL_TENSOR) return DSA_ERR_UNSUPPORTED;
+  void* scratch = nullptr;
+  st = li_static_scratch(&scratch);
+  if (st != DSA_OK) return st;
+  cudaStream_t cs = (cudaStream_t)stream;
+  // the array keeps the previous call's bytes: the status word has to start at zero
+  if (cudaMemsetAsync(scratch, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  float* scores = reinterpret_cast<float*>((char*)scratch + kWorkspaceHeader);
+  if (p->dtype_qk == DSA_DTYPE_BF16) return li_launch<__nv_bfloat16>(p, scores, cs);
+  return li_launch<__half>(p, scores, cs);
+}
+
 int dsa_read_device_status(const void* workspace, void* stream) {
   if (!workspace) return DSA_ERR_NULL;
   int32_t word = 0;

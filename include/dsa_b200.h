@@ -135,6 +135,34 @@ int dsa_li_forward(const DsaLiParams* p, void* workspace, size_t workspace_bytes
 int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes);
 int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * dsa_li_forward_static - the indexer without a caller workspace and without any allocation.
+ * (No counterpart in the reference; added for hosts described below.)
+ *
+ * Some hosts of this operator cannot give it scratch memory: a graph-op boundary like the
+ * reference's `_ms_pyfunc` core hands the kernel launcher exactly the tensors its shape
+ * inference declared, and a launcher running inside such a callback must not call cudaMalloc
+ * either - that would bypass the framework's memory pool, can fail once a serving engine has
+ * reserved all of HBM for its caches, and synchronises the device.  For them the fp32 score
+ * rows (the only scratch the indexer needs) live in a fixed array of
+ * dsa_li_static_scratch_bytes() = 32 MiB inside the library image; every GPU that loads the
+ * library holds that array until the process exits.
+ *
+ *  - Same parameters, results and status codes as dsa_li_forward with the portable kernels
+ *    (kernel = DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE; DSA_KERNEL_TENSOR is refused with
+ *    DSA_ERR_UNSUPPORTED).  The caller still passes every input and output buffer.
+ *  - rows * n2 * round_up(s2, 4) * 4 bytes must fit the array, otherwise DSA_ERR_TOO_LARGE
+ *    (e.g. 1024 query rows x 8192 keys, or 128 rows x 65536 keys).
+ *  - It calls no cudaMalloc / cudaFree or other allocating routine.  The first call on each
+ *    device looks up the array's device address (with that device current); make that first
+ *    call outside any stream capture.
+ *  - All calls on a device share the one array: calls whose kernels may overlap on the GPU
+ *    (different streams, or different threads) race on it and must be serialised by the
+ *    caller.  Nothing in the array needs to survive between calls.
+ */
+int dsa_li_forward_static(const DsaLiParams* p, void* stream);
+size_t dsa_li_static_scratch_bytes(void);
+
 /* Static description of a status code. */
 const char* dsa_status_string(int status);
 /* Synchronises `stream` and returns the device status word stored at the start of a

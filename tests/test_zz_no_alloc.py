@@ -1,0 +1,63 @@
+"""dsa_li_forward_static: the indexer entry point that takes no workspace and allocates nothing.
+
+It exists for hosts that can neither pass scratch memory through their operator boundary nor
+call cudaMalloc inside an operator callback; its score scratch is a fixed 32 MiB array inside
+the library.  Checked here through the C ABI against dsa_li_forward on the same inputs, twice
+in a row (the array keeps the previous call's contents, so the second call must not be
+disturbed by the first), plus the size limit.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(li_mod, q, k, w, count):
+    p, keep, idx, val, shape = li_mod._build_params(q, k, w, None, None, None, "BSND", "BSND", count, 3, True)
+    return p, keep, idx, val
+
+
+def test_static_scratch_entry_point_matches_workspace_entry_point():
+    from dsa_triton_ascend_b200 import _cabi
+    import dsa_triton_ascend_b200.lightning_indexer as li_mod
+
+    assert _cabi.lib.dsa_li_static_scratch_bytes() == 32 << 20
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(123)
+    for call, (S1, S2, count) in enumerate([(300, 1000, 128), (64, 4096, 2048)]):
+        q = torch.randn(2, S1, 64, 128, generator=g, device="cuda").bfloat16()
+        k = torch.randn(2, S2, 1, 128, generator=g, device="cuda").bfloat16()
+        w = torch.randn(2, S1, 64, generator=g, device="cuda") / 8
+
+        p, keep, idx_ref, val_ref = _params(li_mod, q, k, w, count)
+        n = ctypes.c_size_t(0)
+        _cabi.check(_cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)), "workspace_bytes")
+        ws = torch.empty(n.value, dtype=torch.uint8, device="cuda")
+        _cabi.check(_cabi.lib.dsa_li_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), stream), "forward")
+
+        p2, keep2, idx, val = _params(li_mod, q, k, w, count)
+        idx.fill_(-7)
+        before = torch.cuda.memory_allocated()
+        _cabi.check(_cabi.lib.dsa_li_forward_static(ctypes.byref(p2), stream), "forward_static")
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        # integer indices and io-dtype values: the two entry points run the same kernels, so
+        # the tolerance is exact equality
+        assert torch.equal(idx, idx_ref), f"call {call}: indices differ"
+        assert torch.equal(val, val_ref), f"call {call}: values differ"
+        assert _cabi.lib.dsa_read_device_status(ws.data_ptr(), stream) == 0
+
+
+def test_static_scratch_entry_point_rejects_oversized_problems():
+    from dsa_triton_ascend_b200 import _cabi
+    import dsa_triton_ascend_b200.lightning_indexer as li_mod
+
+    q = torch.zeros(1, 2048, 64, 128, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 8192, 1, 128, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(1, 2048, 64, device="cuda")
+    p, keep, idx, val = _params(li_mod, q, k, w, 64)  # 2048 x 8192 x 4 B = 64 MiB > 32 MiB
+    stream = torch.cuda.current_stream().cuda_stream
+    code = _cabi.lib.dsa_li_forward_static(ctypes.byref(p), stream)
+    assert code == -8 and "maximum" in _cabi.status_string(code)
