@@ -7,6 +7,7 @@
 #include "../../include/dsa_b200.h"
 #include "dsa_common.cuh"
 #include "li_score_simt.cuh"
+#include "li_score_sm100.cuh"
 #include "li_topk.cuh"
 #include "sfa_fwd_simt.cuh"
 
@@ -62,14 +63,22 @@ static LiDev li_dev(const DsaLiParams* p) {
   return d;
 }
 
+// The tcgen05 score kernel serves the production shape; everything else runs on the portable one.
+static bool li_takes_tensor_path(const DsaLiParams* p) {
+  return p->kernel != DSA_KERNEL_PORTABLE && li_sm100_eligible(p);
+}
+
 template <typename T>
-static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st) {
+static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32_t* status = nullptr) {
   LiDev d = li_dev(p);
   const int64_t ld = li_score_ld(p);
   const int64_t rown = (int64_t)d.rows * p->n2;
   if (rown == 0) return DSA_OK;
   if (p->phases & DSA_PHASE_SCORE) {
-    if (p->s2 > 0) {
+    if (p->s2 > 0 && status != nullptr && li_takes_tensor_path(p)) {
+      int rc = li_sm100_launch(p, d, scores, ld, status, st);
+      if (rc != DSA_OK) return rc;
+    } else if (p->s2 > 0) {
       dim3 grid((unsigned)rown, (unsigned)((p->s2 + kSimtKeys - 1) / kSimtKeys), 1);
       li_score_simt_kernel<T><<<grid, kSimtKeys, 0, st>>>(d, scores, ld);
       if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
@@ -177,7 +186,7 @@ const char* dsa_status_string(int status) {
 
 int dsa_li_uses_tensor_path(const DsaLiParams* p) {
   if (li_validate(p) != DSA_OK) return 0;
-  return 0;
+  return li_takes_tensor_path(p) ? 1 : 0;
 }
 
 int dsa_sfa_uses_tensor_path(const DsaSfaParams* p) {
@@ -204,8 +213,8 @@ int dsa_li_forward(const DsaLiParams* p, void* workspace, size_t workspace_bytes
   cudaStream_t cs = (cudaStream_t)stream;
   if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
   float* scores = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
-  if (p->dtype_qk == DSA_DTYPE_BF16) return li_launch<__nv_bfloat16>(p, scores, cs);
-  return li_launch<__half>(p, scores, cs);
+  if (p->dtype_qk == DSA_DTYPE_BF16) return li_launch<__nv_bfloat16>(p, scores, cs, (int32_t*)workspace);
+  return li_launch<__half>(p, scores, cs, (int32_t*)workspace);
 }
 
 int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes) {

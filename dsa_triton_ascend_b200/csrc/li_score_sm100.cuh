@@ -1,0 +1,320 @@
+// Lightning-indexer score kernel on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16, BSND layouts.
+//
+// GEMM orientation: KEYS sit on the MMA M axis (128 keys = 128 TMEM lanes) and (token, head)
+// pairs on the N axis (4 tokens x 64 heads = 256 columns), so that after a TMEM load every
+// thread owns one key and the ReLU * weight * head-sum epilogue is thread-local.
+//
+// One CTA works on items of 8 consecutive query rows of one sequence: their Q (8 x 64 x 128,
+// 128 KB) stays in shared memory while 128-key tiles stream through a 3-stage TMA ring.  Each key
+// tile feeds two accumulators (rows 0-3 and rows 4-7, 256 TMEM columns each), which double-buffer
+// the epilogue against the MMAs.  Tiles beyond the causal limit of the item's last row are
+// skipped; the diagonal tile is masked in the epilogue.  Items are statically spread over a
+// persistent grid in snake order of decreasing work.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
+// epilogue (TMEM lane quarter = warp % 4, column half = (warp - 2) / 4).
+#pragma once
+
+#include "li_score_simt.cuh"
+#include "ptx_sm100.cuh"
+
+namespace dsa {
+
+constexpr int kLiTok = 8;        // query rows per item
+constexpr int kLiHalf = 4;       // query rows per accumulator
+constexpr int kLiHeads = 64;
+constexpr int kLiDim = 128;
+constexpr int kLiKeys = 128;     // keys per tile
+constexpr int kLiStages = 3;
+constexpr int kLiThreads = 320;
+constexpr int kLiEpiWarps = 8;
+
+constexpr uint32_t kLiQBlock = 256 * 128;                 // one 64-column block of one half: 256 rows x 128 B
+constexpr uint32_t kLiQBytes = 4 * kLiQBlock;             // 2 halves x 2 column blocks = 128 KB
+constexpr uint32_t kLiKBlock = kLiKeys * 128;             // 128 rows x 128 B
+constexpr uint32_t kLiKStage = 2 * kLiKBlock;             // 32 KB
+constexpr uint32_t kLiOffK = kLiQBytes;
+constexpr uint32_t kLiOffW = kLiOffK + kLiStages * kLiKStage;
+constexpr uint32_t kLiOffBar = kLiOffW + kLiTok * kLiHeads * 4;
+constexpr uint32_t kLiSmemBytes = kLiOffBar + 128;
+
+struct LiSm100Args {
+  LiDev p;
+  float* scores;
+  int64_t ld;
+  int32_t* status;        // device status word (workspace header)
+  int32_t groups_per_seq; // ceil(s1 / 8)
+  int32_t items;          // batch * groups_per_seq
+  uint32_t idesc;
+};
+
+// Item i (0 = most work) -> (sequence b, first row position).  Later rows see more keys under the
+// causal mask, so items are ordered by decreasing position, sequences interleaved.
+__device__ __forceinline__ void li_item(const LiSm100Args& a, int32_t i, int32_t* b, int32_t* pos0) {
+  const int32_t B = a.p.seq.batch;
+  *b = i % B;
+  *pos0 = (a.groups_per_seq - 1 - i / B) * kLiTok;
+}
+// j-th item of CTA c in snake order over a persistent grid of g CTAs (-1 when exhausted).
+__device__ __forceinline__ int32_t li_item_of(int32_t c, int32_t g, int32_t j, int32_t items) {
+  const int32_t i = (j & 1) ? (j * g + (g - 1 - c)) : (j * g + c);
+  return i < items ? i : -1;
+}
+// Visible key count of each of the item's rows and the number of key tiles to process.
+__device__ __forceinline__ int32_t li_item_tiles(const LiSm100Args& a, int32_t b, int32_t pos0, int32_t* vis) {
+  int32_t mx = 0;
+#pragma unroll
+  for (int t = 0; t < kLiTok; ++t) {
+    int32_t v = 0;
+    if (pos0 + t < a.p.seq.s1) v = row_info(a.p.seq, b * a.p.seq.s1 + pos0 + t).visible;
+    if (vis) vis[t] = v;
+    mx = max(mx, v);
+  }
+  return (mx + kLiKeys - 1) / kLiKeys;
+}
+
+__global__ void __launch_bounds__(kLiThreads, 1)
+li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const LiSm100Args a) {
+  extern __shared__ __align__(1024) unsigned char li_smem[];
+  unsigned char* q_s = li_smem;
+  unsigned char* k_s = li_smem + kLiOffK;
+  float* w_s = reinterpret_cast<float*>(li_smem + kLiOffW);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(li_smem + kLiOffBar);
+  uint64_t* full = bars;            // [3] TMA -> MMA
+  uint64_t* empty = bars + 3;       // [3] MMA -> TMA
+  uint64_t* qfull = bars + 6;
+  uint64_t* qempty = bars + 7;
+  uint64_t* tfull = bars + 8;       // [2] MMA -> epilogue
+  uint64_t* tempty = bars + 10;     // [2] epilogue -> MMA
+  uint64_t* wbar = bars + 12;       // epilogue-internal rendezvous around the weight staging
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t cta = blockIdx.x, grid = gridDim.x;
+
+  if ((ptx::smem_u32(li_smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(a.status, 2);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 3; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
+    ptx::mbar_init(qfull, 1);
+    ptx::mbar_init(qempty, 1);
+    for (int i = 0; i < 2; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kLiEpiWarps); }
+    ptx::mbar_init(wbar, kLiEpiWarps * 32);
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      ptx::prefetch_tmap(&tmap_q);
+      ptx::prefetch_tmap(&tmap_k);
+      uint32_t n_item = 0, n_tile = 0;
+      bool ok = true;
+      for (int32_t j = 0; ok; ++j) {
+        const int32_t it = li_item_of(cta, grid, j, a.items);
+        if (it < 0) break;
+        int32_t b, pos0;
+        li_item(a, it, &b, &pos0);
+        const int32_t tiles = li_item_tiles(a, b, pos0, nullptr);
+        if (tiles == 0) continue;
+        ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        ptx::mbar_arrive_expect_tx(qfull, kLiQBytes);
+        const int32_t qrow = (b * a.p.seq.s1 + pos0) * kLiHeads;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+            ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+        ++n_item;
+        const int32_t krow0 = b * a.p.seq.s2;
+        for (int32_t t = 0; t < tiles; ++t, ++n_tile) {
+          const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+          ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          ptx::mbar_arrive_expect_tx(&full[s], kLiKStage);
+          ptx::tma_load_2d(k_s + s * kLiKStage, &tmap_k, &full[s], 0, krow0 + t * kLiKeys);
+          ptx::tma_load_2d(k_s + s * kLiKStage + kLiKBlock, &tmap_k, &full[s], 64, krow0 + t * kLiKeys);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (ptx::elect_one()) {
+      uint32_t n_item = 0, n_tile = 0;
+      bool ok = true;
+      const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s);
+      for (int32_t j = 0; ok; ++j) {
+        const int32_t it = li_item_of(cta, grid, j, a.items);
+        if (it < 0) break;
+        int32_t b, pos0;
+        li_item(a, it, &b, &pos0);
+        const int32_t tiles = li_item_tiles(a, b, pos0, nullptr);
+        if (tiles == 0) continue;
+        ok = ptx::mbar_wait(qfull, n_item & 1, abort_flag);
+        if (!ok) break;
+        ++n_item;
+        for (int32_t t = 0; t < tiles && ok; ++t, ++n_tile) {
+          const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+          ok = ptx::mbar_wait(&full[s], use & 1, abort_flag);
+          if (!ok) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            ok = ptx::mbar_wait(&tempty[h], (n_tile & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < kLiDim / 16; ++ks) {
+              const uint32_t ka = k_addr + s * kLiKStage + (ks >> 2) * kLiKBlock + (ks & 3) * 32;
+              const uint32_t qa = q_addr + h * 2 * kLiQBlock + (ks >> 2) * kLiQBlock + (ks & 3) * 32;
+              ptx::mma_ss(tmem + h * 256, ptx::desc_kmajor_sw128(ka), ptx::desc_kmajor_sw128(qa), a.idesc, ks > 0);
+            }
+            ptx::mma_commit(&tfull[h]);
+          }
+          if (!ok) break;
+          ptx::mma_commit(&empty[s]);
+        }
+        if (ok) ptx::mma_commit(qempty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int chalf = ew >> 2;
+    const int et = threadIdx.x - 64;  // 0..255
+    uint32_t n_tile = 0, n_sync = 0;
+    bool ok = true;
+    for (int32_t j = 0; ok; ++j) {
+      const int32_t it = li_item_of(cta, grid, j, a.items);
+      if (it < 0) break;
+      int32_t b, pos0, vis[kLiTok];
+      li_item(a, it, &b, &pos0);
+      const int32_t tiles = li_item_tiles(a, b, pos0, vis);
+      if (tiles == 0) continue;
+      const int32_t row0 = b * a.p.seq.s1 + pos0;
+      // weights of the item's 8 rows -> shared memory (rows past the sequence end read as zero)
+      // (rendezvous through an mbarrier so that even this wait is bounded)
+      ptx::mbar_arrive(wbar);
+      ok = ptx::mbar_wait(wbar, n_sync++ & 1, abort_flag);
+      if (!ok) break;
+      for (int i = et; i < kLiTok * kLiHeads; i += 256) {
+        const int t = i / kLiHeads;
+        w_s[i] = (pos0 + t < a.p.seq.s1) ? load_weight(a.p.weights, a.p.dtype_w, (int64_t)(row0 + t) * kLiHeads + (i - t * kLiHeads))
+                                        : 0.f;
+      }
+      ptx::mbar_arrive(wbar);
+      ok = ptx::mbar_wait(wbar, n_sync++ & 1, abort_flag);
+      if (!ok) break;
+      for (int32_t t = 0; t < tiles && ok; ++t, ++n_tile) {
+        const int32_t pos = t * kLiKeys + quarter * 32 + lane;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          ok = ptx::mbar_wait(&tfull[h], n_tile & 1, abort_flag);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          uint32_t r0[64], r1[64];
+          const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + h * 256 + chalf * 128;
+          ptx::tmem_ld_x32(taddr, r0);
+          ptx::tmem_ld_x32(taddr + 32, r0 + 32);
+          ptx::tmem_ld_x32(taddr + 64, r1);
+          ptx::tmem_ld_x32(taddr + 96, r1 + 32);
+          ptx::tmem_ld_wait();
+          // the accumulator is in registers: hand the TMEM buffer back before doing the math
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&tempty[h]);
+          const int tok0 = h * kLiHalf + chalf * 2;
+          const float* w0 = w_s + tok0 * kLiHeads;
+          const float* w1 = w0 + kLiHeads;
+          float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
+#pragma unroll
+          for (int g = 0; g < kLiHeads; g += 2) {
+            s0a = fmaf(fmaxf(__uint_as_float(r0[g]), 0.f), w0[g], s0a);
+            s0b = fmaf(fmaxf(__uint_as_float(r0[g + 1]), 0.f), w0[g + 1], s0b);
+            s1a = fmaf(fmaxf(__uint_as_float(r1[g]), 0.f), w1[g], s1a);
+            s1b = fmaf(fmaxf(__uint_as_float(r1[g + 1]), 0.f), w1[g + 1], s1b);
+          }
+          if (pos < vis[tok0]) a.scores[(int64_t)(row0 + tok0) * a.ld + pos] = s0a + s0b + 0.f;
+          if (pos < vis[tok0 + 1]) a.scores[(int64_t)(row0 + tok0 + 1) * a.ld + pos] = s1a + s1b + 0.f;
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // a bounded wait gave up: give copies and MMAs still in flight time to land before the
+    // shared and tensor memory they target is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, 1);
+}
+
+// Host side: eligibility, tensor maps, launch.
+inline bool li_sm100_eligible(const DsaLiParams* p) {
+  if (p->layout_q != DSA_LAYOUT_BSND || p->layout_k != DSA_LAYOUT_BSND) return false;
+  if (p->n1 != kLiHeads || p->n2 != 1 || p->d != kLiDim) return false;
+  if (p->s1 < 1 || p->s2 < 1) return false;
+  if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->key & 15u)) return false;
+  if ((int64_t)p->batch * p->s1 * kLiHeads >= (1ll << 31) || (int64_t)p->batch * p->s2 >= (1ll << 31)) return false;
+  if (p->seq_q_cumulative || p->seq_k_cumulative) return false;
+  return true;
+}
+
+inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, int64_t ld, int32_t* status,
+                           cudaStream_t st) {
+  static int sm_count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
+  if (sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return DSA_ERR_CUDA;
+    if (cudaFuncSetAttribute(li_score_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLiSmemBytes) !=
+        cudaSuccess)
+      return DSA_ERR_CUDA;
+    sm_count[dev] = n;
+  }
+  const bool bf16 = p->dtype_qk == DSA_DTYPE_BF16;
+  CUtensorMap tq, tk;
+  if (!make_tmap_2d_16bit(&tq, p->query, (uint64_t)p->batch * p->s1 * kLiHeads, kLiDim, kLiDim * 2, 256, 64, bf16))
+    return DSA_ERR_CUDA;
+  if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->batch * p->s2, kLiDim, kLiDim * 2, kLiKeys, 64, bf16))
+    return DSA_ERR_CUDA;
+  LiSm100Args a;
+  a.p = d;
+  a.scores = scores;
+  a.ld = ld;
+  a.status = status;
+  a.groups_per_seq = (p->s1 + kLiTok - 1) / kLiTok;
+  a.items = p->batch * a.groups_per_seq;
+  a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
+  const int grid = a.items < sm_count[dev] ? a.items : sm_count[dev];
+  li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  return DSA_OK;
+}
+
+}  // namespace dsa

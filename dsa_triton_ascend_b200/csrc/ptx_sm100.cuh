@@ -36,16 +36,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(8000u)  // suspend-time hint in ns
       : "memory");
   return done != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets the other warps of a CTA leave quickly once
 // one of them has given up.  Returns false on timeout / abort.
-constexpr uint32_t kWaitPolls = 1u << 22;
+constexpr uint32_t kWaitPolls = 1u << 20;  // x (up to) 8 us per poll: gives up within seconds
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kWaitPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;

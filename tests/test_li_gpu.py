@@ -174,3 +174,41 @@ def test_li_full_size_sampled_rows():
     got_i, got_v = host(idx)[0, sel[:, 1]], host(val)[0, sel[:, 1]]
     gap = li_gap_ok(qn, kn, wn, [S], [S], rows, 1, K, 3)
     _check_rows(got_i, got_v, ref_i[0, sel[:, 1]], ref_v[0, sel[:, 1]], gap, min_positional=0.5)
+
+
+def test_li_production_shape_runs_on_the_tensor_core_path():
+    """64 heads x D=128 BSND goes through the tcgen05 kernel; it must agree with the portable
+    CUDA-core kernel on every row and leave a clean device status word."""
+    import ctypes
+    from dsa_triton_ascend_b200 import _cabi
+    li = _li()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    B, S1, S2, K = 2, 300, 1000, 256
+    q = torch.randn(B, S1, 64, 128, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, S2, 1, 128, generator=g, device="cuda").bfloat16()
+    w = torch.randn(B, S1, 64, generator=g, device="cuda") / 8
+    p, keep, idx, val, _ = li._build_params(q, k, w, [300, 77], [1000, 640], None, "BSND", "BSND", K, 3, True)
+    assert _cabi.lib.dsa_li_uses_tensor_path(ctypes.byref(p)) == 1
+    n = ctypes.c_size_t(0)
+    _cabi.check(_cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)), "ws")
+    ws = torch.empty(n.value, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.check(_cabi.lib.dsa_li_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), stream), "tensor")
+    assert _cabi.lib.dsa_read_device_status(ws.data_ptr(), stream) == 0
+    scores_t = ws[256:].view(torch.float32).clone()
+    idx_t, val_t = idx.clone(), val.clone()
+    p.kernel = _cabi.KERNEL_PORTABLE
+    assert _cabi.lib.dsa_li_uses_tensor_path(ctypes.byref(p)) == 0
+    _cabi.check(_cabi.lib.dsa_li_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), stream), "portable")
+    torch.cuda.synchronize()
+    scores_p = ws[256:].view(torch.float32)
+    # compare the visible prefixes of the raw fp32 scores (the rest of the scratch is never written)
+    ld = (S2 + 3) // 4 * 4
+    st, sp = scores_t.view(-1)[:B * S1 * ld].view(B, S1, ld), scores_p.view(-1)[:B * S1 * ld].view(B, S1, ld)
+    for b, (aq, ak) in enumerate([(300, 1000), (77, 640)]):
+        for s in (0, 1, aq // 2, aq - 1):
+            vis = min(max(ak - aq + s + 1, 0), ak)
+            assert torch.allclose(st[b, s, :vis], sp[b, s, :vis], rtol=2e-5, atol=2e-5)
+    same = (idx_t == idx).all(dim=-1).float().mean().item()
+    assert same >= 0.97, f"tensor and portable paths agree on {same:.4f} of the rows"
+    del keep
