@@ -34,6 +34,7 @@ class DsaLiParams(_c.Structure):
         ("block_size", _c.c_int32), ("max_blocks", _c.c_int32),
         ("sparse_count", _c.c_int32), ("sparse_mode", _c.c_int32),
         ("rank_mode", _c.c_int32), ("return_value", _c.c_int32), ("phases", _c.c_int32),
+        ("key_rows", _c.c_int64),
     ]
 
 
@@ -52,6 +53,7 @@ class DsaSfaParams(_c.Structure):
         ("sparse_count", _c.c_int32), ("sparse_block_size", _c.c_int32),
         ("sparse_mode", _c.c_int32), ("return_lse", _c.c_int32),
         ("scale", _c.c_float),
+        ("key_rows", _c.c_int64),
     ]
 
 

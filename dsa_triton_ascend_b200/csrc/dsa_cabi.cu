@@ -10,6 +10,7 @@
 #include "li_score_sm100.cuh"
 #include "li_topk.cuh"
 #include "sfa_fwd_simt.cuh"
+#include "sfa_fwd_sm100.cuh"
 
 namespace dsa {
 
@@ -167,7 +168,7 @@ using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 1; }
+int dsa_abi_version(void) { return 2; }
 
 const char* dsa_status_string(int status) {
   switch (status) {
@@ -191,7 +192,7 @@ int dsa_li_uses_tensor_path(const DsaLiParams* p) {
 
 int dsa_sfa_uses_tensor_path(const DsaSfaParams* p) {
   if (sfa_validate(p) != DSA_OK) return 0;
-  return 0;
+  return (p->kernel != DSA_KERNEL_PORTABLE && sfa_sm100_eligible(p)) ? 1 : 0;
 }
 
 int dsa_li_workspace_bytes(const DsaLiParams* p, size_t* out_bytes) {
@@ -234,6 +235,11 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
   if (p->kernel == DSA_KERNEL_TENSOR && !dsa_sfa_uses_tensor_path(p)) return DSA_ERR_UNSUPPORTED;
   cudaStream_t cs = (cudaStream_t)stream;
   if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  if (dsa_sfa_uses_tensor_path(p)) {
+    SfaDev d = sfa_dev(p);
+    if (d.rows == 0) return DSA_OK;
+    return sfa_sm100_launch(p, d, (int32_t*)workspace, cs);
+  }
   if (p->dtype == DSA_DTYPE_BF16) return sfa_launch_simt<__nv_bfloat16>(p, cs);
   return sfa_launch_simt<__half>(p, cs);
 }

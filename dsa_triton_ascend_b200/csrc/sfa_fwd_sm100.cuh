@@ -1,0 +1,495 @@
+// Sparse flash attention forward on tcgen05 tensor cores for the MLA-absorb production shape:
+// 128 query heads, D = 512 (+64 rope), one KV head, any layout, token- or block-wise indices.
+//
+// Why a 2-CTA cluster per query token.  One token's accumulator O[128 heads x 512] in fp32 is the
+// whole tensor memory of an SM (128 lanes x 512 columns) and its Q[128 x 576] is 147 KB of shared
+// memory, so a single SM cannot hold O, the scores and a deep enough ring of gathered KV rows.
+// The two CTAs of a cluster split the FEATURE axis instead of the heads (which would halve the MMA
+// M dimension and with it the tensor throughput):
+//     CTA 0: nope columns   0..255 + the 64 rope columns  (320 dims of QK^T, value columns   0..255)
+//     CTA 1: nope columns 256..511                         (256 dims of QK^T, value columns 256..511)
+// Each CTA gathers only its own half of every selected KV row (TMA tile::gather4, 128-byte
+// swizzled, 4-stage ring), computes a PARTIAL S = Q_c K_c^T for all 128 heads, sends it to its peer
+// through distributed shared memory, adds the peer's partial, runs the softmax (both CTAs hold the
+// same full S, so no running-max exchange is needed) and accumulates O_c = P V_c with V_c = the
+// nope columns it already holds.  Every MMA is a full-rate 128-row cta_group::1 instruction, every
+// KV byte crosses L2->SM once, and no flop is duplicated except the softmax arithmetic.
+//
+// Tensor memory per CTA (512 columns): O 0..255 | Q (bf16 pairs, MMA A operand) 256..415 |
+// S partial 416..479 | P (bf16 pairs, MMA A operand) 480..511.
+// Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | row queue.
+//
+// Warps (192 threads): 0 = gather producer, 1 = MMA issuer / TMEM owner, 2..5 = softmax + epilogue
+// (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the status word.
+#pragma once
+
+#include "ptx_sm100.cuh"
+#include "sfa_fwd_simt.cuh"
+
+namespace dsa {
+
+constexpr int kSfaHeads = 128;
+constexpr int kSfaBK = 64;         // keys per tile
+constexpr int kSfaStages = 4;
+constexpr int kSfaThreads = 192;
+constexpr int kSfaDvHalf = 256;
+constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
+
+constexpr uint32_t kSfaBlk = kSfaBK * 128;                 // one 64-column block of a stage: 64 rows x 128 B
+constexpr uint32_t kSfaStage = 5 * kSfaBlk;                // 40 KB (rank 1 uses 4 of the 5 blocks)
+constexpr uint32_t kSfaOffX = kSfaStages * kSfaStage;      // 160 KB
+constexpr uint32_t kSfaXBytes = kSfaHeads * kSfaBK * 4;    // 32 KB
+constexpr uint32_t kSfaOffQueue = kSfaOffX + kSfaXBytes;
+constexpr uint32_t kSfaOffBar = kSfaOffQueue + 128 * 4;
+constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 256;
+
+constexpr uint32_t kTmO = 0, kTmQ = 256, kTmS = 416, kTmP = 480;
+constexpr float kSfaRescaleTau = 8.f;  // log2 units: the running reference only moves when exceeded by this
+
+struct SfaSm100Args {
+  SfaDev p;
+  int32_t* status;
+  int32_t rows;
+  uint32_t idesc_qk, idesc_pv;
+  float scale_log2;  // scale * log2(e)
+  int32_t is_bf16;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
+  if (is_bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Number of slots of a row that take part (warp-collective; every lane gets the total).  A slot
+// whose paged block is absent does not take part on this path.
+__device__ __forceinline__ int32_t sfa_count_valid(const SfaDev& p, const RowInfo& ri, const int32_t* idx_row,
+                                                   int32_t slots, int lane) {
+  if (!(ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0)) return 0;
+  int32_t c = 0;
+  for (int32_t j = lane; j < slots; j += 32) {
+    const int32_t tok = sfa_slot_token(p, ri, idx_row, j);
+    c += (tok >= 0 && key_row(p.seq, ri, tok) >= 0) ? 1 : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  return c;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSfaThreads, 1)
+sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_constant__ CUtensorMap tmap_kr,
+                     const SfaSm100Args a) {
+  extern __shared__ __align__(1024) unsigned char sfa_sm[];
+  unsigned char* kv_s = sfa_sm;
+  float* x_s = reinterpret_cast<float*>(sfa_sm + kSfaOffX);
+  int32_t* queue = reinterpret_cast<int32_t*>(sfa_sm + kSfaOffQueue);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
+  uint64_t* kv_full = bars;         // [4] gather -> MMA
+  uint64_t* kv_empty = bars + 4;    // [4] MMA (PV done) -> gather
+  uint64_t* q_full = bars + 8;      // softmax warps (Q stored in TMEM) -> MMA
+  uint64_t* q_empty = bars + 9;     // MMA (last QK of the token done) -> softmax warps
+  uint64_t* s_full = bars + 10;     // MMA -> softmax
+  uint64_t* s_empty = bars + 11;    // softmax (S in registers) -> MMA
+  uint64_t* p_full = bars + 12;     // softmax (P stored, O rescaled) -> MMA
+  uint64_t* p_empty = bars + 13;    // MMA (PV done) -> softmax
+  uint64_t* o_free = bars + 14;     // epilogue (O read out) -> MMA
+  uint64_t* x_full = bars + 15;     // peer's partial S has landed (remote arrivals)
+  uint64_t* x_empty = bars + 16;    // peer has consumed what this CTA sent (remote arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 18);
+  int32_t* tile_cnt = reinterpret_cast<int32_t*>(bars + 19);  // [4] valid keys of the tile in each stage
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const uint32_t peer = rank ^ 1u;
+  const int32_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int nblk = rank == 0 ? 5 : 4;          // 64-column blocks of this CTA's feature half
+  const int nks = nblk * 4;                    // QK^T k-steps (16 dims each)
+  const uint32_t row_bytes = nblk * 128;
+
+  const bool misaligned = (ptx::smem_u32(sfa_sm) & 1023u) != 0;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kSfaStages; ++i) { ptx::mbar_init(&kv_full[i], 1); ptx::mbar_init(&kv_empty[i], 1); }
+    ptx::mbar_init(q_full, 128);
+    ptx::mbar_init(q_empty, 1);
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(s_empty, 128);
+    ptx::mbar_init(p_full, 128);
+    ptx::mbar_init(p_empty, 1);
+    ptx::mbar_init(o_free, 128);
+    ptx::mbar_init(x_full, 128);
+    ptx::mbar_init(x_empty, 128);
+    *abort_flag = misaligned ? 1 : 0;
+    ptx::mbar_fence_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  // the peer's barriers must exist before anything is sent to it
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  const uint32_t tmem = *tmem_slot;
+
+  const int32_t slots = a.p.sparse_count * a.p.sparse_block_size;
+  const int32_t n1d = kSfaHeads * a.p.d;
+
+  if (*abort_flag) {
+    // nothing started: fall through to the teardown
+  } else if (warp == 0) {
+    // ------------------------------------------------------------------ gather producer
+    ptx::prefetch_tmap(&tmap_kn);
+    ptx::prefetch_tmap(&tmap_kr);
+    uint32_t n_tile = 0;
+    bool ok = true;
+    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
+      const RowInfo ri = row_info(a.p.seq, row);
+      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
+      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      int32_t cursor = 0, qhead = 0, qcount = 0;
+      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
+        // compact the physical rows of the next valid slots into the queue (order preserved)
+        while (qcount < cnt) {
+          const int32_t j = cursor + lane;
+          int64_t prow = -1;
+          if (j < slots) {
+            const int32_t tok = sfa_slot_token(a.p, ri, idx_row, j);
+            if (tok >= 0) prow = key_row(a.p.seq, ri, tok);
+          }
+          const uint32_t m = __ballot_sync(0xffffffffu, prow >= 0);
+          if (prow >= 0) queue[(qhead + qcount + __popc(m & ((1u << lane) - 1u))) & 127] = (int32_t)prow;
+          qcount += __popc(m);
+          cursor += 32;
+          __syncwarp();
+        }
+        const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
+        ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          tile_cnt[s] = cnt;
+          ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * row_bytes);
+        }
+        __syncwarp();
+        if (lane < 16) {
+          int32_t r[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int32_t k = lane * 4 + i;
+            r[i] = queue[(qhead + (k < cnt ? k : 0)) & 127];  // slots past the end re-read the first row
+          }
+          unsigned char* dst = kv_s + s * kSfaStage + lane * 512;
+          const int32_t x0 = rank == 0 ? 0 : kSfaDvHalf;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            ptx::tma_gather4_2d(dst + b * kSfaBlk, &tmap_kn, &kv_full[s], x0 + b * 64, r[0], r[1], r[2], r[3]);
+          if (rank == 0) ptx::tma_gather4_2d(dst + 4 * kSfaBlk, &tmap_kr, &kv_full[s], 0, r[0], r[1], r[2], r[3]);
+        }
+        __syncwarp();
+        qhead = (qhead + cnt) & 127;
+        qcount -= cnt;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t n_tile = 0, n_tok = 0;
+    bool ok = true;
+    const uint32_t kv_addr = ptx::smem_u32(kv_s);
+    auto issue_pv = [&](uint32_t tile_no, bool first) -> bool {
+      // O (+)= P V for global tile number `tile_no`
+      if (first && !ptx::mbar_wait(o_free, (n_tok & 1) ^ 1, abort_flag)) return false;
+      if (!ptx::mbar_wait(p_full, tile_no & 1, abort_flag)) return false;
+      ptx::tc_fence_after();
+      const uint32_t s = tile_no % kSfaStages;
+#pragma unroll
+      for (int ks = 0; ks < kSfaBK / 16; ++ks) {
+        const uint64_t bd = ptx::desc_mnmajor_sw128(kv_addr + s * kSfaStage + ks * 16 * 128, kSfaBlk, 1024);
+        ptx::mma_ts(tmem + kTmO, tmem + kTmP + ks * 8, bd, a.idesc_pv, (first && ks == 0) ? 0u : 1u);
+      }
+      ptx::mma_commit(p_empty);
+      ptx::mma_commit(&kv_empty[s]);
+      return true;
+    };
+    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
+      const RowInfo ri = row_info(a.p.seq, row);
+      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
+      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      if (ntiles == 0) continue;
+      if (lane == 0) {
+        ok = ptx::mbar_wait(q_full, n_tok & 1, abort_flag);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
+          ok = ptx::mbar_wait(&kv_full[s], use & 1, abort_flag);
+          if (!ok) break;
+          ok = ptx::mbar_wait(s_empty, (n_tile & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          for (int ks = 0; ks < nks; ++ks) {
+            const uint64_t bd = ptx::desc_kmajor_sw128(kv_addr + s * kSfaStage + (ks >> 2) * kSfaBlk + (ks & 3) * 32);
+            ptx::mma_ts(tmem + kTmS, tmem + kTmQ + ks * 8, bd, a.idesc_qk, ks > 0 ? 1u : 0u);
+          }
+          ptx::mma_commit(s_full);
+          if (t == ntiles - 1) ptx::mma_commit(q_empty);
+          if (t > 0) ok = issue_pv(n_tile - 1, t == 1);
+        }
+        if (ok) ok = issue_pv(n_tile - 1, ntiles == 1);
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
+      ++n_tok;
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int quarter = warp & 3;
+    const int h = quarter * 32 + lane;                       // head == TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t x_peer = ptx::map_to_rank(x_s, peer);
+    const uint32_t x_full_peer = ptx::map_to_rank(x_full, peer);
+    const uint32_t x_empty_peer = ptx::map_to_rank(x_empty, peer);
+    uint32_t n_tile = 0, n_tok = 0;
+    bool ok = true;
+    // waits of these warps are made warp-uniform: the tcgen05 loads / stores that follow are
+    // warp-collective and must never run with part of a warp gone
+    auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+    };
+    auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
+    };
+    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
+      const RowInfo ri = row_info(a.p.seq, row);
+      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
+      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
+      if (ntiles == 0) {
+        // nothing visible: zeros in all three outputs
+#pragma unroll
+        for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+        if (rank == 0 && a.p.return_lse) {
+          a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
+          a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
+        }
+        continue;
+      }
+      // ---- this token's Q half -> tensor memory (bf16 pairs, row h in lane h)
+      ok = wait_w(q_empty, (n_tok & 1) ^ 1);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      {
+        const uint4* qn = reinterpret_cast<const uint4*>((const unsigned char*)a.p.query +
+                                                         ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = __ldg(qn + c * 8 + i);
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+          }
+          ptx::tmem_st_x32(lane_addr + kTmQ + c * 32, w);
+        }
+        if (rank == 0) {
+          const uint4* qr = reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
+                                                           ((int64_t)row * kSfaHeads + h) * a.p.d_rope * 2);
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = __ldg(qr + i);
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+          }
+          ptx::tmem_st_x32(lane_addr + kTmQ + 128, w);
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(q_full);
+      }
+
+      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+        const uint32_t s = n_tile % kSfaStages;
+        // ---- own partial S -> registers
+        ok = wait_w(s_full, n_tile & 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        float sc[kSfaBK];
+        ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sc));
+        ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sc) + 32);
+        ptx::tmem_ld_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(s_empty);
+        const int32_t cnt = tile_cnt[s];
+        // ---- exchange with the peer: send mine (16-byte chunk c of head h at c * 2048 + h * 16)
+        ok = wait_wc(x_empty, (n_tile & 1) ^ 1);
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < kSfaBK / 4; ++c)
+          ptx::st_cluster_v4(x_peer + c * 2048 + h * 16, sc[4 * c], sc[4 * c + 1], sc[4 * c + 2], sc[4 * c + 3]);
+        ptx::mbar_arrive_remote(x_full_peer);
+        ok = wait_wc(x_full, n_tile & 1);
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < kSfaBK / 4; ++c) {
+          const float4 v = *reinterpret_cast<const float4*>(x_s + c * 512 + h * 4);
+          sc[4 * c] += v.x; sc[4 * c + 1] += v.y; sc[4 * c + 2] += v.z; sc[4 * c + 3] += v.w;
+        }
+        ptx::mbar_arrive_remote(x_empty_peer);
+        // ---- softmax in the log2 domain; keys past `cnt` are padding
+        float mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < kSfaBK; ++k) {
+          sc[k] = k < cnt ? sc[k] * a.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sc[k]);
+        }
+        m_true = fmaxf(m_true, mx);
+        float alpha = 1.f;
+        bool rescale = false;
+        if (t == 0) {
+          m_ref = mx;
+        } else if (mx > m_ref + kSfaRescaleTau) {
+          alpha = ex2(m_ref - mx);
+          m_ref = mx;
+          rescale = true;
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < kSfaBK; ++k) {
+          sc[k] = ex2(sc[k] - m_ref);
+          sum += sc[k];
+        }
+        l = l * alpha + sum;
+        if (ntiles == 1) {
+          // a single tile holds the whole row: normalise before rounding, as the golden does
+          const float inv = 1.f / l;
+#pragma unroll
+          for (int k = 0; k < kSfaBK; ++k) sc[k] *= inv;
+        }
+        // ---- P (and, rarely, a rescaled O) -> tensor memory once the previous PV has finished
+        ok = wait_w(p_empty, (n_tile & 1) ^ 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < kSfaDvHalf / 32; ++c) {
+            uint32_t o[32];
+            ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ptx::tmem_st_x32(lane_addr + kTmO + c * 32, o);
+          }
+        }
+        {
+          uint32_t pw[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pw[i] = pack2(sc[2 * i], sc[2 * i + 1], a.is_bf16);
+          ptx::tmem_st_x32(lane_addr + kTmP, pw);
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(p_full);
+      }
+      if (!ok) break;
+      // ---- epilogue: wait for the last PV, normalise, store
+      ok = wait_w(p_empty, (n_tile & 1) ^ 1);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const float inv = ntiles == 1 ? 1.f : 1.f / l;
+#pragma unroll 1
+      for (int c = 0; c < kSfaDvHalf / 32; ++c) {
+        uint32_t o[32];
+        ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
+        ptx::tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(out_row)[c * 4 + i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(o_free);
+      if (rank == 0 && a.p.return_lse) {
+        // max of the scaled scores and sum of exp(score - max), back from the log2 domain
+        a.p.softmax_max[(int64_t)row * kSfaHeads + h] = m_true * 0.6931471805599453f;
+        a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = l * ex2(m_ref - m_true);
+      }
+      ++n_tok;
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);  // let copies / MMAs in flight land
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // neither CTA may leave while its peer can still write into its shared memory
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, misaligned ? 2 : 1);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
+  if (p->n1 != kSfaHeads || p->d != 512 || p->d_rope != 64) return false;
+  if ((int64_t)p->sparse_count * p->sparse_block_size > kSfaMaxSlots) return false;
+  if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->query_rope & 15u) || ((uintptr_t)p->key & 15u) ||
+      ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 15u))
+    return false;
+  if (p->key_rows < 1 || p->key_rows >= (1ll << 31)) return false;
+  return true;
+}
+
+inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* status, cudaStream_t st) {
+  static int sm_count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
+  if (sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 2) return DSA_ERR_CUDA;
+    if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSfaSmemBytes) !=
+        cudaSuccess)
+      return DSA_ERR_CUDA;
+    sm_count[dev] = n;
+  }
+  const bool bf16 = p->dtype == DSA_DTYPE_BF16;
+  CUtensorMap tkn, tkr;
+  if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;
+  if (!make_tmap_gather4_16bit(&tkr, p->key_rope, (uint64_t)p->key_rows, 64, 128, 64, bf16)) return DSA_ERR_CUDA;
+  SfaSm100Args a;
+  a.p = d;
+  a.status = status;
+  a.rows = d.rows;
+  a.idesc_qk = ptx::idesc_f16(bf16 ? 1u : 0u, 128, kSfaBK, 0, 0);
+  a.idesc_pv = ptx::idesc_f16(bf16 ? 1u : 0u, 128, kSfaDvHalf, 0, 1);
+  a.scale_log2 = p->scale * 1.4426950408889634f;
+  a.is_bf16 = bf16 ? 1 : 0;
+  int clusters = sm_count[dev] / 2;
+  if (clusters > d.rows) clusters = d.rows;
+  sfa_fwd_sm100_kernel<<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  return DSA_OK;
+}
+
+}  // namespace dsa

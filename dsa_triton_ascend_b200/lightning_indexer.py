@@ -130,6 +130,7 @@ def _build_params(query, key, weights, actual_seq_lengths_query, actual_seq_leng
     p.rank_mode = _RANK_MODES[_rank_mode]
     p.return_value = 1 if return_value else 0
     p.phases = _cabi.PHASE_ALL
+    p.key_rows = key.numel() // (N2 * D)
     keep = (query, key, weights, seq_q, seq_k, block_table, idx, val)
     out_shape = (s1, N2, sparse_count) if is_tnd else (B, s1, N2, sparse_count)
     return p, keep, idx, val, out_shape

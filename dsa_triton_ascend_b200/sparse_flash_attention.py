@@ -168,6 +168,7 @@ def sparse_flash_attention_triton(
     p.sparse_mode = sparse_mode
     p.return_lse = 1 if return_softmax_lse else 0
     p.scale = float(scale_value)
+    p.key_rows = key.numel() // D
 
     if rows > 0:
         with torch.cuda.device(dev):

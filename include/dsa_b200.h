@@ -92,6 +92,7 @@ typedef struct DsaLiParams {
   int32_t rank_mode;    /* DSA_RANK_* */
   int32_t return_value;
   int32_t phases;       /* DSA_PHASE_*; score-only and top-k-only share the workspace scores  */
+  int64_t key_rows;     /* rows of the key tensor: batch*s2 (BSND), T2 (TND), blocks*block_size (PA) */
 } DsaLiParams;
 
 /*
@@ -125,6 +126,7 @@ typedef struct DsaSfaParams {
   int32_t block_size, max_blocks;
   int32_t sparse_count, sparse_block_size, sparse_mode, return_lse;
   float scale;
+  int64_t key_rows;     /* rows of the key tensor: batch*s2 (BSND), T2 (TND), blocks*block_size (PA) */
 } DsaSfaParams;
 
 /* Workspace size for dsa_li_forward (fp32 score rows + a status word). 256-byte aligned use. */
