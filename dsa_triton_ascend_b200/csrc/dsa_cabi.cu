@@ -222,7 +222,7 @@ int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes) {
   int st = sfa_validate(p);
   if (st != DSA_OK) return st;
   if (!out_bytes) return DSA_ERR_NULL;
-  *out_bytes = kWorkspaceHeader;
+  *out_bytes = kWorkspaceHeader + (dsa_sfa_uses_tensor_path(p) ? sfa_sm100_workspace_bytes(p) : 0);
   return DSA_OK;
 }
 
@@ -238,7 +238,7 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
   if (dsa_sfa_uses_tensor_path(p)) {
     SfaDev d = sfa_dev(p);
     if (d.rows == 0) return DSA_OK;
-    return sfa_sm100_launch(p, d, (int32_t*)workspace, cs);
+    return sfa_sm100_launch(p, d, (int32_t*)workspace, (char*)workspace + kWorkspaceHeader, cs);
   }
   if (p->dtype == DSA_DTYPE_BF16) return sfa_launch_simt<__nv_bfloat16>(p, cs);
   return sfa_launch_simt<__half>(p, cs);

@@ -77,14 +77,33 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t raddr, float a, float b, 
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t raddr_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr_bar) : "memory");
 }
+// Bulk copy of `bytes` (multiple of 16) from this CTA's shared memory into another CTA of the
+// cluster; completion is counted as transaction bytes on an mbarrier of the destination CTA.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t raddr_dst, const void* src, uint32_t bytes,
+                                                  uint32_t raddr_bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(raddr_dst), "r"(smem_u32(src)), "r"(bytes), "r"(raddr_bar)
+      : "memory");
+}
+// Remote arrive that publishes nothing (it only says "I have finished reading"): relaxed, so it
+// does not wait for this thread's outstanding writes.  `dep` ties the instruction to a value that
+// depends on the loads it must not overtake.
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t raddr_bar, uint32_t dep) {
+  asm volatile(
+      "{\n\t.reg .b32 t;\n\tand.b32 t, %1, 0;\n\tadd.u32 t, t, %0;\n\t"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [t];\n\t}\n"
+      ::"r"(raddr_bar), "r"(dep)
+      : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(8000u)
+      : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return done != 0;
 }
@@ -97,10 +116,12 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Pure polling (no suspension): a suspended waiter was seen to sleep for microseconds past a
+// remote arrival.  2^24 polls is roughly a second.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kWaitPolls; ++i) {
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;

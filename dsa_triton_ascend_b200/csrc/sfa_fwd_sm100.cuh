@@ -8,20 +8,36 @@
 // M dimension and with it the tensor throughput):
 //     CTA 0: nope columns   0..255 + the 64 rope columns  (320 dims of QK^T, value columns   0..255)
 //     CTA 1: nope columns 256..511                         (256 dims of QK^T, value columns 256..511)
-// Each CTA gathers only its own half of every selected KV row (TMA tile::gather4, 128-byte
-// swizzled, 4-stage ring), computes a PARTIAL S = Q_c K_c^T for all 128 heads, sends it to its peer
-// through distributed shared memory, adds the peer's partial, runs the softmax (both CTAs hold the
-// same full S, so no running-max exchange is needed) and accumulates O_c = P V_c with V_c = the
-// nope columns it already holds.  Every MMA is a full-rate 128-row cta_group::1 instruction, every
-// KV byte crosses L2->SM once, and no flop is duplicated except the softmax arithmetic.
+// Each CTA gathers only its own half of every selected KV row (TMA tile::gather4 into the
+// 128-byte-swizzled MMA layout, 4-stage ring), computes a PARTIAL S = Q_c K_c^T for all 128 heads,
+// sends it to its peer through distributed shared memory, adds the peer's partial, runs the
+// softmax (both CTAs hold the same full S, so no running-max exchange is needed) and accumulates
+// O_c = P V_c with V_c = the nope columns it already holds.  Every MMA is a full-rate 128-row
+// cta_group::1 instruction, every KV byte crosses L2->SM once, and no flop is duplicated except
+// the softmax arithmetic.
+//
+// Gather issue rate (measured with in-kernel cycle counters and a micro-probe on a B200): one warp
+// issues one 512-byte gather4 load per ~67 cycles (~7.5 B/clk) however its lanes are arranged, a
+// 16-byte cp.async warp instruction costs ~115 cycles (~4.4 B/clk per warp), and both scale
+// linearly with the number of issuing warps (6 warps: ~42 B/clk).  A tile's 80 loads issued from a
+// single warp took ~6100 cycles against ~1150 cycles of MMA work, so the loads of every tile are
+// spread over six producer warps.
+//
+// A small pre-pass kernel turns every row's sparse indices into a front-packed list of physical KV
+// rows plus a count (block-wise ids expanded, -1 / out-of-window entries dropped, paged positions
+// translated through the block table), so the hot loop does no index arithmetic.
 //
 // Tensor memory per CTA (512 columns): O 0..255 | Q (bf16 pairs, MMA A operand) 256..415 |
 // S partial 416..479 | P (bf16 pairs, MMA A operand) 480..511.
-// Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | row queue.
+// Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | 32 KB
+// staging buffer for the outgoing partial.
 //
-// Warps (192 threads): 0 = gather producer, 1 = MMA issuer / TMEM owner, 2..5 = softmax + epilogue
-// (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the status word.
+// Warps (352 threads): 0..5 = gather producers, 6 = MMA issuer / TMEM owner, 7..10 = softmax +
+// epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
+// status word.
 #pragma once
+
+#include <stdlib.h>
 
 #include "ptx_sm100.cuh"
 #include "sfa_fwd_simt.cuh"
@@ -31,7 +47,9 @@ namespace dsa {
 constexpr int kSfaHeads = 128;
 constexpr int kSfaBK = 64;         // keys per tile
 constexpr int kSfaStages = 4;
-constexpr int kSfaThreads = 192;
+constexpr int kSfaThreads = 352;
+constexpr int kSfaProducerWarps = 6;
+constexpr int kSfaMmaWarp = 6;
 constexpr int kSfaDvHalf = 256;
 constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
 
@@ -39,8 +57,8 @@ constexpr uint32_t kSfaBlk = kSfaBK * 128;                 // one 64-column bloc
 constexpr uint32_t kSfaStage = 5 * kSfaBlk;                // 40 KB (rank 1 uses 4 of the 5 blocks)
 constexpr uint32_t kSfaOffX = kSfaStages * kSfaStage;      // 160 KB
 constexpr uint32_t kSfaXBytes = kSfaHeads * kSfaBK * 4;    // 32 KB
-constexpr uint32_t kSfaOffQueue = kSfaOffX + kSfaXBytes;
-constexpr uint32_t kSfaOffBar = kSfaOffQueue + 128 * 4;
+constexpr uint32_t kSfaOffStage = kSfaOffX + kSfaXBytes;  // outgoing copy of this CTA's partial S
+constexpr uint32_t kSfaOffBar = kSfaOffStage + kSfaXBytes;
 constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 256;
 
 constexpr uint32_t kTmO = 0, kTmQ = 256, kTmS = 416, kTmP = 480;
@@ -53,6 +71,9 @@ struct SfaSm100Args {
   uint32_t idesc_qk, idesc_pv;
   float scale_log2;  // scale * log2(e)
   int32_t is_bf16;
+  long long* prof;   // optional: cycle counters of one thread per role (phase breakdown)
+  const int32_t* nvalid;    // [rows] number of participating slots (pre-pass output)
+  const int32_t* key_list;  // [rows, slots] their physical KV rows, front-packed
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -69,19 +90,32 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Number of slots of a row that take part (warp-collective; every lane gets the total).  A slot
-// whose paged block is absent does not take part on this path.
-__device__ __forceinline__ int32_t sfa_count_valid(const SfaDev& p, const RowInfo& ri, const int32_t* idx_row,
-                                                   int32_t slots, int lane) {
-  if (!(ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0)) return 0;
-  int32_t c = 0;
-  for (int32_t j = lane; j < slots; j += 32) {
-    const int32_t tok = sfa_slot_token(p, ri, idx_row, j);
-    c += (tok >= 0 && key_row(p.seq, ri, tok) >= 0) ? 1 : 0;
+// Pre-pass: one warp per query row.  Writes the physical KV rows of the slots that take part, in
+// slot order, and their count.  A slot whose paged block is absent does not take part here.
+__global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int32_t* __restrict__ nvalid,
+                                                          int32_t* __restrict__ key_list) {
+  const int lane = threadIdx.x & 31;
+  const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const RowInfo ri = row_info(p.seq, row);
+  const int32_t slots = p.sparse_count * p.sparse_block_size;
+  const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.sparse_count;
+  int32_t* out = key_list + (int64_t)row * slots;
+  int32_t n = 0;
+  if (ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0) {
+    for (int32_t j0 = 0; j0 < slots; j0 += 32) {
+      const int32_t j = j0 + lane;
+      int64_t prow = -1;
+      if (j < slots) {
+        const int32_t tok = sfa_slot_token(p, ri, idx_row, j);
+        if (tok >= 0) prow = key_row(p.seq, ri, tok);
+      }
+      const uint32_t m = __ballot_sync(0xffffffffu, prow >= 0);
+      if (prow >= 0) out[n + __popc(m & ((1u << lane) - 1u))] = (int32_t)prow;
+      n += __popc(m);
+    }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-  return c;
+  if (lane == 0) nvalid[row] = n;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSfaThreads, 1)
@@ -90,7 +124,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   extern __shared__ __align__(1024) unsigned char sfa_sm[];
   unsigned char* kv_s = sfa_sm;
   float* x_s = reinterpret_cast<float*>(sfa_sm + kSfaOffX);
-  int32_t* queue = reinterpret_cast<int32_t*>(sfa_sm + kSfaOffQueue);
+  float* xo_s = reinterpret_cast<float*>(sfa_sm + kSfaOffStage);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
   uint64_t* kv_full = bars;         // [4] gather -> MMA
   uint64_t* kv_empty = bars + 4;    // [4] MMA (PV done) -> gather
@@ -105,7 +139,6 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   uint64_t* x_empty = bars + 16;    // peer has consumed what this CTA sent (remote arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 18);
-  int32_t* tile_cnt = reinterpret_cast<int32_t*>(bars + 19);  // [4] valid keys of the tile in each stage
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -113,7 +146,6 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   const int32_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int nblk = rank == 0 ? 5 : 4;          // 64-column blocks of this CTA's feature half
   const int nks = nblk * 4;                    // QK^T k-steps (16 dims each)
-  const uint32_t row_bytes = nblk * 128;
 
   const bool misaligned = (ptx::smem_u32(sfa_sm) & 1023u) != 0;
   if (threadIdx.x == 0) {
@@ -125,12 +157,12 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     ptx::mbar_init(p_full, 128);
     ptx::mbar_init(p_empty, 1);
     ptx::mbar_init(o_free, 128);
-    ptx::mbar_init(x_full, 128);
-    ptx::mbar_init(x_empty, 128);
+    ptx::mbar_init(x_full, 1);
+    ptx::mbar_init(x_empty, 4);
     *abort_flag = misaligned ? 1 : 0;
     ptx::mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == kSfaMmaWarp) {
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
   }
@@ -147,71 +179,64 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 
   if (*abort_flag) {
     // nothing started: fall through to the teardown
-  } else if (warp == 0) {
-    // ------------------------------------------------------------------ gather producer
-    ptx::prefetch_tmap(&tmap_kn);
-    ptx::prefetch_tmap(&tmap_kr);
+  } else if (warp < kSfaProducerWarps) {
+    // ------------------------------------------------------------------ gather producers
+    // A tile is 16 row groups (4 keys each) x nblk column blocks = 80 (rank 0) or 64 (rank 1)
+    // gather4 loads of 512 bytes.  A warp issues one such load every ~67 cycles whatever the lane
+    // pattern, but warps issue in parallel, so the loads of every tile are dealt out over six
+    // warps (load o goes to warp o % 6, lane o / 6).  Warp 0 also arms the stage's barrier.
     uint32_t n_tile = 0;
     bool ok = true;
+    long long pprof[4] = {0, 0, 0, 0};
+    const int nops = 16 * nblk;
+    const int o = warp + kSfaProducerWarps * lane;     // this lane's load of every tile
+    const int grp = o / nblk, blk = o - grp * nblk;     // row group, column block
+    const bool active = o < nops;
+    const int32_t x = rank == 0 ? (blk < 4 ? blk * 64 : 0) : kSfaDvHalf + blk * 64;
+    const CUtensorMap* tm = (rank == 0 && blk == 4) ? &tmap_kr : &tmap_kn;
+    if (lane == 0) { ptx::prefetch_tmap(&tmap_kn); ptx::prefetch_tmap(&tmap_kr); }
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const RowInfo ri = row_info(a.p.seq, row);
-      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
-      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      int32_t cursor = 0, qhead = 0, qcount = 0;
+      const int32_t* list = a.key_list + (int64_t)row * slots;
       for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
-        // compact the physical rows of the next valid slots into the queue (order preserved)
-        while (qcount < cnt) {
-          const int32_t j = cursor + lane;
-          int64_t prow = -1;
-          if (j < slots) {
-            const int32_t tok = sfa_slot_token(a.p, ri, idx_row, j);
-            if (tok >= 0) prow = key_row(a.p.seq, ri, tok);
-          }
-          const uint32_t m = __ballot_sync(0xffffffffu, prow >= 0);
-          if (prow >= 0) queue[(qhead + qcount + __popc(m & ((1u << lane) - 1u))) & 127] = (int32_t)prow;
-          qcount += __popc(m);
-          cursor += 32;
-          __syncwarp();
-        }
         const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
-        ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) {
-          tile_cnt[s] = cnt;
-          ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * row_bytes);
-        }
-        __syncwarp();
-        if (lane < 16) {
-          int32_t r[4];
+        const long long p1 = clock64();
+        // physical rows of this lane's 4 keys (keys past the end of the row re-read the tile's first)
+        int32_t r[4] = {0, 0, 0, 0};
+        if (active) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int32_t k = lane * 4 + i;
-            r[i] = queue[(qhead + (k < cnt ? k : 0)) & 127];  // slots past the end re-read the first row
+            const int32_t k = t * kSfaBK + grp * 4 + i;
+            r[i] = list[k < nvalid ? k : t * kSfaBK];
           }
-          unsigned char* dst = kv_s + s * kSfaStage + lane * 512;
-          const int32_t x0 = rank == 0 ? 0 : kSfaDvHalf;
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-            ptx::tma_gather4_2d(dst + b * kSfaBlk, &tmap_kn, &kv_full[s], x0 + b * 64, r[0], r[1], r[2], r[3]);
-          if (rank == 0) ptx::tma_gather4_2d(dst + 4 * kSfaBlk, &tmap_kr, &kv_full[s], 0, r[0], r[1], r[2], r[3]);
         }
+        if (lane == 0) ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        const long long p2 = clock64();
+        if (warp == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * nblk * 128);
+        if (active)
+          ptx::tma_gather4_2d(kv_s + s * kSfaStage + blk * kSfaBlk + grp * 512, tm, &kv_full[s], x, r[0], r[1], r[2], r[3]);
         __syncwarp();
-        qhead = (qhead + cnt) & 127;
-        qcount -= cnt;
+        pprof[1] += p2 - p1; pprof[2] += clock64() - p2;
       }
     }
-  } else if (warp == 1) {
+    if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+      for (int i = 0; i < 4; ++i) a.prof[16 + i] = pprof[i];
+    }
+  } else if (warp == kSfaMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     uint32_t n_tile = 0, n_tok = 0;
     bool ok = true;
+    long long mprof[4] = {0, 0, 0, 0};
     const uint32_t kv_addr = ptx::smem_u32(kv_s);
     auto issue_pv = [&](uint32_t tile_no, bool first) -> bool {
       // O (+)= P V for global tile number `tile_no`
       if (first && !ptx::mbar_wait(o_free, (n_tok & 1) ^ 1, abort_flag)) return false;
+      const long long m0 = clock64();
       if (!ptx::mbar_wait(p_full, tile_no & 1, abort_flag)) return false;
+      mprof[2] += clock64() - m0;
       ptx::tc_fence_after();
       const uint32_t s = tile_no % kSfaStages;
 #pragma unroll
@@ -224,19 +249,20 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       return true;
     };
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const RowInfo ri = row_info(a.p.seq, row);
-      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
-      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
       if (ntiles == 0) continue;
       if (lane == 0) {
         ok = ptx::mbar_wait(q_full, n_tok & 1, abort_flag);
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
           const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
+          const long long m0 = clock64();
           ok = ptx::mbar_wait(&kv_full[s], use & 1, abort_flag);
           if (!ok) break;
+          const long long m1 = clock64();
           ok = ptx::mbar_wait(s_empty, (n_tile & 1) ^ 1, abort_flag);
           if (!ok) break;
+          mprof[0] += m1 - m0; mprof[1] += clock64() - m1;
           ptx::tc_fence_after();
           for (int ks = 0; ks < nks; ++ks) {
             const uint64_t bd = ptx::desc_kmajor_sw128(kv_addr + s * kSfaStage + (ks >> 2) * kSfaBlk + (ks & 3) * 32);
@@ -252,6 +278,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
       ++n_tok;
     }
+    if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) {
+      for (int i = 0; i < 3; ++i) a.prof[12 + i] = mprof[i];
+    }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int quarter = warp & 3;
@@ -262,6 +291,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     const uint32_t x_empty_peer = ptx::map_to_rank(x_empty, peer);
     uint32_t n_tile = 0, n_tok = 0;
     bool ok = true;
+    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // cycle sums per phase (stored only when profiling)
     // waits of these warps are made warp-uniform: the tcgen05 loads / stores that follow are
     // warp-collective and must never run with part of a warp gone
     auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
@@ -271,9 +301,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
     };
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const RowInfo ri = row_info(a.p.seq, row);
-      const int32_t* idx_row = a.p.sparse_indices + (int64_t)row * a.p.sparse_count;
-      const int32_t nvalid = sfa_count_valid(a.p, ri, idx_row, slots, lane);
+      const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
       unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
       if (ntiles == 0) {
@@ -287,6 +315,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         continue;
       }
       // ---- this token's Q half -> tensor memory (bf16 pairs, row h in lane h)
+      const long long cq0 = clock64();
       ok = wait_w(q_empty, (n_tok & 1) ^ 1);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -319,9 +348,11 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::mbar_arrive(q_full);
       }
 
+      const long long cq1 = clock64();
+      prof[6] += cq1 - cq0;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
       for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const uint32_t s = n_tile % kSfaStages;
+        const long long c0 = clock64();
         // ---- own partial S -> registers
         ok = wait_w(s_full, n_tile & 1);
         if (!ok) break;
@@ -332,29 +363,56 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::tmem_ld_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(s_empty);
-        const int32_t cnt = tile_cnt[s];
-        // ---- exchange with the peer: send mine (16-byte chunk c of head h at c * 2048 + h * 16)
-        ok = wait_wc(x_empty, (n_tile & 1) ^ 1);
+        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
+        const long long c1 = clock64();
+        // ---- exchange with the peer.  The partial goes to a local staging buffer (warp w owns
+        // 8 KB: 16-byte chunk c of lane at w * 8192 + c * 512 + lane * 16) and from there by one
+        // bulk copy per warp into the peer's landing buffer, counted on the peer's x_full barrier.
+        ok = wait_wc(x_empty, (n_tile & 1) ^ 1);   // peer has consumed the previous one
         if (!ok) break;
+        const long long cx1 = clock64();
+        if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(x_full, kSfaXBytes);  // arm my own landing barrier
+        {
+          float* mine = xo_s + quarter * 2048 + lane * 4;
 #pragma unroll
-        for (int c = 0; c < kSfaBK / 4; ++c)
-          ptx::st_cluster_v4(x_peer + c * 2048 + h * 16, sc[4 * c], sc[4 * c + 1], sc[4 * c + 2], sc[4 * c + 3]);
-        ptx::mbar_arrive_remote(x_full_peer);
+          for (int c = 0; c < kSfaBK / 4; ++c)
+            *reinterpret_cast<float4*>(mine + c * 128) = make_float4(sc[4 * c], sc[4 * c + 1], sc[4 * c + 2], sc[4 * c + 3]);
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) ptx::bulk_copy_to_peer(x_peer + quarter * 8192, xo_s + quarter * 2048, 8192, x_full_peer);
+        const long long cx2 = clock64();
         ok = wait_wc(x_full, n_tile & 1);
         if (!ok) break;
+        const long long cx3 = clock64();
+        prof[8] += cx1 - c1; prof[9] += cx2 - cx1; prof[10] += cx3 - cx2;
+        {
+          const float* theirs = x_s + quarter * 2048 + lane * 4;
 #pragma unroll
-        for (int c = 0; c < kSfaBK / 4; ++c) {
-          const float4 v = *reinterpret_cast<const float4*>(x_s + c * 512 + h * 4);
-          sc[4 * c] += v.x; sc[4 * c + 1] += v.y; sc[4 * c + 2] += v.z; sc[4 * c + 3] += v.w;
+          for (int c = 0; c < kSfaBK / 4; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(theirs + c * 128);
+            sc[4 * c] += v.x; sc[4 * c + 1] += v.y; sc[4 * c + 2] += v.z; sc[4 * c + 3] += v.w;
+          }
         }
-        ptx::mbar_arrive_remote(x_empty_peer);
+        const long long c2 = clock64();
         // ---- softmax in the log2 domain; keys past `cnt` are padding
-        float mx = -INFINITY;
+        if (cnt == kSfaBK) {
 #pragma unroll
-        for (int k = 0; k < kSfaBK; ++k) {
-          sc[k] = k < cnt ? sc[k] * a.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, sc[k]);
+          for (int k = 0; k < kSfaBK; ++k) sc[k] *= a.scale_log2;
+        } else {
+#pragma unroll
+          for (int k = 0; k < kSfaBK; ++k) sc[k] = k < cnt ? sc[k] * a.scale_log2 : -INFINITY;
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int k = 0; k < kSfaBK; k += 4) {
+          mx4[0] = fmaxf(mx4[0], sc[k]); mx4[1] = fmaxf(mx4[1], sc[k + 1]);
+          mx4[2] = fmaxf(mx4[2], sc[k + 2]); mx4[3] = fmaxf(mx4[3], sc[k + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // the landing buffer has been read completely (mx depends on every load): hand it back
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_remote_relaxed(x_empty_peer, __float_as_uint(mx));
         m_true = fmaxf(m_true, mx);
         float alpha = 1.f;
         bool rescale = false;
@@ -365,21 +423,24 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           m_ref = mx;
           rescale = true;
         }
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int k = 0; k < kSfaBK; ++k) {
-          sc[k] = ex2(sc[k] - m_ref);
-          sum += sc[k];
+        for (int k = 0; k < kSfaBK; k += 4) {
+          sc[k] = ex2(sc[k] - m_ref); sc[k + 1] = ex2(sc[k + 1] - m_ref);
+          sc[k + 2] = ex2(sc[k + 2] - m_ref); sc[k + 3] = ex2(sc[k + 3] - m_ref);
+          sum4[0] += sc[k]; sum4[1] += sc[k + 1]; sum4[2] += sc[k + 2]; sum4[3] += sc[k + 3];
         }
-        l = l * alpha + sum;
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         if (ntiles == 1) {
           // a single tile holds the whole row: normalise before rounding, as the golden does
           const float inv = 1.f / l;
 #pragma unroll
           for (int k = 0; k < kSfaBK; ++k) sc[k] *= inv;
         }
+        const long long c3 = clock64();
         // ---- P (and, rarely, a rescaled O) -> tensor memory once the previous PV has finished
         ok = wait_w(p_empty, (n_tile & 1) ^ 1);
+        const long long c4 = clock64();
         if (!ok) break;
         ptx::tc_fence_after();
         if (__any_sync(0xffffffffu, rescale)) {
@@ -402,9 +463,12 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(p_full);
+        prof[0] += c1 - c0; prof[1] += c2 - c1; prof[2] += c3 - c2; prof[3] += c4 - c3; prof[4] += clock64() - c4;
+        prof[5] += 1;
       }
       if (!ok) break;
       // ---- epilogue: wait for the last PV, normalise, store
+      const long long ce0 = clock64();
       ok = wait_w(p_empty, (n_tile & 1) ^ 1);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -424,12 +488,17 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(o_free);
+      prof[7] += clock64() - ce0;
       if (rank == 0 && a.p.return_lse) {
         // max of the scaled scores and sum of exp(score - max), back from the log2 domain
         a.p.softmax_max[(int64_t)row * kSfaHeads + h] = m_true * 0.6931471805599453f;
         a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = l * ex2(m_ref - m_true);
       }
       ++n_tok;
+    }
+    if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 12; ++i) a.prof[i] = prof[i];
     }
   }
 
@@ -443,7 +512,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   // neither CTA may leave while its peer can still write into its shared memory
   ptx::cluster_arrive();
   ptx::cluster_wait();
-  if (warp == 1) {
+  if (warp == kSfaMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, 512);
   }
@@ -461,7 +530,14 @@ inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
   return true;
 }
 
-inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* status, cudaStream_t st) {
+// Workspace beyond the header: nvalid[rows] then key_list[rows * slots].
+inline size_t sfa_sm100_workspace_bytes(const DsaSfaParams* p) {
+  const int64_t rows = p->layout_q == DSA_LAYOUT_TND ? p->s1 : (int64_t)p->batch * p->s1;
+  const int64_t slots = (int64_t)p->sparse_count * p->sparse_block_size;
+  return (size_t)(((rows * 4 + 255) / 256) * 256 + rows * slots * 4);
+}
+
+inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* status, void* scratch, cudaStream_t st) {
   static int sm_count[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
@@ -474,9 +550,10 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
     sm_count[dev] = n;
   }
   const bool bf16 = p->dtype == DSA_DTYPE_BF16;
-  CUtensorMap tkn, tkr;
-  if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;
-  if (!make_tmap_gather4_16bit(&tkr, p->key_rope, (uint64_t)p->key_rows, 64, 128, 64, bf16)) return DSA_ERR_CUDA;
+  int32_t* nvalid = reinterpret_cast<int32_t*>(scratch);
+  int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + (((int64_t)d.rows * 4 + 255) / 256) * 256);
+  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   SfaSm100Args a;
   a.p = d;
   a.status = status;
@@ -485,8 +562,14 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.idesc_pv = ptx::idesc_f16(bf16 ? 1u : 0u, 128, kSfaDvHalf, 0, 1);
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.is_bf16 = bf16 ? 1 : 0;
+  a.prof = getenv("DSA_SFA_PROFILE") ? reinterpret_cast<long long*>(status + 16) : nullptr;
+  a.nvalid = nvalid;
+  a.key_list = key_list;
   int clusters = sm_count[dev] / 2;
   if (clusters > d.rows) clusters = d.rows;
+  CUtensorMap tkn, tkr;
+  if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;
+  if (!make_tmap_gather4_16bit(&tkr, p->key_rope, (uint64_t)p->key_rows, 64, 128, 64, bf16)) return DSA_ERR_CUDA;
   sfa_fwd_sm100_kernel<<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   return DSA_OK;
