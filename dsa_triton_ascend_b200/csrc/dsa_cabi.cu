@@ -86,18 +86,28 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
     }
   }
   if (p->phases & DSA_PHASE_TOPK) {
-    int32_t cap = 1;
-    while (cap < p->sparse_count) cap <<= 1;
-    const size_t smem = (size_t)cap * 8 + (size_t)kTopkKeyCache * 4;
-    cudaError_t e;
-    if (p->rank_mode == DSA_RANK_IO_DTYPE) {
-      e = cudaFuncSetAttribute(li_topk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return DSA_ERR_CUDA;
-      li_topk_kernel<T, true><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+    const bool rank16 = p->rank_mode == DSA_RANK_IO_DTYPE;
+    if (p->s2 <= kTopkThreads * kTopkFastKeys && p->sparse_count <= kTopkThreads * 4) {
+      // register / shuffle kernel: rows of up to 8192 keys, up to 2048 outputs
+      const int e = p->sparse_count <= kTopkThreads ? 1 : (p->sparse_count <= 2 * kTopkThreads ? 2 : 4);
+#define DSA_TOPK_FAST(R, E) li_topk_fast_kernel<T, R, E><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld)
+      if (rank16) { if (e == 1) DSA_TOPK_FAST(true, 1); else if (e == 2) DSA_TOPK_FAST(true, 2); else DSA_TOPK_FAST(true, 4); }
+      else { if (e == 1) DSA_TOPK_FAST(false, 1); else if (e == 2) DSA_TOPK_FAST(false, 2); else DSA_TOPK_FAST(false, 4); }
+#undef DSA_TOPK_FAST
     } else {
-      e = cudaFuncSetAttribute(li_topk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return DSA_ERR_CUDA;
-      li_topk_kernel<T, false><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+      int32_t cap = 1;
+      while (cap < p->sparse_count) cap <<= 1;
+      const size_t smem = (size_t)cap * 8 + (size_t)kTopkKeyCache * 4;
+      cudaError_t e;
+      if (rank16) {
+        e = cudaFuncSetAttribute(li_topk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return DSA_ERR_CUDA;
+        li_topk_kernel<T, true><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+      } else {
+        e = cudaFuncSetAttribute(li_topk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return DSA_ERR_CUDA;
+        li_topk_kernel<T, false><<<(unsigned)rown, kTopkThreads, smem, st>>>(d, scores, ld, cap);
+      }
     }
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   }

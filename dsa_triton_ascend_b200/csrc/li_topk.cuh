@@ -180,4 +180,216 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Fast path for rows of up to 8192 visible keys and sparse_count <= 512 * E (E = 1, 2, 4):
+//   * every thread keeps 16 rank keys in registers (position = j * 512 + tid);
+//   * the k-th key is found by bisection on the key value: each step counts the keys >= mid with a
+//     warp reduction and one shared-memory add per warp (no histogram, hence no atomic contention
+//     on the few exponent bins that hold nearly all scores);
+//   * ties at the threshold are cut by a second bisection on the position;
+//   * the survivors are written as composites (key, ~position) and sorted by a bitonic network
+//     that runs in registers / warp shuffles, touching shared memory only for the four largest
+//     strides;
+//   * values are rebuilt from the composite, so the scores are read exactly once.
+// Composite: 32 bits (16-bit key | 16-bit ~position) when ranking the io dtype, else 64 bits.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTopkFastKeys = 16;   // keys per thread -> rows of up to 8192 visible keys
+
+template <bool kRank16> struct TopkComposite { typedef uint64_t type; };
+template <> struct TopkComposite<true> { typedef uint32_t type; };
+
+template <typename C> __device__ __forceinline__ C shfl_xor_c(C v, int m);
+template <> __device__ __forceinline__ uint32_t shfl_xor_c<uint32_t>(uint32_t v, int m) {
+  return __shfl_xor_sync(0xffffffffu, v, m);
+}
+template <> __device__ __forceinline__ uint64_t shfl_xor_c<uint64_t>(uint64_t v, int m) {
+  return __shfl_xor_sync(0xffffffffu, (unsigned long long)v, m);
+}
+
+// Block-wide sum of one small integer per thread; `slot` must be a zeroed shared counter that is
+// not reused before the next __syncthreads of the caller's own loop.
+__device__ __forceinline__ uint32_t block_count(uint32_t c, uint32_t* slot) {
+  const uint32_t w = __reduce_add_sync(0xffffffffu, c);
+  if ((threadIdx.x & 31) == 0 && w) atomicAdd(slot, w);
+  __syncthreads();
+  return *slot;
+}
+
+template <typename T, bool kRank16, int E>
+__global__ void __launch_bounds__(kTopkThreads) li_topk_fast_kernel(LiDev p, const float* __restrict__ scores,
+                                                                    int64_t ld) {
+  typedef typename TopkComposite<kRank16>::type C;
+  constexpr int P2 = kTopkThreads * E;
+  __shared__ C sbuf[P2];
+  __shared__ uint32_t counters[64];
+  __shared__ uint32_t sh_count;
+
+  const int tid = threadIdx.x;
+  const int32_t rown = blockIdx.x;
+  const int32_t row = rown / p.n2;
+  const RowInfo ri = row_info(p.seq, row);
+  const int32_t n = ri.visible;
+  const int32_t K = p.sparse_count;
+  const int32_t nsel = min(n, K);
+  int32_t* oi = p.out_indices + (int64_t)rown * K;
+  T* ov = (p.return_value && p.out_values != nullptr) ? (T*)p.out_values + (int64_t)rown * K : nullptr;
+
+  if (nsel == 0) {
+    for (int i = tid; i < K; i += kTopkThreads) {
+      oi[i] = -1;
+      if (ov) ov[i] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  const float* s = scores + (int64_t)rown * ld;
+  uint32_t key[kTopkFastKeys];
+#pragma unroll
+  for (int j = 0; j < kTopkFastKeys; ++j) {
+    const int pos = j * kTopkThreads + tid;
+    key[j] = pos < n ? rank_key<T, kRank16>(s[pos]) : 0u;   // 0 is below every real key
+  }
+  if (tid < 64) counters[tid] = 0;
+  if (tid == 0) sh_count = 0;
+  __syncthreads();
+
+  uint32_t thr_key = 0, pos_limit = 0xFFFFFFFFu;
+  if (n > K) {
+    // largest T with count(key >= T) >= K
+    uint32_t lo = 1, hi = kRank16 ? 0xFFFFu : 0xFFFFFFFFu;
+    constexpr int kSteps = kRank16 ? 16 : 32;
+    int slot = 0;
+#pragma unroll 1
+    for (int it = 0; it < kSteps; ++it, ++slot) {
+      const uint32_t mid = lo + ((hi - lo) >> 1) + ((hi - lo) & 1u);   // upper middle
+      uint32_t c = 0;
+#pragma unroll
+      for (int j = 0; j < kTopkFastKeys; ++j) c += key[j] >= mid;
+      const uint32_t total = block_count(c, &counters[slot]);
+      if (total >= (uint32_t)K) lo = mid; else hi = mid - 1;
+      if (lo == hi) { ++slot; break; }
+    }
+    thr_key = lo;
+    uint32_t cgt = 0, ceq = 0;
+#pragma unroll
+    for (int j = 0; j < kTopkFastKeys; ++j) { cgt += key[j] > thr_key; ceq += key[j] == thr_key; }
+    const uint32_t n_gt = block_count(cgt, &counters[slot++]);
+    const uint32_t n_eq = block_count(ceq, &counters[slot++]);
+    const uint32_t need = (uint32_t)K - n_gt;
+    if (need < n_eq) {
+      // smallest P with count(key == T and pos <= P) >= need
+      uint32_t plo = 0, phi = (uint32_t)n - 1;
+#pragma unroll 1
+      while (plo < phi) {
+        const uint32_t mid = plo + ((phi - plo) >> 1);
+        uint32_t c = 0;
+#pragma unroll
+        for (int j = 0; j < kTopkFastKeys; ++j)
+          c += (key[j] == thr_key) && ((uint32_t)(j * kTopkThreads + tid) <= mid);
+        const uint32_t total = block_count(c, &counters[slot++]);
+        if (total >= need) phi = mid; else plo = mid + 1;
+      }
+      pos_limit = plo;
+    }
+  }
+
+  // ---- survivors -> composites in shared memory (any order: the sort fixes it)
+#pragma unroll
+  for (int j = 0; j < kTopkFastKeys; ++j) {
+    const uint32_t pos = j * kTopkThreads + tid;
+    const bool sel = (int32_t)pos < n && (key[j] > thr_key || (key[j] == thr_key && pos <= pos_limit));
+    const uint32_t m = __ballot_sync(0xffffffffu, sel);
+    uint32_t base = 0;
+    if ((tid & 31) == 0 && m) base = atomicAdd(&sh_count, __popc(m));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (sel) {
+      const uint32_t slot = base + __popc(m & ((1u << (tid & 31)) - 1u));
+      if (slot < (uint32_t)P2) {
+        if (kRank16) sbuf[slot] = (C)((key[j] << 16) | (0xFFFFu - pos));
+        else sbuf[slot] = (C)(((uint64_t)key[j] << 32) | (uint64_t)(0xFFFFFFFFu - pos));
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- bitonic sort, descending; element e = tid * E + j
+  C v[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int e = tid * E + j;
+    v[j] = e < nsel ? sbuf[e] : (C)0;
+  }
+#pragma unroll 1
+  for (int size = 2; size <= P2; size <<= 1) {
+#pragma unroll 1
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= 32 * E) {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < E; ++j) sbuf[tid * E + j] = v[j];
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const int e = tid * E + j;
+          const C o = sbuf[e ^ stride];
+          const bool take_max = (((e & stride) == 0) == ((e & size) == 0));
+          v[j] = take_max ? (v[j] > o ? v[j] : o) : (v[j] < o ? v[j] : o);
+        }
+      } else if (stride >= E) {
+        const int m = stride / E;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const int e = tid * E + j;
+          const C o = shfl_xor_c<C>(v[j], m);
+          const bool take_max = (((e & stride) == 0) == ((e & size) == 0));
+          v[j] = take_max ? (v[j] > o ? v[j] : o) : (v[j] < o ? v[j] : o);
+        }
+      } else {
+        // partner inside the thread: compile-time strides keep v[] in registers
+#pragma unroll
+        for (int S = E / 2; S > 0; S >>= 1) {
+          if (stride == S) {
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+              if ((j & S) == 0) {
+                const int e = tid * E + j;
+                const bool desc = (e & size) == 0;
+                const C a = v[j], b = v[j | S];
+                const bool sw = desc ? (a < b) : (a > b);
+                v[j] = sw ? b : a;
+                v[j | S] = sw ? a : b;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- emit: positions and values come out of the composites
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int e = tid * E + j;
+    if (e < K) {
+      if (e < nsel) {
+        uint32_t pos, k32;
+        if (kRank16) { pos = 0xFFFFu - ((uint32_t)v[j] & 0xFFFFu); k32 = (uint32_t)v[j] >> 16; }
+        else { pos = 0xFFFFFFFFu - (uint32_t)v[j]; k32 = (uint32_t)((uint64_t)v[j] >> 32); }
+        oi[e] = (int32_t)pos;
+        if (ov) {
+          if (kRank16) {
+            const uint16_t h = (k32 & 0x8000u) ? (uint16_t)(k32 & 0x7FFFu) : (uint16_t)(~k32);
+            ov[e] = *reinterpret_cast<const T*>(&h);
+          } else {
+            const uint32_t u = (k32 & 0x80000000u) ? (k32 & 0x7FFFFFFFu) : ~k32;
+            ov[e] = from_f32<T>(__uint_as_float(u));
+          }
+        }
+      } else {
+        oi[e] = -1;
+        if (ov) ov[e] = from_f32<T>(0.f);
+      }
+    }
+  }
+}
+
 }  // namespace dsa

@@ -32,8 +32,9 @@
 // Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | 32 KB
 // staging buffer for the outgoing partial.
 //
-// Warps (352 threads): 0..5 = gather producers, 6 = MMA issuer / TMEM owner, 7..10 = softmax +
-// epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
+// Warps (512 threads, registers redistributed with setmaxnreg): 0..5 = gather producers, 6 = MMA
+// issuer (QK^T) / TMEM owner, 7 = MMA issuer (PV), 8..11 = senders (partial S: TMEM -> staging -> peer; Q -> TMEM),
+// 12..15 = softmax + epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
 // status word.
 #pragma once
 
@@ -47,9 +48,11 @@ namespace dsa {
 constexpr int kSfaHeads = 128;
 constexpr int kSfaBK = 64;         // keys per tile
 constexpr int kSfaStages = 4;
-constexpr int kSfaThreads = 352;
+constexpr int kSfaThreads = 512;
 constexpr int kSfaProducerWarps = 6;
 constexpr int kSfaMmaWarp = 6;
+constexpr int kSfaSendWarp0 = 8;     // warps 8..11: partial-score senders + Q loaders
+constexpr int kSfaSoftWarp0 = 12;    // warps 12..15: softmax + epilogue
 constexpr int kSfaDvHalf = 256;
 constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
 
@@ -135,10 +138,15 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   uint64_t* p_full = bars + 12;     // softmax (P stored, O rescaled) -> MMA
   uint64_t* p_empty = bars + 13;    // MMA (PV done) -> softmax
   uint64_t* o_free = bars + 14;     // epilogue (O read out) -> MMA
-  uint64_t* x_full = bars + 15;     // peer's partial S has landed (remote arrivals)
-  uint64_t* x_empty = bars + 16;    // peer has consumed what this CTA sent (remote arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 18);
+  // The partial scores of a tile travel in two halves (keys 0..31 and 32..63), each with its own
+  // 16 KB staging and landing buffer and its own barriers, so that the next tile's first half can be
+  // on its way while the softmax warps still work on the current tile.
+  uint64_t* x_full = bars + 15;     // [2] peer's partial S has landed (transaction bytes)
+  uint64_t* x_empty = bars + 17;    // [2] peer has consumed what this CTA sent (remote arrivals)
+  uint64_t* own_full = bars + 19;   // [2] senders: own partial is in the staging buffer -> softmax
+  uint64_t* own_free = bars + 21;   // [2] softmax has read the staging buffer -> senders
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 24);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -157,8 +165,12 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     ptx::mbar_init(p_full, 128);
     ptx::mbar_init(p_empty, 1);
     ptx::mbar_init(o_free, 128);
-    ptx::mbar_init(x_full, 1);
-    ptx::mbar_init(x_empty, 4);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&x_full[i], 1);
+      ptx::mbar_init(&x_empty[i], 4);
+      ptx::mbar_init(&own_full[i], 4);
+      ptx::mbar_init(&own_free[i], 4);
+    }
     *abort_flag = misaligned ? 1 : 0;
     ptx::mbar_fence_init();
   }
@@ -173,11 +185,15 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   ptx::cluster_arrive();
   ptx::cluster_wait();
   const uint32_t tmem = *tmem_slot;
+  // 512 threads start with 128 registers each; every role branch below first trades registers:
+  // the softmax warps need more, everyone else less (whole warpgroups of 4 warps change together).
 
   const int32_t slots = a.p.sparse_count * a.p.sparse_block_size;
   const int32_t n1d = kSfaHeads * a.p.d;
 
-  if (*abort_flag) {
+  if (warp < 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+   if (*abort_flag) {
     // nothing started: fall through to the teardown
   } else if (warp < kSfaProducerWarps) {
     // ------------------------------------------------------------------ gather producers
@@ -226,28 +242,14 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       for (int i = 0; i < 4; ++i) a.prof[16 + i] = pprof[i];
     }
   } else if (warp == kSfaMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ QK^T issuer (warp 6)
+    // S = Q_c K_c^T for every tile, as early as the KV ring and the single S buffer allow; it
+    // never waits for the softmax, so the score exchange of later tiles overlaps the softmax of
+    // earlier ones.
     uint32_t n_tile = 0, n_tok = 0;
     bool ok = true;
     long long mprof[4] = {0, 0, 0, 0};
     const uint32_t kv_addr = ptx::smem_u32(kv_s);
-    auto issue_pv = [&](uint32_t tile_no, bool first) -> bool {
-      // O (+)= P V for global tile number `tile_no`
-      if (first && !ptx::mbar_wait(o_free, (n_tok & 1) ^ 1, abort_flag)) return false;
-      const long long m0 = clock64();
-      if (!ptx::mbar_wait(p_full, tile_no & 1, abort_flag)) return false;
-      mprof[2] += clock64() - m0;
-      ptx::tc_fence_after();
-      const uint32_t s = tile_no % kSfaStages;
-#pragma unroll
-      for (int ks = 0; ks < kSfaBK / 16; ++ks) {
-        const uint64_t bd = ptx::desc_mnmajor_sw128(kv_addr + s * kSfaStage + ks * 16 * 128, kSfaBlk, 1024);
-        ptx::mma_ts(tmem + kTmO, tmem + kTmP + ks * 8, bd, a.idesc_pv, (first && ks == 0) ? 0u : 1u);
-      }
-      ptx::mma_commit(p_empty);
-      ptx::mma_commit(&kv_empty[s]);
-      return true;
-    };
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
       const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
@@ -270,30 +272,67 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           }
           ptx::mma_commit(s_full);
           if (t == ntiles - 1) ptx::mma_commit(q_empty);
-          if (t > 0) ok = issue_pv(n_tile - 1, t == 1);
         }
-        if (ok) ok = issue_pv(n_tile - 1, ntiles == 1);
       }
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
       ++n_tok;
     }
     if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) {
-      for (int i = 0; i < 3; ++i) a.prof[12 + i] = mprof[i];
+      for (int i = 0; i < 2; ++i) a.prof[12 + i] = mprof[i];
     }
-  } else {
-    // ------------------------------------------------------------------ softmax + epilogue
+  } else if (warp == kSfaMmaWarp + 1) {
+    // ------------------------------------------------------------------ PV issuer (warp 7)
+    // O (+)= P V_c once the softmax warps have stored P; frees the KV stage and the P buffer.
+    uint32_t n_tile = 0, n_tok = 0;
+    bool ok = true;
+    long long wait_p = 0;
+    const uint32_t kv_addr = ptx::smem_u32(kv_s);
+    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
+      const int32_t nvalid = a.nvalid[row];
+      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      if (ntiles == 0) continue;
+      if (lane == 0) {
+        ok = ptx::mbar_wait(o_free, (n_tok & 1) ^ 1, abort_flag);   // previous token's O has been read out
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
+          ok = ptx::mbar_wait(&kv_full[s], use & 1, abort_flag);    // long complete; observed for ordering
+          if (!ok) break;
+          const long long m0 = clock64();
+          ok = ptx::mbar_wait(p_full, n_tile & 1, abort_flag);
+          if (!ok) break;
+          wait_p += clock64() - m0;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kSfaBK / 16; ++ks) {
+            const uint64_t bd = ptx::desc_mnmajor_sw128(kv_addr + s * kSfaStage + ks * 16 * 128, kSfaBlk, 1024);
+            ptx::mma_ts(tmem + kTmO, tmem + kTmP + ks * 8, bd, a.idesc_pv, (t == 0 && ks == 0) ? 0u : 1u);
+          }
+          ptx::mma_commit(p_empty);
+          ptx::mma_commit(&kv_empty[s]);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
+      ++n_tok;
+    }
+    if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) a.prof[14] = wait_p;
+  }
+  } else if (warp < kSfaSoftWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    if (!*abort_flag) {
+    // ------------------------------------------------------------------ senders
+    // Per token: this CTA's Q half into tensor memory.  Per tile: the partial S from tensor memory
+    // into the staging buffer (warp w owns 8 KB: 16-byte chunk c of a lane at w * 8192 + c * 512 +
+    // lane * 16), one bulk copy per warp into the peer's landing buffer (counted on the peer's
+    // x_full barrier), and a local hand-over of the same staging buffer to the softmax warps.
     const int quarter = warp & 3;
-    const int h = quarter * 32 + lane;                       // head == TMEM lane
+    const int h = quarter * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t x_peer = ptx::map_to_rank(x_s, peer);
     const uint32_t x_full_peer = ptx::map_to_rank(x_full, peer);
-    const uint32_t x_empty_peer = ptx::map_to_rank(x_empty, peer);
     uint32_t n_tile = 0, n_tok = 0;
     bool ok = true;
-    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // cycle sums per phase (stored only when profiling)
-    // waits of these warps are made warp-uniform: the tcgen05 loads / stores that follow are
-    // warp-collective and must never run with part of a warp gone
     auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
     };
@@ -303,19 +342,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
       const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
-      if (ntiles == 0) {
-        // nothing visible: zeros in all three outputs
-#pragma unroll
-        for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
-        if (rank == 0 && a.p.return_lse) {
-          a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
-          a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
-        }
-        continue;
-      }
+      if (ntiles == 0) continue;
       // ---- this token's Q half -> tensor memory (bf16 pairs, row h in lane h)
-      const long long cq0 = clock64();
       ok = wait_w(q_empty, (n_tok & 1) ^ 1);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -347,54 +375,112 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::tc_fence_before();
         ptx::mbar_arrive(q_full);
       }
-
-      const long long cq1 = clock64();
-      prof[6] += cq1 - cq0;
-      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
       for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const long long c0 = clock64();
-        // ---- own partial S -> registers
         ok = wait_w(s_full, n_tile & 1);
         if (!ok) break;
         ptx::tc_fence_after();
-        float sc[kSfaBK];
-        ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sc));
-        ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sc) + 32);
+        float sv[kSfaBK];
+        ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sv));
+        ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
         ptx::tmem_ld_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(s_empty);
-        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
-        const long long c1 = clock64();
-        // ---- exchange with the peer.  The partial goes to a local staging buffer (warp w owns
-        // 8 KB: 16-byte chunk c of lane at w * 8192 + c * 512 + lane * 16) and from there by one
-        // bulk copy per warp into the peer's landing buffer, counted on the peer's x_full barrier.
-        ok = wait_wc(x_empty, (n_tile & 1) ^ 1);   // peer has consumed the previous one
-        if (!ok) break;
-        const long long cx1 = clock64();
-        if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(x_full, kSfaXBytes);  // arm my own landing barrier
-        {
-          float* mine = xo_s + quarter * 2048 + lane * 4;
+        // a staging half is free once the peer has consumed what was copied out of it and the
+        // local softmax warps have read it (half hf: 4 KB per warp, 16-byte chunk c of a lane at
+        // w * 4096 + c * 512 + lane * 16)
 #pragma unroll
-          for (int c = 0; c < kSfaBK / 4; ++c)
-            *reinterpret_cast<float4*>(mine + c * 128) = make_float4(sc[4 * c], sc[4 * c + 1], sc[4 * c + 2], sc[4 * c + 3]);
-        }
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) ptx::bulk_copy_to_peer(x_peer + quarter * 8192, xo_s + quarter * 2048, 8192, x_full_peer);
-        const long long cx2 = clock64();
-        ok = wait_wc(x_full, n_tile & 1);
-        if (!ok) break;
-        const long long cx3 = clock64();
-        prof[8] += cx1 - c1; prof[9] += cx2 - cx1; prof[10] += cx3 - cx2;
-        {
-          const float* theirs = x_s + quarter * 2048 + lane * 4;
+        for (int hf = 0; hf < 2; ++hf) {
+          ok = wait_wc(&x_empty[hf], (n_tile & 1) ^ 1);
+          if (!ok) break;
+          ok = wait_w(&own_free[hf], (n_tile & 1) ^ 1);
+          if (!ok) break;
+          if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&x_full[hf], kSfaXBytes / 2);  // arm my landing half
+          float* mine = xo_s + hf * 4096 + quarter * 1024 + lane * 4;
 #pragma unroll
-          for (int c = 0; c < kSfaBK / 4; ++c) {
-            const float4 v = *reinterpret_cast<const float4*>(theirs + c * 128);
-            sc[4 * c] += v.x; sc[4 * c + 1] += v.y; sc[4 * c + 2] += v.z; sc[4 * c + 3] += v.w;
+          for (int c = 0; c < kSfaBK / 8; ++c) {
+            const int k = hf * 32 + 4 * c;
+            *reinterpret_cast<float4*>(mine + c * 128) = make_float4(sv[k], sv[k + 1], sv[k + 2], sv[k + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::bulk_copy_to_peer(x_peer + hf * 16384 + quarter * 4096, xo_s + hf * 4096 + quarter * 1024, 4096,
+                                   x_full_peer + hf * 8);
+            ptx::mbar_arrive(&own_full[hf]);
           }
         }
-        const long long c2 = clock64();
+      }
+      ++n_tok;
+    }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    if (!*abort_flag) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int quarter = warp & 3;
+    const int h = quarter * 32 + lane;                       // head == TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t x_empty_peer = ptx::map_to_rank(x_empty, peer);
+    uint32_t n_tile = 0;
+    bool ok = true;
+    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // cycle sums per phase (stored only when profiling)
+    // waits of these warps are made warp-uniform: the tcgen05 loads / stores that follow are
+    // warp-collective and must never run with part of a warp gone
+    auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+    };
+    auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
+    };
+    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
+      const int32_t nvalid = a.nvalid[row];
+      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
+      if (ntiles == 0) {
+        // nothing visible: zeros in all three outputs
+#pragma unroll
+        for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+        if (rank == 0 && a.p.return_lse) {
+          a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
+          a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
+        }
+        continue;
+      }
+      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+        const long long c0 = clock64();
+        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
+        // ---- full S = own partial (staging halves) + the peer's partial (landing halves); each
+        // half is handed back as soon as it has been read
+        float sc[kSfaBK];
+        long long c1 = c0;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          ok = wait_wc(&x_full[hf], n_tile & 1);
+          if (!ok) break;
+          ok = wait_w(&own_full[hf], n_tile & 1);
+          if (!ok) break;
+          if (hf == 0) c1 = clock64();
+          const float* theirs = x_s + hf * 4096 + quarter * 1024 + lane * 4;
+          const float* mine = xo_s + hf * 4096 + quarter * 1024 + lane * 4;
+          float dep = 0.f;
+#pragma unroll
+          for (int c = 0; c < kSfaBK / 8; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(theirs + c * 128);
+            const float4 o = *reinterpret_cast<const float4*>(mine + c * 128);
+            const int k = hf * 32 + 4 * c;
+            sc[k] = v.x + o.x; sc[k + 1] = v.y + o.y; sc[k + 2] = v.z + o.z; sc[k + 3] = v.w + o.w;
+            dep += sc[k] + sc[k + 1] + sc[k + 2] + sc[k + 3];
+          }
+          __syncwarp();
+          if (lane == 0) {
+            // relaxed: nothing is published, the peer only learns that the reads are done (`dep`
+            // depends on every load of this half)
+            ptx::mbar_arrive_remote_relaxed(x_empty_peer + hf * 8, __float_as_uint(dep));
+            ptx::mbar_arrive(&own_free[hf]);
+          }
+        }
+        if (!ok) break;
         // ---- softmax in the log2 domain; keys past `cnt` are padding
         if (cnt == kSfaBK) {
 #pragma unroll
@@ -410,9 +496,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           mx4[2] = fmaxf(mx4[2], sc[k + 2]); mx4[3] = fmaxf(mx4[3], sc[k + 3]);
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        // the landing buffer has been read completely (mx depends on every load): hand it back
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_remote_relaxed(x_empty_peer, __float_as_uint(mx));
+        const long long c2 = clock64();
         m_true = fmaxf(m_true, mx);
         float alpha = 1.f;
         bool rescale = false;
@@ -494,11 +578,11 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         a.p.softmax_max[(int64_t)row * kSfaHeads + h] = m_true * 0.6931471805599453f;
         a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = l * ex2(m_ref - m_true);
       }
-      ++n_tok;
     }
     if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
 #pragma unroll
       for (int i = 0; i < 12; ++i) a.prof[i] = prof[i];
+    }
     }
   }
 

@@ -32,6 +32,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         w = torch.randn(2, S1, 64, generator=g, device="cuda") / 8
 
         p, keep, idx_ref, val_ref = _params(li_mod, q, k, w, count)
+        p.kernel = _cabi.KERNEL_PORTABLE   # the static entry point runs the portable kernels
         n = ctypes.c_size_t(0)
         _cabi.check(_cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(n)), "workspace_bytes")
         ws = torch.empty(n.value, dtype=torch.uint8, device="cuda")
