@@ -157,8 +157,8 @@ def run_gpu(args):
     from dsa_triton_ascend_b200 import _cabi
     import dsa_triton_ascend_b200.lightning_indexer as li_mod
 
-    lens = [L // 8 for L in SEQ_LENS] if args.quick else SEQ_LENS
-    topk = TOPK // 8 if args.quick else TOPK
+    lens = [L // args.scale for L in SEQ_LENS]
+    topk = TOPK // args.scale
     globals()["TOPK"] = topk
     batch = make_gpu_batch(torch, 1000 + rank, lens, args.quick)
     S, T = lens[0], sum(lens)
@@ -406,8 +406,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    lens = [L // 8 for L in SEQ_LENS] if args.quick else SEQ_LENS
-    topk = TOPK // 8 if args.quick else TOPK
+    lens = [L // args.scale for L in SEQ_LENS]
+    topk = TOPK // args.scale
     vals, last = [], None
     for _ in range(max(1, min(args.steps, 3))):
         last = cpu_reference(sample_s=args.cpu_seconds, lens=lens, topk=topk)
@@ -435,9 +435,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="1/8-size workload (debugging only; not a bench value)")
+    ap.add_argument("--scale", type=int, default=1,
+                    help="divide sequence lengths and top-k by this (profiling captures; not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
+    if args.quick:
+        args.scale = max(args.scale, 8)
+    args.quick = args.scale > 1
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -91,7 +91,12 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       // register / shuffle kernel: rows of up to 8192 keys, up to 2048 outputs
       const int e = p->sparse_count <= kTopkThreads ? 1 : (p->sparse_count <= 2 * kTopkThreads ? 2 : 4);
 #define DSA_TOPK_FAST(R, E) li_topk_fast_kernel<T, R, E><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld)
-      if (rank16) { if (e == 1) DSA_TOPK_FAST(true, 1); else if (e == 2) DSA_TOPK_FAST(true, 2); else DSA_TOPK_FAST(true, 4); }
+      if (rank16) {
+        // io-dtype ranking: counting (radix) kernel
+        if (e == 1) li_topk_radix_kernel<T, 1><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+        else if (e == 2) li_topk_radix_kernel<T, 2><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+        else li_topk_radix_kernel<T, 4><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+      }
       else { if (e == 1) DSA_TOPK_FAST(false, 1); else if (e == 2) DSA_TOPK_FAST(false, 2); else DSA_TOPK_FAST(false, 4); }
 #undef DSA_TOPK_FAST
     } else {

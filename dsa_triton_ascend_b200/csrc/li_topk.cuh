@@ -392,4 +392,227 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_fast_kernel(LiDev p, con
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Radix path (io-dtype ranking, rows of up to 8192 visible keys, sparse_count <= 2048).
+// The rank key has only 16 bits, so the whole job is done with counting instead of comparing:
+//   1. threshold: two 256-bin histograms (high byte, then low byte inside the chosen bin), filled
+//      with warp-aggregated adds (__match_any_sync) because nearly all scores share a few bins;
+//   2. ordered compaction: per (round, warp) counts of "key > T" and "key == T" elements are
+//      prefix-summed in position order, which both places the survivors in ascending position
+//      and cuts the ties at the threshold to the first `need` positions without any search;
+//   3. stable LSD radix sort of the <= 2048 survivors on the key, 4 bits per pass, descending;
+//      passes over bit groups in which all survivors agree are skipped (usually 1-2 of the 4).
+//      Equal keys keep their ascending position order, which is the required tie-break.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_tot /*[16]*/, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  uint32_t base = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < kTopkThreads / 32; ++w) {
+    const uint32_t t = warp_tot[w];
+    if (w < warp) base += t;
+    all += t;
+  }
+  if (total) *total = all;
+  __syncthreads();   // warp_tot may be reused right away
+  return base + inc - v;
+}
+
+template <typename T, int E>
+__global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p, const float* __restrict__ scores,
+                                                                     int64_t ld) {
+  constexpr int P2 = kTopkThreads * E;
+  constexpr int NW = kTopkThreads / 32;
+  __shared__ uint32_t buf[2][P2];
+  constexpr int TN = 16 * E * NW;                 // (digit, round, warp) counters of a sort pass
+  __shared__ uint32_t tab[TN < 512 ? 512 : TN];   // also holds the 2 x 256 compaction counters
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t warp_tot[NW];
+  __shared__ uint32_t sh_a, sh_b, sh_c, sh_diff, sh_ref;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
+  const int32_t rown = blockIdx.x;
+  const int32_t row = rown / p.n2;
+  const RowInfo ri = row_info(p.seq, row);
+  const int32_t n = ri.visible;
+  const int32_t K = p.sparse_count;
+  const int32_t nsel = min(n, K);
+  int32_t* oi = p.out_indices + (int64_t)rown * K;
+  T* ov = (p.return_value && p.out_values != nullptr) ? (T*)p.out_values + (int64_t)rown * K : nullptr;
+  if (nsel == 0) {
+    for (int i = tid; i < K; i += kTopkThreads) {
+      oi[i] = -1;
+      if (ov) ov[i] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  const float* s = scores + (int64_t)rown * ld;
+  // rounds (of 512 positions) that hold visible keys; the per-key loops below skip the rest
+  const int rounds = (n + kTopkThreads - 1) / kTopkThreads;
+  uint32_t key[kTopkFastKeys];
+#pragma unroll
+  for (int j = 0; j < kTopkFastKeys; ++j) {
+    const int pos = j * kTopkThreads + tid;
+    key[j] = (j < rounds && pos < n) ? rank_key<T, true>(s[pos]) : 0u;   // real keys are >= 1
+  }
+
+  // ---- 1. threshold key T, number of keys above it and of ties to keep
+  uint32_t thr = 0, need = 0;
+  if (n > K) {
+    uint32_t remaining = (uint32_t)K, hi = 0;
+#pragma unroll 1
+    for (int level = 0; level < 2; ++level) {
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < kTopkFastKeys; ++j) {
+        if (j >= rounds) break;
+        const bool in = key[j] != 0 && (level == 0 || (key[j] >> 8) == hi);
+        const uint32_t d = level == 0 ? (key[j] >> 8) : (key[j] & 255u);
+        const uint32_t vm = __ballot_sync(0xffffffffu, in);
+        const uint32_t m = __match_any_sync(0xffffffffu, d) & vm;
+        if (in && (m & lt) == 0) atomicAdd(&hist[255 - d], __popc(m));   // lowest lane of each group
+      }
+      __syncthreads();
+      const uint32_t cnt = tid < 256 ? hist[tid] : 0;
+      const uint32_t below = block_exclusive_scan(cnt, warp_tot, nullptr);
+      if (tid < 256 && below < remaining && remaining <= below + cnt) { sh_a = 255 - tid; sh_b = below; }
+      __syncthreads();
+      if (level == 0) hi = sh_a; else thr = (hi << 8) | sh_a;
+      remaining -= sh_b;
+      __syncthreads();
+    }
+    need = remaining;   // ties at the threshold that still fit
+  } else {
+    thr = 0;            // every real key is above 0: everything is kept
+  }
+
+  // ---- 2. ordered compaction through per (round, warp) counters
+  uint32_t* cnt_g = tab;          // [16 rounds][16 warps]
+  uint32_t* cnt_e = tab + 256;
+#pragma unroll
+  for (int j = 0; j < kTopkFastKeys; ++j) {
+    uint32_t g = 0, e = 0;
+    if (j < rounds) {
+      g = __ballot_sync(0xffffffffu, key[j] > thr);
+      e = __ballot_sync(0xffffffffu, thr != 0 && key[j] == thr);
+    }
+    if (lane == 0) { cnt_g[j * NW + warp] = __popc(g); cnt_e[j * NW + warp] = __popc(e); }
+  }
+  __syncthreads();
+  {
+    // threads 0..255 scan the "above" counters, 256..511 the "tie" counters (both in position order)
+    const uint32_t v = tab[tid];
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    uint32_t base = 0;
+    const int w0 = warp < 8 ? 0 : 8;
+    for (int w = w0; w < warp; ++w) base += warp_tot[w];
+    if (tid == 0) {
+      uint32_t g = 0;
+      for (int w = 0; w < 8; ++w) g += warp_tot[w];
+      sh_c = g;   // number of keys above the threshold
+      sh_diff = 0;
+      sh_ref = thr ? thr : key[0];   // some key that is kept (position 0 is always visible)
+    }
+    __syncthreads();
+    tab[tid] = base + inc - v;
+  }
+  __syncthreads();
+  const uint32_t n_gt = sh_c, ref = sh_ref;
+  uint32_t diff = 0;   // bits in which some kept key differs from `ref`
+#pragma unroll
+  for (int j = 0; j < kTopkFastKeys; ++j) {
+    if (j >= rounds) break;
+    const uint32_t pos = j * kTopkThreads + tid;
+    const uint32_t entry = (key[j] << 16) | pos;
+    const bool is_g = key[j] > thr, is_e = thr != 0 && key[j] == thr;
+    const uint32_t g = __ballot_sync(0xffffffffu, is_g);
+    const uint32_t e = __ballot_sync(0xffffffffu, is_e);
+    if (is_g) {
+      buf[0][cnt_g[j * NW + warp] + __popc(g & lt)] = entry;
+      diff |= key[j] ^ ref;
+    } else if (is_e) {
+      const uint32_t ord = cnt_e[j * NW + warp] + __popc(e & lt);
+      if (ord < need) buf[0][n_gt + ord] = entry;
+    }
+  }
+  diff = __reduce_or_sync(0xffffffffu, diff);
+  if (lane == 0 && diff) atomicOr(&sh_diff, diff);
+  for (int i = nsel + tid; i < P2; i += kTopkThreads) buf[0][i] = 0x0000FFFFu;   // padding: key 0 sorts last
+  __syncthreads();
+  const uint32_t differing = sh_diff & 0xFFFFu;
+
+  // ---- 3. stable LSD radix sort on the key, descending (digit' = 15 - digit)
+  int cur = 0;
+#pragma unroll 1
+  for (int g = 0; g < 4; ++g) {
+    if (((differing >> (4 * g)) & 15u) == 0) continue;
+    for (int i = tid; i < TN; i += kTopkThreads) tab[i] = 0;
+    __syncthreads();
+    uint32_t ent[E], rk[E], dg[E];
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      ent[r] = buf[cur][r * kTopkThreads + tid];
+      dg[r] = 15u - ((ent[r] >> (16 + 4 * g)) & 15u);
+      const uint32_t m = __match_any_sync(0xffffffffu, dg[r]);
+      rk[r] = __popc(m & lt);
+      if (rk[r] == 0) tab[(dg[r] * E + r) * NW + warp] = __popc(m);
+    }
+    __syncthreads();
+    {
+      // exclusive scan of the (digit, round, warp) counters: 2 * E ... entries per thread
+      constexpr int PER = (TN + kTopkThreads - 1) / kTopkThreads;
+      uint32_t loc[PER], sum = 0;
+#pragma unroll
+      for (int q = 0; q < PER; ++q) {
+        loc[q] = tid * PER + q < TN ? tab[tid * PER + q] : 0u;
+        sum += loc[q];
+      }
+      uint32_t base = block_exclusive_scan(sum, warp_tot, nullptr);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) {
+        if (tid * PER + q < TN) tab[tid * PER + q] = base;
+        base += loc[q];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < E; ++r) buf[cur ^ 1][tab[(dg[r] * E + r) * NW + warp] + rk[r]] = ent[r];
+    __syncthreads();
+    cur ^= 1;
+  }
+
+  // ---- 4. emit
+  for (int i = tid; i < K; i += kTopkThreads) {
+    if (i < nsel) {
+      const uint32_t e = buf[cur][i];
+      oi[i] = (int32_t)(e & 0xFFFFu);
+      if (ov) {
+        const uint32_t k16 = e >> 16;
+        const uint16_t h = (k16 & 0x8000u) ? (uint16_t)(k16 & 0x7FFFu) : (uint16_t)(~k16);
+        ov[i] = *reinterpret_cast<const T*>(&h);
+      }
+    } else {
+      oi[i] = -1;
+      if (ov) ov[i] = from_f32<T>(0.f);
+    }
+  }
+}
+
 }  // namespace dsa

@@ -1,0 +1,100 @@
+"""Query-row sharding of the hot path across the GPUs of one node.
+
+Both operators are row-parallel: one output row (one query token) depends on its own q / weight /
+index row and on the keys of its sequence, never on another row.  The path therefore shards by
+query rows with the (small) key tensors replicated and needs no collective; `torch.distributed`
+is only used by callers for barriers and for gathering results when they want them in one place.
+
+A contiguous slice [r0, r1) of the S1 query rows of a BSND problem is itself a valid BSND problem
+for the unchanged operators: with act_q' = r1 - r0 and act_k' = act_k - (act_q - r1) the
+rightDownCausal limit of local row s' is act_k' - act_q' + s' + 1 = act_k - act_q + (r0 + s') + 1,
+the global row's limit, and keys at or beyond act_k' are hidden from every row of the slice in the
+global problem as well.  `row_slices` balances the slices by causal work (the number of visible
+keys), not by row count.
+"""
+from typing import List, Sequence, Tuple
+
+
+def causal_work(act_q: int, act_k: int, r0: int, r1: int, cap: int = 0) -> int:
+    """Visible (query, key) pairs of rows [r0, r1) under the rightDownCausal mask; `cap` > 0 clips each
+    row's count (top-k attention only touches min(cap, visible) keys)."""
+    total = 0
+    for s in range(r0, r1):
+        v = min(max(act_k - act_q + s + 1, 0), act_k)
+        total += min(v, cap) if cap > 0 else v
+    return total
+
+
+def row_slices(act_q: int, act_k: int, world: int, cap: int = 0, align: int = 8) -> List[Tuple[int, int]]:
+    """Split rows [0, act_q) into `world` contiguous slices of nearly equal causal work.
+
+    Boundaries are multiples of `align` (the tensor-core kernels work on groups of 8 rows)."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    per_row = []
+    for s in range(act_q):
+        v = min(max(act_k - act_q + s + 1, 0), act_k)
+        per_row.append(min(v, cap) if cap > 0 else v)
+    total = sum(per_row)
+    bounds, acc, r = [0], 0, 0
+    for i in range(1, world):
+        target = total * i / world
+        while r < act_q and acc + per_row[r] / 2 < target:
+            acc += per_row[r]
+            r += 1
+        b = min(act_q, (r + align // 2) // align * align)
+        b = max(b, bounds[-1])
+        bounds.append(b)
+        # keep the running sum consistent with the aligned boundary
+        acc, r = sum(per_row[:b]), b
+    bounds.append(act_q)
+    return [(bounds[i], bounds[i + 1]) for i in range(world)]
+
+
+def slice_lengths(act_q: int, act_k: int, r0: int, r1: int) -> Tuple[int, int]:
+    """(act_q', act_k') that make rows [r0, r1) a stand-alone problem (see module docstring)."""
+    if not (0 <= r0 <= r1 <= act_q):
+        raise ValueError("slice outside the sequence")
+    return r1 - r0, max(act_k - (act_q - r1), 0)
+
+
+def lightning_indexer_rows(query, key, weights, r0: int, r1: int, act_q: Sequence[int] = None,
+                           act_k: Sequence[int] = None, **kw):
+    """lightning_indexer_triton on query rows [r0, r1) of every sequence of a BSND batch.
+
+    `query` / `weights` are the FULL tensors (or any tensors whose dim 1 covers [r0, r1)); the key is
+    the replicated full key.  Returns what the full call would return for those rows."""
+    from .lightning_indexer import lightning_indexer_triton
+    B, S1 = query.shape[0], query.shape[1]
+    S2 = key.shape[1]
+    act_q = [S1] * B if act_q is None else [int(v) for v in act_q]
+    act_k = [S2] * B if act_k is None else [int(v) for v in act_k]
+    lq, lk = [], []
+    for b in range(B):
+        e = min(r1, act_q[b])
+        s = min(r0, e)
+        q_, k_ = slice_lengths(act_q[b], act_k[b], s, e)
+        lq.append(q_)
+        lk.append(k_)
+    return lightning_indexer_triton(query[:, r0:r1], key, weights[:, r0:r1], actual_seq_lengths_query=lq,
+                                    actual_seq_lengths_key=lk, **kw)
+
+
+def sparse_flash_attention_rows(query, key, sparse_indices, query_rope, key_rope, r0: int, r1: int,
+                                act_q: Sequence[int] = None, act_k: Sequence[int] = None, **kw):
+    """sparse_flash_attention_triton on query rows [r0, r1) of every sequence of a BSND batch."""
+    from .sparse_flash_attention import sparse_flash_attention_triton
+    B, S1 = query.shape[0], query.shape[1]
+    S2 = key.shape[1]
+    act_q = [S1] * B if act_q is None else [int(v) for v in act_q]
+    act_k = [S2] * B if act_k is None else [int(v) for v in act_k]
+    lq, lk = [], []
+    for b in range(B):
+        e = min(r1, act_q[b])
+        s = min(r0, e)
+        q_, k_ = slice_lengths(act_q[b], act_k[b], s, e)
+        lq.append(q_)
+        lk.append(k_)
+    return sparse_flash_attention_triton(
+        query[:, r0:r1], key, key, sparse_indices[:, r0:r1], actual_seq_lengths_query=lq,
+        actual_seq_lengths_kv=lk, query_rope=query_rope[:, r0:r1], key_rope=key_rope, **kw)

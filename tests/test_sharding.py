@@ -1,0 +1,75 @@
+"""Host logic of the multi-GPU path: row slices are balanced, cover every row once, and a slice run
+as a stand-alone problem reproduces the rows of the full problem (checked with the oracle, and
+across two gloo ranks on CPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from dsa_triton_ascend_b200.sharding import causal_work, row_slices, slice_lengths
+from oracle import lightning_indexer_oracle, sparse_flash_attention_oracle
+from oracle.inputs import li_inputs, sfa_inputs, sparse_indices
+
+
+@pytest.mark.parametrize("act_q,act_k,world,cap", [(8192, 8192, 8, 0), (8192, 8192, 4, 2048), (1000, 4000, 3, 0),
+                                                   (300, 100, 2, 0), (64, 64, 8, 16), (7, 7, 4, 0)])
+def test_row_slices_cover_and_balance(act_q, act_k, world, cap):
+    sl = row_slices(act_q, act_k, world, cap)
+    assert len(sl) == world and sl[0][0] == 0 and sl[-1][1] == act_q
+    assert all(a[1] == b[0] for a, b in zip(sl, sl[1:])) and all(a <= b for a, b in sl)
+    work = [causal_work(act_q, act_k, a, b, cap) for a, b in sl]
+    assert sum(work) == causal_work(act_q, act_k, 0, act_q, cap)
+    if act_q >= 64 * world:
+        assert max(work) <= 1.15 * sum(work) / world, work
+
+
+def test_slice_is_a_standalone_problem_for_the_indexer():
+    B, S1, S2, N1, D, K = 1, 96, 160, 8, 64, 24
+    q, k, w = li_inputs(3, B, S1, S2, N1, 1, D, "bf16")
+    aq, ak = [80], [150]
+    full_i, full_v = lightning_indexer_oracle(q, k, w, aq, ak, sparse_count=K, sparse_mode=3, return_value=True)
+    for r0, r1 in row_slices(aq[0], ak[0], 3):
+        lq, lk = slice_lengths(aq[0], ak[0], r0, r1)
+        i, v = lightning_indexer_oracle(q[:, r0:r1], k, w[:, r0:r1], [lq], [lk], sparse_count=K, sparse_mode=3,
+                                        return_value=True)
+        np.testing.assert_array_equal(i[:, :lq], full_i[:, r0:r1])
+        np.testing.assert_array_equal(v[:, :lq], full_v[:, r0:r1])
+
+
+def _rank_main(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, S1, S2, N1, D, K = 1, 40, 96, 8, 128, 16
+        q, k, qr, kr = sfa_inputs(5, B, S1, S2, N1, D)
+        idx = sparse_indices(6, B, S1, S2, K)
+        scale = 1.0 / np.sqrt(D + 64.0)
+        r0, r1 = row_slices(S1, S2, world)[rank]
+        lq, lk = slice_lengths(S1, S2, r0, r1)
+        out, smax, ssum = sparse_flash_attention_oracle(q[:, r0:r1], k, idx[:, r0:r1], qr[:, r0:r1], kr, scale,
+                                                        [lq], [lk], sparse_mode=3, dtype="bf16")
+        # every rank ends up with all rows: this gather is outside the hot path
+        parts = [None] * world
+        dist.all_gather_object(parts, (r0, r1, out, smax, ssum))
+        if rank == 0:
+            full = sparse_flash_attention_oracle(q, k, idx, qr, kr, scale, [S1], [S2], sparse_mode=3, dtype="bf16")
+            got = np.concatenate([p[2] for p in sorted(parts, key=lambda p: p[0])], axis=1)
+            got_m = np.concatenate([p[3] for p in sorted(parts, key=lambda p: p[0])], axis=2)
+            np.testing.assert_array_equal(got, full[0])
+            np.testing.assert_array_equal(got_m, full[1])
+            open(os.path.join(tmp, "ok"), "w").write("ok")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_full_problem(tmp_path):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok").exists()
