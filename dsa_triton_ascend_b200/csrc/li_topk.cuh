@@ -426,6 +426,17 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* w
   return base + inc - v;
 }
 
+// Mask of the lanes whose 4-bit digit equals this lane's (four ballots; cheaper than a match).
+__device__ __forceinline__ uint32_t same_digit4(uint32_t d) {
+  uint32_t m = 0xffffffffu;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const uint32_t v = __ballot_sync(0xffffffffu, (d >> b) & 1u);
+    m &= ((d >> b) & 1u) ? v : ~v;
+  }
+  return m;
+}
+
 template <typename T, int E>
 __global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p, const float* __restrict__ scores,
                                                                      int64_t ld) {
@@ -478,9 +489,14 @@ __global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p,
         if (j >= rounds) break;
         const bool in = key[j] != 0 && (level == 0 || (key[j] >> 8) == hi);
         const uint32_t d = level == 0 ? (key[j] >> 8) : (key[j] & 255u);
-        const uint32_t vm = __ballot_sync(0xffffffffu, in);
-        const uint32_t m = __match_any_sync(0xffffffffu, d) & vm;
-        if (in && (m & lt) == 0) atomicAdd(&hist[255 - d], __popc(m));   // lowest lane of each group
+        if (level == 0) {
+          // high byte: nearly all keys share a few values, so add once per group of equal values
+          const uint32_t vm = __ballot_sync(0xffffffffu, in);
+          const uint32_t m = __match_any_sync(0xffffffffu, d) & vm;
+          if (in && (m & lt) == 0) atomicAdd(&hist[255 - d], __popc(m));
+        } else if (in) {
+          atomicAdd(&hist[255 - d], 1u);   // low byte inside the chosen bin: spread over the bins
+        }
       }
       __syncthreads();
       const uint32_t cnt = tid < 256 ? hist[tid] : 0;
@@ -570,7 +586,7 @@ __global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p,
     for (int r = 0; r < E; ++r) {
       ent[r] = buf[cur][r * kTopkThreads + tid];
       dg[r] = 15u - ((ent[r] >> (16 + 4 * g)) & 15u);
-      const uint32_t m = __match_any_sync(0xffffffffu, dg[r]);
+      const uint32_t m = same_digit4(dg[r]);
       rk[r] = __popc(m & lt);
       if (rk[r] == 0) tab[(dg[r] * E + r) * NW + warp] = __popc(m);
     }
