@@ -100,10 +100,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)  // suspend-time hint in ns
       : "memory");
   return done != 0;
 }
@@ -116,12 +116,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Pure polling (no suspension): a suspended waiter was seen to sleep for microseconds past a
-// remote arrival.  2^24 polls is roughly a second.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 24); ++i) {
+  for (uint32_t i = 0; i < (kWaitPolls << 2); ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;

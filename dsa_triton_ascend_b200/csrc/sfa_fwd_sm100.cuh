@@ -21,7 +21,8 @@
 // 16-byte cp.async warp instruction costs ~115 cycles (~4.4 B/clk per warp), and both scale
 // linearly with the number of issuing warps (6 warps: ~42 B/clk).  A tile's 80 loads issued from a
 // single warp took ~6100 cycles against ~1150 cycles of MMA work, so the loads of every tile are
-// spread over six producer warps.
+// spread over ten producer warps (under load, next to the MMAs and the
+// bulk copies, a producer warp needs ~170 cycles per load).
 //
 // A small pre-pass kernel turns every row's sparse indices into a front-packed list of physical KV
 // rows plus a count (block-wise ids expanded, -1 / out-of-window entries dropped, paged positions
@@ -32,9 +33,9 @@
 // Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | 32 KB
 // staging buffer for the outgoing partial.
 //
-// Warps (512 threads, registers redistributed with setmaxnreg): 0..5 = gather producers, 6 = MMA
-// issuer (QK^T) / TMEM owner, 7 = MMA issuer (PV), 8..11 = senders (partial S: TMEM -> staging -> peer; Q -> TMEM),
-// 12..15 = softmax + epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
+// Warps (640 threads, registers redistributed with setmaxnreg): 0..9 = gather producers, 10 = MMA
+// issuer (QK^T) / TMEM owner, 11 = MMA issuer (PV), 12..15 = senders (partial S: TMEM -> staging ->
+// peer; Q -> TMEM), 16..19 = softmax + epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
 // status word.
 #pragma once
 
@@ -48,11 +49,11 @@ namespace dsa {
 constexpr int kSfaHeads = 128;
 constexpr int kSfaBK = 64;         // keys per tile
 constexpr int kSfaStages = 4;
-constexpr int kSfaThreads = 512;
-constexpr int kSfaProducerWarps = 6;
-constexpr int kSfaMmaWarp = 6;
-constexpr int kSfaSendWarp0 = 8;     // warps 8..11: partial-score senders + Q loaders
-constexpr int kSfaSoftWarp0 = 12;    // warps 12..15: softmax + epilogue
+constexpr int kSfaThreads = 640;
+constexpr int kSfaProducerWarps = 10;
+constexpr int kSfaMmaWarp = 10;
+constexpr int kSfaSendWarp0 = 12;    // warps 12..15: partial-score senders + Q loaders
+constexpr int kSfaSoftWarp0 = 16;    // warps 16..19: softmax + epilogue
 constexpr int kSfaDvHalf = 256;
 constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
 
@@ -191,16 +192,16 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   const int32_t slots = a.p.sparse_count * a.p.sparse_block_size;
   const int32_t n1d = kSfaHeads * a.p.d;
 
-  if (warp < 8) {
-   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp < kSfaSendWarp0) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
    if (*abort_flag) {
     // nothing started: fall through to the teardown
   } else if (warp < kSfaProducerWarps) {
     // ------------------------------------------------------------------ gather producers
     // A tile is 16 row groups (4 keys each) x nblk column blocks = 80 (rank 0) or 64 (rank 1)
     // gather4 loads of 512 bytes.  A warp issues one such load every ~67 cycles whatever the lane
-    // pattern, but warps issue in parallel, so the loads of every tile are dealt out over six
-    // warps (load o goes to warp o % 6, lane o / 6).  Warp 0 also arms the stage's barrier.
+    // pattern, but warps issue in parallel, so the loads of every tile are dealt out over ten
+    // warps (load o goes to warp o % 10, lane o / 10).  Warp 0 also arms the stage's barrier.
     uint32_t n_tile = 0;
     bool ok = true;
     long long pprof[4] = {0, 0, 0, 0};
@@ -211,32 +212,48 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     const int32_t x = rank == 0 ? (blk < 4 ? blk * 64 : 0) : kSfaDvHalf + blk * 64;
     const CUtensorMap* tm = (rank == 0 && blk == 4) ? &tmap_kr : &tmap_kn;
     if (lane == 0) { ptx::prefetch_tmap(&tmap_kn); ptx::prefetch_tmap(&tmap_kr); }
-    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const int32_t nvalid = a.nvalid[row];
-      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      const int32_t* list = a.key_list + (int64_t)row * slots;
-      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
-        const long long p1 = clock64();
-        // physical rows of this lane's 4 keys (keys past the end of the row re-read the tile's first)
-        int32_t r[4] = {0, 0, 0, 0};
-        if (active) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int32_t k = t * kSfaBK + grp * 4 + i;
-            r[i] = list[k < nvalid ? k : t * kSfaBK];
-          }
-        }
-        if (lane == 0) ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok) break;
-        const long long p2 = clock64();
-        if (warp == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * nblk * 128);
-        if (active)
-          ptx::tma_gather4_2d(kv_s + s * kSfaStage + blk * kSfaBlk + grp * 512, tm, &kv_full[s], x, r[0], r[1], r[2], r[3]);
-        __syncwarp();
-        pprof[1] += p2 - p1; pprof[2] += clock64() - p2;
+    // The row numbers of a tile come from global memory (the pre-pass list); they are fetched one
+    // tile ahead so that their latency never sits between a freed stage and the gather.
+    struct TilePos { int32_t row, t, ntiles, nvalid; };
+    auto first_from = [&](int32_t row) -> TilePos {
+      for (; row < a.rows; row += n_clusters) {
+        const int32_t nv = a.nvalid[row];
+        if (nv > 0) return TilePos{row, 0, (nv + kSfaBK - 1) / kSfaBK, nv};
       }
+      return TilePos{a.rows, 0, 0, 0};
+    };
+    auto load_rows = [&](const TilePos& tp, int32_t* r) {
+      const int32_t* list = a.key_list + (int64_t)tp.row * slots;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int32_t k = tp.t * kSfaBK + grp * 4 + i;
+        // keys past the end of the row re-read the tile's first key
+        r[i] = (active && tp.row < a.rows) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
+      }
+    };
+    TilePos cur = first_from(cluster_id);
+    int32_t rc[4], rn[4];
+    load_rows(cur, rc);
+    while (cur.row < a.rows && ok) {
+      TilePos nxt = cur;
+      if (++nxt.t >= nxt.ntiles) nxt = first_from(cur.row + n_clusters);
+      load_rows(nxt, rn);
+      const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
+      const long long p1 = clock64();
+      if (lane == 0) ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      const long long p2 = clock64();
+      if (warp == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * nblk * 128);
+      if (active)
+        ptx::tma_gather4_2d(kv_s + s * kSfaStage + blk * kSfaBlk + grp * 512, tm, &kv_full[s], x, rc[0], rc[1], rc[2],
+                            rc[3]);
+      __syncwarp();
+      pprof[1] += p2 - p1; pprof[2] += clock64() - p2;
+      ++n_tile;
+      cur = nxt;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rc[i] = rn[i];
     }
     if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
       for (int i = 0; i < 4; ++i) a.prof[16 + i] = pprof[i];
@@ -319,7 +336,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) a.prof[14] = wait_p;
   }
   } else if (warp < kSfaSoftWarp0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     if (!*abort_flag) {
     // ------------------------------------------------------------------ senders
     // Per token: this CTA's Q half into tensor memory.  Per tile: the partial S from tensor memory
@@ -333,6 +350,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     const uint32_t x_full_peer = ptx::map_to_rank(x_full, peer);
     uint32_t n_tile = 0, n_tok = 0;
     bool ok = true;
+    long long sprof[4] = {0, 0, 0, 0};
     auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
     };
@@ -376,8 +394,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::mbar_arrive(q_full);
       }
       for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+        const long long s0 = clock64();
         ok = wait_w(s_full, n_tile & 1);
         if (!ok) break;
+        sprof[0] += clock64() - s0;
         ptx::tc_fence_after();
         float sv[kSfaBK];
         ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sv));
@@ -390,10 +410,13 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         // w * 4096 + c * 512 + lane * 16)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
+          const long long s1 = clock64();
           ok = wait_wc(&x_empty[hf], (n_tile & 1) ^ 1);
           if (!ok) break;
+          const long long s2 = clock64();
           ok = wait_w(&own_free[hf], (n_tile & 1) ^ 1);
           if (!ok) break;
+          sprof[1] += s2 - s1; sprof[2] += clock64() - s2;
           if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&x_full[hf], kSfaXBytes / 2);  // arm my landing half
           float* mine = xo_s + hf * 4096 + quarter * 1024 + lane * 4;
 #pragma unroll
@@ -411,6 +434,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         }
       }
       ++n_tok;
+    }
+    if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
+      for (int i = 0; i < 3; ++i) a.prof[20 + i] = sprof[i];
     }
     }
   } else {
