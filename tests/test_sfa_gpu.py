@@ -215,3 +215,60 @@ def test_sfa_full_size_tnd_sampled_rows():
                                             [L], [L], sparse_mode=3, dtype="bf16", rows=[(0, s)])
         _compare(host(out[t]), host(smax[0, t]), host(ssum[0, t]), ref[0][0, s], ref[1][0, 0, s],
                  ref[2][0, 0, s], "bf16")
+
+
+def test_sfa_tensor_path_agrees_with_portable_path_and_reports_clean_status():
+    """128 heads x D=512 runs on the tcgen05 kernel: block-wise indices, ragged lengths, fp16 and a
+    paged cache must agree with the portable CUDA-core kernel, and the status word must stay 0."""
+    import ctypes
+    from dsa_triton_ascend_b200 import _cabi
+    sfa = _sfa()
+    held = []
+    orig = sfa.workspace
+
+    def keep_ws(n, dev):
+        t = orig(n, dev)
+        held.append(t)
+        return t
+
+    rng = np.random.RandomState(77)
+    B, S1, S2, N1, D, K, bs = 2, 24, 640, 128, 512, 40, 4
+    lens_q, lens_k = [24, 9], [640, 333]
+    for dtype, tdt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+        q = round_io(rng.randn(B, S1, N1, D).astype(np.float32), dtype)
+        k = round_io(rng.randn(B, S2, 1, D).astype(np.float32), dtype)
+        qr = round_io(rng.randn(B, S1, N1, 64).astype(np.float32), dtype)
+        kr = round_io(rng.randn(B, S2, 1, 64).astype(np.float32), dtype)
+        idx = sparse_indices(78, B, S1, S2, K, bs, 3, lens_q, lens_k)
+        idx[0, 5, 0, 3] = -1          # a hole in the middle of a row
+        args = (dev(q, tdt), dev(k, tdt), dev(k, tdt), torch.from_numpy(idx).cuda())
+        kw = dict(scale_value=1.0 / 24.0, actual_seq_lengths_query=lens_q, actual_seq_lengths_kv=lens_k,
+                  query_rope=dev(qr, tdt), key_rope=dev(kr, tdt), sparse_block_size=bs, sparse_mode=3,
+                  return_softmax_lse=True)
+        sfa.workspace = keep_ws
+        try:
+            sfa.set_kernel("tensor")
+            got = sfa.sparse_flash_attention_triton(*args, **kw)
+            stream = torch.cuda.current_stream().cuda_stream
+            assert _cabi.lib.dsa_read_device_status(held[-1].data_ptr(), stream) == 0
+            sfa.set_kernel("portable")
+            ref = sfa.sparse_flash_attention_triton(*args, **kw)
+        finally:
+            sfa.set_kernel("auto")
+            sfa.workspace = orig
+        sfa_acceptance_rule(*(host(t) for t in got), *(host(t) for t in ref))
+
+
+def test_sfa_portable_kernel_request_is_honoured_for_other_shapes():
+    """Shapes outside the tensor path (16 heads) refuse kernel='tensor' with a clear error."""
+    sfa = _sfa()
+    q, k, qr, kr, idx, act_q, act_k, scale, c = sfa_case_inputs("sfa_tiny")
+    dt = torch.bfloat16
+    sfa.set_kernel("tensor")
+    try:
+        with pytest.raises(RuntimeError):
+            sfa.sparse_flash_attention_triton(dev(q, dt), dev(k, dt), dev(k, dt), torch.from_numpy(idx).cuda(),
+                                              scale_value=scale, query_rope=dev(qr, dt), key_rope=dev(kr, dt),
+                                              sparse_mode=3)
+    finally:
+        sfa.set_kernel("auto")
