@@ -1,6 +1,7 @@
 // Lightning-indexer score kernel on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16, BSND layouts.
+// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16, BSND or TND
+// layouts (not paged keys).
 //
 // GEMM orientation: KEYS sit on the MMA M axis (128 keys = 128 TMEM lanes) and (token, head)
 // pairs on the N axis (4 tokens x 64 heads = 256 columns), so that after a TMEM load every
@@ -50,12 +51,42 @@ struct LiSm100Args {
   uint32_t idesc;
 };
 
-// Item i (0 = most work) -> (sequence b, first row position).  Later rows see more keys under the
-// causal mask, so items are ordered by decreasing position, sequences interleaved.
-__device__ __forceinline__ void li_item(const LiSm100Args& a, int32_t i, int32_t* b, int32_t* pos0) {
-  const int32_t B = a.p.seq.batch;
-  *b = i % B;
-  *pos0 = (a.groups_per_seq - 1 - i / B) * kLiTok;
+// One work item: up to 8 consecutive query rows of one sequence.
+struct LiItem {
+  int32_t row0;    // first global query row (BSND: b * s1 + pos, TND: token index); -1 = no such item
+  int32_t nrows;   // 1..8 rows that exist in the sequence
+  int64_t krow0;   // first key row of the sequence in the key tensor
+};
+// Item i -> rows.  BSND: sequences interleaved, later row groups first (under the causal mask they
+// see more keys, so item 0 is the most work).  TND: sequences in order (their group counts are
+// only known on the device), later groups first inside each sequence.
+__device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
+  LiItem it;
+  it.row0 = -1; it.nrows = 0; it.krow0 = 0;
+  const SeqDesc& s = a.p.seq;
+  int32_t b, pos0, len_q, start_q;
+  if (s.layout_q == DSA_LAYOUT_TND) {
+    int32_t acc = 0, prev = 0;
+    for (b = 0; b < s.batch; ++b) {
+      const int32_t end = s.seq_q[b];
+      const int32_t g = (end - prev + kLiTok - 1) / kLiTok;
+      if (i < acc + g) {
+        start_q = prev; len_q = end - prev;
+        pos0 = (g - 1 - (i - acc)) * kLiTok;
+        break;
+      }
+      acc += g; prev = end;
+    }
+    if (b >= s.batch) return it;
+  } else {
+    b = i % s.batch;
+    pos0 = (a.groups_per_seq - 1 - i / s.batch) * kLiTok;
+    start_q = b * s.s1; len_q = s.s1;
+  }
+  it.row0 = start_q + pos0;
+  it.nrows = min(kLiTok, len_q - pos0);
+  it.krow0 = row_info(s, it.row0).key_base;
+  return it;
 }
 // j-th item of CTA c in snake order over a persistent grid of g CTAs (-1 when exhausted).
 __device__ __forceinline__ int32_t li_item_of(int32_t c, int32_t g, int32_t j, int32_t items) {
@@ -63,12 +94,12 @@ __device__ __forceinline__ int32_t li_item_of(int32_t c, int32_t g, int32_t j, i
   return i < items ? i : -1;
 }
 // Visible key count of each of the item's rows and the number of key tiles to process.
-__device__ __forceinline__ int32_t li_item_tiles(const LiSm100Args& a, int32_t b, int32_t pos0, int32_t* vis) {
+__device__ __forceinline__ int32_t li_item_tiles(const LiSm100Args& a, const LiItem& it, int32_t* vis) {
   int32_t mx = 0;
 #pragma unroll
   for (int t = 0; t < kLiTok; ++t) {
     int32_t v = 0;
-    if (pos0 + t < a.p.seq.s1) v = row_info(a.p.seq, b * a.p.seq.s1 + pos0 + t).visible;
+    if (t < it.nrows) v = row_info(a.p.seq, it.row0 + t).visible;
     if (vis) vis[t] = v;
     mx = max(mx, v);
   }
@@ -128,21 +159,21 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       for (int32_t j = 0; ok; ++j) {
         const int32_t it = li_item_of(cta, grid, j, a.items);
         if (it < 0) break;
-        int32_t b, pos0;
-        li_item(a, it, &b, &pos0);
-        const int32_t tiles = li_item_tiles(a, b, pos0, nullptr);
+        const LiItem item = li_item(a, it);
+        if (item.row0 < 0) continue;
+        const int32_t tiles = li_item_tiles(a, item, nullptr);
         if (tiles == 0) continue;
         ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(qfull, kLiQBytes);
-        const int32_t qrow = (b * a.p.seq.s1 + pos0) * kLiHeads;
+        const int32_t qrow = item.row0 * kLiHeads;
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int c = 0; c < 2; ++c)
             ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
         ++n_item;
-        const int32_t krow0 = b * a.p.seq.s2;
+        const int32_t krow0 = (int32_t)item.krow0;
         for (int32_t t = 0; t < tiles; ++t, ++n_tile) {
           const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
           ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
@@ -162,9 +193,9 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       for (int32_t j = 0; ok; ++j) {
         const int32_t it = li_item_of(cta, grid, j, a.items);
         if (it < 0) break;
-        int32_t b, pos0;
-        li_item(a, it, &b, &pos0);
-        const int32_t tiles = li_item_tiles(a, b, pos0, nullptr);
+        const LiItem item = li_item(a, it);
+        if (item.row0 < 0) continue;
+        const int32_t tiles = li_item_tiles(a, item, nullptr);
         if (tiles == 0) continue;
         ok = ptx::mbar_wait(qfull, n_item & 1, abort_flag);
         if (!ok) break;
@@ -203,11 +234,12 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int32_t j = 0; ok; ++j) {
       const int32_t it = li_item_of(cta, grid, j, a.items);
       if (it < 0) break;
-      int32_t b, pos0, vis[kLiTok];
-      li_item(a, it, &b, &pos0);
-      const int32_t tiles = li_item_tiles(a, b, pos0, vis);
+      int32_t vis[kLiTok];
+      const LiItem item = li_item(a, it);
+      if (item.row0 < 0) continue;
+      const int32_t tiles = li_item_tiles(a, item, vis);
       if (tiles == 0) continue;
-      const int32_t row0 = b * a.p.seq.s1 + pos0;
+      const int32_t row0 = item.row0;
       // weights of the item's 8 rows -> shared memory (rows past the sequence end read as zero)
       // (rendezvous through an mbarrier so that even this wait is bounded)
       ptx::mbar_arrive(wbar);
@@ -215,7 +247,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (!ok) break;
       for (int i = et; i < kLiTok * kLiHeads; i += 256) {
         const int t = i / kLiHeads;
-        w_s[i] = (pos0 + t < a.p.seq.s1) ? load_weight(a.p.weights, a.p.dtype_w, (int64_t)(row0 + t) * kLiHeads + (i - t * kLiHeads))
+        w_s[i] = (t < item.nrows) ? load_weight(a.p.weights, a.p.dtype_w, (int64_t)(row0 + t) * kLiHeads + (i - t * kLiHeads))
                                         : 0.f;
       }
       ptx::mbar_arrive(wbar);
@@ -275,12 +307,13 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
 // Host side: eligibility, tensor maps, launch.
 inline bool li_sm100_eligible(const DsaLiParams* p) {
-  if (p->layout_q != DSA_LAYOUT_BSND || p->layout_k != DSA_LAYOUT_BSND) return false;
+  if (p->layout_k == DSA_LAYOUT_PA_BSND) return false;   // paged keys are not contiguous per sequence
   if (p->n1 != kLiHeads || p->n2 != 1 || p->d != kLiDim) return false;
   if (p->s1 < 1 || p->s2 < 1) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->key & 15u)) return false;
-  if ((int64_t)p->batch * p->s1 * kLiHeads >= (1ll << 31) || (int64_t)p->batch * p->s2 >= (1ll << 31)) return false;
-  if (p->seq_q_cumulative || p->seq_k_cumulative) return false;
+  const int64_t rows = p->layout_q == DSA_LAYOUT_TND ? (int64_t)p->s1 : (int64_t)p->batch * p->s1;
+  if (rows * kLiHeads >= (1ll << 31) || p->key_rows < 1 || p->key_rows >= (1ll << 31)) return false;
+  if (p->layout_q == DSA_LAYOUT_BSND && p->seq_q_cumulative) return false;
   return true;
 }
 
@@ -299,9 +332,10 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   }
   const bool bf16 = p->dtype_qk == DSA_DTYPE_BF16;
   CUtensorMap tq, tk;
-  if (!make_tmap_2d_16bit(&tq, p->query, (uint64_t)p->batch * p->s1 * kLiHeads, kLiDim, kLiDim * 2, 256, 64, bf16))
-    return DSA_ERR_CUDA;
-  if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->batch * p->s2, kLiDim, kLiDim * 2, kLiKeys, 64, bf16))
+  const bool tnd = p->layout_q == DSA_LAYOUT_TND;
+  const uint64_t qrows = tnd ? (uint64_t)p->s1 : (uint64_t)p->batch * p->s1;
+  if (!make_tmap_2d_16bit(&tq, p->query, qrows * kLiHeads, kLiDim, kLiDim * 2, 256, 64, bf16)) return DSA_ERR_CUDA;
+  if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->key_rows, kLiDim, kLiDim * 2, kLiKeys, 64, bf16))
     return DSA_ERR_CUDA;
   LiSm100Args a;
   a.p = d;
@@ -309,7 +343,9 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   a.ld = ld;
   a.status = status;
   a.groups_per_seq = (p->s1 + kLiTok - 1) / kLiTok;
-  a.items = p->batch * a.groups_per_seq;
+  // TND: the group count of a sequence is only known on the device; this is an upper bound and
+  // li_item() reports the surplus as empty
+  a.items = tnd ? (p->s1 + kLiTok - 1) / kLiTok + p->batch : p->batch * a.groups_per_seq;
   a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
   const int grid = a.items < sm_count[dev] ? a.items : sm_count[dev];
   li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);

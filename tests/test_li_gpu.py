@@ -212,3 +212,29 @@ def test_li_production_shape_runs_on_the_tensor_core_path():
     same = (idx_t == idx).all(dim=-1).float().mean().item()
     assert same >= 0.97, f"tensor and portable paths agree on {same:.4f} of the rows"
     del keep
+
+
+def test_li_tnd_production_shape_on_the_tensor_core_path():
+    """TND query and key with 64 heads x D=128 run on the tcgen05 kernel (ragged sequences, lengths
+    that are not multiples of the 8-row work items)."""
+    import ctypes
+    from dsa_triton_ascend_b200 import _cabi
+    li = _li()
+    rng = np.random.RandomState(15)
+    lens_q, lens_k = [37, 1, 200, 64], [150, 9, 200, 300]
+    K = 48
+    from oracle.inputs import round_io
+    q = round_io(rng.randn(sum(lens_q), 64, 128).astype(np.float32), "bf16")
+    k = round_io(rng.randn(sum(lens_k), 1, 128).astype(np.float32), "bf16")
+    w = (rng.randn(sum(lens_q), 64) / 8).astype(np.float32)
+    cu_q, cu_k = np.cumsum(lens_q).tolist(), np.cumsum(lens_k).tolist()
+    ref_i, ref_v = layouts.li_oracle_tnd(q, k, w, cu_q, cu_k, sparse_count=K, sparse_mode=3, return_value=True)
+    qd, kd, wd = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(w)
+    p, keep, _, _, _ = li._build_params(qd, kd, wd, cu_q, cu_k, None, "TND", "TND", K, 3, True)
+    assert _cabi.lib.dsa_li_uses_tensor_path(ctypes.byref(p)) == 1
+    del keep
+    idx, val = li.lightning_indexer_triton(qd, kd, wd, actual_seq_lengths_query=cu_q, actual_seq_lengths_key=cu_k,
+                                           layout_query="TND", layout_key="TND", sparse_count=K, sparse_mode=3,
+                                           return_value=True)
+    li_reference_rule(host(idx), host(val), ref_i, ref_v)
+    assert (host(idx) == ref_i).all(axis=(1, 2)).mean() >= 0.97
