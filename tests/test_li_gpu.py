@@ -238,3 +238,19 @@ def test_li_tnd_production_shape_on_the_tensor_core_path():
                                            return_value=True)
     li_reference_rule(host(idx), host(val), ref_i, ref_v)
     assert (host(idx) == ref_i).all(axis=(1, 2)).mean() >= 0.97
+
+
+def test_li_full_mode_on_the_tensor_core_path():
+    """sparse_mode=0 (no causal mask, only act_k) with the production head shape, fp16."""
+    li = _li()
+    from oracle.inputs import li_inputs
+    B, S1, S2, K = 2, 40, 300, 64
+    q, k, w = li_inputs(23, B, S1, S2, 64, 1, 128, "fp16", w_scale=0.125)
+    act_q, act_k = [40, 17], [300, 129]
+    ref_i, ref_v = lightning_indexer_oracle(q, k, w, act_q, act_k, sparse_count=K, sparse_mode=0,
+                                            return_value=True, value_dtype="fp16")
+    idx, val = li.lightning_indexer_triton(dev(q, torch.float16), dev(k, torch.float16), dev(w),
+                                           actual_seq_lengths_query=act_q, actual_seq_lengths_key=act_k,
+                                           sparse_count=K, sparse_mode=0, return_value=True)
+    li_reference_rule(host(idx), host(val), ref_i, ref_v)
+    assert (host(idx) == ref_i).all(axis=(2, 3)).mean() >= 0.97

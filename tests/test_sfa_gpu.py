@@ -272,3 +272,23 @@ def test_sfa_portable_kernel_request_is_honoured_for_other_shapes():
                                               sparse_mode=3)
     finally:
         sfa.set_kernel("auto")
+
+
+def test_sfa_full_mode_on_the_tensor_core_path():
+    """sparse_mode=0 with 128 heads: every index below act_k takes part, whatever the row."""
+    sfa = _sfa()
+    rng = np.random.RandomState(91)
+    B, S1, S2, N1, D, K = 1, 6, 400, 128, 512, 200
+    q = round_io(rng.randn(B, S1, N1, D).astype(np.float32), "bf16")
+    k = round_io(rng.randn(B, S2, 1, D).astype(np.float32), "bf16")
+    qr = round_io(rng.randn(B, S1, N1, 64).astype(np.float32), "bf16")
+    kr = round_io(rng.randn(B, S2, 1, 64).astype(np.float32), "bf16")
+    idx = sparse_indices(92, B, S1, S2, K, 1, 0, [S1], [350])
+    scale = 1.0 / 24.0
+    ref = sparse_flash_attention_oracle(q, k, idx, qr, kr, scale, [S1], [350], sparse_mode=0, dtype="bf16")
+    dt = torch.bfloat16
+    got = sfa.sparse_flash_attention_triton(
+        dev(q, dt), dev(k, dt), dev(k, dt), torch.from_numpy(idx).cuda(), scale_value=scale,
+        actual_seq_lengths_kv=[350], query_rope=dev(qr, dt), key_rope=dev(kr, dt), sparse_mode=0,
+        return_softmax_lse=True)
+    _compare(*(host(t) for t in got), *ref, "bf16")
