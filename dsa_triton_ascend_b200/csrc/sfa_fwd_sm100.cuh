@@ -357,6 +357,14 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
     };
+    auto q_half = [&](int32_t r) -> const uint4* {
+      return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query +
+                                            ((int64_t)r * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2);
+    };
+    auto q_rope = [&](int32_t r) -> const uint4* {
+      return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
+                                            ((int64_t)r * kSfaHeads + h) * a.p.d_rope * 2);
+    };
     for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
       const int32_t nvalid = a.nvalid[row];
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
@@ -366,21 +374,22 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       if (!ok) break;
       ptx::tc_fence_after();
       {
-        const uint4* qn = reinterpret_cast<const uint4*>((const unsigned char*)a.p.query +
-                                                         ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2);
+        // 16 loads in flight per batch (a batch of 8 left the five batches' latencies in a row at
+        // every token boundary)
+        const uint4* qn = q_half(row);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[32];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t w[64];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint4 v = __ldg(qn + c * 8 + i);
+          for (int i = 0; i < 16; ++i) {
+            const uint4 v = __ldg(qn + c * 16 + i);
             w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
           }
-          ptx::tmem_st_x32(lane_addr + kTmQ + c * 32, w);
+          ptx::tmem_st_x32(lane_addr + kTmQ + c * 64, w);
+          ptx::tmem_st_x32(lane_addr + kTmQ + c * 64 + 32, w + 32);
         }
         if (rank == 0) {
-          const uint4* qr = reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
-                                                           ((int64_t)row * kSfaHeads + h) * a.p.d_rope * 2);
+          const uint4* qr = q_rope(row);
           uint32_t w[32];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -392,6 +401,15 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(q_full);
+        // the next token's Q rows go to L2 now, a whole token's worth of tiles before they are read
+        int32_t nrow = row + n_clusters;
+        while (nrow < a.rows && a.nvalid[nrow] == 0) nrow += n_clusters;
+        if (nrow < a.rows) {
+          const unsigned char* nq = reinterpret_cast<const unsigned char*>(q_half(nrow));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ptx::prefetch_l2(nq + i * 128);
+          if (rank == 0) ptx::prefetch_l2(q_rope(nrow));
+        }
       }
       for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
         const long long s0 = clock64();
@@ -581,6 +599,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       const long long ce0 = clock64();
       ok = wait_w(p_empty, (n_tile & 1) ^ 1);
       if (!ok) break;
+      prof[8] += clock64() - ce0;
       ptx::tc_fence_after();
       const float inv = ntiles == 1 ? 1.f : 1.f / l;
 #pragma unroll 1
@@ -592,9 +611,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          reinterpret_cast<uint4*>(out_row)[c * 4 + i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's, so every
+        // store of a warp touches 32 different lines and the request count is what costs
+        ptx::st_global_v8(out_row + c * 64, w);
+        ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(o_free);
@@ -634,7 +654,7 @@ inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
   if (p->n1 != kSfaHeads || p->d != 512 || p->d_rope != 64) return false;
   if ((int64_t)p->sparse_count * p->sparse_block_size > kSfaMaxSlots) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->query_rope & 15u) || ((uintptr_t)p->key & 15u) ||
-      ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 15u))
+      ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 31u))
     return false;
   if (p->key_rows < 1 || p->key_rows >= (1ll << 31)) return false;
   return true;
