@@ -159,6 +159,73 @@ def make_gpu_batch(torch, seed, lens, quick):
     return b
 
 
+def decode_c5(torch, rank, world, flush, iters=5):
+    """Configuration 5 (decode): lightning_indexer then sparse_flash_attention over paged caches,
+    B=64 sequences split over the ranks, S1=2, KV lengths uniform in [16384, 65536], block 128.
+    Reported beside the headline numbers; the indexer here is bound by reading the index-K cache."""
+    from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
+    B, S1, bs, K = max(1, 64 // world), 2, 128, TOPK
+    rng = np.random.RandomState(4000 + rank)
+    lens = rng.randint(16384, 65537, size=B)
+    need = [int(-(-L // bs)) for L in lens]
+    nblk, max_blocks = sum(need), max(need)
+    perm = rng.permutation(nblk)
+    bt = np.full((B, max_blocks), -1, np.int32)
+    used = 0
+    for b in range(B):
+        bt[b, :need[b]] = perm[used:used + need[b]]
+        used += need[b]
+    g = torch.Generator(device="cuda").manual_seed(4000 + rank)
+    bf = torch.bfloat16
+
+    def randn_bf16(*shape):
+        out = torch.empty(shape, dtype=bf, device="cuda")
+        step = max(1, (1 << 26) // int(np.prod(shape[1:])))
+        for i in range(0, shape[0], step):
+            out[i:i + step] = torch.randn((min(step, shape[0] - i),) + tuple(shape[1:]), generator=g, device="cuda")
+        return out
+
+    ik, kv, kr = randn_bf16(nblk, bs, 1, LI_D), randn_bf16(nblk, bs, 1, SFA_D), randn_bf16(nblk, bs, 1, SFA_DR)
+    iq, iw = randn_bf16(B, S1, LI_HEADS, LI_D), torch.randn(B, S1, LI_HEADS, generator=g, device="cuda") / 8
+    q, qr = randn_bf16(B, S1, SFA_HEADS, SFA_D), randn_bf16(B, S1, SFA_HEADS, SFA_DR)
+    table = torch.from_numpy(bt).cuda()
+    lens_l = [int(v) for v in lens]
+    scale = 1.0 / np.sqrt(SFA_D + SFA_DR)
+
+    def li():
+        return lightning_indexer_triton(iq, ik, iw, actual_seq_lengths_key=lens_l, block_table=table,
+                                        layout_key="PA_BSND", sparse_count=K, sparse_mode=3)[0]
+
+    def sfa(idx):
+        return sparse_flash_attention_triton(q, kv, kv, idx, scale_value=scale, block_table=table,
+                                             actual_seq_lengths_kv=lens_l, query_rope=qr, key_rope=kr,
+                                             layout_kv="PA_BSND", sparse_mode=3, return_softmax_lse=True,
+                                             block_size=bs)
+
+    idx = li()
+    sfa(idx)
+    torch.cuda.synchronize()
+    t_li, t_sfa = [], []
+    for i in range(iters):
+        flush.fill_(i & 0xFF)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        idx = li()
+        e[1].record()
+        sfa(idx)
+        e[2].record()
+        torch.cuda.synchronize()
+        t_li.append(e[0].elapsed_time(e[1]))
+        t_sfa.append(e[1].elapsed_time(e[2]))
+    li_ms, sfa_ms = float(np.median(t_li)), float(np.median(t_sfa))
+    ik_bytes = float(sum(lens_l)) * LI_D * 2                     # index-K rows the indexer must read
+    gathered = float(B * S1 * K) * (SFA_D + SFA_DR) * 2          # KV rows the attention gathers
+    return {"workload": "B=%d S1=2 L~U[16384,65536] paged block 128, LI 64x128 -> top-%d -> SFA 128x(512+64)" % (B, K),
+            "li_ms": li_ms, "sfa_ms": sfa_ms, "step_ms": li_ms + sfa_ms,
+            "li_index_k_GBps": ik_bytes / (li_ms * 1e-3) / 1e9, "sfa_gather_GBps": gathered / (sfa_ms * 1e-3) / 1e9,
+            "tokens_per_s": B * S1 / ((li_ms + sfa_ms) * 1e-3) * world}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -370,6 +437,11 @@ def run_gpu(args):
         "gpu_launches": 4 * args.steps,  # li_score, top-k, sfa_compact, sfa_fwd per step
         "clocks": clocks, "wall_s": t_wall,
     }
+    if args.scale == 1 and not args.quick and not args.no_decode:
+        del host_in, out_h
+        dec = decode_c5(torch, rank, world, flush)
+        dec["step_ms"] = reduce_max(dec["step_ms"])
+        line["decode_c5"] = dec
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference(sample_s=args.cpu_seconds, procs=1, lens=lens, topk=topk)
     if rank == 0:
@@ -511,6 +583,7 @@ def main():
     ap.add_argument("--scale", type=int, default=1,
                     help="divide sequence lengths and top-k by this (profiling captures; not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the configuration-5 (paged decode) side measurement")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.quick:

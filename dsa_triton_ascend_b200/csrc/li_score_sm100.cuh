@@ -1,7 +1,9 @@
 // Lightning-indexer score kernel on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16, BSND or TND
-// layouts (not paged keys).
+// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16; BSND, TND or paged
+// keys (block size 16/32/64 or a multiple of 128: a 128-key tile is then one or a few whole-block
+// TMA loads whose rows come from the block table; an absent block loads as zeros through an
+// out-of-range row coordinate).
 //
 // GEMM orientation: KEYS sit on the MMA M axis (128 keys = 128 TMEM lanes) and (token, head)
 // pairs on the N axis (4 tokens x 64 heads = 256 columns), so that after a TMEM load every
@@ -12,7 +14,9 @@
 // tile feeds two accumulators (rows 0-3 and rows 4-7, 256 TMEM columns each), which double-buffer
 // the epilogue against the MMAs.  Tiles beyond the causal limit of the item's last row are
 // skipped; the diagonal tile is masked in the epilogue.  Items are statically spread over a
-// persistent grid in snake order of decreasing work.
+// persistent grid in snake order of decreasing work.  When there are too few row groups to fill
+// the GPU (decode: a few rows against very long key sequences) an item is a row group times a
+// chunk of key tiles, and groups of at most 4 rows use only the first accumulator.
 //
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
 // epilogue (TMEM lane quarter = warp % 4, column half = (warp - 2) / 4).
@@ -47,7 +51,11 @@ struct LiSm100Args {
   int64_t ld;
   int32_t* status;        // device status word (workspace header)
   int32_t groups_per_seq; // ceil(s1 / 8)
-  int32_t items;          // batch * groups_per_seq
+  int32_t items;          // row groups (an upper bound for TND) * nchunks
+  int32_t nchunks;        // key chunks per row group (1 = a group takes all its key tiles)
+  int32_t chunk_tiles;    // key tiles per chunk
+  int32_t sub_rows;       // key rows per TMA load: 128, or the block size of a paged cache if smaller
+  int32_t krow_oob;       // a row coordinate past the key tensor (loads as zeros)
   uint32_t idesc;
 };
 
@@ -55,14 +63,18 @@ struct LiSm100Args {
 struct LiItem {
   int32_t row0;    // first global query row (BSND: b * s1 + pos, TND: token index); -1 = no such item
   int32_t nrows;   // 1..8 rows that exist in the sequence
-  int64_t krow0;   // first key row of the sequence in the key tensor
+  int32_t b;       // sequence
+  int32_t chunk;   // key chunk
+  int64_t krow0;   // first key row of the sequence in the key tensor (not paged)
 };
 // Item i -> rows.  BSND: sequences interleaved, later row groups first (under the causal mask they
 // see more keys, so item 0 is the most work).  TND: sequences in order (their group counts are
 // only known on the device), later groups first inside each sequence.
 __device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
   LiItem it;
-  it.row0 = -1; it.nrows = 0; it.krow0 = 0;
+  it.row0 = -1; it.nrows = 0; it.krow0 = 0; it.b = 0;
+  it.chunk = i % a.nchunks;
+  i /= a.nchunks;
   const SeqDesc& s = a.p.seq;
   int32_t b, pos0, len_q, start_q;
   if (s.layout_q == DSA_LAYOUT_TND) {
@@ -85,6 +97,7 @@ __device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
   }
   it.row0 = start_q + pos0;
   it.nrows = min(kLiTok, len_q - pos0);
+  it.b = b;
   it.krow0 = row_info(s, it.row0).key_base;
   return it;
 }
@@ -93,8 +106,9 @@ __device__ __forceinline__ int32_t li_item_of(int32_t c, int32_t g, int32_t j, i
   const int32_t i = (j & 1) ? (j * g + (g - 1 - c)) : (j * g + c);
   return i < items ? i : -1;
 }
-// Visible key count of each of the item's rows and the number of key tiles to process.
-__device__ __forceinline__ int32_t li_item_tiles(const LiSm100Args& a, const LiItem& it, int32_t* vis) {
+// Visible key count of each of the item's rows and the item's key tiles [t0, t1); false if none.
+__device__ __forceinline__ bool li_item_range(const LiSm100Args& a, const LiItem& it, int32_t* vis, int32_t* t0,
+                                              int32_t* t1) {
   int32_t mx = 0;
 #pragma unroll
   for (int t = 0; t < kLiTok; ++t) {
@@ -103,7 +117,10 @@ __device__ __forceinline__ int32_t li_item_tiles(const LiSm100Args& a, const LiI
     if (vis) vis[t] = v;
     mx = max(mx, v);
   }
-  return (mx + kLiKeys - 1) / kLiKeys;
+  const int32_t tiles = (mx + kLiKeys - 1) / kLiKeys;
+  *t0 = it.chunk * a.chunk_tiles;
+  *t1 = min(tiles, *t0 + a.chunk_tiles);
+  return *t1 > *t0;
 }
 
 __global__ void __launch_bounds__(kLiThreads, 1)
@@ -151,43 +168,105 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (ptx::elect_one()) {
+    // Lane 0 issues; the other lanes only help with the block table of a paged cache (lane u looks
+    // up the u-th whole-block load of a tile, one tile ahead of its use).
+    if (lane == 0) {
       ptx::prefetch_tmap(&tmap_q);
       ptx::prefetch_tmap(&tmap_k);
-      uint32_t n_item = 0, n_tile = 0;
-      bool ok = true;
-      for (int32_t j = 0; ok; ++j) {
-        const int32_t it = li_item_of(cta, grid, j, a.items);
-        if (it < 0) break;
-        const LiItem item = li_item(a, it);
-        if (item.row0 < 0) continue;
-        const int32_t tiles = li_item_tiles(a, item, nullptr);
-        if (tiles == 0) continue;
-        ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        ptx::mbar_arrive_expect_tx(qfull, kLiQBytes);
-        const int32_t qrow = item.row0 * kLiHeads;
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-            ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
-        ++n_item;
-        const int32_t krow0 = (int32_t)item.krow0;
-        for (int32_t t = 0; t < tiles; ++t, ++n_tile) {
-          const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
-          ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
+    }
+    const SeqDesc& sq = a.p.seq;
+    const bool paged = sq.layout_k == DSA_LAYOUT_PA_BSND;
+    const int nsub = kLiKeys / a.sub_rows;
+    uint32_t n_item = 0, n_tile = 0;
+    bool ok = true;
+    if (!paged) {
+      // contiguous keys: one thread does everything
+      if (lane == 0) {
+        for (int32_t j = 0; ok; ++j) {
+          const int32_t it = li_item_of(cta, grid, j, a.items);
+          if (it < 0) break;
+          const LiItem item = li_item(a, it);
+          if (item.row0 < 0) continue;
+          int32_t t0, t1;
+          if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+          const int nh = item.nrows > kLiHalf ? 2 : 1;
+          ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
           if (!ok) break;
-          ptx::mbar_arrive_expect_tx(&full[s], kLiKStage);
-          ptx::tma_load_2d(k_s + s * kLiKStage, &tmap_k, &full[s], 0, krow0 + t * kLiKeys);
-          ptx::tma_load_2d(k_s + s * kLiKStage + kLiKBlock, &tmap_k, &full[s], 64, krow0 + t * kLiKeys);
+          ptx::mbar_arrive_expect_tx(qfull, nh * 2 * kLiQBlock);
+          const int32_t qrow = item.row0 * kLiHeads;
+          for (int h = 0; h < nh; ++h)
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+          ++n_item;
+          const int32_t krow0 = (int32_t)item.krow0;
+          for (int32_t t = t0; t < t1; ++t, ++n_tile) {
+            const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+            ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            ptx::mbar_arrive_expect_tx(&full[s], kLiKStage);
+            ptx::tma_load_2d(k_s + s * kLiKStage, &tmap_k, &full[s], 0, krow0 + t * kLiKeys);
+            ptx::tma_load_2d(k_s + s * kLiKStage + kLiKBlock, &tmap_k, &full[s], 64, krow0 + t * kLiKeys);
+          }
         }
+      }
+    } else
+    for (int32_t j = 0; ok; ++j) {
+      const int32_t it = li_item_of(cta, grid, j, a.items);
+      if (it < 0) break;
+      const LiItem item = li_item(a, it);
+      if (item.row0 < 0) continue;
+      int32_t t0, t1;
+      if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+      const int nh = item.nrows > kLiHalf ? 2 : 1;
+      if (lane == 0) {
+        ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
+        if (ok) {
+          ptx::mbar_arrive_expect_tx(qfull, nh * 2 * kLiQBlock);
+          const int32_t qrow = item.row0 * kLiHeads;
+          for (int h = 0; h < nh; ++h)
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      ++n_item;
+      // first key row of this lane's load of tile t
+      auto sub_row = [&](int32_t t) -> int32_t {
+        const int32_t p = t * kLiKeys + lane * a.sub_rows;
+        if (!paged) return (int32_t)item.krow0 + p;
+        const int32_t bi = p / sq.block_size;
+        if (lane >= nsub || bi >= sq.max_blocks) return a.krow_oob;
+        const int32_t blk = sq.block_table[(int64_t)item.b * sq.max_blocks + bi];
+        if (blk < 0) return a.krow_oob;
+        const int64_t r = (int64_t)blk * sq.block_size + (p - bi * sq.block_size);
+        return r < (int64_t)a.krow_oob ? (int32_t)r : a.krow_oob;
+      };
+      int32_t cur = sub_row(t0);
+      for (int32_t t = t0; t < t1; ++t, ++n_tile) {
+        const int32_t nxt = (t + 1 < t1) ? sub_row(t + 1) : 0;
+        const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+        if (lane == 0) ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        if (lane == 0) ptx::mbar_arrive_expect_tx(&full[s], kLiKStage);
+        for (int u = 0; u < nsub; ++u) {
+          const int32_t r = __shfl_sync(0xffffffffu, cur, u);
+          if (lane == 0) {
+            unsigned char* dst = k_s + s * kLiKStage + u * a.sub_rows * 128;
+            ptx::tma_load_2d(dst, &tmap_k, &full[s], 0, r);
+            ptx::tma_load_2d(dst + kLiKBlock, &tmap_k, &full[s], 64, r);
+          }
+        }
+        cur = nxt;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      uint32_t n_item = 0, n_tile = 0;
+      uint32_t n_item = 0, n_tile = 0, n_h1 = 0;
       bool ok = true;
       const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s);
       for (int32_t j = 0; ok; ++j) {
@@ -195,18 +274,21 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (it < 0) break;
         const LiItem item = li_item(a, it);
         if (item.row0 < 0) continue;
-        const int32_t tiles = li_item_tiles(a, item, nullptr);
-        if (tiles == 0) continue;
+        int32_t t0, t1;
+        if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+        const int nh = item.nrows > kLiHalf ? 2 : 1;
         ok = ptx::mbar_wait(qfull, n_item & 1, abort_flag);
         if (!ok) break;
         ++n_item;
-        for (int32_t t = 0; t < tiles && ok; ++t, ++n_tile) {
+        for (int32_t t = t0; t < t1 && ok; ++t, ++n_tile) {
           const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
           ok = ptx::mbar_wait(&full[s], use & 1, abort_flag);
           if (!ok) break;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            ok = ptx::mbar_wait(&tempty[h], (n_tile & 1) ^ 1, abort_flag);
+            if (h >= nh) break;
+            // uses of accumulator 1 are counted separately: items of up to 4 rows skip it
+            ok = ptx::mbar_wait(&tempty[h], ((h ? n_h1 : n_tile) & 1) ^ 1, abort_flag);
             if (!ok) break;
             ptx::tc_fence_after();
 #pragma unroll
@@ -218,6 +300,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             ptx::mma_commit(&tfull[h]);
           }
           if (!ok) break;
+          if (nh == 2) ++n_h1;
           ptx::mma_commit(&empty[s]);
         }
         if (ok) ptx::mma_commit(qempty);
@@ -229,7 +312,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int quarter = warp & 3;
     const int chalf = ew >> 2;
     const int et = threadIdx.x - 64;  // 0..255
-    uint32_t n_tile = 0, n_sync = 0;
+    uint32_t n_tile = 0, n_h1 = 0, n_sync = 0;
     bool ok = true;
     for (int32_t j = 0; ok; ++j) {
       const int32_t it = li_item_of(cta, grid, j, a.items);
@@ -237,8 +320,9 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       int32_t vis[kLiTok];
       const LiItem item = li_item(a, it);
       if (item.row0 < 0) continue;
-      const int32_t tiles = li_item_tiles(a, item, vis);
-      if (tiles == 0) continue;
+      int32_t t0, t1;
+      if (!li_item_range(a, item, vis, &t0, &t1)) continue;
+      const int nh = item.nrows > kLiHalf ? 2 : 1;
       const int32_t row0 = item.row0;
       // weights of the item's 8 rows -> shared memory (rows past the sequence end read as zero)
       // (rendezvous through an mbarrier so that even this wait is bounded)
@@ -253,13 +337,17 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       ptx::mbar_arrive(wbar);
       ok = ptx::mbar_wait(wbar, n_sync++ & 1, abort_flag);
       if (!ok) break;
-      for (int32_t t = 0; t < tiles && ok; ++t, ++n_tile) {
+      for (int32_t t = t0; t < t1 && ok; ++t, ++n_tile) {
         const int32_t pos = t * kLiKeys + quarter * 32 + lane;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          ok = ptx::mbar_wait(&tfull[h], n_tile & 1, abort_flag);
+          if (h >= nh) break;
+          ok = ptx::mbar_wait(&tfull[h], (h ? n_h1 : n_tile) & 1, abort_flag);
           if (!ok) break;
           ptx::tc_fence_after();
+          const int tok0 = h * kLiHalf + chalf * 2;
+          // (rows that do not exist are computed as well and dropped by the `vis` test below: making
+          // the loads conditional cost the full-size case 45 %)
           uint32_t r0[64], r1[64];
           const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + h * 256 + chalf * 128;
           ptx::tmem_ld_x32(taddr, r0);
@@ -271,7 +359,6 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&tempty[h]);
-          const int tok0 = h * kLiHalf + chalf * 2;
           const float* w0 = w_s + tok0 * kLiHeads;
           const float* w1 = w0 + kLiHeads;
           float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
@@ -285,6 +372,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           if (pos < vis[tok0]) a.scores[(int64_t)(row0 + tok0) * a.ld + pos] = s0a + s0b + 0.f;
           if (pos < vis[tok0 + 1]) a.scores[(int64_t)(row0 + tok0 + 1) * a.ld + pos] = s1a + s1b + 0.f;
         }
+        if (nh == 2) ++n_h1;
       }
     }
   }
@@ -307,7 +395,12 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
 // Host side: eligibility, tensor maps, launch.
 inline bool li_sm100_eligible(const DsaLiParams* p) {
-  if (p->layout_k == DSA_LAYOUT_PA_BSND) return false;   // paged keys are not contiguous per sequence
+  if (p->layout_k == DSA_LAYOUT_PA_BSND) {
+    // a 128-key tile must be whole blocks, or lie inside one
+    const int bs = p->block_size;
+    if (!(bs == 16 || bs == 32 || bs == 64 || (bs >= 128 && bs % 128 == 0))) return false;
+    if (p->block_table == nullptr || p->max_blocks < 1) return false;
+  }
   if (p->n1 != kLiHeads || p->n2 != 1 || p->d != kLiDim) return false;
   if (p->s1 < 1 || p->s2 < 1) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->key & 15u)) return false;
@@ -335,7 +428,9 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   const bool tnd = p->layout_q == DSA_LAYOUT_TND;
   const uint64_t qrows = tnd ? (uint64_t)p->s1 : (uint64_t)p->batch * p->s1;
   if (!make_tmap_2d_16bit(&tq, p->query, qrows * kLiHeads, kLiDim, kLiDim * 2, 256, 64, bf16)) return DSA_ERR_CUDA;
-  if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->key_rows, kLiDim, kLiDim * 2, kLiKeys, 64, bf16))
+  const bool paged = p->layout_k == DSA_LAYOUT_PA_BSND;
+  const int sub_rows = (paged && p->block_size < kLiKeys) ? p->block_size : kLiKeys;
+  if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->key_rows, kLiDim, kLiDim * 2, sub_rows, 64, bf16))
     return DSA_ERR_CUDA;
   LiSm100Args a;
   a.p = d;
@@ -345,7 +440,21 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   a.groups_per_seq = (p->s1 + kLiTok - 1) / kLiTok;
   // TND: the group count of a sequence is only known on the device; this is an upper bound and
   // li_item() reports the surplus as empty
-  a.items = tnd ? (p->s1 + kLiTok - 1) / kLiTok + p->batch : p->batch * a.groups_per_seq;
+  const int32_t groups = tnd ? (p->s1 + kLiTok - 1) / kLiTok + p->batch : p->batch * a.groups_per_seq;
+  // few row groups (decode): split each group's key tiles into chunks so that every SM gets work
+  const int64_t keys_max = paged ? (int64_t)p->max_blocks * p->block_size : (int64_t)p->s2;
+  const int32_t tiles_max = (int32_t)((keys_max + kLiKeys - 1) / kLiKeys);
+  a.nchunks = 1;
+  a.chunk_tiles = tiles_max > 0 ? tiles_max : 1;
+  if (groups < 2 * sm_count[dev] && tiles_max > 1) {
+    int32_t want = (4 * sm_count[dev] + groups - 1) / groups;
+    if (want > tiles_max) want = tiles_max;
+    a.chunk_tiles = (tiles_max + want - 1) / want;
+    a.nchunks = (tiles_max + a.chunk_tiles - 1) / a.chunk_tiles;
+  }
+  a.items = groups * a.nchunks;
+  a.sub_rows = sub_rows;
+  a.krow_oob = (int32_t)p->key_rows;
   a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
   const int grid = a.items < sm_count[dev] ? a.items : sm_count[dev];
   li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);

@@ -51,6 +51,21 @@ def row_slices(act_q: int, act_k: int, world: int, cap: int = 0, align: int = 8)
     return [(bounds[i], bounds[i + 1]) for i in range(world)]
 
 
+def sequence_shards(kv_lengths: Sequence[int], world: int) -> List[List[int]]:
+    """Decode: whole sequences per rank (each rank holds its own sequences' paged cache).  The
+    indexer reads every cached key of a sequence, so sequences are dealt out longest first to the
+    rank with the least cached keys so far; each rank's list is returned in ascending order."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    shards: List[List[int]] = [[] for _ in range(world)]
+    load = [0] * world
+    for b in sorted(range(len(kv_lengths)), key=lambda i: (-int(kv_lengths[i]), i)):
+        r = min(range(world), key=lambda i: (load[i], len(shards[i]), i))
+        shards[r].append(b)
+        load[r] += int(kv_lengths[b])
+    return [sorted(x) for x in shards]
+
+
 def slice_lengths(act_q: int, act_k: int, r0: int, r1: int) -> Tuple[int, int]:
     """(act_q', act_k') that make rows [r0, r1) a stand-alone problem (see module docstring)."""
     if not (0 <= r0 <= r1 <= act_q):

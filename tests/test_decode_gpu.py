@@ -65,3 +65,80 @@ def test_paged_decode_indexer_then_attention():
     sfa_acceptance_rule(host(out)[sel[:, 0], sel[:, 1]], host(smax)[sel[:, 0], 0, sel[:, 1]],
                         host(ssum)[sel[:, 0], 0, sel[:, 1]], ref[0][sel[:, 0], sel[:, 1]],
                         ref[1][sel[:, 0], 0, sel[:, 1]], ref[2][sel[:, 0], 0, sel[:, 1]])
+
+
+def test_config5_full_size_sampled_sequences():
+    """Configuration 5 at its full size (B=64, S1=2, KV lengths uniform in [16384, 65536], block 128,
+    block table = random permutation): properties on every row, the oracle on three sequences."""
+    from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
+    B, S1, bs, K = 64, 2, 128, 2048
+    rng = np.random.RandomState(4)
+    lens = rng.randint(16384, 65537, size=B)
+    need = [int(-(-L // bs)) for L in lens]
+    max_blocks = max(need)
+    nblk = sum(need)
+    perm = rng.permutation(nblk)
+    bt = np.full((B, max_blocks), -1, np.int32)
+    used = 0
+    for b in range(B):
+        bt[b, :need[b]] = perm[used:used + need[b]]
+        used += need[b]
+    g = torch.Generator(device="cuda").manual_seed(4)
+    bf = torch.bfloat16
+
+    def randn_bf16(*shape):   # in pieces: the fp32 staging of a whole cache would double its footprint
+        out = torch.empty(shape, dtype=bf, device="cuda")
+        step = max(1, (1 << 26) // int(np.prod(shape[1:])))
+        for i in range(0, shape[0], step):
+            out[i:i + step] = torch.randn((min(step, shape[0] - i),) + tuple(shape[1:]), generator=g, device="cuda")
+        return out
+
+    ik_cache = randn_bf16(nblk, bs, 1, 128)
+    kv_cache = randn_bf16(nblk, bs, 1, 512)
+    kr_cache = randn_bf16(nblk, bs, 1, 64)
+    iq = randn_bf16(B, S1, 64, 128)
+    iw = torch.randn(B, S1, 64, generator=g, device="cuda") / 8
+    q = randn_bf16(B, S1, 128, 512)
+    qr = randn_bf16(B, S1, 128, 64)
+    table = torch.from_numpy(bt).cuda()
+    lens_l = [int(v) for v in lens]
+    scale = 1.0 / np.sqrt(576.0)
+
+    idx, val = lightning_indexer_triton(iq, ik_cache, iw, actual_seq_lengths_key=lens_l, block_table=table,
+                                        layout_key="PA_BSND", sparse_count=K, sparse_mode=3, return_value=True)
+    out, smax, ssum = sparse_flash_attention_triton(
+        q, kv_cache, kv_cache, idx, scale_value=scale, block_table=table, actual_seq_lengths_kv=lens_l,
+        query_rope=qr, key_rope=kr_cache, layout_kv="PA_BSND", sparse_mode=3, return_softmax_lse=True,
+        block_size=bs)
+    torch.cuda.synchronize()
+
+    # every row: 2048 distinct positions inside the causal window, values descending, sum >= 1
+    lens_t = torch.tensor(lens_l, device="cuda")
+    limit = (lens_t[:, None] - S1 + torch.arange(S1, device="cuda")[None, :] + 1)[:, :, None, None]
+    assert bool((idx >= 0).all()) and bool((idx < limit).all())
+    srt = torch.sort(idx[:, :, 0], dim=-1).values
+    assert bool((srt[..., 1:] != srt[..., :-1]).all())
+    v = val[:, :, 0].float()
+    assert bool((v[..., 1:] <= v[..., :-1]).all())
+    assert bool(torch.isfinite(out.float()).all()) and bool((ssum >= 1.0 - 1e-5).all())
+
+    # three sequences against the oracle on their un-paged caches
+    pick = [0, int(np.argmax(lens)), B - 1]
+    S2 = max_blocks * bs
+    sub_bt = np.full((len(pick), max_blocks), -1, np.int32)
+    blocks = []
+    for i, b in enumerate(pick):
+        sub_bt[i, :need[b]] = np.arange(len(blocks), len(blocks) + need[b])
+        blocks.extend(bt[b, :need[b]].tolist())
+    sel = torch.tensor(blocks, device="cuda")
+    ik = layouts.pa_to_bsnd(host(ik_cache[sel]), sub_bt, S2)
+    lens_p = [lens_l[b] for b in pick]
+    ref_i, ref_v = lightning_indexer_oracle(host(iq[pick]), ik, host(iw[pick]), [S1] * len(pick), lens_p,
+                                            sparse_count=K, sparse_mode=3, return_value=True)
+    li_reference_rule(host(idx[pick]), host(val[pick]), ref_i, ref_v)
+    assert (host(idx[pick]) == ref_i).mean() >= 0.99
+    kv = layouts.pa_to_bsnd(host(kv_cache[sel]), sub_bt, S2)
+    kr = layouts.pa_to_bsnd(host(kr_cache[sel]), sub_bt, S2)
+    ref = sparse_flash_attention_oracle(host(q[pick]), kv, host(idx[pick]), host(qr[pick]), kr, scale,
+                                        [S1] * len(pick), lens_p, sparse_mode=3, dtype="bf16")
+    sfa_acceptance_rule(host(out[pick]), host(smax[pick]), host(ssum[pick]), ref[0], ref[1], ref[2])

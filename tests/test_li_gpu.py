@@ -134,6 +134,51 @@ def test_li_paged_key_matches_unpaged_oracle():
     assert (host(idx) == ref_i).all(axis=(2, 3)).mean() >= 0.97
 
 
+@pytest.mark.parametrize("bs", [16, 64, 128, 256])
+def test_li_paged_key_on_the_tensor_core_path(bs):
+    """64 heads x 128 dims over a paged cache runs the tcgen05 kernel: a 128-key tile is 128/bs
+    whole-block loads (or part of one block), rows come from the block table, and a block that is
+    absent inside the valid length reads as zeros like the reference's un-paging."""
+    li = _li()
+    from dsa_triton_ascend_b200 import _cabi
+    rng = np.random.RandomState(60 + bs)
+    B, S1, N1, D, K = 3, 2, 64, 128, 256
+    lens_k = [1500, 700, 2300]
+    max_blocks = -(-max(lens_k) // bs) + 1
+    need = [-(-L // bs) for L in lens_k]
+    nblk = sum(need) + 5
+    from oracle.inputs import round_io
+    cache = round_io(rng.randn(nblk, bs, 1, D).astype(np.float32), "bf16")
+    q = round_io(rng.randn(B, S1, N1, D).astype(np.float32), "bf16")
+    w = (rng.randn(B, S1, N1) / 8).astype(np.float32)
+    perm = rng.permutation(nblk)
+    bt = np.full((B, max_blocks), -1, dtype=np.int32)
+    used = 0
+    for b in range(B):
+        bt[b, :need[b]] = perm[used:used + need[b]]
+        used += need[b]
+    bt[2, 3] = -1                       # a hole inside sequence 2
+    dense = layouts.pa_to_bsnd(cache, bt, max_blocks * bs)
+    ref_i, ref_v = lightning_indexer_oracle(q, dense, w, [S1] * B, lens_k, sparse_count=K, sparse_mode=3,
+                                            return_value=True)
+    args = (dev(q, torch.bfloat16), dev(cache, torch.bfloat16), dev(w))
+    kw = dict(actual_seq_lengths_key=lens_k, block_table=torch.from_numpy(bt).cuda(), layout_key="PA_BSND",
+              sparse_count=K, sparse_mode=3, return_value=True)
+    li.set_kernel("tensor")
+    try:
+        idx, val = li.lightning_indexer_triton(*args, **kw)
+    finally:
+        li.set_kernel("auto")
+    li_reference_rule(host(idx), host(val), ref_i, ref_v)
+    assert (host(idx) == ref_i).mean() >= 0.99
+    li.set_kernel("portable")
+    try:
+        idx_p, val_p = li.lightning_indexer_triton(*args, **kw)
+    finally:
+        li.set_kernel("auto")
+    assert (host(idx) == host(idx_p)).mean() >= 0.99
+
+
 def test_li_is_bitwise_repeatable_and_ordered():
     """No atomics on the data path: two runs agree bit for bit; values come out descending and
     the indices of a row are distinct, inside the causal window and front-packed."""

@@ -73,3 +73,19 @@ def test_two_gloo_ranks_reproduce_the_full_problem(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "ok").exists()
+
+
+def test_sequence_shards_cover_and_balance():
+    """Decode sharding: every sequence on exactly one rank, cached keys per rank nearly equal."""
+    from dsa_triton_ascend_b200.sharding import sequence_shards
+    rng = np.random.RandomState(4)
+    lens = rng.randint(16384, 65537, size=64)
+    for world in (1, 2, 4, 8):
+        shards = sequence_shards(lens, world)
+        assert sorted(b for s in shards for b in s) == list(range(64))
+        loads = [int(lens[s].sum()) for s in shards]
+        assert max(loads) - min(loads) <= 65536
+        assert all(len(s) == 64 // world for s in shards) or world == 1 or max(loads) / min(loads) < 1.05
+    assert sequence_shards([5, 1], 4) == [[0], [1], [], []]
+    with pytest.raises(ValueError):
+        sequence_shards([1], 0)
