@@ -32,7 +32,8 @@ constexpr int kLiHalf = 4;       // query rows per accumulator
 constexpr int kLiHeads = 64;
 constexpr int kLiDim = 128;
 constexpr int kLiKeys = 128;     // keys per tile
-constexpr int kLiStages = 3;
+constexpr int kLiStages = 3;      // key stages behind the 128 KB of Q
+constexpr int kLiMaxStages = 5;   // two more in the unused half of the Q buffer when no item has more than 4 rows
 constexpr int kLiThreads = 320;
 constexpr int kLiEpiWarps = 8;
 
@@ -43,7 +44,11 @@ constexpr uint32_t kLiKStage = 2 * kLiKBlock;             // 32 KB
 constexpr uint32_t kLiOffK = kLiQBytes;
 constexpr uint32_t kLiOffW = kLiOffK + kLiStages * kLiKStage;
 constexpr uint32_t kLiOffBar = kLiOffW + kLiTok * kLiHeads * 4;
-constexpr uint32_t kLiSmemBytes = kLiOffBar + 128;
+constexpr uint32_t kLiSmemBytes = kLiOffBar + 256;
+// Byte offset of key stage s: stages 3 and 4 live in the second half of the Q buffer.
+__host__ __device__ constexpr uint32_t li_stage_off(uint32_t s) {
+  return s < (uint32_t)kLiStages ? kLiOffK + s * kLiKStage : 2 * kLiQBlock + (s - kLiStages) * kLiKStage;
+}
 
 struct LiSm100Args {
   LiDev p;
@@ -51,12 +56,15 @@ struct LiSm100Args {
   int64_t ld;
   int32_t* status;        // device status word (workspace header)
   int32_t groups_per_seq; // ceil(s1 / 8)
-  int32_t items;          // row groups (an upper bound for TND) * nchunks
+  int32_t groups;         // row groups (an upper bound for TND)
+  int32_t items;          // groups * nchunks
   int32_t nchunks;        // key chunks per row group (1 = a group takes all its key tiles)
   int32_t chunk_tiles;    // key tiles per chunk
+  int32_t stages;         // key stages in use: 3, or 5 when no row group has more than 4 rows
   int32_t sub_rows;       // key rows per TMA load: 128, or the block size of a paged cache if smaller
   int32_t krow_oob;       // a row coordinate past the key tensor (loads as zeros)
-  uint32_t idesc;
+  uint32_t idesc;         // M=128, N=256: four rows per accumulator
+  uint32_t idesc_n128;    // M=128, N=128: row groups of at most two rows
 };
 
 // One work item: up to 8 consecutive query rows of one sequence.
@@ -73,8 +81,10 @@ struct LiItem {
 __device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
   LiItem it;
   it.row0 = -1; it.nrows = 0; it.krow0 = 0; it.b = 0;
-  it.chunk = i % a.nchunks;
-  i /= a.nchunks;
+  // chunk-major: the first chunks exist for every sequence, later ones only for the long sequences,
+  // so work decreases with the item number as the snake order assumes
+  it.chunk = i / a.groups;
+  i -= it.chunk * a.groups;
   const SeqDesc& s = a.p.seq;
   int32_t b, pos0, len_q, start_q;
   if (s.layout_q == DSA_LAYOUT_TND) {
@@ -128,18 +138,17 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                       const LiSm100Args a) {
   extern __shared__ __align__(1024) unsigned char li_smem[];
   unsigned char* q_s = li_smem;
-  unsigned char* k_s = li_smem + kLiOffK;
   float* w_s = reinterpret_cast<float*>(li_smem + kLiOffW);
   uint64_t* bars = reinterpret_cast<uint64_t*>(li_smem + kLiOffBar);
-  uint64_t* full = bars;            // [3] TMA -> MMA
-  uint64_t* empty = bars + 3;       // [3] MMA -> TMA
-  uint64_t* qfull = bars + 6;
-  uint64_t* qempty = bars + 7;
-  uint64_t* tfull = bars + 8;       // [2] MMA -> epilogue
-  uint64_t* tempty = bars + 10;     // [2] epilogue -> MMA
-  uint64_t* wbar = bars + 12;       // epilogue-internal rendezvous around the weight staging
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
+  uint64_t* full = bars;            // [5] TMA -> MMA
+  uint64_t* empty = bars + 5;       // [5] MMA -> TMA
+  uint64_t* qfull = bars + 10;
+  uint64_t* qempty = bars + 11;
+  uint64_t* tfull = bars + 12;      // [2] MMA -> epilogue
+  uint64_t* tempty = bars + 14;     // [2] epilogue -> MMA
+  uint64_t* wbar = bars + 16;       // epilogue-internal rendezvous around the weight staging
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 18);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t cta = blockIdx.x, grid = gridDim.x;
@@ -149,7 +158,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     return;
   }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 3; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < kLiMaxStages; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     ptx::mbar_init(qfull, 1);
     ptx::mbar_init(qempty, 1);
     for (int i = 0; i < 2; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kLiEpiWarps); }
@@ -177,7 +186,8 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const SeqDesc& sq = a.p.seq;
     const bool paged = sq.layout_k == DSA_LAYOUT_PA_BSND;
     const int nsub = kLiKeys / a.sub_rows;
-    uint32_t n_item = 0, n_tile = 0;
+    uint32_t n_item = 0, s = 0, use = 0;   // ring position: stage and how often the ring went round
+    const uint32_t stages = a.stages;
     bool ok = true;
     if (!paged) {
       // contiguous keys: one thread does everything
@@ -200,13 +210,14 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
               ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
           ++n_item;
           const int32_t krow0 = (int32_t)item.krow0;
-          for (int32_t t = t0; t < t1; ++t, ++n_tile) {
-            const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+          for (int32_t t = t0; t < t1; ++t) {
             ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
             if (!ok) break;
             ptx::mbar_arrive_expect_tx(&full[s], kLiKStage);
-            ptx::tma_load_2d(k_s + s * kLiKStage, &tmap_k, &full[s], 0, krow0 + t * kLiKeys);
-            ptx::tma_load_2d(k_s + s * kLiKStage + kLiKBlock, &tmap_k, &full[s], 64, krow0 + t * kLiKeys);
+            unsigned char* dst = li_smem + li_stage_off(s);
+            ptx::tma_load_2d(dst, &tmap_k, &full[s], 0, krow0 + t * kLiKeys);
+            ptx::tma_load_2d(dst + kLiKBlock, &tmap_k, &full[s], 64, krow0 + t * kLiKeys);
+            if (++s == stages) { s = 0; ++use; }
           }
         }
       }
@@ -245,9 +256,8 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         return r < (int64_t)a.krow_oob ? (int32_t)r : a.krow_oob;
       };
       int32_t cur = sub_row(t0);
-      for (int32_t t = t0; t < t1; ++t, ++n_tile) {
+      for (int32_t t = t0; t < t1; ++t) {
         const int32_t nxt = (t + 1 < t1) ? sub_row(t + 1) : 0;
-        const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
         if (lane == 0) ok = ptx::mbar_wait(&empty[s], (use & 1) ^ 1, abort_flag);
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
@@ -255,20 +265,22 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         for (int u = 0; u < nsub; ++u) {
           const int32_t r = __shfl_sync(0xffffffffu, cur, u);
           if (lane == 0) {
-            unsigned char* dst = k_s + s * kLiKStage + u * a.sub_rows * 128;
+            unsigned char* dst = li_smem + li_stage_off(s) + u * a.sub_rows * 128;
             ptx::tma_load_2d(dst, &tmap_k, &full[s], 0, r);
             ptx::tma_load_2d(dst + kLiKBlock, &tmap_k, &full[s], 64, r);
           }
         }
         cur = nxt;
+        if (++s == stages) { s = 0; ++use; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      uint32_t n_item = 0, n_tile = 0, n_h1 = 0;
+      uint32_t n_item = 0, s = 0, use = 0, n_use0 = 0, n_use1 = 0;   // ring position; uses of each accumulator
+      const uint32_t stages = a.stages;
       bool ok = true;
-      const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s);
+      const uint32_t q_addr = ptx::smem_u32(q_s), smem_base = ptx::smem_u32(li_smem);
       for (int32_t j = 0; ok; ++j) {
         const int32_t it = li_item_of(cta, grid, j, a.items);
         if (it < 0) break;
@@ -277,31 +289,36 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         int32_t t0, t1;
         if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
         const int nh = item.nrows > kLiHalf ? 2 : 1;
+        const uint32_t idesc = item.nrows <= 2 ? a.idesc_n128 : a.idesc;
         ok = ptx::mbar_wait(qfull, n_item & 1, abort_flag);
         if (!ok) break;
         ++n_item;
-        for (int32_t t = t0; t < t1 && ok; ++t, ++n_tile) {
-          const uint32_t s = n_tile % kLiStages, use = n_tile / kLiStages;
+        for (int32_t t = t0; t < t1 && ok; ++t) {
           ok = ptx::mbar_wait(&full[s], use & 1, abort_flag);
           if (!ok) break;
+          const uint32_t k_addr = smem_base + li_stage_off(s);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             if (h >= nh) break;
-            // uses of accumulator 1 are counted separately: items of up to 4 rows skip it
-            ok = ptx::mbar_wait(&tempty[h], ((h ? n_h1 : n_tile) & 1) ^ 1, abort_flag);
+            // row half h of the item goes to accumulator `acc`: a group of at most four rows has one
+            // half only and alternates between the two accumulators from tile to tile, so that its
+            // epilogue still overlaps the next tile's MMAs
+            const int acc = nh == 2 ? h : (int)(n_use0 + n_use1) & 1;
+            ok = ptx::mbar_wait(&tempty[acc], ((acc ? n_use1 : n_use0) & 1) ^ 1, abort_flag);
             if (!ok) break;
             ptx::tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < kLiDim / 16; ++ks) {
-              const uint32_t ka = k_addr + s * kLiKStage + (ks >> 2) * kLiKBlock + (ks & 3) * 32;
+              const uint32_t ka = k_addr + (ks >> 2) * kLiKBlock + (ks & 3) * 32;
               const uint32_t qa = q_addr + h * 2 * kLiQBlock + (ks >> 2) * kLiQBlock + (ks & 3) * 32;
-              ptx::mma_ss(tmem + h * 256, ptx::desc_kmajor_sw128(ka), ptx::desc_kmajor_sw128(qa), a.idesc, ks > 0);
+              ptx::mma_ss(tmem + acc * 256, ptx::desc_kmajor_sw128(ka), ptx::desc_kmajor_sw128(qa), idesc, ks > 0);
             }
-            ptx::mma_commit(&tfull[h]);
+            ptx::mma_commit(&tfull[acc]);
+            if (acc) ++n_use1; else ++n_use0;
           }
           if (!ok) break;
-          if (nh == 2) ++n_h1;
           ptx::mma_commit(&empty[s]);
+          if (++s == stages) { s = 0; ++use; }
         }
         if (ok) ptx::mma_commit(qempty);
       }
@@ -312,7 +329,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int quarter = warp & 3;
     const int chalf = ew >> 2;
     const int et = threadIdx.x - 64;  // 0..255
-    uint32_t n_tile = 0, n_h1 = 0, n_sync = 0;
+    uint32_t n_tile = 0, n_use0 = 0, n_use1 = 0, n_sync = 0;
     bool ok = true;
     for (int32_t j = 0; ok; ++j) {
       const int32_t it = li_item_of(cta, grid, j, a.items);
@@ -342,14 +359,16 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (h >= nh) break;
-          ok = ptx::mbar_wait(&tfull[h], (h ? n_h1 : n_tile) & 1, abort_flag);
+          const int acc = nh == 2 ? h : (int)(n_use0 + n_use1) & 1;   // as in the MMA issuer
+          ok = ptx::mbar_wait(&tfull[acc], (acc ? n_use1 : n_use0) & 1, abort_flag);
           if (!ok) break;
+          if (acc) ++n_use1; else ++n_use0;
           ptx::tc_fence_after();
           const int tok0 = h * kLiHalf + chalf * 2;
           // (rows that do not exist are computed as well and dropped by the `vis` test below: making
           // the loads conditional cost the full-size case 45 %)
           uint32_t r0[64], r1[64];
-          const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + h * 256 + chalf * 128;
+          const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + acc * 256 + chalf * 128;
           ptx::tmem_ld_x32(taddr, r0);
           ptx::tmem_ld_x32(taddr + 32, r0 + 32);
           ptx::tmem_ld_x32(taddr + 64, r1);
@@ -358,21 +377,24 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           // the accumulator is in registers: hand the TMEM buffer back before doing the math
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&tempty[h]);
-          const float* w0 = w_s + tok0 * kLiHeads;
-          const float* w1 = w0 + kLiHeads;
-          float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
+          if (lane == 0) ptx::mbar_arrive(&tempty[acc]);
+          // the arithmetic (not the loads above) is skipped for rows that do not exist; in decode
+          // that is half of the epilogue warps
+          if (tok0 < item.nrows) {
+            const float* w0 = w_s + tok0 * kLiHeads;
+            const float* w1 = w0 + kLiHeads;
+            float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
 #pragma unroll
-          for (int g = 0; g < kLiHeads; g += 2) {
-            s0a = fmaf(fmaxf(__uint_as_float(r0[g]), 0.f), w0[g], s0a);
-            s0b = fmaf(fmaxf(__uint_as_float(r0[g + 1]), 0.f), w0[g + 1], s0b);
-            s1a = fmaf(fmaxf(__uint_as_float(r1[g]), 0.f), w1[g], s1a);
-            s1b = fmaf(fmaxf(__uint_as_float(r1[g + 1]), 0.f), w1[g + 1], s1b);
+            for (int g = 0; g < kLiHeads; g += 2) {
+              s0a = fmaf(fmaxf(__uint_as_float(r0[g]), 0.f), w0[g], s0a);
+              s0b = fmaf(fmaxf(__uint_as_float(r0[g + 1]), 0.f), w0[g + 1], s0b);
+              s1a = fmaf(fmaxf(__uint_as_float(r1[g]), 0.f), w1[g], s1a);
+              s1b = fmaf(fmaxf(__uint_as_float(r1[g + 1]), 0.f), w1[g + 1], s1b);
+            }
+            if (pos < vis[tok0]) a.scores[(int64_t)(row0 + tok0) * a.ld + pos] = s0a + s0b + 0.f;
+            if (pos < vis[tok0 + 1]) a.scores[(int64_t)(row0 + tok0 + 1) * a.ld + pos] = s1a + s1b + 0.f;
           }
-          if (pos < vis[tok0]) a.scores[(int64_t)(row0 + tok0) * a.ld + pos] = s0a + s0b + 0.f;
-          if (pos < vis[tok0 + 1]) a.scores[(int64_t)(row0 + tok0 + 1) * a.ld + pos] = s1a + s1b + 0.f;
         }
-        if (nh == 2) ++n_h1;
       }
     }
   }
@@ -447,15 +469,21 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   a.nchunks = 1;
   a.chunk_tiles = tiles_max > 0 ? tiles_max : 1;
   if (groups < 2 * sm_count[dev] && tiles_max > 1) {
-    int32_t want = (4 * sm_count[dev] + groups - 1) / groups;
+    // static assignment: many small chunks (>= 8 tiles each) even out sequences of unequal length;
+    // about eight items per SM measured best on 64 sequences of 16K-64K keys (28 tiles per chunk)
+    int32_t want = (8 * sm_count[dev] + groups - 1) / groups;
     if (want > tiles_max) want = tiles_max;
     a.chunk_tiles = (tiles_max + want - 1) / want;
+    if (a.chunk_tiles < 8) a.chunk_tiles = tiles_max < 8 ? tiles_max : 8;
     a.nchunks = (tiles_max + a.chunk_tiles - 1) / a.chunk_tiles;
   }
+  a.groups = groups;
+  a.stages = (!tnd && p->s1 <= kLiHalf) ? kLiMaxStages : kLiStages;
   a.items = groups * a.nchunks;
   a.sub_rows = sub_rows;
   a.krow_oob = (int32_t)p->key_rows;
   a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
+  a.idesc_n128 = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 128, 0, 0);
   const int grid = a.items < sm_count[dev] ? a.items : sm_count[dev];
   li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
