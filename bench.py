@@ -425,8 +425,8 @@ def run_gpu(args):
         "roofline": {"bound": "tensor", "achieved": sfa_tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": sfa_tf / pk["bf16_tflops"],
                      # dram read + write of sfa_fwd_sm100_kernel per launch: ncu capture of the 1/4-size
-                     # workload (3840 tokens: 1.036 GB) scaled by the token count (q and out dominate)
-                     "traffic": 1.036e9 * T / 3840.0, "kernel": "sfa_fwd_sm100_kernel",
+                     # workload (3840 tokens: 1.0435 GB) scaled by the token count (q and out dominate)
+                     "traffic": 1.0435e9 * T / 3840.0, "kernel": "sfa_fwd_sm100_kernel",
                      "peak_source": pk["source"] + " (burst bf16 GEMM)"},
         "roofline_li_score": {"bound": "tensor", "achieved": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
                               "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
