@@ -76,8 +76,16 @@ struct SfaSm100Args {
   float scale_log2;  // scale * log2(e)
   int32_t is_bf16;
   long long* prof;   // optional: cycle counters of one thread per role (phase breakdown)
-  const int32_t* nvalid;    // [rows] number of participating slots (pre-pass output)
+  const int2* nvalid;       // [rows * split] per work item: .x participating slots, .y first entry in key_list (pre-pass output)
   const int32_t* key_list;  // [rows, slots] their physical KV rows, front-packed
+  // Split-KV (few query rows, e.g. decode at small batch): a row's slots are cut into `split` parts
+  // of `part_keys` slots (a multiple of 64); work item v = row * split + part.  Each part leaves a
+  // normalised fp32 partial output with its own maximum and sum, merged by sfa_merge_kernel.
+  int32_t split, part_keys;
+  int32_t items;            // rows * split
+  float* part_o;            // [items, 128, 512] fp32 (split > 1)
+  float* part_m;            // [items, 128] maximum of the scaled scores of the part (natural log units)
+  float* part_l;            // [items, 128] sum of exp(score - maximum); 0 marks an empty part
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -96,8 +104,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
 
 // Pre-pass: one warp per query row.  Writes the physical KV rows of the slots that take part, in
 // slot order, and their count.  A slot whose paged block is absent does not take part here.
-__global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int32_t* __restrict__ nvalid,
-                                                          int32_t* __restrict__ key_list) {
+__global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __restrict__ nvalid,
+                                                          int32_t* __restrict__ key_list, int32_t split,
+                                                          int32_t part_keys) {
   const int lane = threadIdx.x & 31;
   const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -119,9 +128,15 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int32_t* __r
       n += __popc(m);
     }
   }
-  if (lane == 0) nvalid[row] = n;
+  // the row's list is cut into `split` consecutive parts of `part_keys` entries
+  if (lane < split)
+    nvalid[(int64_t)row * split + lane] =
+        make_int2(max(0, min(part_keys, n - lane * part_keys)), (int32_t)((int64_t)row * slots + lane * part_keys));
 }
 
+// kSplit: work items are parts of rows (split-KV) and leave fp32 partials; compiled apart so that the
+// prefill instantiation carries none of it.
+template <bool kSplit>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSfaThreads, 1)
 sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_constant__ CUtensorMap tmap_kr,
                      const SfaSm100Args a) {
@@ -189,7 +204,6 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   // 512 threads start with 128 registers each; every role branch below first trades registers:
   // the softmax warps need more, everyone else less (whole warpgroups of 4 warps change together).
 
-  const int32_t slots = a.p.sparse_count * a.p.sparse_block_size;
   const int32_t n1d = kSfaHeads * a.p.d;
 
   if (warp < kSfaSendWarp0) {
@@ -214,27 +228,27 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     if (lane == 0) { ptx::prefetch_tmap(&tmap_kn); ptx::prefetch_tmap(&tmap_kr); }
     // The row numbers of a tile come from global memory (the pre-pass list); they are fetched one
     // tile ahead so that their latency never sits between a freed stage and the gather.
-    struct TilePos { int32_t row, t, ntiles, nvalid; };
-    auto first_from = [&](int32_t row) -> TilePos {
-      for (; row < a.rows; row += n_clusters) {
-        const int32_t nv = a.nvalid[row];
-        if (nv > 0) return TilePos{row, 0, (nv + kSfaBK - 1) / kSfaBK, nv};
+    struct TilePos { int32_t row, t, ntiles, nvalid, off; };
+    auto first_from = [&](int32_t row) -> TilePos {   // `row` counts work items here
+      for (; row < a.items; row += n_clusters) {
+        const int2 d = a.nvalid[row];
+        if (d.x > 0) return TilePos{row, 0, (d.x + kSfaBK - 1) / kSfaBK, d.x, d.y};
       }
-      return TilePos{a.rows, 0, 0, 0};
+      return TilePos{a.items, 0, 0, 0, 0};
     };
     auto load_rows = [&](const TilePos& tp, int32_t* r) {
-      const int32_t* list = a.key_list + (int64_t)tp.row * slots;
+      const int32_t* list = a.key_list + tp.off;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int32_t k = tp.t * kSfaBK + grp * 4 + i;
         // keys past the end of the row re-read the tile's first key
-        r[i] = (active && tp.row < a.rows) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
+        r[i] = (active && tp.row < a.items) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
       }
     };
     TilePos cur = first_from(cluster_id);
     int32_t rc[4], rn[4];
     load_rows(cur, rc);
-    while (cur.row < a.rows && ok) {
+    while (cur.row < a.items && ok) {
       TilePos nxt = cur;
       if (++nxt.t >= nxt.ntiles) nxt = first_from(cur.row + n_clusters);
       load_rows(nxt, rn);
@@ -267,8 +281,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     bool ok = true;
     long long mprof[4] = {0, 0, 0, 0};
     const uint32_t kv_addr = ptx::smem_u32(kv_s);
-    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const int32_t nvalid = a.nvalid[row];
+    for (int32_t row = cluster_id; row < a.items && ok; row += n_clusters) {   // work items
+      const int32_t nvalid = a.nvalid[row].x;
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
       if (ntiles == 0) continue;
       if (lane == 0) {
@@ -305,8 +319,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     bool ok = true;
     long long wait_p = 0;
     const uint32_t kv_addr = ptx::smem_u32(kv_s);
-    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const int32_t nvalid = a.nvalid[row];
+    for (int32_t row = cluster_id; row < a.items && ok; row += n_clusters) {   // work items
+      const int32_t nvalid = a.nvalid[row].x;
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
       if (ntiles == 0) continue;
       if (lane == 0) {
@@ -365,10 +379,11 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
                                             ((int64_t)r * kSfaHeads + h) * a.p.d_rope * 2);
     };
-    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const int32_t nvalid = a.nvalid[row];
+    for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+      const int32_t nvalid = a.nvalid[item].x;
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
       if (ntiles == 0) continue;
+      const int32_t row = kSplit ? item / a.split : item;   // the query row of this work item
       // ---- this token's Q half -> tensor memory (bf16 pairs, row h in lane h)
       ok = wait_w(q_empty, (n_tok & 1) ^ 1);
       if (!ok) break;
@@ -402,9 +417,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ptx::tc_fence_before();
         ptx::mbar_arrive(q_full);
         // the next token's Q rows go to L2 now, a whole token's worth of tiles before they are read
-        int32_t nrow = row + n_clusters;
-        while (nrow < a.rows && a.nvalid[nrow] == 0) nrow += n_clusters;
-        if (nrow < a.rows) {
+        int32_t nitem = item + n_clusters;
+        while (nitem < a.items && a.nvalid[nitem].x == 0) nitem += n_clusters;
+        if (nitem < a.items) {
+          const int32_t nrow = kSplit ? nitem / a.split : nitem;
           const unsigned char* nq = reinterpret_cast<const unsigned char*>(q_half(nrow));
 #pragma unroll
           for (int i = 0; i < 4; ++i) ptx::prefetch_l2(nq + i * 128);
@@ -476,17 +492,25 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
     };
-    for (int32_t row = cluster_id; row < a.rows && ok; row += n_clusters) {
-      const int32_t nvalid = a.nvalid[row];
+    for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+      const int32_t nvalid = a.nvalid[item].x;
       const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+      const int32_t row = kSplit ? item / a.split : item;
       unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
+      float* part_row = kSplit ? a.part_o + ((int64_t)item * kSfaHeads + h) * (2 * kSfaDvHalf) + rank * kSfaDvHalf
+                                    : nullptr;
       if (ntiles == 0) {
-        // nothing visible: zeros in all three outputs
+        if constexpr (kSplit) {
+          // an empty part: the merge skips it
+          if (rank == 0) { a.part_m[(int64_t)item * kSfaHeads + h] = 0.f; a.part_l[(int64_t)item * kSfaHeads + h] = 0.f; }
+        } else {
+          // nothing visible: zeros in all three outputs
 #pragma unroll
-        for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
-        if (rank == 0 && a.p.return_lse) {
-          a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
-          a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
+          for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+          if (rank == 0 && a.p.return_lse) {
+            a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
+            a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
+          }
         }
         continue;
       }
@@ -607,19 +631,33 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         uint32_t o[32];
         ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
         ptx::tmem_ld_wait();
-        uint32_t w[16];
+        if constexpr (kSplit) {
+          // split-KV: the normalised partial output stays fp32 for the merge
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
-        // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's, so every
-        // store of a warp touches 32 different lines and the request count is what costs
-        ptx::st_global_v8(out_row + c * 64, w);
-        ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(part_row + c * 32)[i] =
+                make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                            __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+        } else {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
+          // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's, so every
+          // store of a warp touches 32 different lines and the request count is what costs
+          ptx::st_global_v8(out_row + c * 64, w);
+          ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
+        }
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(o_free);
       prof[7] += clock64() - ce0;
-      if (rank == 0 && a.p.return_lse) {
+      if constexpr (kSplit) {
+        if (rank == 0) {
+          a.part_m[(int64_t)item * kSfaHeads + h] = m_true * 0.6931471805599453f;
+          a.part_l[(int64_t)item * kSfaHeads + h] = l * ex2(m_ref - m_true);
+        }
+      } else if (rank == 0 && a.p.return_lse) {
         // max of the scaled scores and sum of exp(score - max), back from the log2 domain
         a.p.softmax_max[(int64_t)row * kSfaHeads + h] = m_true * 0.6931471805599453f;
         a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = l * ex2(m_ref - m_true);
@@ -657,14 +695,86 @@ inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
       ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 31u))
     return false;
   if (p->key_rows < 1 || p->key_rows >= (1ll << 31)) return false;
+  const int64_t rows_ = p->layout_q == DSA_LAYOUT_TND ? p->s1 : (int64_t)p->batch * p->s1;
+  if (rows_ * p->sparse_count * p->sparse_block_size >= (1ll << 31)) return false;   // key_list offsets are int32
   return true;
 }
 
-// Workspace beyond the header: nvalid[rows] then key_list[rows * slots].
+// Merge of the split-KV partials: one CTA per query row and group of 8 heads, thread = 4 output
+// columns of one head at a time.  out = sum_p w_p O_p / sum_p w_p with w_p = l_p exp(m_p - max_p m_p); empty parts have l = 0.
+__global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split, const float* __restrict__ part_o,
+                                                        const float* __restrict__ part_m,
+                                                        const float* __restrict__ part_l, int32_t is_bf16) {
+  const int32_t row = blockIdx.x;
+  // blockIdx.y: group of 8 heads
+  for (int32_t e = threadIdx.x; e < 8 * (2 * kSfaDvHalf / 4); e += 256) {
+    const int32_t h = blockIdx.y * 8 + e / (2 * kSfaDvHalf / 4), c4 = e % (2 * kSfaDvHalf / 4);
+    float mx = -INFINITY;
+    for (int32_t q = 0; q < split; ++q) {
+      const int64_t i = ((int64_t)row * split + q) * kSfaHeads + h;
+      if (part_l[i] > 0.f) mx = fmaxf(mx, part_m[i]);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (int32_t q = 0; q < split; ++q) {
+      const int64_t i = ((int64_t)row * split + q) * kSfaHeads + h;
+      const float l = part_l[i];
+      if (l > 0.f) {
+        const float w = l * __expf(part_m[i] - mx);
+        const float4 o = reinterpret_cast<const float4*>(part_o + i * (2 * kSfaDvHalf))[c4];
+        acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+        den += w;
+      }
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    uint2 packed;
+    packed.x = pack2(acc.x * inv, acc.y * inv, is_bf16);
+    packed.y = pack2(acc.z * inv, acc.w * inv, is_bf16);
+    reinterpret_cast<uint2*>((unsigned char*)p.out + ((int64_t)row * kSfaHeads + h) * (2 * kSfaDvHalf) * 2)[c4] = packed;
+    if (c4 == 0 && p.return_lse) {
+      p.softmax_max[(int64_t)row * kSfaHeads + h] = den > 0.f ? mx : 0.f;
+      p.softmax_sum[(int64_t)row * kSfaHeads + h] = den;
+    }
+  }
+}
+
+// Split factor: only when there are too few query rows to give every CTA pair one (decode at small
+// batch); at least four 64-key tiles per part.  74 CTA pairs are assumed here (the answer must not
+// depend on the device, the workspace size is derived from it); any other count is still correct.
+inline int32_t sfa_sm100_split(int64_t rows, int64_t slots) {
+  const int64_t pairs = 74;
+  if (rows < 1 || rows * 2 > pairs) return 1;
+  int64_t s = pairs / rows;
+  const int64_t tiles = (slots + kSfaBK - 1) / kSfaBK;
+  if (s > tiles / 4) s = tiles / 4;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : (int32_t)s;
+}
+inline int32_t sfa_sm100_part_keys(int64_t slots, int32_t split) {
+  const int64_t tiles = (slots + kSfaBK - 1) / kSfaBK;
+  return (int32_t)(((tiles + split - 1) / split) * kSfaBK);
+}
+
+// Workspace beyond the header: nvalid[rows * split], key_list[rows * slots], and for split > 1 the
+// partial maxima, sums and outputs.
+struct SfaWsLayout { size_t nvalid, key_list, part_m, part_l, part_o, total; };
+inline SfaWsLayout sfa_sm100_ws_layout(int64_t rows, int64_t slots) {
+  const int32_t split = sfa_sm100_split(rows, slots);
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  SfaWsLayout w;
+  w.nvalid = 0;
+  w.key_list = up((size_t)rows * split * 8);
+  w.part_m = w.key_list + up((size_t)rows * slots * 4);
+  const size_t stats = split > 1 ? up((size_t)rows * split * kSfaHeads * 4) : 0;
+  w.part_l = w.part_m + stats;
+  w.part_o = w.part_l + stats;
+  w.total = w.part_o + (split > 1 ? (size_t)rows * split * kSfaHeads * 2 * kSfaDvHalf * 4 : 0);
+  return w;
+}
 inline size_t sfa_sm100_workspace_bytes(const DsaSfaParams* p) {
   const int64_t rows = p->layout_q == DSA_LAYOUT_TND ? p->s1 : (int64_t)p->batch * p->s1;
   const int64_t slots = (int64_t)p->sparse_count * p->sparse_block_size;
-  return (size_t)(((rows * 4 + 255) / 256) * 256 + rows * slots * 4);
+  return sfa_sm100_ws_layout(rows, slots).total;
 }
 
 inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* status, void* scratch, cudaStream_t st) {
@@ -674,15 +784,21 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   if (sm_count[dev] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 2) return DSA_ERR_CUDA;
-    if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSfaSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSfaSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(sfa_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSfaSmemBytes) != cudaSuccess)
       return DSA_ERR_CUDA;
     sm_count[dev] = n;
   }
   const bool bf16 = p->dtype == DSA_DTYPE_BF16;
-  int32_t* nvalid = reinterpret_cast<int32_t*>(scratch);
-  int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + (((int64_t)d.rows * 4 + 255) / 256) * 256);
-  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list);
+  const int64_t slots = (int64_t)p->sparse_count * p->sparse_block_size;
+  const SfaWsLayout w = sfa_sm100_ws_layout(d.rows, slots);
+  const int32_t split = sfa_sm100_split(d.rows, slots);
+  const int32_t part_keys = split > 1 ? sfa_sm100_part_keys(slots, split) : (int32_t)((slots + kSfaBK - 1) / kSfaBK) * kSfaBK;
+  int2* nvalid = reinterpret_cast<int2*>((char*)scratch + w.nvalid);
+  int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + w.key_list);
+  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   SfaSm100Args a;
   a.p = d;
@@ -695,13 +811,24 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.prof = getenv("DSA_SFA_PROFILE") ? reinterpret_cast<long long*>(status + 16) : nullptr;
   a.nvalid = nvalid;
   a.key_list = key_list;
+  a.split = split;
+  a.part_keys = part_keys;
+  a.items = d.rows * split;
+  a.part_m = reinterpret_cast<float*>((char*)scratch + w.part_m);
+  a.part_l = reinterpret_cast<float*>((char*)scratch + w.part_l);
+  a.part_o = reinterpret_cast<float*>((char*)scratch + w.part_o);
   int clusters = sm_count[dev] / 2;
-  if (clusters > d.rows) clusters = d.rows;
+  if (clusters > a.items) clusters = a.items;
   CUtensorMap tkn, tkr;
   if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;
   if (!make_tmap_gather4_16bit(&tkr, p->key_rope, (uint64_t)p->key_rows, 64, 128, 64, bf16)) return DSA_ERR_CUDA;
-  sfa_fwd_sm100_kernel<<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
+  if (split > 1) sfa_fwd_sm100_kernel<true><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
+  else sfa_fwd_sm100_kernel<false><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  if (split > 1) {
+    sfa_merge_kernel<<<dim3(d.rows, kSfaHeads / 8), 256, 0, st>>>(d, split, a.part_o, a.part_m, a.part_l, a.is_bf16);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  }
   return DSA_OK;
 }
 

@@ -292,3 +292,49 @@ def test_sfa_full_mode_on_the_tensor_core_path():
         actual_seq_lengths_kv=[350], query_rope=dev(qr, dt), key_rope=dev(kr, dt), sparse_mode=0,
         return_softmax_lse=True)
     _compare(*(host(t) for t in got), *ref, "bf16")
+
+
+@pytest.mark.parametrize("B,S1,S2,K", [(1, 2, 5000, 2048), (4, 2, 3000, 1024), (1, 6, 700, 512), (2, 1, 9000, 2048)])
+def test_sfa_split_kv_for_few_rows_matches_oracle(B, S1, S2, K):
+    """Decode at small batch: with fewer query rows than CTA pairs a row's selected keys are cut into
+    parts that run on different pairs and are merged afterwards.  Covers rows whose last parts are
+    empty (short sequences), a -1 hole, and the statistics of the merged result."""
+    sfa = _sfa()
+    rng = np.random.RandomState(300 + B * 10 + S1)
+    N1, D = 128, 512
+    q = round_io(rng.randn(B, S1, N1, D).astype(np.float32), "bf16")
+    k = round_io(rng.randn(B, S2, 1, D).astype(np.float32), "bf16")
+    qr = round_io(rng.randn(B, S1, N1, 64).astype(np.float32), "bf16")
+    kr = round_io(rng.randn(B, S2, 1, 64).astype(np.float32), "bf16")
+    act_k = [S2 - 37 * b for b in range(B)]
+    if B > 1:
+        act_k[-1] = 300                  # a short sequence: most of its parts are empty
+    idx = sparse_indices(301, B, S1, S2, K, 1, 3, [S1] * B, act_k)
+    scale = 1.0 / 24.0
+    ref = sparse_flash_attention_oracle(q, k, idx, qr, kr, scale, [S1] * B, act_k, sparse_mode=3, dtype="bf16")
+    dt = torch.bfloat16
+    args = (dev(q, dt), dev(k, dt), dev(k, dt), torch.from_numpy(idx).cuda())
+    kw = dict(scale_value=scale, actual_seq_lengths_kv=act_k, query_rope=dev(qr, dt), key_rope=dev(kr, dt),
+              sparse_mode=3, return_softmax_lse=True)
+    sfa.set_kernel("tensor")
+    try:
+        got = sfa.sparse_flash_attention_triton(*args, **kw)
+        again = sfa.sparse_flash_attention_triton(*args, **kw)
+    finally:
+        sfa.set_kernel("auto")
+    _compare(*(host(t) for t in got), *ref, "bf16")
+    assert all(torch.equal(x, y) for x, y in zip(got, again))
+    # the skipping semantics survive the split: punch a hole into the middle of every row
+    idx2 = idx.copy()
+    idx2[:, :, :, K // 3] = -1
+    sfa.set_kernel("tensor")
+    try:
+        got2 = sfa.sparse_flash_attention_triton(args[0], args[1], args[2], torch.from_numpy(idx2).cuda(), **kw)
+    finally:
+        sfa.set_kernel("auto")
+    sfa.set_kernel("portable")
+    try:
+        want2 = sfa.sparse_flash_attention_triton(args[0], args[1], args[2], torch.from_numpy(idx2).cuda(), **kw)
+    finally:
+        sfa.set_kernel("auto")
+    sfa_acceptance_rule(*(host(t) for t in got2), *(host(t) for t in want2))
