@@ -218,10 +218,40 @@ def decode_c5(torch, rank, world, flush, iters=5):
         t_li.append(e[0].elapsed_time(e[1]))
         t_sfa.append(e[1].elapsed_time(e[2]))
     li_ms, sfa_ms = float(np.median(t_li)), float(np.median(t_sfa))
+    # the same step captured once in a CUDA graph (lengths in a device tensor) and replayed
+    lens_t = torch.tensor(lens_l, dtype=torch.int32, device="cuda")
+
+    def step_dev():
+        i_ = lightning_indexer_triton(iq, ik, iw, actual_seq_lengths_key=lens_t, block_table=table,
+                                      layout_key="PA_BSND", sparse_count=K, sparse_mode=3)[0]
+        return sparse_flash_attention_triton(q, kv, kv, i_, scale_value=scale, block_table=table,
+                                             actual_seq_lengths_kv=lens_t, query_rope=qr, key_rope=kr,
+                                             layout_kv="PA_BSND", sparse_mode=3, return_softmax_lse=True,
+                                             block_size=bs)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step_dev()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            step_dev()
+    torch.cuda.current_stream().wait_stream(side)
+    t_g = []
+    for i in range(iters):
+        flush.fill_(i & 0xFF)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        e[0].record()
+        graph.replay()
+        e[1].record()
+        torch.cuda.synchronize()
+        t_g.append(e[0].elapsed_time(e[1]))
+    graph_ms = float(np.median(t_g))
     ik_bytes = float(sum(lens_l)) * LI_D * 2                     # index-K rows the indexer must read
     gathered = float(B * S1 * K) * (SFA_D + SFA_DR) * 2          # KV rows the attention gathers
     return {"workload": "B=%d S1=2 L~U[16384,65536] paged block 128, LI 64x128 -> top-%d -> SFA 128x(512+64)" % (B, K),
-            "li_ms": li_ms, "sfa_ms": sfa_ms, "step_ms": li_ms + sfa_ms,
+            "li_ms": li_ms, "sfa_ms": sfa_ms, "step_ms": li_ms + sfa_ms, "graph_replay_step_ms": graph_ms,
             "li_index_k_GBps": ik_bytes / (li_ms * 1e-3) / 1e9, "sfa_gather_GBps": gathered / (sfa_ms * 1e-3) / 1e9,
             "tokens_per_s": B * S1 / ((li_ms + sfa_ms) * 1e-3) * world}
 

@@ -142,3 +142,61 @@ def test_config5_full_size_sampled_sequences():
     ref = sparse_flash_attention_oracle(host(q[pick]), kv, host(idx[pick]), host(qr[pick]), kr, scale,
                                         [S1] * len(pick), lens_p, sparse_mode=3, dtype="bf16")
     sfa_acceptance_rule(host(out[pick]), host(smax[pick]), host(ssum[pick]), ref[0], ref[1], ref[2])
+
+
+def test_decode_step_replays_from_a_cuda_graph():
+    """The decode step (paged indexer -> paged attention) makes no host synchronisation and no
+    allocation the caching allocator cannot serve under capture, so it can be captured once and
+    replayed; with the lengths and tables in device tensors a replay follows updated inputs."""
+    from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
+    B, S1, bs, K = 4, 2, 128, 1024
+    rng = np.random.RandomState(44)
+    max_blocks, nblk = 40, 200
+    g = torch.Generator(device="cuda").manual_seed(44)
+    bf = torch.bfloat16
+    ik_cache = torch.randn(nblk, bs, 1, 128, generator=g, device="cuda").to(bf)
+    kv_cache = torch.randn(nblk, bs, 1, 512, generator=g, device="cuda").to(bf)
+    kr_cache = torch.randn(nblk, bs, 1, 64, generator=g, device="cuda").to(bf)
+    iq = torch.randn(B, S1, 64, 128, generator=g, device="cuda").to(bf)
+    iw = torch.randn(B, S1, 64, generator=g, device="cuda") / 8
+    q = torch.randn(B, S1, 128, 512, generator=g, device="cuda").to(bf)
+    qr = torch.randn(B, S1, 128, 64, generator=g, device="cuda").to(bf)
+    table = torch.from_numpy(rng.permutation(nblk)[:B * max_blocks].reshape(B, max_blocks).astype(np.int32)).cuda()
+    lens = torch.tensor([3000, 4100, 2222, 5000], dtype=torch.int32, device="cuda")
+    scale = 1.0 / np.sqrt(576.0)
+
+    def step():
+        idx, _ = lightning_indexer_triton(iq, ik_cache, iw, actual_seq_lengths_key=lens, block_table=table,
+                                          layout_key="PA_BSND", sparse_count=K, sparse_mode=3)
+        out, smax, ssum = sparse_flash_attention_triton(
+            q, kv_cache, kv_cache, idx, scale_value=scale, block_table=table, actual_seq_lengths_kv=lens,
+            query_rope=qr, key_rope=kr_cache, layout_kv="PA_BSND", sparse_mode=3, return_softmax_lse=True,
+            block_size=bs)
+        return idx, out, smax, ssum
+
+    eager = [t.clone() for t in step()]          # also the warm-up that sets the kernels' attributes
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            captured = step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(eager, captured):
+        assert torch.equal(a, b)
+    # new step: one more token per sequence, different queries; same graph
+    lens += 1
+    q.copy_(torch.randn(q.shape, generator=g, device="cuda").to(bf))
+    iq.copy_(torch.randn(iq.shape, generator=g, device="cuda").to(bf))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = [t.clone() for t in captured]
+    fresh = step()
+    torch.cuda.synchronize()
+    for a, b in zip(replayed, fresh):
+        assert torch.equal(a, b)
