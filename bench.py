@@ -437,6 +437,7 @@ def run_gpu(args):
 
     li_ms, sfa_ms, e2e_ms = reduce_max(li_ms), reduce_max(sfa_ms), reduce_max(e2e_ms)
     pk = peaks()
+    topk_bytes = float(li_flops(S)[1]) * 4.0 + float(S) * topk * 4.0
     sfa_tf = flops_sfa / (sfa_ms * 1e-3) / 1e12
     tensor_sfa = bool(getattr(run_gpu, "_sfa_tensor", False))
     line = {
@@ -461,6 +462,11 @@ def run_gpu(args):
         "roofline_li_score": {"bound": "tensor", "achieved": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
                               "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                               "frac": flops_li / (phase_ms["score"] * 1e-3) / 1e12 / pk["bf16_tflops"]},
+        # top-k: reads every visible fp32 score once, writes k int32 indices per row
+        "roofline_li_topk": {"bound": "hbm", "achieved": topk_bytes / (phase_ms["topk"] * 1e-3) / 1e9,
+                             "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": topk_bytes / (phase_ms["topk"] * 1e-3) / 1e9 / pk["hbm_gbs"],
+                             "note": "instruction-bound (ordered selection), not memory-bound"},
         "e2e": {"value": flops_sfa / (e2e_ms * 1e-3) / 1e12 * world, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "li_topk_qtok_per_s": S / (e2e_ms * 1e-3) * world},
@@ -471,6 +477,9 @@ def run_gpu(args):
         del host_in, out_h
         dec = decode_c5(torch, rank, world, flush)
         dec["step_ms"] = reduce_max(dec["step_ms"])
+        dec["roofline_li"] = {"bound": "hbm", "achieved": dec["li_index_k_GBps"], "peak": pk["hbm_gbs"],
+                              "unit": "GB/s", "frac": dec["li_index_k_GBps"] / pk["hbm_gbs"],
+                              "note": "index-K cache bytes / indexer time (score + top-k)"}
         line["decode_c5"] = dec
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference(sample_s=args.cpu_seconds, procs=1, lens=lens, topk=topk)
