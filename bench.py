@@ -435,6 +435,16 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # per-rank device times and clocks (the headline uses the slowest rank)
+    per_rank = None
+    if world > 1:
+        mine = torch.tensor([li_ms, sfa_ms, e2e_ms, float(clocks.get("sm_mhz") or 0.0),
+                             float(len(clocks.get("reasons") or []))], dtype=torch.float64, device="cuda")
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        per_rank = {"li_ms": [float(t[0]) for t in allr], "sfa_ms": [float(t[1]) for t in allr],
+                    "e2e_ms": [float(t[2]) for t in allr], "sm_mhz": [float(t[3]) for t in allr],
+                    "throttle_reasons": [int(t[4]) for t in allr]}
     li_ms, sfa_ms, e2e_ms = reduce_max(li_ms), reduce_max(sfa_ms), reduce_max(e2e_ms)
     pk = peaks()
     topk_bytes = float(li_flops(S)[1]) * 4.0 + float(S) * topk * 4.0
@@ -473,6 +483,8 @@ def run_gpu(args):
         "gpu_launches": 4 * args.steps,  # li_score, top-k, sfa_compact, sfa_fwd per step
         "clocks": clocks, "wall_s": t_wall,
     }
+    if per_rank is not None:
+        line["per_rank"] = per_rank
     if args.scale == 1 and not args.quick and not args.no_decode:
         del host_in, out_h
         dec = decode_c5(torch, rank, world, flush)

@@ -47,8 +47,18 @@
 namespace dsa {
 
 constexpr int kSfaHeads = 128;
-constexpr int kSfaBK = 64;         // keys per tile
-constexpr int kSfaStages = 4;
+// Tile size and ring depth (64 keys x 4 stages measured best: 48 keys x 5 stages, which also fits
+// the 227 KB of shared memory, was 18 % slower - the cost of a tile is mostly fixed).
+#ifndef DSA_SFA_BK
+#define DSA_SFA_BK 64
+#endif
+#ifndef DSA_SFA_STAGES
+#define DSA_SFA_STAGES 4
+#endif
+constexpr int kSfaBK = DSA_SFA_BK;      // keys per tile (a multiple of 16)
+constexpr int kSfaStages = DSA_SFA_STAGES;
+constexpr int kSfaHalf = kSfaBK / 2;   // the scores of a tile travel in two halves
+static_assert(kSfaBK % 16 == 0 && kSfaBK <= 64 && kSfaHalf % 8 == 0, "tile size");
 constexpr int kSfaThreads = 640;
 constexpr int kSfaProducerWarps = 10;
 constexpr int kSfaMmaWarp = 10;
@@ -57,13 +67,17 @@ constexpr int kSfaSoftWarp0 = 16;    // warps 16..19: softmax + epilogue
 constexpr int kSfaDvHalf = 256;
 constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
 
-constexpr uint32_t kSfaBlk = kSfaBK * 128;                 // one 64-column block of a stage: 64 rows x 128 B
-constexpr uint32_t kSfaStage = 5 * kSfaBlk;                // 40 KB (rank 1 uses 4 of the 5 blocks)
-constexpr uint32_t kSfaOffX = kSfaStages * kSfaStage;      // 160 KB
-constexpr uint32_t kSfaXBytes = kSfaHeads * kSfaBK * 4;    // 32 KB
+constexpr uint32_t kSfaBlk = kSfaBK * 128;                 // one 64-column block of a stage: BK rows x 128 B
+constexpr uint32_t kSfaStage = 5 * kSfaBlk;                // (rank 1 uses 4 of the 5 blocks)
+constexpr uint32_t kSfaOffX = kSfaStages * kSfaStage;
+constexpr uint32_t kSfaXBytes = kSfaHeads * kSfaBK * 4;    // partial scores of a tile, fp32
+constexpr uint32_t kSfaXHalfF = kSfaHeads * kSfaHalf;      // floats of one half (all heads)
+constexpr uint32_t kSfaXWarpF = 32 * kSfaHalf;             // floats of one warp's part of a half
+static_assert(kSfaStage % 1024 == 0, "stage alignment");
 constexpr uint32_t kSfaOffStage = kSfaOffX + kSfaXBytes;  // outgoing copy of this CTA's partial S
 constexpr uint32_t kSfaOffBar = kSfaOffStage + kSfaXBytes;
 constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 256;
+static_assert(kSfaSmemBytes <= 232448, "shared memory");
 
 constexpr uint32_t kTmO = 0, kTmQ = 256, kTmS = 416, kTmP = 480;
 constexpr float kSfaRescaleTau = 8.f;  // log2 units: the running reference only moves when exceeded by this
@@ -145,24 +159,25 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   float* x_s = reinterpret_cast<float*>(sfa_sm + kSfaOffX);
   float* xo_s = reinterpret_cast<float*>(sfa_sm + kSfaOffStage);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
-  uint64_t* kv_full = bars;         // [4] gather -> MMA
-  uint64_t* kv_empty = bars + 4;    // [4] MMA (PV done) -> gather
-  uint64_t* q_full = bars + 8;      // softmax warps (Q stored in TMEM) -> MMA
-  uint64_t* q_empty = bars + 9;     // MMA (last QK of the token done) -> softmax warps
-  uint64_t* s_full = bars + 10;     // MMA -> softmax
-  uint64_t* s_empty = bars + 11;    // softmax (S in registers) -> MMA
-  uint64_t* p_full = bars + 12;     // softmax (P stored, O rescaled) -> MMA
-  uint64_t* p_empty = bars + 13;    // MMA (PV done) -> softmax
-  uint64_t* o_free = bars + 14;     // epilogue (O read out) -> MMA
+  uint64_t* kv_full = bars;                   // [stages] gather -> MMA
+  uint64_t* kv_empty = bars + kSfaStages;     // [stages] MMA (PV done) -> gather
+  uint64_t* q_full = bars + 2 * kSfaStages;   // softmax warps (Q stored in TMEM) -> MMA
+  uint64_t* q_empty = q_full + 1;   // MMA (last QK of the token done) -> softmax warps
+  uint64_t* s_full = q_full + 2;    // MMA -> softmax
+  uint64_t* s_empty = q_full + 3;   // softmax (S in registers) -> MMA
+  uint64_t* p_full = q_full + 4;    // softmax (P stored, O rescaled) -> MMA
+  uint64_t* p_empty = q_full + 5;   // MMA (PV done) -> softmax
+  uint64_t* o_free = q_full + 6;    // epilogue (O read out) -> MMA
   // The partial scores of a tile travel in two halves (keys 0..31 and 32..63), each with its own
   // 16 KB staging and landing buffer and its own barriers, so that the next tile's first half can be
   // on its way while the softmax warps still work on the current tile.
-  uint64_t* x_full = bars + 15;     // [2] peer's partial S has landed (transaction bytes)
-  uint64_t* x_empty = bars + 17;    // [2] peer has consumed what this CTA sent (remote arrivals)
-  uint64_t* own_full = bars + 19;   // [2] senders: own partial is in the staging buffer -> softmax
-  uint64_t* own_free = bars + 21;   // [2] softmax has read the staging buffer -> senders
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 24);
+  uint64_t* x_full = q_full + 7;    // [2] peer's partial S has landed (transaction bytes)
+  uint64_t* x_empty = q_full + 9;   // [2] peer has consumed what this CTA sent (remote arrivals)
+  uint64_t* own_full = q_full + 11; // [2] senders: own partial is in the staging buffer -> softmax
+  uint64_t* own_free = q_full + 13; // [2] softmax has read the staging buffer -> senders
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(q_full + 16);
+  static_assert((2 * kSfaStages + 17) * 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -219,7 +234,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     uint32_t n_tile = 0;
     bool ok = true;
     long long pprof[4] = {0, 0, 0, 0};
-    const int nops = 16 * nblk;
+    const int nops = (kSfaBK / 4) * nblk;
     const int o = warp + kSfaProducerWarps * lane;     // this lane's load of every tile
     const int grp = o / nblk, blk = o - grp * nblk;     // row group, column block
     const bool active = o < nops;
@@ -433,15 +448,16 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         if (!ok) break;
         sprof[0] += clock64() - s0;
         ptx::tc_fence_after();
-        float sv[kSfaBK];
+        float sv[64];   // kSfaBK of them are scores
         ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sv));
-        ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+        if (kSfaBK > 48) ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+        else if (kSfaBK > 32) ptx::tmem_ld_x16(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
         ptx::tmem_ld_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(s_empty);
         // a staging half is free once the peer has consumed what was copied out of it and the
-        // local softmax warps have read it (half hf: 4 KB per warp, 16-byte chunk c of a lane at
-        // w * 4096 + c * 512 + lane * 16)
+        // local softmax warps have read it (half hf: kSfaXWarpF floats per warp, 16-byte chunk c of
+        // a lane at c * 512 + lane * 16 inside the warp's part)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const long long s1 = clock64();
@@ -452,17 +468,17 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           if (!ok) break;
           sprof[1] += s2 - s1; sprof[2] += clock64() - s2;
           if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&x_full[hf], kSfaXBytes / 2);  // arm my landing half
-          float* mine = xo_s + hf * 4096 + quarter * 1024 + lane * 4;
+          float* mine = xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
 #pragma unroll
           for (int c = 0; c < kSfaBK / 8; ++c) {
-            const int k = hf * 32 + 4 * c;
+            const int k = hf * kSfaHalf + 4 * c;
             *reinterpret_cast<float4*>(mine + c * 128) = make_float4(sv[k], sv[k + 1], sv[k + 2], sv[k + 3]);
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            ptx::bulk_copy_to_peer(x_peer + hf * 16384 + quarter * 4096, xo_s + hf * 4096 + quarter * 1024, 4096,
-                                   x_full_peer + hf * 8);
+            ptx::bulk_copy_to_peer(x_peer + (hf * kSfaXHalfF + quarter * kSfaXWarpF) * 4,
+                                   xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF, kSfaXWarpF * 4, x_full_peer + hf * 8);
             ptx::mbar_arrive(&own_full[hf]);
           }
         }
@@ -529,14 +545,14 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           ok = wait_w(&own_full[hf], n_tile & 1);
           if (!ok) break;
           if (hf == 0) c1 = clock64();
-          const float* theirs = x_s + hf * 4096 + quarter * 1024 + lane * 4;
-          const float* mine = xo_s + hf * 4096 + quarter * 1024 + lane * 4;
+          const float* theirs = x_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
+          const float* mine = xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
           float dep = 0.f;
 #pragma unroll
           for (int c = 0; c < kSfaBK / 8; ++c) {
             const float4 v = *reinterpret_cast<const float4*>(theirs + c * 128);
             const float4 o = *reinterpret_cast<const float4*>(mine + c * 128);
-            const int k = hf * 32 + 4 * c;
+            const int k = hf * kSfaHalf + 4 * c;
             sc[k] = v.x + o.x; sc[k + 1] = v.y + o.y; sc[k + 2] = v.z + o.z; sc[k + 3] = v.w + o.w;
             dep += sc[k] + sc[k + 1] + sc[k + 2] + sc[k + 3];
           }
@@ -609,7 +625,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         {
           uint32_t pw[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pw[i] = pack2(sc[2 * i], sc[2 * i + 1], a.is_bf16);
+          for (int i = 0; i < 32; ++i) pw[i] = i < kSfaBK / 2 ? pack2(sc[2 * i], sc[2 * i + 1], a.is_bf16) : 0u;
           ptx::tmem_st_x32(lane_addr + kTmP, pw);
         }
         ptx::tmem_st_wait();
