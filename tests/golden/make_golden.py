@@ -72,4 +72,6 @@ def _row_mask(shape, sel):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of WhFanatic/dsa_triton_ascend>")
+    main(sys.argv[1])
