@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
   __shared__ uint32_t sh_digit, sh_below, sh_cnt, sh_count;
 
   const int tid = threadIdx.x;
+  const uint32_t lt = (1u << (tid & 31)) - 1u;
   const int32_t rown = blockIdx.x;
   const int32_t row = rown / p.n2;
   const RowInfo ri = row_info(p.seq, row);
@@ -86,6 +87,23 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
     __syncthreads();
   }
   auto key_at = [&](int i) -> uint32_t { return cached ? kcache[i] : rank_key<T, kRank16>(s[i]); };
+  // keys of positions i..i+3 (i a multiple of 4; rows start 16-byte aligned); 0 past the end of the
+  // row (real keys are >= 1)
+  auto keys4_at = [&](int i, uint32_t* k4) {
+    if (i + 3 < n) {
+      if (cached) {
+        const uint4 v = *reinterpret_cast<const uint4*>(kcache + i);
+        k4[0] = v.x; k4[1] = v.y; k4[2] = v.z; k4[3] = v.w;
+      } else {
+        const float4 v = *reinterpret_cast<const float4*>(s + i);
+        k4[0] = rank_key<T, kRank16>(v.x); k4[1] = rank_key<T, kRank16>(v.y);
+        k4[2] = rank_key<T, kRank16>(v.z); k4[3] = rank_key<T, kRank16>(v.w);
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) k4[u] = i + u < n ? key_at(i + u) : 0u;
+    }
+  };
 
   uint32_t thr_key = 0, pos_limit = 0xFFFFFFFFu;
   if (n > K) {
@@ -97,9 +115,15 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
       const int shift = byte * 8;
       if (tid < 256) hist[tid] = 0;
       __syncthreads();
-      for (int i = tid; i < n; i += kTopkThreads) {
-        uint32_t key = key_at(i);
-        if ((key & mask) == prefix) atomicAdd(&hist[255 - ((key >> shift) & 255u)], 1u);
+      // 2 x 4 keys per thread in flight (16-byte loads): long rows are not cached in shared memory,
+      // and one 4-byte dependent load per iteration leaves the pass bound by memory latency
+      for (int i0 = 0; i0 < n; i0 += 8 * kTopkThreads) {
+        uint32_t key[8];
+        keys4_at(i0 + 4 * tid, key);
+        keys4_at(i0 + 4 * kTopkThreads + 4 * tid, key + 4);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (key[u] != 0u && (key[u] & mask) == prefix) atomicAdd(&hist[255 - ((key[u] >> shift) & 255u)], 1u);
       }
       __syncthreads();
       uint32_t cnt = tid < 256 ? hist[tid] : 0;
@@ -124,9 +148,15 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
         const int shift = byte * 8;
         if (tid < 256) hist[tid] = 0;
         __syncthreads();
-        for (int i = tid; i < n; i += kTopkThreads) {
-          if (((uint32_t)i & pmask) == pprefix && key_at(i) == thr_key)
-            atomicAdd(&hist[((uint32_t)i >> shift) & 255u], 1u);
+        for (int i0 = 0; i0 < n; i0 += 8 * kTopkThreads) {
+          uint32_t key[8];
+          keys4_at(i0 + 4 * tid, key);
+          keys4_at(i0 + 4 * kTopkThreads + 4 * tid, key + 4);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t i = (uint32_t)(i0 + (u >> 2) * 4 * kTopkThreads + 4 * tid + (u & 3));
+            if (key[u] == thr_key && (i & pmask) == pprefix) atomicAdd(&hist[(i >> shift) & 255u], 1u);
+          }
         }
         __syncthreads();
         uint32_t cnt = tid < 256 ? hist[tid] : 0;
@@ -147,11 +177,24 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_kernel(LiDev p, const fl
   // ---- compact the survivors as (key, ~position) composites; all composites are distinct
   if (tid == 0) sh_count = 0;
   __syncthreads();
-  for (int i = tid; i < n; i += kTopkThreads) {
-    uint32_t key = key_at(i);
-    if (key > thr_key || (key == thr_key && (uint32_t)i <= pos_limit)) {
-      uint32_t slot = atomicAdd(&sh_count, 1u);
-      if (slot < (uint32_t)sort_cap) sbuf[slot] = ((uint64_t)key << 32) | (uint64_t)(0xFFFFFFFFu - (uint32_t)i);
+  for (int i0 = 0; i0 < n; i0 += 8 * kTopkThreads) {
+    // 2 x 4 keys per thread in flight; one shared-memory add per warp and key slot (the order
+    // inside the buffer does not matter: it is sorted below)
+    uint32_t key[8];
+    keys4_at(i0 + 4 * tid, key);
+    keys4_at(i0 + 4 * kTopkThreads + 4 * tid, key + 4);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + (u >> 2) * 4 * kTopkThreads + 4 * tid + (u & 3);
+      const bool keep = key[u] != 0u && (key[u] > thr_key || (key[u] == thr_key && (uint32_t)i <= pos_limit));
+      const uint32_t km = __ballot_sync(0xffffffffu, keep);
+      uint32_t base = 0;
+      if ((tid & 31) == 0 && km) base = atomicAdd(&sh_count, (uint32_t)__popc(km));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (keep) {
+        const uint32_t slot = base + __popc(km & lt);
+        if (slot < (uint32_t)sort_cap) sbuf[slot] = ((uint64_t)key[u] << 32) | (uint64_t)(0xFFFFFFFFu - (uint32_t)i);
+      }
     }
   }
   int32_t p2 = 1;
