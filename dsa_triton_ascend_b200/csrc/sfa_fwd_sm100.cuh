@@ -1,5 +1,8 @@
 // Sparse flash attention forward on tcgen05 tensor cores for the MLA-absorb production shape:
 // 128 query heads, D = 512 (+64 rope), one KV head, any layout, token- or block-wise indices.
+// 16..127 heads (a tensor-parallel shard of the 128) run the same code with the spare accumulator
+// lanes carrying zero queries; few query rows (decode at small batch) are split along their keys
+// into parts whose partial results a small kernel merges.
 //
 // Why a 2-CTA cluster per query token.  One token's accumulator O[128 heads x 512] in fp32 is the
 // whole tensor memory of an SM (128 lanes x 512 columns) and its Q[128 x 576] is 147 KB of shared
@@ -219,7 +222,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   // 512 threads start with 128 registers each; every role branch below first trades registers:
   // the softmax warps need more, everyone else less (whole warpgroups of 4 warps change together).
 
-  const int32_t n1d = kSfaHeads * a.p.d;
+  const int32_t n1 = a.p.n1;                   // real heads (<= 128); lanes past them carry zero queries
+  const int32_t n1d = n1 * a.p.d;
 
   if (warp < kSfaSendWarp0) {
    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
@@ -392,7 +396,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     };
     auto q_rope = [&](int32_t r) -> const uint4* {
       return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
-                                            ((int64_t)r * kSfaHeads + h) * a.p.d_rope * 2);
+                                            ((int64_t)r * n1 + h) * a.p.d_rope * 2);
     };
     for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
       const int32_t nvalid = a.nvalid[item].x;
@@ -412,7 +416,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           uint32_t w[64];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const uint4 v = __ldg(qn + c * 16 + i);
+            const uint4 v = h < n1 ? __ldg(qn + c * 16 + i) : make_uint4(0, 0, 0, 0);
             w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
           }
           ptx::tmem_st_x32(lane_addr + kTmQ + c * 64, w);
@@ -423,7 +427,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           uint32_t w[32];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const uint4 v = __ldg(qr + i);
+            const uint4 v = h < n1 ? __ldg(qr + i) : make_uint4(0, 0, 0, 0);
             w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
           }
           ptx::tmem_st_x32(lane_addr + kTmQ + 128, w);
@@ -434,7 +438,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         // the next token's Q rows go to L2 now, a whole token's worth of tiles before they are read
         int32_t nitem = item + n_clusters;
         while (nitem < a.items && a.nvalid[nitem].x == 0) nitem += n_clusters;
-        if (nitem < a.items) {
+        if (nitem < a.items && h < n1) {
           const int32_t nrow = kSplit ? nitem / a.split : nitem;
           const unsigned char* nq = reinterpret_cast<const unsigned char*>(q_half(nrow));
 #pragma unroll
@@ -521,11 +525,13 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           if (rank == 0) { a.part_m[(int64_t)item * kSfaHeads + h] = 0.f; a.part_l[(int64_t)item * kSfaHeads + h] = 0.f; }
         } else {
           // nothing visible: zeros in all three outputs
+          if (h < n1) {
 #pragma unroll
-          for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
-          if (rank == 0 && a.p.return_lse) {
-            a.p.softmax_max[(int64_t)row * kSfaHeads + h] = 0.f;
-            a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = 0.f;
+            for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+            if (rank == 0 && a.p.return_lse) {
+              a.p.softmax_max[(int64_t)row * n1 + h] = 0.f;
+              a.p.softmax_sum[(int64_t)row * n1 + h] = 0.f;
+            }
           }
         }
         continue;
@@ -661,8 +667,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
           // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's, so every
           // store of a warp touches 32 different lines and the request count is what costs
-          ptx::st_global_v8(out_row + c * 64, w);
-          ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
+          if (h < n1) {
+            ptx::st_global_v8(out_row + c * 64, w);
+            ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
+          }
         }
       }
       ptx::tc_fence_before();
@@ -673,10 +681,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           a.part_m[(int64_t)item * kSfaHeads + h] = m_true * 0.6931471805599453f;
           a.part_l[(int64_t)item * kSfaHeads + h] = l * ex2(m_ref - m_true);
         }
-      } else if (rank == 0 && a.p.return_lse) {
+      } else if (rank == 0 && a.p.return_lse && h < n1) {
         // max of the scaled scores and sum of exp(score - max), back from the log2 domain
-        a.p.softmax_max[(int64_t)row * kSfaHeads + h] = m_true * 0.6931471805599453f;
-        a.p.softmax_sum[(int64_t)row * kSfaHeads + h] = l * ex2(m_ref - m_true);
+        a.p.softmax_max[(int64_t)row * n1 + h] = m_true * 0.6931471805599453f;
+        a.p.softmax_sum[(int64_t)row * n1 + h] = l * ex2(m_ref - m_true);
       }
     }
     if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
@@ -705,7 +713,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 
 // ---- host side ---------------------------------------------------------------------------------
 inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
-  if (p->n1 != kSfaHeads || p->d != 512 || p->d_rope != 64) return false;
+  // fewer than 128 heads (a tensor-parallel shard) run with the spare lanes carrying zero queries;
+  // below 16 heads the portable kernel wastes less
+  if (p->n1 < 16 || p->n1 > kSfaHeads || p->d != 512 || p->d_rope != 64) return false;
   if ((int64_t)p->sparse_count * p->sparse_block_size > kSfaMaxSlots) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->query_rope & 15u) || ((uintptr_t)p->key & 15u) ||
       ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 31u))
@@ -725,6 +735,7 @@ __global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split,
   // blockIdx.y: group of 8 heads
   for (int32_t e = threadIdx.x; e < 8 * (2 * kSfaDvHalf / 4); e += 256) {
     const int32_t h = blockIdx.y * 8 + e / (2 * kSfaDvHalf / 4), c4 = e % (2 * kSfaDvHalf / 4);
+    if (h >= p.n1) continue;
     float mx = -INFINITY;
     for (int32_t q = 0; q < split; ++q) {
       const int64_t i = ((int64_t)row * split + q) * kSfaHeads + h;
@@ -746,10 +757,10 @@ __global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split,
     uint2 packed;
     packed.x = pack2(acc.x * inv, acc.y * inv, is_bf16);
     packed.y = pack2(acc.z * inv, acc.w * inv, is_bf16);
-    reinterpret_cast<uint2*>((unsigned char*)p.out + ((int64_t)row * kSfaHeads + h) * (2 * kSfaDvHalf) * 2)[c4] = packed;
+    reinterpret_cast<uint2*>((unsigned char*)p.out + ((int64_t)row * p.n1 + h) * (2 * kSfaDvHalf) * 2)[c4] = packed;
     if (c4 == 0 && p.return_lse) {
-      p.softmax_max[(int64_t)row * kSfaHeads + h] = den > 0.f ? mx : 0.f;
-      p.softmax_sum[(int64_t)row * kSfaHeads + h] = den;
+      p.softmax_max[(int64_t)row * p.n1 + h] = den > 0.f ? mx : 0.f;
+      p.softmax_sum[(int64_t)row * p.n1 + h] = den;
     }
   }
 }

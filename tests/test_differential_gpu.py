@@ -41,6 +41,7 @@ def test_sfa_tensor_path_equals_portable_on_random_problems(seed):
     layout = ("BSND", "TND", "PA_BSND")[seed % 3]
     mode = 0 if seed % 5 == 4 else 3
     B = int(rng.randint(1, 5))
+    N1 = int(rng.choice([128, 128, 64, 40, 16]))      # fewer than 128 heads: a tensor-parallel shard
     blk = int(rng.choice([1, 1, 2, 8]))
     count = int(rng.choice([24, 96, 300, 1024 // blk]))
     S1 = int(rng.choice([1, 2, 5, 40]))
@@ -64,7 +65,7 @@ def test_sfa_tensor_path_equals_portable_on_random_problems(seed):
     scale = 1.0 / 24.0
     kw = dict(scale_value=scale, sparse_block_size=blk, sparse_mode=mode, return_softmax_lse=bool(seed % 2 == 0))
     if layout == "BSND":
-        q, qr = _rand_bf16(rng, B, S1, 128, 512, dtype=dtype), _rand_bf16(rng, B, S1, 128, 64, dtype=dtype)
+        q, qr = _rand_bf16(rng, B, S1, N1, 512, dtype=dtype), _rand_bf16(rng, B, S1, N1, 64, dtype=dtype)
         k, kr = _rand_bf16(rng, B, S2, 1, 512, dtype=dtype), _rand_bf16(rng, B, S2, 1, 64, dtype=dtype)
         args = (q, k, k, torch.from_numpy(idx).cuda())
         kw.update(query_rope=qr, key_rope=kr, actual_seq_lengths_query=lens_q, actual_seq_lengths_kv=lens_k)
@@ -72,7 +73,7 @@ def test_sfa_tensor_path_equals_portable_on_random_problems(seed):
         lens_q = [max(1, v) for v in lens_q]
         lens_k = [max(lens_k[b], 1) for b in range(B)]
         T1, T2 = sum(lens_q), sum(lens_k)
-        q, qr = _rand_bf16(rng, T1, 128, 512, dtype=dtype), _rand_bf16(rng, T1, 128, 64, dtype=dtype)
+        q, qr = _rand_bf16(rng, T1, N1, 512, dtype=dtype), _rand_bf16(rng, T1, N1, 64, dtype=dtype)
         k, kr = _rand_bf16(rng, T2, 1, 512, dtype=dtype), _rand_bf16(rng, T2, 1, 64, dtype=dtype)
         flat = np.concatenate([idx[b, :lens_q[b]] for b in range(B)], axis=0)
         args = (q, k, k, torch.from_numpy(np.ascontiguousarray(flat)).cuda())
@@ -81,7 +82,7 @@ def test_sfa_tensor_path_equals_portable_on_random_problems(seed):
     else:
         bs = int(rng.choice([16, 128]))
         (kc, krc), table, _ = _paged(rng, B, lens_k, bs, (512, 64), dtype, holes=bool(seed % 2))
-        q, qr = _rand_bf16(rng, B, S1, 128, 512, dtype=dtype), _rand_bf16(rng, B, S1, 128, 64, dtype=dtype)
+        q, qr = _rand_bf16(rng, B, S1, N1, 512, dtype=dtype), _rand_bf16(rng, B, S1, N1, 64, dtype=dtype)
         args = (q, kc, kc, torch.from_numpy(idx).cuda())
         kw.update(query_rope=qr, key_rope=krc, layout_kv="PA_BSND", block_table=table, block_size=bs,
                   actual_seq_lengths_query=lens_q, actual_seq_lengths_kv=lens_k)

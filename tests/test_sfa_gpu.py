@@ -260,7 +260,8 @@ def test_sfa_tensor_path_agrees_with_portable_path_and_reports_clean_status():
 
 
 def test_sfa_portable_kernel_request_is_honoured_for_other_shapes():
-    """Shapes outside the tensor path (16 heads) refuse kernel='tensor' with a clear error."""
+    """Shapes outside the tensor path (fewer than 16 heads, other head dims) refuse kernel='tensor'
+    with a clear error."""
     sfa = _sfa()
     q, k, qr, kr, idx, act_q, act_k, scale, c = sfa_case_inputs("sfa_tiny")
     dt = torch.bfloat16
