@@ -1,6 +1,6 @@
 // Lightning-indexer score kernel on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Shape served: 64 query heads sharing one key head, head dim 128, bf16 or fp16; BSND, TND or paged
+// Shape served: 16..64 query heads sharing one key head, head dim 128, bf16 or fp16; BSND, TND or paged
 // keys (block size 16/32/64 or a multiple of 128: a 128-key tile is then one or a few whole-block
 // TMA loads whose rows come from the block table; an absent block loads as zeros through an
 // out-of-range row coordinate).
@@ -166,6 +166,12 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     *abort_flag = 0;
     ptx::mbar_fence_init();
   }
+  if (a.p.n1 != kLiHeads) {
+    // fewer than 64 heads: the spare rows of every token's slot in the Q buffer must read as zero
+    for (uint32_t i = threadIdx.x; i < kLiQBytes / 16; i += kLiThreads)
+      reinterpret_cast<uint4*>(li_smem)[i] = make_uint4(0, 0, 0, 0);
+    ptx::fence_proxy_async_smem();
+  }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
@@ -174,6 +180,28 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // Q of an item -> shared memory.  64 heads: one 256-row box per half and column block.  Fewer
+  // heads (16..63): one box of n1 rows per token into the token's 64-row slot; the slot's other
+  // rows were zeroed once at kernel start and are never written, and their weights are zero.
+  const int32_t n1 = a.p.n1;
+  auto q_bytes = [&](int nh) -> uint32_t {
+    return n1 == kLiHeads ? (uint32_t)nh * 2u * kLiQBlock : (uint32_t)nh * kLiHalf * 2u * (uint32_t)n1 * 128u;
+  };
+  auto load_q = [&](int32_t row0, int nh) {
+    if (n1 == kLiHeads) {
+      const int32_t qrow = row0 * kLiHeads;
+      for (int h = 0; h < nh; ++h)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+    } else {
+      for (int t = 0; t < nh * kLiHalf; ++t)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          ptx::tma_load_2d(q_s + ((t / kLiHalf) * 2 + c) * kLiQBlock + (t % kLiHalf) * kLiHeads * 128, &tmap_q, qfull,
+                           c * 64, (row0 + t) * n1);
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -202,12 +230,8 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const int nh = item.nrows > kLiHalf ? 2 : 1;
           ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
           if (!ok) break;
-          ptx::mbar_arrive_expect_tx(qfull, nh * 2 * kLiQBlock);
-          const int32_t qrow = item.row0 * kLiHeads;
-          for (int h = 0; h < nh; ++h)
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+          ptx::mbar_arrive_expect_tx(qfull, q_bytes(nh));
+          load_q(item.row0, nh);
           ++n_item;
           const int32_t krow0 = (int32_t)item.krow0;
           for (int32_t t = t0; t < t1; ++t) {
@@ -233,12 +257,8 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (lane == 0) {
         ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
         if (ok) {
-          ptx::mbar_arrive_expect_tx(qfull, nh * 2 * kLiQBlock);
-          const int32_t qrow = item.row0 * kLiHeads;
-          for (int h = 0; h < nh; ++h)
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              ptx::tma_load_2d(q_s + (h * 2 + c) * kLiQBlock, &tmap_q, qfull, c * 64, qrow + h * kLiHalf * kLiHeads);
+          ptx::mbar_arrive_expect_tx(qfull, q_bytes(nh));
+          load_q(item.row0, nh);
         }
       }
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -348,8 +368,8 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (!ok) break;
       for (int i = et; i < kLiTok * kLiHeads; i += 256) {
         const int t = i / kLiHeads;
-        w_s[i] = (t < item.nrows) ? load_weight(a.p.weights, a.p.dtype_w, (int64_t)(row0 + t) * kLiHeads + (i - t * kLiHeads))
-                                        : 0.f;
+        const int hh = i - t * kLiHeads;
+        w_s[i] = (t < item.nrows && hh < n1) ? load_weight(a.p.weights, a.p.dtype_w, (int64_t)(row0 + t) * n1 + hh) : 0.f;
       }
       ptx::mbar_arrive(wbar);
       ok = ptx::mbar_wait(wbar, n_sync++ & 1, abort_flag);
@@ -423,7 +443,8 @@ inline bool li_sm100_eligible(const DsaLiParams* p) {
     if (!(bs == 16 || bs == 32 || bs == 64 || (bs >= 128 && bs % 128 == 0))) return false;
     if (p->block_table == nullptr || p->max_blocks < 1) return false;
   }
-  if (p->n1 != kLiHeads || p->n2 != 1 || p->d != kLiDim) return false;
+  // 16..63 heads (a tensor-parallel shard) run with zero rows and zero weights in the spare slots
+  if (p->n1 < 16 || p->n1 > kLiHeads || p->n2 != 1 || p->d != kLiDim) return false;
   if (p->s1 < 1 || p->s2 < 1) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->key & 15u)) return false;
   const int64_t rows = p->layout_q == DSA_LAYOUT_TND ? (int64_t)p->s1 : (int64_t)p->batch * p->s1;
@@ -449,7 +470,8 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   CUtensorMap tq, tk;
   const bool tnd = p->layout_q == DSA_LAYOUT_TND;
   const uint64_t qrows = tnd ? (uint64_t)p->s1 : (uint64_t)p->batch * p->s1;
-  if (!make_tmap_2d_16bit(&tq, p->query, qrows * kLiHeads, kLiDim, kLiDim * 2, 256, 64, bf16)) return DSA_ERR_CUDA;
+  if (!make_tmap_2d_16bit(&tq, p->query, qrows * p->n1, kLiDim, kLiDim * 2, p->n1 == kLiHeads ? 256 : p->n1, 64, bf16))
+    return DSA_ERR_CUDA;
   const bool paged = p->layout_k == DSA_LAYOUT_PA_BSND;
   const int sub_rows = (paged && p->block_size < kLiKeys) ? p->block_size : kLiKeys;
   if (!make_tmap_2d_16bit(&tk, p->key, (uint64_t)p->key_rows, kLiDim, kLiDim * 2, sub_rows, 64, bf16))

@@ -109,6 +109,7 @@ def test_li_tensor_path_equals_portable_on_random_problems(seed):
     layout = ("BSND", "TND", "PA_BSND")[seed % 3]
     mode = 0 if seed % 4 == 3 else 3
     B = int(rng.randint(1, 5))
+    H = int(rng.choice([64, 64, 48, 32, 16]))         # fewer than 64 heads: a tensor-parallel shard
     S1 = int(rng.choice([1, 2, 7, 33, 130]))
     S2 = int(rng.choice([100, 900, 3000]))
     count = int(rng.choice([16, 200, 1024]))
@@ -117,20 +118,20 @@ def test_li_tensor_path_equals_portable_on_random_problems(seed):
     wdt = (torch.float32, torch.bfloat16, torch.float16)[seed % 3] if dtype == torch.bfloat16 else torch.float32
     kw = dict(sparse_count=count, sparse_mode=mode, return_value=True)
     if layout == "BSND":
-        q, k = _rand_bf16(rng, B, S1, 64, 128, dtype=dtype), _rand_bf16(rng, B, S2, 1, 128, dtype=dtype)
-        w = (torch.from_numpy(rng.randn(B, S1, 64).astype(np.float32)).cuda() / 8).to(wdt)
+        q, k = _rand_bf16(rng, B, S1, H, 128, dtype=dtype), _rand_bf16(rng, B, S2, 1, 128, dtype=dtype)
+        w = (torch.from_numpy(rng.randn(B, S1, H).astype(np.float32)).cuda() / 8).to(wdt)
         kw.update(actual_seq_lengths_query=lens_q, actual_seq_lengths_key=lens_k)
     elif layout == "TND":
         T1, T2 = sum(lens_q), sum(lens_k)
-        q, k = _rand_bf16(rng, T1, 64, 128, dtype=dtype), _rand_bf16(rng, T2, 1, 128, dtype=dtype)
-        w = (torch.from_numpy(rng.randn(T1, 64).astype(np.float32)).cuda() / 8).to(wdt)
+        q, k = _rand_bf16(rng, T1, H, 128, dtype=dtype), _rand_bf16(rng, T2, 1, 128, dtype=dtype)
+        w = (torch.from_numpy(rng.randn(T1, H).astype(np.float32)).cuda() / 8).to(wdt)
         kw.update(layout_query="TND", layout_key="TND", actual_seq_lengths_query=list(np.cumsum(lens_q)),
                   actual_seq_lengths_key=list(np.cumsum(lens_k)))
     else:
         bs = int(rng.choice([16, 32, 64, 128, 256]))
         (k,), table, _ = _paged(rng, B, lens_k, bs, (128,), dtype, holes=bool(seed % 2))
-        q = _rand_bf16(rng, B, S1, 64, 128, dtype=dtype)
-        w = (torch.from_numpy(rng.randn(B, S1, 64).astype(np.float32)).cuda() / 8).to(wdt)
+        q = _rand_bf16(rng, B, S1, H, 128, dtype=dtype)
+        w = (torch.from_numpy(rng.randn(B, S1, H).astype(np.float32)).cuda() / 8).to(wdt)
         kw.update(layout_key="PA_BSND", block_table=table, actual_seq_lengths_query=lens_q,
                   actual_seq_lengths_key=lens_k)
     out = {}
