@@ -89,3 +89,51 @@ def test_sequence_shards_cover_and_balance():
     assert sequence_shards([5, 1], 4) == [[0], [1], [], []]
     with pytest.raises(ValueError):
         sequence_shards([1], 0)
+
+
+def _decode_rank_main(rank, world, port, tmp):
+    """Decode: each rank runs indexer -> attention on its own sequences (its own paged cache in the
+    real path; the un-paged equivalent here), nothing crosses ranks but the final gather."""
+    from dsa_triton_ascend_b200.sharding import sequence_shards
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, S1, S2, N1, D, K = 5, 2, 160, 8, 128, 24
+        rng = np.random.RandomState(17)
+        lens = rng.randint(40, S2 + 1, size=B)
+        iq, ik, iw = li_inputs(18, B, S1, S2, N1, 1, D)
+        q, k, qr, kr = sfa_inputs(19, B, S1, S2, 8, 512)
+        scale = 1.0 / 24.0
+
+        def step(sel):
+            lk = [int(lens[b]) for b in sel]
+            idx, _ = lightning_indexer_oracle(iq[sel], ik[sel], iw[sel], [S1] * len(sel), lk, sparse_count=K,
+                                              sparse_mode=3, return_value=True)
+            out = sparse_flash_attention_oracle(q[sel], k[sel], idx, qr[sel], kr[sel], scale, [S1] * len(sel), lk,
+                                                sparse_mode=3, dtype="bf16")
+            return idx, out[0]
+
+        mine = sequence_shards(lens, world)[rank]
+        res = step(mine) if mine else None
+        parts = [None] * world
+        dist.all_gather_object(parts, (mine, res))
+        if rank == 0:
+            full_idx, full_out = step(list(range(B)))
+            for sel, r in parts:
+                for j, b in enumerate(sel):
+                    np.testing.assert_array_equal(r[0][j], full_idx[b])
+                    np.testing.assert_array_equal(r[1][j], full_out[b])
+            assert sorted(b for sel, _ in parts for b in sel) == list(range(B))
+            open(os.path.join(tmp, "ok_decode"), "w").write("ok")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_decode_their_own_sequences(tmp_path):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_decode_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok_decode").exists()
