@@ -3,12 +3,15 @@
 Public API = the two operators of WhFanatic/dsa_triton_ascend with unchanged signatures:
 `lightning_indexer_triton` / `LightningIndexerTriton` and `sparse_flash_attention_triton` /
 `SparseFlashAttentionTriton`.  Both are thin wrappers over the C-ABI CUDA library built from
-`dsa_triton_ascend_b200/csrc` (declared in `include/dsa_b200.h`).
+`dsa_triton_ascend_b200/csrc` (declared in `include/dsa_b200.h`).  `check_status()` (an
+addition) reports a device-side wait that ran out in the latest call of either operator.
 """
+from ._host import check_status  # noqa: F401
 from .lightning_indexer import LightningIndexerTriton, lightning_indexer_triton  # noqa: F401
 from .sparse_flash_attention import SparseFlashAttentionTriton, sparse_flash_attention_triton  # noqa: F401
 
 __all__ = [
     "lightning_indexer_triton", "LightningIndexerTriton",
     "sparse_flash_attention_triton", "SparseFlashAttentionTriton",
+    "check_status",
 ]

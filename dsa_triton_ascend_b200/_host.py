@@ -1,5 +1,7 @@
 """Host-side helpers shared by the two operator wrappers: dtype/length handling, workspace
 and stream plumbing.  torch is used for device memory and streams only."""
+import os
+
 import torch
 
 from . import _cabi
@@ -57,3 +59,29 @@ def workspace(nbytes, device):
 
 def current_stream(device):
     return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---- device status ----------------------------------------------------------------------------------
+# Every device-side wait of the tensor-core kernels is bounded; one that runs out leaves a non-zero
+# status word at the start of the call's workspace and the outputs of that call are garbage.  The
+# reference reports nothing from the device, so the operators stay asynchronous by default and
+# remember the workspace of the latest call per (operator, device): `check_status()` reads those
+# words (it synchronises) and raises.  DSA_CHECK_STATUS=1 makes every call check itself.
+_last_ws = {}
+_eager_check = os.environ.get("DSA_CHECK_STATUS", "0") not in ("", "0")
+
+
+def note_launch(op, ws, device):
+    _last_ws[(op, torch.device(device).index)] = ws
+    if _eager_check:
+        check_status()
+
+
+def check_status():
+    """Raise RuntimeError if the latest lightning_indexer / sparse_flash_attention call on any
+    device recorded a failed device-side wait.  Synchronises the streams involved."""
+    for (op, index), ws in list(_last_ws.items()):
+        with torch.cuda.device(index):
+            st = _cabi.lib.dsa_read_device_status(ws.data_ptr(), current_stream(ws.device))
+        if st != 0:
+            raise RuntimeError(f"{op} on cuda:{index}: {_cabi.status_string(st)}; the outputs of that call are invalid")

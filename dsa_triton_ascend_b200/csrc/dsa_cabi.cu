@@ -301,6 +301,13 @@ int dsa_li_forward_static(const DsaLiParams* p, void* stream) {
   return li_launch<__half>(p, scores, cs);
 }
 
+#ifdef DSA_SFA_PROFILE
+// development builds only: the attention kernel's cycle counters (128 values)
+int dsa_debug_sfa_profile(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_sfa_prof, sizeof(long long) * 128) == cudaSuccess ? DSA_OK : DSA_ERR_CUDA;
+}
+#endif
+
 int dsa_read_device_status(const void* workspace, void* stream) {
   if (!workspace) return DSA_ERR_NULL;
   int32_t word = 0;

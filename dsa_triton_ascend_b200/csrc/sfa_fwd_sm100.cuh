@@ -1,99 +1,93 @@
 // Sparse flash attention forward on tcgen05 tensor cores for the MLA-absorb production shape:
-// 128 query heads, D = 512 (+64 rope), one KV head, any layout, token- or block-wise indices.
-// 16..127 heads (a tensor-parallel shard of the 128) run the same code with the spare accumulator
-// lanes carrying zero queries; few query rows (decode at small batch) are split along their keys
-// into parts whose partial results a small kernel merges.
+// up to 128 query heads, D = 512 (+64 rope), one KV head, any layout, token- or block-wise
+// indices.  16..127 heads (a tensor-parallel shard of the 128) run the same code with the spare
+// accumulator rows carrying zero queries; few query rows (decode at small batch) are split along
+// their keys into parts whose partial results a small kernel merges.
 //
-// Why a 2-CTA cluster per query token.  One token's accumulator O[128 heads x 512] in fp32 is the
-// whole tensor memory of an SM (128 lanes x 512 columns) and its Q[128 x 576] is 147 KB of shared
-// memory, so a single SM cannot hold O, the scores and a deep enough ring of gathered KV rows.
-// The two CTAs of a cluster split the FEATURE axis instead of the heads (which would halve the MMA
-// M dimension and with it the tensor throughput):
-//     CTA 0: nope columns   0..255 + the 64 rope columns  (320 dims of QK^T, value columns   0..255)
-//     CTA 1: nope columns 256..511                         (256 dims of QK^T, value columns 256..511)
-// Each CTA gathers only its own half of every selected KV row (TMA tile::gather4 into the
-// 128-byte-swizzled MMA layout, 4-stage ring), computes a PARTIAL S = Q_c K_c^T for all 128 heads,
-// sends it to its peer through distributed shared memory, adds the peer's partial, runs the
-// softmax (both CTAs hold the same full S, so no running-max exchange is needed) and accumulates
-// O_c = P V_c with V_c = the nope columns it already holds.  Every MMA is a full-rate 128-row
-// cta_group::1 instruction, every KV byte crosses L2->SM once, and no flop is duplicated except
-// the softmax arithmetic.
+// One query token is processed by a CTA PAIR (a 2-CTA cluster) that splits the HEADS: CTA c owns
+// heads 64c..64c+63, i.e. its own rows of S = Q K^T and of O = P V, so the softmax of a row never
+// needs data from the other CTA.  Both contractions are pair MMAs (tcgen05.mma.cta_group::2,
+// M = 128 = 2 x 64 rows): each CTA feeds its own A rows and HALF of the B operand, which the
+// hardware shares between the two tensor cores.  That fixes what each CTA has to gather:
+//   S tile  [128 heads x 64 keys]  : B = K rows, split along the keys  -> CTA c gathers 32 of the
+//                                    tile's 64 keys with all 576 features  (36 KB, K-major)
+//   O       [128 heads x 512 cols] : B = V rows, split along the value columns -> CTA c gathers
+//                                    all 64 keys, columns {c*128.., 256+c*128..} (32 KB, MN-major)
+// (two N = 256 MMAs per 16-key step: the first produces value columns 0..255, the second
+// 256..511).  The two operand blocks of a CTA cannot alias: a pair MMA reads both CTAs at the SAME
+// shared-memory offsets, the score product needs identical features at an offset and the value
+// product identical keys.  Gathers are TMA tile::gather4 loads into the 128-byte-swizzled MMA
+// layout, issued by twelve producer warps from a front-packed list of physical KV rows that a
+// pre-pass kernel writes.
 //
-// Gather issue rate (measured with in-kernel cycle counters and a micro-probe on a B200): one warp
-// issues one 512-byte gather4 load per ~67 cycles (~7.5 B/clk) however its lanes are arranged, a
-// 16-byte cp.async warp instruction costs ~115 cycles (~4.4 B/clk per warp), and both scale
-// linearly with the number of issuing warps (6 warps: ~42 B/clk).  A tile's 80 loads issued from a
-// single warp took ~6100 cycles against ~1150 cycles of MMA work, so the loads of every tile are
-// spread over ten producer warps (under load, next to the MMAs and the
-// bulk copies, a producer warp needs ~170 cycles per load).
+// Accumulator layout of a pair MMA with M = 128 (measured): lanes 0..63 hold a CTA's rows with the
+// first half of N, lanes 64..127 the same rows with the second half.  So TMEM lane L of CTA c
+// belongs to head 64c + (L & 63); for S it holds the tile's keys 32*(L>>6) .. +31, for O the value
+// columns j*256 + 128*(L>>6) .. +127 of MMA j.  The two threads of a head exchange their running
+// maxima and sums through shared memory.
 //
-// A small pre-pass kernel turns every row's sparse indices into a front-packed list of physical KV
-// rows plus a count (block-wise ids expanded, -1 / out-of-window entries dropped, paged positions
-// translated through the block table), so the hot loop does no index arithmetic.
+// Tensor memory per CTA: O 0..255 | S (two buffers) 256..319.
+// Shared memory per CTA: Q_c 72 KB (A operand, loaded per token by TMA) | 2 x 36 KB K slots |
+// 2 x 32 KB V slots | 2 x 8 KB P (A operand of the value product, written by the softmax warps).
 //
-// Tensor memory per CTA (512 columns): O 0..255 | Q (bf16 pairs, MMA A operand) 256..415 |
-// S partial 416..479 | P (bf16 pairs, MMA A operand) 480..511.
-// Shared memory: 4 x 40 KB KV stages | 32 KB landing buffer for the peer's partial S | 32 KB
-// staging buffer for the outgoing partial.
-//
-// Warps (640 threads, registers redistributed with setmaxnreg): 0..9 = gather producers, 10 = MMA
-// issuer (QK^T) / TMEM owner, 11 = MMA issuer (PV), 12..15 = senders (partial S: TMEM -> staging ->
-// peer; Q -> TMEM), 16..19 = softmax + epilogue (thread = head = TMEM lane).  All waits are bounded; a wait that gives up sets the
-// status word.
+// Warps (640 threads): 0..5 K producers, 6..11 V producers, 12/13 QK^T issuers (even / odd tiles,
+// two issuing threads keep the tensor pipe fed with the short N = 64 MMAs), 14 PV issuer, 15 Q
+// loader, 16..19 softmax + epilogue.  MMAs are issued by the even CTA only; in the odd CTA the
+// issuer warps relay "my operand has landed" to the even CTA's barriers instead.  All waits are
+// bounded; a wait that gives up sets the status word.
 #pragma once
 
-#include <stdlib.h>
+#include <atomic>
+#include <mutex>
 
 #include "ptx_sm100.cuh"
 #include "sfa_fwd_simt.cuh"
 
 namespace dsa {
 
-constexpr int kSfaHeads = 128;
-// Tile size and ring depth (64 keys x 4 stages measured best: 48 keys x 5 stages, which also fits
-// the 227 KB of shared memory, was 18 % slower - the cost of a tile is mostly fixed).
-#ifndef DSA_SFA_BK
-#define DSA_SFA_BK 64
-#endif
-#ifndef DSA_SFA_STAGES
-#define DSA_SFA_STAGES 4
-#endif
-constexpr int kSfaBK = DSA_SFA_BK;      // keys per tile (a multiple of 16)
-constexpr int kSfaStages = DSA_SFA_STAGES;
-constexpr int kSfaHalf = kSfaBK / 2;   // the scores of a tile travel in two halves
-static_assert(kSfaBK % 16 == 0 && kSfaBK <= 64 && kSfaHalf % 8 == 0, "tile size");
+constexpr int kSfaHeads = 128;       // heads per CTA pair
+constexpr int kSfaCtaHeads = 64;
+constexpr int kSfaBK = 64;           // keys per tile
+constexpr int kSfaHalfBK = 32;       // keys of a tile each CTA gathers for the score product
 constexpr int kSfaThreads = 640;
-constexpr int kSfaProducerWarps = 10;
-constexpr int kSfaMmaWarp = 10;
-constexpr int kSfaSendWarp0 = 12;    // warps 12..15: partial-score senders + Q loaders
-constexpr int kSfaSoftWarp0 = 16;    // warps 16..19: softmax + epilogue
-constexpr int kSfaDvHalf = 256;
-constexpr int kSfaMaxSlots = 8192; // sparse_count * sparse_block_size served by this kernel
+constexpr int kSfaQkLanes = 3;       // QK^T issuers; issuer i owns feature blocks 3i..3i+2 and a partial S
+constexpr int kSfaKWarps = 6;        // warps 0..5: K gather producers, two per issuer
+constexpr int kSfaVWarp = 6;         // V copier
+constexpr int kSfaQWarp = 7;         // Q loader
+constexpr int kSfaQkWarp0 = 8;       // warps 8..10
+constexpr int kSfaPvWarp = 11;
+constexpr int kSfaSoftWarp0 = 16;    // warps 16..19 (12..15 idle)
+constexpr int kSfaDv = 512;
+constexpr int kSfaMaxSlots = 8192;   // sparse_count * sparse_block_size served by this kernel
 
-constexpr uint32_t kSfaBlk = kSfaBK * 128;                 // one 64-column block of a stage: BK rows x 128 B
-constexpr uint32_t kSfaStage = 5 * kSfaBlk;                // (rank 1 uses 4 of the 5 blocks)
-constexpr uint32_t kSfaOffX = kSfaStages * kSfaStage;
-constexpr uint32_t kSfaXBytes = kSfaHeads * kSfaBK * 4;    // partial scores of a tile, fp32
-constexpr uint32_t kSfaXHalfF = kSfaHeads * kSfaHalf;      // floats of one half (all heads)
-constexpr uint32_t kSfaXWarpF = 32 * kSfaHalf;             // floats of one warp's part of a half
-static_assert(kSfaStage % 1024 == 0, "stage alignment");
-constexpr uint32_t kSfaOffStage = kSfaOffX + kSfaXBytes;  // outgoing copy of this CTA's partial S
-constexpr uint32_t kSfaOffBar = kSfaOffStage + kSfaXBytes;
-constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 256;
+constexpr uint32_t kSfaQBlk = kSfaCtaHeads * 128;            // 64 heads x 64 features
+constexpr uint32_t kSfaQBytes = 9 * kSfaQBlk;                // 73 728
+constexpr uint32_t kSfaKBlk = kSfaHalfBK * 128;              // 32 keys x 64 features
+constexpr uint32_t kSfaKSlot = 9 * kSfaKBlk;                 // 36 864
+constexpr uint32_t kSfaKSub = 3 * kSfaKBlk;                  // the three blocks of one issuer
+constexpr uint32_t kSfaVBlk = kSfaBK * 128;                  // 64 keys x 64 value columns
+constexpr uint32_t kSfaVSlot = 4 * kSfaVBlk;                 // 32 768
+constexpr uint32_t kSfaPBuf = kSfaCtaHeads * kSfaBK * 2;     // 8 192
+constexpr uint32_t kSfaOffQ = 0;
+constexpr uint32_t kSfaOffK = kSfaOffQ + kSfaQBytes;
+constexpr uint32_t kSfaOffV = kSfaOffK + 2 * kSfaKSlot;
+constexpr uint32_t kSfaOffP = kSfaOffV + 2 * kSfaVSlot;
+constexpr uint32_t kSfaOffX = kSfaOffP + 2 * kSfaPBuf;       // float xm[2][128], xs[128]
+constexpr uint32_t kSfaOffBar = kSfaOffX + 3 * 128 * 4;
+constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 512;
+static_assert(kSfaOffK % 1024 == 0 && kSfaOffV % 1024 == 0 && kSfaOffP % 1024 == 0, "operand alignment");
 static_assert(kSfaSmemBytes <= 232448, "shared memory");
 
-constexpr uint32_t kTmO = 0, kTmQ = 256, kTmS = 416, kTmP = 480;
+constexpr uint32_t kTmO = 0, kTmS = 256;
 constexpr float kSfaRescaleTau = 8.f;  // log2 units: the running reference only moves when exceeded by this
 
 struct SfaSm100Args {
   SfaDev p;
   int32_t* status;
-  int32_t rows;
   uint32_t idesc_qk, idesc_pv;
   float scale_log2;  // scale * log2(e)
   int32_t is_bf16;
-  long long* prof;   // optional: cycle counters of one thread per role (phase breakdown)
-  const int2* nvalid;       // [rows * split] per work item: .x participating slots, .y first entry in key_list (pre-pass output)
+  const int2* nvalid;       // [items] .x participating slots, .y first entry in key_list (pre-pass output)
   const int32_t* key_list;  // [rows, slots] their physical KV rows, front-packed
   // Split-KV (few query rows, e.g. decode at small batch): a row's slots are cut into `split` parts
   // of `part_keys` slots (a multiple of 64); work item v = row * split + part.  Each part leaves a
@@ -119,11 +113,28 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Development aid, compiled only with -DDSA_SFA_PROFILE: cycle sums per role of the first cluster
+// (slot = role * 8 + counter, odd CTA + 64), read back with dsa_debug_sfa_profile().
+#ifdef DSA_SFA_PROFILE
+__device__ long long g_sfa_prof[128];
+#define SFA_PROF_DECL long long pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt = clock64()
+#define SFA_PROF(i) do { const long long pn = clock64(); pacc[i] += pn - pt; pt = pn; } while (0)
+#define SFA_PROF_STORE(role, cond) do { if (blockIdx.x < 2 && (cond)) { \
+    for (int pi = 0; pi < 8; ++pi) g_sfa_prof[(blockIdx.x & 1) * 64 + (role) * 8 + pi] = pacc[pi]; } } while (0)
+#else
+#define SFA_PROF_DECL
+#define SFA_PROF(i)
+#define SFA_PROF_STORE(role, cond)
+#endif
+
 // Pre-pass: one warp per query row.  Writes the physical KV rows of the slots that take part, in
-// slot order, and their count.  A slot whose paged block is absent does not take part here.
+// slot order, and their count.  A slot whose paged block is absent inside the valid length takes
+// part as a zero row, like the reference's un-paged cache
+// (sparse_flash_attention_triton.py:1012-1033): it gets the row number `oob_row` (= the number of
+// KV rows), which the gather loads as zeros.
 __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __restrict__ nvalid,
                                                           int32_t* __restrict__ key_list, int32_t split,
-                                                          int32_t part_keys) {
+                                                          int32_t part_keys, int32_t oob_row) {
   const int lane = threadIdx.x & 31;
   const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -138,7 +149,10 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __rest
       int64_t prow = -1;
       if (j < slots) {
         const int32_t tok = sfa_slot_token(p, ri, idx_row, j);
-        if (tok >= 0) prow = key_row(p.seq, ri, tok);
+        if (tok >= 0) {
+          prow = key_row(p.seq, ri, tok);
+          if (prow < 0 || prow >= oob_row) prow = oob_row;
+        }
       }
       const uint32_t m = __ballot_sync(0xffffffffu, prow >= 0);
       if (prow >= 0) out[n + __popc(m & ((1u << lane) - 1u))] = (int32_t)prow;
@@ -156,61 +170,62 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __rest
 template <bool kSplit>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSfaThreads, 1)
 sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_constant__ CUtensorMap tmap_kr,
+                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_qr,
                      const SfaSm100Args a) {
   extern __shared__ __align__(1024) unsigned char sfa_sm[];
-  unsigned char* kv_s = sfa_sm;
-  float* x_s = reinterpret_cast<float*>(sfa_sm + kSfaOffX);
-  float* xo_s = reinterpret_cast<float*>(sfa_sm + kSfaOffStage);
+  unsigned char* q_s = sfa_sm + kSfaOffQ;
+  unsigned char* k_s = sfa_sm + kSfaOffK;
+  unsigned char* v_s = sfa_sm + kSfaOffV;
+  unsigned char* p_s = sfa_sm + kSfaOffP;
+  float* xm = reinterpret_cast<float*>(sfa_sm + kSfaOffX);   // [2][128] running-maximum exchange
+  float* xs = xm + 256;                                       // [128] row-sum exchange
   uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
-  uint64_t* kv_full = bars;                   // [stages] gather -> MMA
-  uint64_t* kv_empty = bars + kSfaStages;     // [stages] MMA (PV done) -> gather
-  uint64_t* q_full = bars + 2 * kSfaStages;   // softmax warps (Q stored in TMEM) -> MMA
-  uint64_t* q_empty = q_full + 1;   // MMA (last QK of the token done) -> softmax warps
-  uint64_t* s_full = q_full + 2;    // MMA -> softmax
-  uint64_t* s_empty = q_full + 3;   // softmax (S in registers) -> MMA
-  uint64_t* p_full = q_full + 4;    // softmax (P stored, O rescaled) -> MMA
-  uint64_t* p_empty = q_full + 5;   // MMA (PV done) -> softmax
-  uint64_t* o_free = q_full + 6;    // epilogue (O read out) -> MMA
-  // The partial scores of a tile travel in two halves (keys 0..31 and 32..63), each with its own
-  // 16 KB staging and landing buffer and its own barriers, so that the next tile's first half can be
-  // on its way while the softmax warps still work on the current tile.
-  uint64_t* x_full = q_full + 7;    // [2] peer's partial S has landed (transaction bytes)
-  uint64_t* x_empty = q_full + 9;   // [2] peer has consumed what this CTA sent (remote arrivals)
-  uint64_t* own_full = q_full + 11; // [2] senders: own partial is in the staging buffer -> softmax
-  uint64_t* own_free = q_full + 13; // [2] softmax has read the staging buffer -> senders
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 15);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(q_full + 16);
-  static_assert((2 * kSfaStages + 17) * 8 <= 256, "barrier area");
+  // K barriers are indexed [slot * 3 + issuer]: every issuer's three feature blocks are handed over
+  // and released on their own.
+  uint64_t* k_full = bars;         // [6] gather -> QK issuer / relay                 (tx bytes)
+  uint64_t* k_empty = bars + 6;    // [6] blocks read by the issuer's MMAs (commit) and by both CTAs' V copiers -> K producers
+  uint64_t* k_ready = bars + 12;   // [6] even CTA only: the odd CTA's blocks have landed
+  uint64_t* v_full = bars + 18;    // [2] bulk copies of both CTAs -> PV issuer / relay, V copier (tx bytes)
+  uint64_t* v_empty = bars + 20;   // [2] PV of the tile done -> V copier              (commit, both CTAs)
+  uint64_t* v_ready = bars + 22;   // [2] even CTA only: the odd CTA's V slot has landed
+  uint64_t* s_full = bars + 24;    // [2] all three partial products done -> softmax   (commit x 3, both CTAs)
+  uint64_t* s_empty = bars + 26;   // [2] even CTA only: softmax warps of both CTAs hold S in registers
+  uint64_t* p_full = bars + 28;    // [2] even CTA only: P stored (O rescaled) in both CTAs
+  uint64_t* p_empty = bars + 30;   // [2] PV done -> softmax                           (commit, both CTAs)
+  uint64_t* q_full = bars + 32;    // this CTA's Q has landed (tx bytes)
+  uint64_t* q_ready = bars + 33;   // even CTA only: the odd CTA's Q has landed
+  uint64_t* q_empty = bars + 34;   // all QK issuers are through with the token        (commit x 3, both CTAs)
+  uint64_t* o_free = bars + 35;    // even CTA only: epilogue warps of both CTAs have read O
+  uint64_t* x_bar = bars + 36;     // softmax warps: exchange buffer written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 37);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 38);
+  static_assert(39 * 8 <= 512, "barrier area");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
-  const uint32_t peer = rank ^ 1u;
   const int32_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  const int nblk = rank == 0 ? 5 : 4;          // 64-column blocks of this CTA's feature half
-  const int nks = nblk * 4;                    // QK^T k-steps (16 dims each)
 
   const bool misaligned = (ptx::smem_u32(sfa_sm) & 1023u) != 0;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kSfaStages; ++i) { ptx::mbar_init(&kv_full[i], 1); ptx::mbar_init(&kv_empty[i], 1); }
-    ptx::mbar_init(q_full, 128);
-    ptx::mbar_init(q_empty, 1);
-    ptx::mbar_init(s_full, 1);
-    ptx::mbar_init(s_empty, 128);
-    ptx::mbar_init(p_full, 128);
-    ptx::mbar_init(p_empty, 1);
-    ptx::mbar_init(o_free, 128);
-    for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&x_full[i], 1);
-      ptx::mbar_init(&x_empty[i], 4);
-      ptx::mbar_init(&own_full[i], 4);
-      ptx::mbar_init(&own_free[i], 4);
+    for (int i = 0; i < 6; ++i) {
+      ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 3); ptx::mbar_init(&k_ready[i], 1);
     }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1); ptx::mbar_init(&v_ready[i], 1);
+      ptx::mbar_init(&s_full[i], kSfaQkLanes); ptx::mbar_init(&s_empty[i], 8);
+      ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
+    }
+    ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_ready, 1);
+    ptx::mbar_init(q_empty, kSfaQkLanes);
+    ptx::mbar_init(o_free, 8);
+    ptx::mbar_init(x_bar, 4);
     *abort_flag = misaligned ? 1 : 0;
     ptx::mbar_fence_init();
   }
-  if (warp == kSfaMmaWarp) {
-    ptx::tmem_alloc(tmem_slot, 512);
-    ptx::tmem_relinquish();
+  if (warp == kSfaQkWarp0) {
+    ptx::tmem_alloc_pair(tmem_slot, 512);
+    ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -219,478 +234,514 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   ptx::cluster_arrive();
   ptx::cluster_wait();
   const uint32_t tmem = *tmem_slot;
-  // 512 threads start with 128 registers each; every role branch below first trades registers:
-  // the softmax warps need more, everyone else less (whole warpgroups of 4 warps change together).
 
-  const int32_t n1 = a.p.n1;                   // real heads (<= 128); lanes past them carry zero queries
-  const int32_t n1d = n1 * a.p.d;
+  const int32_t n1 = a.p.n1;                   // real heads (<= 128); rows past them carry zero queries
+  auto item_tiles = [&](int32_t item) -> int32_t { return (a.nvalid[item].x + kSfaBK - 1) / kSfaBK; };
 
-  if (warp < kSfaSendWarp0) {
-   asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-   if (*abort_flag) {
-    // nothing started: fall through to the teardown
-  } else if (warp < kSfaProducerWarps) {
-    // ------------------------------------------------------------------ gather producers
-    // A tile is 16 row groups (4 keys each) x nblk column blocks = 80 (rank 0) or 64 (rank 1)
-    // gather4 loads of 512 bytes.  A warp issues one such load every ~67 cycles whatever the lane
-    // pattern, but warps issue in parallel, so the loads of every tile are dealt out over ten
-    // warps (load o goes to warp o % 10, lane o / 10).  Warp 0 also arms the stage's barrier.
-    uint32_t n_tile = 0;
-    bool ok = true;
-    long long pprof[4] = {0, 0, 0, 0};
-    const int nops = (kSfaBK / 4) * nblk;
-    const int o = warp + kSfaProducerWarps * lane;     // this lane's load of every tile
-    const int grp = o / nblk, blk = o - grp * nblk;     // row group, column block
-    const bool active = o < nops;
-    const int32_t x = rank == 0 ? (blk < 4 ? blk * 64 : 0) : kSfaDvHalf + blk * 64;
-    const CUtensorMap* tm = (rank == 0 && blk == 4) ? &tmap_kr : &tmap_kn;
-    if (lane == 0) { ptx::prefetch_tmap(&tmap_kn); ptx::prefetch_tmap(&tmap_kr); }
-    // The row numbers of a tile come from global memory (the pre-pass list); they are fetched one
-    // tile ahead so that their latency never sits between a freed stage and the gather.
-    struct TilePos { int32_t row, t, ntiles, nvalid, off; };
-    auto first_from = [&](int32_t row) -> TilePos {   // `row` counts work items here
-      for (; row < a.items; row += n_clusters) {
-        const int2 d = a.nvalid[row];
-        if (d.x > 0) return TilePos{row, 0, (d.x + kSfaBK - 1) / kSfaBK, d.x, d.y};
-      }
-      return TilePos{a.items, 0, 0, 0, 0};
-    };
-    auto load_rows = [&](const TilePos& tp, int32_t* r) {
-      const int32_t* list = a.key_list + tp.off;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int32_t k = tp.t * kSfaBK + grp * 4 + i;
-        // keys past the end of the row re-read the tile's first key
-        r[i] = (active && tp.row < a.items) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
-      }
-    };
-    TilePos cur = first_from(cluster_id);
-    int32_t rc[4], rn[4];
-    load_rows(cur, rc);
-    while (cur.row < a.items && ok) {
-      TilePos nxt = cur;
-      if (++nxt.t >= nxt.ntiles) nxt = first_from(cur.row + n_clusters);
-      load_rows(nxt, rn);
-      const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
-      const long long p1 = clock64();
-      if (lane == 0) ok = ptx::mbar_wait(&kv_empty[s], (use & 1) ^ 1, abort_flag);
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      if (!ok) break;
-      const long long p2 = clock64();
-      if (warp == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&kv_full[s], kSfaBK * nblk * 128);
-      if (active)
-        ptx::tma_gather4_2d(kv_s + s * kSfaStage + blk * kSfaBlk + grp * 512, tm, &kv_full[s], x, rc[0], rc[1], rc[2],
-                            rc[3]);
-      __syncwarp();
-      pprof[1] += p2 - p1; pprof[2] += clock64() - p2;
-      ++n_tile;
-      cur = nxt;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) rc[i] = rn[i];
-    }
-    if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
-      for (int i = 0; i < 4; ++i) a.prof[16 + i] = pprof[i];
-    }
-  } else if (warp == kSfaMmaWarp) {
-    // ------------------------------------------------------------------ QK^T issuer (warp 6)
-    // S = Q_c K_c^T for every tile, as early as the KV ring and the single S buffer allow; it
-    // never waits for the softmax, so the score exchange of later tiles overlaps the softmax of
-    // earlier ones.
-    uint32_t n_tile = 0, n_tok = 0;
-    bool ok = true;
-    long long mprof[4] = {0, 0, 0, 0};
-    const uint32_t kv_addr = ptx::smem_u32(kv_s);
-    for (int32_t row = cluster_id; row < a.items && ok; row += n_clusters) {   // work items
-      const int32_t nvalid = a.nvalid[row].x;
-      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      if (ntiles == 0) continue;
-      if (lane == 0) {
-        ok = ptx::mbar_wait(q_full, n_tok & 1, abort_flag);
-        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-          const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
-          const long long m0 = clock64();
-          ok = ptx::mbar_wait(&kv_full[s], use & 1, abort_flag);
-          if (!ok) break;
-          const long long m1 = clock64();
-          ok = ptx::mbar_wait(s_empty, (n_tile & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          mprof[0] += m1 - m0; mprof[1] += clock64() - m1;
-          ptx::tc_fence_after();
-          for (int ks = 0; ks < nks; ++ks) {
-            const uint64_t bd = ptx::desc_kmajor_sw128(kv_addr + s * kSfaStage + (ks >> 2) * kSfaBlk + (ks & 3) * 32);
-            ptx::mma_ts(tmem + kTmS, tmem + kTmQ + ks * 8, bd, a.idesc_qk, ks > 0 ? 1u : 0u);
-          }
-          ptx::mma_commit(s_full);
-          if (t == ntiles - 1) ptx::mma_commit(q_empty);
+  if (warp < kSfaSoftWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (*abort_flag) {
+      // nothing started: fall through to the teardown
+    } else if (warp < kSfaKWarps) {
+      // ------------------------------------------------------------------ K gather producers
+      // Two warps per QK^T issuer: 8 row groups (4 of this CTA's 32 keys each) x the issuer's 3
+      // column blocks = 24 gather4 loads of 512 bytes per tile, dealt out over the two warps (a
+      // warp issues one such load every ~70 cycles whatever the lane pattern, warps issue in
+      // parallel, the SM's TMA unit takes one every ~18 cycles).
+      const int qi = warp >> 1;                          // the issuer this warp feeds
+      const int gw = warp & 1;
+      const int o = gw + 2 * lane;
+      const bool active = o < 24;
+      const int grp = o / 3, blk = 3 * qi + (o - grp * 3);
+      const int key0 = (int)rank * kSfaHalfBK + grp * 4;   // first key (within the tile) of this load
+      const int32_t x = blk < 8 ? blk * 64 : 0;
+      const CUtensorMap* tm = blk == 8 ? &tmap_kr : &tmap_kn;
+      unsigned char* slot0 = k_s + blk * kSfaKBlk + grp * 512;
+      uint64_t* full = k_full + qi;                      // slot s: full[s * 3]
+      uint64_t* empty = k_empty + qi;
+      if (lane == 0) { ptx::prefetch_tmap(&tmap_kn); ptx::prefetch_tmap(&tmap_kr); }
+      // The row numbers of a tile come from global memory (the pre-pass list); they are fetched one
+      // tile ahead so that their latency never sits between a freed slot and the gather.
+      struct TilePos { int32_t item, t, ntiles, nvalid, off; };
+      auto first_from = [&](int32_t item) -> TilePos {
+        for (; item < a.items; item += n_clusters) {
+          const int2 d = a.nvalid[item];
+          if (d.x > 0) return TilePos{item, 0, (d.x + kSfaBK - 1) / kSfaBK, d.x, d.y};
         }
-      }
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
-      ++n_tok;
-    }
-    if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) {
-      for (int i = 0; i < 2; ++i) a.prof[12 + i] = mprof[i];
-    }
-  } else if (warp == kSfaMmaWarp + 1) {
-    // ------------------------------------------------------------------ PV issuer (warp 7)
-    // O (+)= P V_c once the softmax warps have stored P; frees the KV stage and the P buffer.
-    uint32_t n_tile = 0, n_tok = 0;
-    bool ok = true;
-    long long wait_p = 0;
-    const uint32_t kv_addr = ptx::smem_u32(kv_s);
-    for (int32_t row = cluster_id; row < a.items && ok; row += n_clusters) {   // work items
-      const int32_t nvalid = a.nvalid[row].x;
-      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      if (ntiles == 0) continue;
-      if (lane == 0) {
-        ok = ptx::mbar_wait(o_free, (n_tok & 1) ^ 1, abort_flag);   // previous token's O has been read out
-        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-          const uint32_t s = n_tile % kSfaStages, use = n_tile / kSfaStages;
-          ok = ptx::mbar_wait(&kv_full[s], use & 1, abort_flag);    // long complete; observed for ordering
-          if (!ok) break;
-          const long long m0 = clock64();
-          ok = ptx::mbar_wait(p_full, n_tile & 1, abort_flag);
-          if (!ok) break;
-          wait_p += clock64() - m0;
-          ptx::tc_fence_after();
+        return TilePos{a.items, 0, 0, 0, 0};
+      };
+      auto load_rows = [&](const TilePos& tp, int32_t* r) {
+        const int32_t* list = a.key_list + tp.off;
 #pragma unroll
-          for (int ks = 0; ks < kSfaBK / 16; ++ks) {
-            const uint64_t bd = ptx::desc_mnmajor_sw128(kv_addr + s * kSfaStage + ks * 16 * 128, kSfaBlk, 1024);
-            ptx::mma_ts(tmem + kTmO, tmem + kTmP + ks * 8, bd, a.idesc_pv, (t == 0 && ks == 0) ? 0u : 1u);
-          }
-          ptx::mma_commit(p_empty);
-          ptx::mma_commit(&kv_empty[s]);
+        for (int i = 0; i < 4; ++i) {
+          const int32_t k = tp.t * kSfaBK + key0 + i;
+          // keys past the end of the row re-read the tile's first key (masked by the softmax)
+          r[i] = (active && tp.item < a.items) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
         }
-      }
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      n_tile = __shfl_sync(0xffffffffu, n_tile, 0);
-      ++n_tok;
-    }
-    if (a.prof != nullptr && blockIdx.x == 0 && lane == 0) a.prof[14] = wait_p;
-  }
-  } else if (warp < kSfaSoftWarp0) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-    if (!*abort_flag) {
-    // ------------------------------------------------------------------ senders
-    // Per token: this CTA's Q half into tensor memory.  Per tile: the partial S from tensor memory
-    // into the staging buffer (warp w owns 8 KB: 16-byte chunk c of a lane at w * 8192 + c * 512 +
-    // lane * 16), one bulk copy per warp into the peer's landing buffer (counted on the peer's
-    // x_full barrier), and a local hand-over of the same staging buffer to the softmax warps.
-    const int quarter = warp & 3;
-    const int h = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t x_peer = ptx::map_to_rank(x_s, peer);
-    const uint32_t x_full_peer = ptx::map_to_rank(x_full, peer);
-    uint32_t n_tile = 0, n_tok = 0;
-    bool ok = true;
-    long long sprof[4] = {0, 0, 0, 0};
-    auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
-    };
-    auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
-    };
-    auto q_half = [&](int32_t r) -> const uint4* {
-      return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query +
-                                            ((int64_t)r * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2);
-    };
-    auto q_rope = [&](int32_t r) -> const uint4* {
-      return reinterpret_cast<const uint4*>((const unsigned char*)a.p.query_rope +
-                                            ((int64_t)r * n1 + h) * a.p.d_rope * 2);
-    };
-    for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
-      const int32_t nvalid = a.nvalid[item].x;
-      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      if (ntiles == 0) continue;
-      const int32_t row = kSplit ? item / a.split : item;   // the query row of this work item
-      // ---- this token's Q half -> tensor memory (bf16 pairs, row h in lane h)
-      ok = wait_w(q_empty, (n_tok & 1) ^ 1);
-      if (!ok) break;
-      ptx::tc_fence_after();
-      {
-        // 16 loads in flight per batch (a batch of 8 left the five batches' latencies in a row at
-        // every token boundary)
-        const uint4* qn = q_half(row);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t w[64];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint4 v = h < n1 ? __ldg(qn + c * 16 + i) : make_uint4(0, 0, 0, 0);
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-          }
-          ptx::tmem_st_x32(lane_addr + kTmQ + c * 64, w);
-          ptx::tmem_st_x32(lane_addr + kTmQ + c * 64 + 32, w + 32);
-        }
-        if (rank == 0) {
-          const uint4* qr = q_rope(row);
-          uint32_t w[32];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint4 v = h < n1 ? __ldg(qr + i) : make_uint4(0, 0, 0, 0);
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-          }
-          ptx::tmem_st_x32(lane_addr + kTmQ + 128, w);
-        }
-        ptx::tmem_st_wait();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(q_full);
-        // the next token's Q rows go to L2 now, a whole token's worth of tiles before they are read
-        int32_t nitem = item + n_clusters;
-        while (nitem < a.items && a.nvalid[nitem].x == 0) nitem += n_clusters;
-        if (nitem < a.items && h < n1) {
-          const int32_t nrow = kSplit ? nitem / a.split : nitem;
-          const unsigned char* nq = reinterpret_cast<const unsigned char*>(q_half(nrow));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) ptx::prefetch_l2(nq + i * 128);
-          if (rank == 0) ptx::prefetch_l2(q_rope(nrow));
-        }
-      }
-      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const long long s0 = clock64();
-        ok = wait_w(s_full, n_tile & 1);
+      };
+      uint32_t n_tile = 0;
+      bool ok = true;
+      SFA_PROF_DECL;
+      TilePos cur = first_from(cluster_id);
+      int32_t rc[4], rn[4];
+      load_rows(cur, rc);
+      while (cur.item < a.items && ok) {
+        TilePos nxt = cur;
+        if (++nxt.t >= nxt.ntiles) nxt = first_from(cur.item + n_clusters);
+        load_rows(nxt, rn);
+        const uint32_t s = n_tile & 1, use = n_tile >> 1;
+        SFA_PROF(0);
+        if (lane == 0) ok = ptx::mbar_wait_cluster(&empty[s * 3], (use & 1) ^ 1, abort_flag);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
-        sprof[0] += clock64() - s0;
-        ptx::tc_fence_after();
-        float sv[64];   // kSfaBK of them are scores
-        ptx::tmem_ld_x32(lane_addr + kTmS, reinterpret_cast<uint32_t*>(sv));
-        if (kSfaBK > 48) ptx::tmem_ld_x32(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
-        else if (kSfaBK > 32) ptx::tmem_ld_x16(lane_addr + kTmS + 32, reinterpret_cast<uint32_t*>(sv) + 32);
-        ptx::tmem_ld_wait();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(s_empty);
-        // a staging half is free once the peer has consumed what was copied out of it and the
-        // local softmax warps have read it (half hf: kSfaXWarpF floats per warp, 16-byte chunk c of
-        // a lane at c * 512 + lane * 16 inside the warp's part)
+        SFA_PROF(1);
+        if (gw == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&full[s * 3], kSfaKSub);
+        if (active) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, tm, &full[s * 3], x, rc[0], rc[1], rc[2], rc[3]);
+        __syncwarp();
+        SFA_PROF(2);
+        ++n_tile;
+        cur = nxt;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const long long s1 = clock64();
-          ok = wait_wc(&x_empty[hf], (n_tile & 1) ^ 1);
+        for (int i = 0; i < 4; ++i) rc[i] = rn[i];
+      }
+      SFA_PROF_STORE(0, lane == 0 && warp == 0);
+    } else if (warp == kSfaVWarp) {
+      // ------------------------------------------------------------------ V copier
+      // The value operand of a tile (all 64 keys x this CTA's 256 value columns) is not gathered
+      // again: every CTA already holds its own 32 keys with all columns in its K slot.  Per tile
+      // eight 4 KB bulk copies (lanes 0..7) move the four column blocks that this CTA owns into
+      // its own V slot and the four that the peer owns into the peer's V slot (distributed shared
+      // memory), rows 32*rank.. of every block.  A K slot may be refilled once the score MMAs AND
+      // these copies have read it: the copier tells its own K producers when its V slot is complete
+      // (its local copies are then done) and the peer's K producers at the same moment (the peer's
+      // copies into this CTA are then done).
+      const uint32_t peer = rank ^ 1u;
+      const int dst_rank = (lane & 4) ? (int)peer : (int)rank;          // lanes 0..3 local, 4..7 to the peer
+      const int pblk = lane & 3;                                        // V block: j = pblk >> 1, h = pblk & 1
+      const int fblk = 4 * (pblk >> 1) + 2 * dst_rank + (pblk & 1);     // feature block holding those columns
+      const uint32_t dst0 = ptx::map_to_rank(v_s + pblk * kSfaVBlk + rank * kSfaKBlk, (uint32_t)dst_rank);
+      const uint32_t bar0 = ptx::map_to_rank(v_full, (uint32_t)dst_rank);
+      const uint32_t k_empty_peer = ptx::map_to_rank(k_empty, peer);
+      uint32_t n_tile = 0;
+      bool ok = true;
+      SFA_PROF_DECL;
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t ntiles = item_tiles(item);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          SFA_PROF(0);
+          // V slot b is free in both CTAs once the product that read it has completed
+          ok = ptx::mbar_wait_warp(&v_empty[b], (use & 1) ^ 1, abort_flag);
           if (!ok) break;
-          const long long s2 = clock64();
-          ok = wait_w(&own_free[hf], (n_tile & 1) ^ 1);
+          SFA_PROF(1);
+          if (lane == 0) ptx::mbar_arrive_expect_tx(&v_full[b], kSfaVSlot);
+          ok = ptx::mbar_wait_warp(&k_full[b * 3], use & 1, abort_flag) && ptx::mbar_wait_warp(&k_full[b * 3 + 1], use & 1, abort_flag) &&
+               ptx::mbar_wait_warp(&k_full[b * 3 + 2], use & 1, abort_flag);
           if (!ok) break;
-          sprof[1] += s2 - s1; sprof[2] += clock64() - s2;
-          if (quarter == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&x_full[hf], kSfaXBytes / 2);  // arm my landing half
-          float* mine = xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
-#pragma unroll
-          for (int c = 0; c < kSfaBK / 8; ++c) {
-            const int k = hf * kSfaHalf + 4 * c;
-            *reinterpret_cast<float4*>(mine + c * 128) = make_float4(sv[k], sv[k + 1], sv[k + 2], sv[k + 3]);
-          }
-          ptx::fence_proxy_async_smem();
+          SFA_PROF(2);
+          if (lane < 8)
+            ptx::bulk_copy_to_peer(dst0 + b * kSfaVSlot, k_s + b * kSfaKSlot + fblk * kSfaKBlk, kSfaKBlk, bar0 + b * 8);
           __syncwarp();
-          if (lane == 0) {
-            ptx::bulk_copy_to_peer(x_peer + (hf * kSfaXHalfF + quarter * kSfaXWarpF) * 4,
-                                   xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF, kSfaXWarpF * 4, x_full_peer + hf * 8);
-            ptx::mbar_arrive(&own_full[hf]);
-          }
+          SFA_PROF(3);
+          ok = ptx::mbar_wait_cluster_warp(&v_full[b], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(4);
+          if (lane < 3) ptx::mbar_arrive(&k_empty[b * 3 + lane]);
+          else if (lane < 6) ptx::mbar_arrive_remote_relaxed(k_empty_peer + (b * 3 + lane - 3) * 8, 0u);
+          __syncwarp();
         }
       }
-      ++n_tok;
-    }
-    if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
-      for (int i = 0; i < 3; ++i) a.prof[20 + i] = sprof[i];
-    }
+      SFA_PROF_STORE(1, lane == 0);
+    } else if (warp == kSfaQWarp) {
+      // ------------------------------------------------------------------ Q loader
+      // Per token: this CTA's 64 heads x 576 features into shared memory (nine 64 x 64 boxes; heads
+      // past n1 read as zeros), as soon as all QK^T issuers are through with the previous token.
+      // The other lanes pull the next token's rows into L2 meanwhile.
+      uint32_t n_tok = 0;
+      bool ok = true;
+      const uint32_t q_ready_lead = ptx::map_to_rank(q_ready, 0);
+      if (lane == 0) { ptx::prefetch_tmap(&tmap_q); ptx::prefetch_tmap(&tmap_qr); }
+      const int32_t h0 = (int32_t)rank * kSfaCtaHeads;
+      const int32_t hn = min(kSfaCtaHeads, n1 - h0);     // this CTA's real heads (may be <= 0)
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        if (item_tiles(item) == 0) continue;
+        const int32_t row = kSplit ? item / a.split : item;
+        if (lane == 0) {
+          ok = ptx::mbar_wait(q_empty, (n_tok & 1) ^ 1, abort_flag);
+          if (ok) {
+            ptx::mbar_arrive_expect_tx(q_full, kSfaQBytes);
+#pragma unroll 1
+            for (int f = 0; f < 9; ++f)
+              ptx::tma_load_3d(q_s + f * kSfaQBlk, f < 8 ? &tmap_q : &tmap_qr, q_full, f < 8 ? f * 64 : 0, h0, row);
+            if (rank != 0) {
+              ok = ptx::mbar_wait(q_full, n_tok & 1, abort_flag);
+              if (ok) { ptx::fence_proxy_async_smem(); ptx::mbar_arrive_remote(q_ready_lead); }
+            }
+          }
+        } else if (hn > 0) {
+          int32_t nitem = item + n_clusters;
+          while (nitem < a.items && a.nvalid[nitem].x == 0) nitem += n_clusters;
+          if (nitem < a.items) {
+            const int32_t nrow = kSplit ? nitem / a.split : nitem;
+            const unsigned char* qn = (const unsigned char*)a.p.query + ((int64_t)nrow * n1 + h0) * (kSfaDv * 2);
+            const unsigned char* qr = (const unsigned char*)a.p.query_rope + ((int64_t)nrow * n1 + h0) * 128;
+            for (int32_t i = lane - 1; i < hn * 8; i += 31) ptx::prefetch_l2(qn + (int64_t)i * 128);
+            for (int32_t i = lane - 1; i < hn; i += 31) ptx::prefetch_l2(qr + (int64_t)i * 128);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        ++n_tok;
+      }
+    } else if (warp < kSfaPvWarp) {
+      // ------------------------------------------------------------------ QK^T issuers (even CTA) / K relays (odd CTA)
+      // Issuer i multiplies feature blocks 3i..3i+2 of every tile into its own partial S; the
+      // softmax adds the three partials.  One thread issues a short (N = 64) MMA only every 60-90
+      // cycles, three keep the tensor pipe busy.  The loop is warp-uniform (every lane waits) and
+      // only the MMA and the commits are issued by one elected lane.
+      const uint32_t qi = warp - kSfaQkWarp0;
+      uint32_t n_tile = 0, n_tok = 0;
+      bool ok = true;
+      const uint32_t q_addr = ptx::smem_u32(q_s) + qi * 3 * kSfaQBlk;
+      const uint32_t k_addr = ptx::smem_u32(k_s) + qi * kSfaKSub;
+      const uint32_t k_ready_lead = ptx::map_to_rank(k_ready, 0);
+      SFA_PROF_DECL;
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t ntiles = item_tiles(item);
+        if (ntiles == 0) continue;
+        SFA_PROF(0);
+        if (rank == 0) {
+          ok = ptx::mbar_wait_warp(q_full, n_tok & 1, abort_flag) && ptx::mbar_wait_cluster_warp(q_ready, n_tok & 1, abort_flag);
+        }
+        SFA_PROF(5);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1, kb = b * kSfaQkLanes + qi;
+          SFA_PROF(0);
+          ok = ptx::mbar_wait_warp(&k_full[kb], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(1);
+          if (rank != 0) {
+            if (ptx::elect_one()) {
+              ptx::fence_proxy_async_smem();
+              ptx::mbar_arrive_remote(k_ready_lead + kb * 8);
+            }
+            __syncwarp();
+            continue;
+          }
+          ok = ptx::mbar_wait_cluster_warp(&k_ready[kb], use & 1, abort_flag);
+          SFA_PROF(2);
+          ok = ok && ptx::mbar_wait_cluster_warp(&s_empty[b], (use & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(3);
+          ptx::tc_fence_after();
+          if (ptx::elect_one()) {
+#pragma unroll
+            for (int f = 0; f < 3; ++f) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                const uint64_t ad = ptx::desc_kmajor_sw128(q_addr + f * kSfaQBlk + kk * 32);
+                const uint64_t bd = ptx::desc_kmajor_sw128(k_addr + b * kSfaKSlot + f * kSfaKBlk + kk * 32);
+                ptx::mma_ss_pair(tmem + kTmS + kb * 32, ad, bd, a.idesc_qk, (f | kk) ? 1u : 0u);
+              }
+            }
+            ptx::mma_commit_pair(&s_full[b]);
+            ptx::mma_commit_pair(&k_empty[kb]);
+          }
+          __syncwarp();
+          SFA_PROF(4);
+        }
+        // the token's Q may be replaced once every issuer's products have completed
+        if (ok && rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(q_empty);
+        __syncwarp();
+        ++n_tok;
+      }
+      SFA_PROF_STORE(2, lane == 0 && qi == 0);
+    } else if (warp == kSfaPvWarp) {
+      // ------------------------------------------------------------------ PV issuer (even CTA) / V relay (odd CTA)
+      uint32_t n_tile = 0, n_tok = 0;
+      bool ok = true;
+      const uint32_t p_addr = ptx::smem_u32(p_s), v_addr = ptx::smem_u32(v_s);
+      const uint32_t v_ready_lead = ptx::map_to_rank(v_ready, 0);
+      SFA_PROF_DECL;
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t ntiles = item_tiles(item);
+        if (ntiles == 0) continue;
+        // the previous token's O has been read out in both CTAs
+        SFA_PROF(0);
+        if (rank == 0) ok = ptx::mbar_wait_cluster_warp(o_free, (n_tok & 1) ^ 1, abort_flag);
+        SFA_PROF(5);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          SFA_PROF(0);
+          ok = ptx::mbar_wait_warp(&v_full[b], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(1);
+          if (rank != 0) {
+            if (ptx::elect_one()) {
+              ptx::fence_proxy_async_smem();
+              ptx::mbar_arrive_remote(v_ready_lead + b * 8);
+            }
+            __syncwarp();
+            continue;
+          }
+          ok = ptx::mbar_wait_cluster_warp(&v_ready[b], use & 1, abort_flag);
+          SFA_PROF(2);
+          ok = ok && ptx::mbar_wait_cluster_warp(&p_full[b], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(3);
+          ptx::tc_fence_after();
+          if (ptx::elect_one()) {
+#pragma unroll
+            for (int ks = 0; ks < kSfaBK / 16; ++ks) {
+              const uint64_t ad = ptx::desc_kmajor_sw128(p_addr + b * kSfaPBuf + ks * 32);
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const uint64_t bd = ptx::desc_mnmajor_sw128(v_addr + b * kSfaVSlot + j * 2 * kSfaVBlk + ks * 16 * 128,
+                                                            kSfaVBlk, 1024);
+                ptx::mma_ss_pair(tmem + kTmO + j * 128, ad, bd, a.idesc_pv, (t == 0 && ks == 0) ? 0u : 1u);
+              }
+            }
+            ptx::mma_commit_pair(&p_empty[b]);
+            ptx::mma_commit_pair(&v_empty[b]);
+          }
+          __syncwarp();
+          SFA_PROF(4);
+        }
+        ++n_tok;
+      }
+      SFA_PROF_STORE(3, lane == 0);
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     if (!*abort_flag) {
-    // ------------------------------------------------------------------ softmax + epilogue
-    const int quarter = warp & 3;
-    const int h = quarter * 32 + lane;                       // head == TMEM lane
-    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t x_empty_peer = ptx::map_to_rank(x_empty, peer);
-    uint32_t n_tile = 0;
-    bool ok = true;
-    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // cycle sums per phase (stored only when profiling)
-    // waits of these warps are made warp-uniform: the tcgen05 loads / stores that follow are
-    // warp-collective and must never run with part of a warp gone
-    auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
-    };
-    auto wait_wc = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait_cluster(bar, parity, abort_flag));
-    };
-    for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
-      const int32_t nvalid = a.nvalid[item].x;
-      const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
-      const int32_t row = kSplit ? item / a.split : item;
-      unsigned char* out_row = (unsigned char*)a.p.out + ((int64_t)row * n1d + (int64_t)h * a.p.d + rank * kSfaDvHalf) * 2;
-      float* part_row = kSplit ? a.part_o + ((int64_t)item * kSfaHeads + h) * (2 * kSfaDvHalf) + rank * kSfaDvHalf
-                                    : nullptr;
-      if (ntiles == 0) {
-        if constexpr (kSplit) {
-          // an empty part: the merge skips it
-          if (rank == 0) { a.part_m[(int64_t)item * kSfaHeads + h] = 0.f; a.part_l[(int64_t)item * kSfaHeads + h] = 0.f; }
-        } else {
-          // nothing visible: zeros in all three outputs
-          if (h < n1) {
+      // ------------------------------------------------------------------ softmax + epilogue
+      const int quarter = warp & 3;
+      const int L = quarter * 32 + lane;            // TMEM lane
+      const int hl = L & 63, half = L >> 6;         // head within this CTA; which half of N this lane holds
+      const int32_t hg = (int32_t)rank * kSfaCtaHeads + hl;
+      const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t s_empty_lead = ptx::map_to_rank(s_empty, 0);
+      const uint32_t p_full_lead = ptx::map_to_rank(p_full, 0);
+      const uint32_t o_free_lead = ptx::map_to_rank(o_free, 0);
+      uint32_t n_tile = 0, n_x = 0;
+      bool ok = true;
+      SFA_PROF_DECL;
+      // waits are warp-wide: the tcgen05 loads / stores that follow are warp-collective and must
+      // never run with part of a warp gone
+      auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool { return ptx::mbar_wait_warp(bar, parity, abort_flag); };
+      // One arrival per warp on a barrier of the even CTA.  From the odd CTA it is a relaxed remote
+      // arrival: a cluster-scope release costs ~1000 cycles here, and what the arrival announces has
+      // already been made visible by the fences before it (tcgen05.wait + tcgen05 fence for tensor
+      // memory, fence.proxy.async for the P rows, which lie in this CTA's own shared memory).
+      auto signal_lead = [&](uint64_t* local, uint32_t remote) {
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) ptx::mbar_arrive(local);
+          else ptx::mbar_arrive_remote_relaxed(remote, 0u);
+        }
+      };
+      // value of the head's other thread (lane L ^ 64, another warp) through shared memory
+      auto exchange = [&](float* buf, float v, float& other) -> bool {
+        buf[L] = v;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(x_bar);
+        const bool got = wait_w(x_bar, n_x & 1);
+        ++n_x;
+        other = buf[L ^ 64];
+        return got;
+      };
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t nvalid = a.nvalid[item].x;
+        const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
+        const int32_t row = kSplit ? item / a.split : item;
+        // this lane's output columns: j * 256 + half * 128 + 0..127 for j = 0, 1
+        unsigned char* out_row = (unsigned char*)a.p.out + (((int64_t)row * n1 + hg) * kSfaDv + half * 128) * 2;
+        float* part_row = kSplit ? a.part_o + ((int64_t)item * kSfaHeads + hg) * kSfaDv + half * 128 : nullptr;
+        if (ntiles == 0) {
+          if constexpr (kSplit) {
+            // an empty part: the merge skips it
+            if (half == 0) { a.part_m[(int64_t)item * kSfaHeads + hg] = 0.f; a.part_l[(int64_t)item * kSfaHeads + hg] = 0.f; }
+          } else if (hg < n1) {
+            // nothing visible: zeros in all three outputs
 #pragma unroll
-            for (int c = 0; c < kSfaDvHalf * 2 / 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
-            if (rank == 0 && a.p.return_lse) {
-              a.p.softmax_max[(int64_t)row * n1 + h] = 0.f;
-              a.p.softmax_sum[(int64_t)row * n1 + h] = 0.f;
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+              for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(out_row + j * 512)[c] = make_uint4(0, 0, 0, 0);
+            if (half == 0 && a.p.return_lse) {
+              a.p.softmax_max[(int64_t)row * n1 + hg] = 0.f;
+              a.p.softmax_sum[(int64_t)row * n1 + hg] = 0.f;
+            }
+          }
+          continue;
+        }
+        float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, l_tot = 0.f;
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK) - half * kSfaHalfBK;   // valid keys among this lane's 32
+          SFA_PROF(7);
+          ok = wait_w(&s_full[b], use & 1);
+          if (!ok) break;
+          SFA_PROF(0);
+          ptx::tc_fence_after();
+          float sc[kSfaHalfBK];
+          {
+            // the three issuers' partial products
+            float s1[kSfaHalfBK], s2[kSfaHalfBK];
+            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes) * 32, reinterpret_cast<uint32_t*>(sc));
+            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes + 1) * 32, reinterpret_cast<uint32_t*>(s1));
+            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes + 2) * 32, reinterpret_cast<uint32_t*>(s2));
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] = (sc[k] + s1[k]) + s2[k];
+          }
+          ptx::tc_fence_before();
+          signal_lead(&s_empty[b], s_empty_lead + b * 8);
+          SFA_PROF(1);
+          // ---- softmax in the log2 domain; keys past `cnt` are padding
+          if (cnt >= kSfaHalfBK) {
+#pragma unroll
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] *= a.scale_log2;
+          } else {
+#pragma unroll
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] = k < cnt ? sc[k] * a.scale_log2 : -INFINITY;
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int k = 0; k < kSfaHalfBK; k += 4) {
+            mx4[0] = fmaxf(mx4[0], sc[k]); mx4[1] = fmaxf(mx4[1], sc[k + 1]);
+            mx4[2] = fmaxf(mx4[2], sc[k + 2]); mx4[3] = fmaxf(mx4[3], sc[k + 3]);
+          }
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
+          SFA_PROF(2);
+          ok = exchange(xm + b * 128, mx, mx_other);
+          if (!ok) break;
+          SFA_PROF(3);
+          mx = fmaxf(mx, mx_other);       // the tile's maximum for this head (the first half always has a valid key)
+          m_true = fmaxf(m_true, mx);
+          float alpha = 1.f;
+          bool rescale = false;
+          if (t == 0) {
+            m_ref = mx;
+          } else if (mx > m_ref + kSfaRescaleTau) {
+            alpha = ex2(m_ref - mx);
+            m_ref = mx;
+            rescale = true;
+          }
+          float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int k = 0; k < kSfaHalfBK; k += 4) {
+            sc[k] = ex2(sc[k] - m_ref); sc[k + 1] = ex2(sc[k + 1] - m_ref);
+            sc[k + 2] = ex2(sc[k + 2] - m_ref); sc[k + 3] = ex2(sc[k + 3] - m_ref);
+            sum4[0] += sc[k]; sum4[1] += sc[k + 1]; sum4[2] += sc[k + 2]; sum4[3] += sc[k + 3];
+          }
+          l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+          if (ntiles == 1) {
+            // a single tile holds the whole row: normalise before rounding, as the golden does
+            float l_other;
+            ok = exchange(xs, l, l_other);
+            if (!ok) break;
+            l_tot = l + l_other;
+            const float inv = 1.f / l_tot;
+#pragma unroll
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] *= inv;
+          }
+          // ---- P (and, rarely, a rescaled O) once the product that last read this P buffer has finished
+          SFA_PROF(2);
+          ok = wait_w(&p_empty[b], (use & 1) ^ 1);
+          if (!ok) break;
+          SFA_PROF(4);
+          if (__any_sync(0xffffffffu, rescale)) {
+            // O must be quiescent: the previous tile's product (other P buffer) has to be complete too
+            const uint32_t prev = n_tile - 1;
+            ok = wait_w(&p_empty[prev & 1], (prev >> 1) & 1);
+            if (!ok) break;
+            ptx::tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              ptx::tmem_st_x32(lane_addr + kTmO + c * 32, o);
+            }
+            ptx::tmem_st_wait();
+          }
+          {
+            // row hl of the K-major, 128-byte-swizzled A operand: keys half*32 .. +31 are the 16-byte
+            // chunks half*4 .. +3 of the row
+            unsigned char* prow = p_s + b * kSfaPBuf + hl * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 w;
+              w.x = pack2(sc[8 * c], sc[8 * c + 1], a.is_bf16);
+              w.y = pack2(sc[8 * c + 2], sc[8 * c + 3], a.is_bf16);
+              w.z = pack2(sc[8 * c + 4], sc[8 * c + 5], a.is_bf16);
+              w.w = pack2(sc[8 * c + 6], sc[8 * c + 7], a.is_bf16);
+              *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (hl & 7)) << 4)) = w;
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          ptx::tc_fence_before();
+          signal_lead(&p_full[b], p_full_lead + b * 8);
+          SFA_PROF(5);
+        }
+        if (!ok) break;
+        SFA_PROF(7);
+        // ---- epilogue: wait for the last product, normalise, store
+        {
+          const uint32_t last = n_tile - 1;
+          ok = wait_w(&p_empty[last & 1], (last >> 1) & 1);
+          if (!ok) break;
+        }
+        ptx::tc_fence_after();
+        if (ntiles > 1) {
+          float l_other;
+          ok = exchange(xs, l, l_other);
+          if (!ok) break;
+          l_tot = l + l_other;
+        }
+        const float inv = ntiles == 1 ? 1.f : 1.f / l_tot;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          // c = j * 4 + chunk: accumulator columns c*32 .. +31 = value columns j*256 + half*128 + chunk*32 ..
+          uint32_t o[32];
+          ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
+          ptx::tmem_ld_wait();
+          const int col = (c >> 2) * 256 + (c & 3) * 32;   // relative to half * 128
+          if constexpr (kSplit) {
+            // split-KV: the normalised partial output stays fp32 for the merge
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(part_row + col)[i] =
+                  make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                              __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+          } else {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
+            // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's
+            if (hg < n1) {
+              ptx::st_global_v8(out_row + col * 2, w);
+              ptx::st_global_v8(out_row + col * 2 + 32, w + 8);
             }
           }
         }
-        continue;
-      }
-      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
-      for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-        const long long c0 = clock64();
-        const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK);
-        // ---- full S = own partial (staging halves) + the peer's partial (landing halves); each
-        // half is handed back as soon as it has been read
-        float sc[kSfaBK];
-        long long c1 = c0;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          ok = wait_wc(&x_full[hf], n_tile & 1);
-          if (!ok) break;
-          ok = wait_w(&own_full[hf], n_tile & 1);
-          if (!ok) break;
-          if (hf == 0) c1 = clock64();
-          const float* theirs = x_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
-          const float* mine = xo_s + hf * kSfaXHalfF + quarter * kSfaXWarpF + lane * 4;
-          float dep = 0.f;
-#pragma unroll
-          for (int c = 0; c < kSfaBK / 8; ++c) {
-            const float4 v = *reinterpret_cast<const float4*>(theirs + c * 128);
-            const float4 o = *reinterpret_cast<const float4*>(mine + c * 128);
-            const int k = hf * kSfaHalf + 4 * c;
-            sc[k] = v.x + o.x; sc[k + 1] = v.y + o.y; sc[k + 2] = v.z + o.z; sc[k + 3] = v.w + o.w;
-            dep += sc[k] + sc[k + 1] + sc[k + 2] + sc[k + 3];
-          }
-          __syncwarp();
-          if (lane == 0) {
-            // relaxed: nothing is published, the peer only learns that the reads are done (`dep`
-            // depends on every load of this half)
-            ptx::mbar_arrive_remote_relaxed(x_empty_peer + hf * 8, __float_as_uint(dep));
-            ptx::mbar_arrive(&own_free[hf]);
-          }
-        }
-        if (!ok) break;
-        // ---- softmax in the log2 domain; keys past `cnt` are padding
-        if (cnt == kSfaBK) {
-#pragma unroll
-          for (int k = 0; k < kSfaBK; ++k) sc[k] *= a.scale_log2;
-        } else {
-#pragma unroll
-          for (int k = 0; k < kSfaBK; ++k) sc[k] = k < cnt ? sc[k] * a.scale_log2 : -INFINITY;
-        }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int k = 0; k < kSfaBK; k += 4) {
-          mx4[0] = fmaxf(mx4[0], sc[k]); mx4[1] = fmaxf(mx4[1], sc[k + 1]);
-          mx4[2] = fmaxf(mx4[2], sc[k + 2]); mx4[3] = fmaxf(mx4[3], sc[k + 3]);
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const long long c2 = clock64();
-        m_true = fmaxf(m_true, mx);
-        float alpha = 1.f;
-        bool rescale = false;
-        if (t == 0) {
-          m_ref = mx;
-        } else if (mx > m_ref + kSfaRescaleTau) {
-          alpha = ex2(m_ref - mx);
-          m_ref = mx;
-          rescale = true;
-        }
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int k = 0; k < kSfaBK; k += 4) {
-          sc[k] = ex2(sc[k] - m_ref); sc[k + 1] = ex2(sc[k + 1] - m_ref);
-          sc[k + 2] = ex2(sc[k + 2] - m_ref); sc[k + 3] = ex2(sc[k + 3] - m_ref);
-          sum4[0] += sc[k]; sum4[1] += sc[k + 1]; sum4[2] += sc[k + 2]; sum4[3] += sc[k + 3];
-        }
-        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        if (ntiles == 1) {
-          // a single tile holds the whole row: normalise before rounding, as the golden does
-          const float inv = 1.f / l;
-#pragma unroll
-          for (int k = 0; k < kSfaBK; ++k) sc[k] *= inv;
-        }
-        const long long c3 = clock64();
-        // ---- P (and, rarely, a rescaled O) -> tensor memory once the previous PV has finished
-        ok = wait_w(p_empty, (n_tile & 1) ^ 1);
-        const long long c4 = clock64();
-        if (!ok) break;
-        ptx::tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {
-#pragma unroll 1
-          for (int c = 0; c < kSfaDvHalf / 32; ++c) {
-            uint32_t o[32];
-            ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ptx::tmem_st_x32(lane_addr + kTmO + c * 32, o);
-          }
-        }
-        {
-          uint32_t pw[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pw[i] = i < kSfaBK / 2 ? pack2(sc[2 * i], sc[2 * i + 1], a.is_bf16) : 0u;
-          ptx::tmem_st_x32(lane_addr + kTmP, pw);
-        }
-        ptx::tmem_st_wait();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(p_full);
-        prof[0] += c1 - c0; prof[1] += c2 - c1; prof[2] += c3 - c2; prof[3] += c4 - c3; prof[4] += clock64() - c4;
-        prof[5] += 1;
-      }
-      if (!ok) break;
-      // ---- epilogue: wait for the last PV, normalise, store
-      const long long ce0 = clock64();
-      ok = wait_w(p_empty, (n_tile & 1) ^ 1);
-      if (!ok) break;
-      prof[8] += clock64() - ce0;
-      ptx::tc_fence_after();
-      const float inv = ntiles == 1 ? 1.f : 1.f / l;
-#pragma unroll 1
-      for (int c = 0; c < kSfaDvHalf / 32; ++c) {
-        uint32_t o[32];
-        ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
-        ptx::tmem_ld_wait();
-        if constexpr (kSplit) {
-          // split-KV: the normalised partial output stays fp32 for the merge
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            reinterpret_cast<float4*>(part_row + c * 32)[i] =
-                make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
-                            __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
-        } else {
-          uint32_t w[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
-          // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's, so every
-          // store of a warp touches 32 different lines and the request count is what costs
-          if (h < n1) {
-            ptx::st_global_v8(out_row + c * 64, w);
-            ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
+        signal_lead(o_free, o_free_lead);
+        SFA_PROF(6);
+        if (half == 0) {
+          // max of the scaled scores and sum of exp(score - max), back from the log2 domain
+          if constexpr (kSplit) {
+            a.part_m[(int64_t)item * kSfaHeads + hg] = m_true * 0.6931471805599453f;
+            a.part_l[(int64_t)item * kSfaHeads + hg] = l_tot * ex2(m_ref - m_true);
+          } else if (a.p.return_lse && hg < n1) {
+            a.p.softmax_max[(int64_t)row * n1 + hg] = m_true * 0.6931471805599453f;
+            a.p.softmax_sum[(int64_t)row * n1 + hg] = l_tot * ex2(m_ref - m_true);
           }
         }
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(o_free);
-      prof[7] += clock64() - ce0;
-      if constexpr (kSplit) {
-        if (rank == 0) {
-          a.part_m[(int64_t)item * kSfaHeads + h] = m_true * 0.6931471805599453f;
-          a.part_l[(int64_t)item * kSfaHeads + h] = l * ex2(m_ref - m_true);
-        }
-      } else if (rank == 0 && a.p.return_lse && h < n1) {
-        // max of the scaled scores and sum of exp(score - max), back from the log2 domain
-        a.p.softmax_max[(int64_t)row * n1 + h] = m_true * 0.6931471805599453f;
-        a.p.softmax_sum[(int64_t)row * n1 + h] = l * ex2(m_ref - m_true);
-      }
-    }
-    if (a.prof != nullptr && blockIdx.x == 0 && quarter == 0 && lane == 0) {
-#pragma unroll
-      for (int i = 0; i < 12; ++i) a.prof[i] = prof[i];
-    }
+      SFA_PROF_STORE(4, threadIdx.x == kSfaSoftWarp0 * 32);
     }
   }
 
@@ -701,26 +752,26 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   }
   ptx::tc_fence_before();
   __syncthreads();
-  // neither CTA may leave while its peer can still write into its shared memory
+  // neither CTA may leave while its peer can still signal it or run a pair MMA on its memory
   ptx::cluster_arrive();
   ptx::cluster_wait();
-  if (warp == kSfaMmaWarp) {
+  if (warp == kSfaQkWarp0) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, 512);
+    ptx::tmem_dealloc_pair(tmem, 512);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(a.status, misaligned ? 2 : 1);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
 inline bool sfa_sm100_eligible(const DsaSfaParams* p) {
-  // fewer than 128 heads (a tensor-parallel shard) run with the spare lanes carrying zero queries;
+  // fewer than 128 heads (a tensor-parallel shard) run with the spare rows carrying zero queries;
   // below 16 heads the portable kernel wastes less
   if (p->n1 < 16 || p->n1 > kSfaHeads || p->d != 512 || p->d_rope != 64) return false;
   if ((int64_t)p->sparse_count * p->sparse_block_size > kSfaMaxSlots) return false;
   if (((uintptr_t)p->query & 15u) || ((uintptr_t)p->query_rope & 15u) || ((uintptr_t)p->key & 15u) ||
       ((uintptr_t)p->key_rope & 15u) || ((uintptr_t)p->out & 31u))
     return false;
-  if (p->key_rows < 1 || p->key_rows >= (1ll << 31)) return false;
+  if (p->key_rows < 1 || p->key_rows >= (1ll << 31) - 1) return false;
   const int64_t rows_ = p->layout_q == DSA_LAYOUT_TND ? p->s1 : (int64_t)p->batch * p->s1;
   if (rows_ * p->sparse_count * p->sparse_block_size >= (1ll << 31)) return false;   // key_list offsets are int32
   return true;
@@ -733,8 +784,8 @@ __global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split,
                                                         const float* __restrict__ part_l, int32_t is_bf16) {
   const int32_t row = blockIdx.x;
   // blockIdx.y: group of 8 heads
-  for (int32_t e = threadIdx.x; e < 8 * (2 * kSfaDvHalf / 4); e += 256) {
-    const int32_t h = blockIdx.y * 8 + e / (2 * kSfaDvHalf / 4), c4 = e % (2 * kSfaDvHalf / 4);
+  for (int32_t e = threadIdx.x; e < 8 * (kSfaDv / 4); e += 256) {
+    const int32_t h = blockIdx.y * 8 + e / (kSfaDv / 4), c4 = e % (kSfaDv / 4);
     if (h >= p.n1) continue;
     float mx = -INFINITY;
     for (int32_t q = 0; q < split; ++q) {
@@ -748,7 +799,7 @@ __global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split,
       const float l = part_l[i];
       if (l > 0.f) {
         const float w = l * __expf(part_m[i] - mx);
-        const float4 o = reinterpret_cast<const float4*>(part_o + i * (2 * kSfaDvHalf))[c4];
+        const float4 o = reinterpret_cast<const float4*>(part_o + i * kSfaDv)[c4];
         acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
         den += w;
       }
@@ -757,7 +808,7 @@ __global__ void __launch_bounds__(256) sfa_merge_kernel(SfaDev p, int32_t split,
     uint2 packed;
     packed.x = pack2(acc.x * inv, acc.y * inv, is_bf16);
     packed.y = pack2(acc.z * inv, acc.w * inv, is_bf16);
-    reinterpret_cast<uint2*>((unsigned char*)p.out + ((int64_t)row * p.n1 + h) * (2 * kSfaDvHalf) * 2)[c4] = packed;
+    reinterpret_cast<uint2*>((unsigned char*)p.out + ((int64_t)row * p.n1 + h) * kSfaDv * 2)[c4] = packed;
     if (c4 == 0 && p.return_lse) {
       p.softmax_max[(int64_t)row * p.n1 + h] = den > 0.f ? mx : 0.f;
       p.softmax_sum[(int64_t)row * p.n1 + h] = den;
@@ -795,7 +846,7 @@ inline SfaWsLayout sfa_sm100_ws_layout(int64_t rows, int64_t slots) {
   const size_t stats = split > 1 ? up((size_t)rows * split * kSfaHeads * 4) : 0;
   w.part_l = w.part_m + stats;
   w.part_o = w.part_l + stats;
-  w.total = w.part_o + (split > 1 ? (size_t)rows * split * kSfaHeads * 2 * kSfaDvHalf * 4 : 0);
+  w.total = w.part_o + (split > 1 ? (size_t)rows * split * kSfaHeads * kSfaDv * 4 : 0);
   return w;
 }
 inline size_t sfa_sm100_workspace_bytes(const DsaSfaParams* p) {
@@ -804,20 +855,32 @@ inline size_t sfa_sm100_workspace_bytes(const DsaSfaParams* p) {
   return sfa_sm100_ws_layout(rows, slots).total;
 }
 
+// SM count of a device, queried once per device; the first call on a device also raises the
+// kernels' shared-memory limit there.  Safe to call from several host threads.
+inline int sfa_sm100_device_sms(int dev) {
+  static std::atomic<int> sm_count[64];
+  static std::mutex setup_lock;
+  if (dev < 0 || dev >= 64) return 0;
+  int n = sm_count[dev].load(std::memory_order_acquire);
+  if (n > 0) return n;
+  std::lock_guard<std::mutex> g(setup_lock);
+  n = sm_count[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 2) return 0;
+  if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)kSfaSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(sfa_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)kSfaSmemBytes) != cudaSuccess)
+    return 0;
+  sm_count[dev].store(n, std::memory_order_release);
+  return n;
+}
+
 inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* status, void* scratch, cudaStream_t st) {
-  static int sm_count[64] = {0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
-  if (sm_count[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 2) return DSA_ERR_CUDA;
-    if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kSfaSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(sfa_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kSfaSmemBytes) != cudaSuccess)
-      return DSA_ERR_CUDA;
-    sm_count[dev] = n;
-  }
+  if (cudaGetDevice(&dev) != cudaSuccess) return DSA_ERR_CUDA;
+  const int sms = sfa_sm100_device_sms(dev);
+  if (sms < 2) return DSA_ERR_CUDA;
   const bool bf16 = p->dtype == DSA_DTYPE_BF16;
   const int64_t slots = (int64_t)p->sparse_count * p->sparse_block_size;
   const SfaWsLayout w = sfa_sm100_ws_layout(d.rows, slots);
@@ -825,17 +888,15 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   const int32_t part_keys = split > 1 ? sfa_sm100_part_keys(slots, split) : (int32_t)((slots + kSfaBK - 1) / kSfaBK) * kSfaBK;
   int2* nvalid = reinterpret_cast<int2*>((char*)scratch + w.nvalid);
   int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + w.key_list);
-  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys);
+  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   SfaSm100Args a;
   a.p = d;
   a.status = status;
-  a.rows = d.rows;
   a.idesc_qk = ptx::idesc_f16(bf16 ? 1u : 0u, 128, kSfaBK, 0, 0);
-  a.idesc_pv = ptx::idesc_f16(bf16 ? 1u : 0u, 128, kSfaDvHalf, 0, 1);
+  a.idesc_pv = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 1);
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.is_bf16 = bf16 ? 1 : 0;
-  a.prof = getenv("DSA_SFA_PROFILE") ? reinterpret_cast<long long*>(status + 16) : nullptr;
   a.nvalid = nvalid;
   a.key_list = key_list;
   a.split = split;
@@ -844,13 +905,22 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.part_m = reinterpret_cast<float*>((char*)scratch + w.part_m);
   a.part_l = reinterpret_cast<float*>((char*)scratch + w.part_l);
   a.part_o = reinterpret_cast<float*>((char*)scratch + w.part_o);
-  int clusters = sm_count[dev] / 2;
+  int clusters = sms / 2;
+#ifdef DSA_SFA_MAX_CLUSTERS
+  clusters = DSA_SFA_MAX_CLUSTERS;
+#endif
   if (clusters > a.items) clusters = a.items;
-  CUtensorMap tkn, tkr;
+  CUtensorMap tkn, tkr, tq, tqr;
   if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;
   if (!make_tmap_gather4_16bit(&tkr, p->key_rope, (uint64_t)p->key_rows, 64, 128, 64, bf16)) return DSA_ERR_CUDA;
-  if (split > 1) sfa_fwd_sm100_kernel<true><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
-  else sfa_fwd_sm100_kernel<false><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, a);
+  if (!make_tmap_3d_16bit(&tq, p->query, (uint64_t)d.rows, (uint64_t)p->n1, 512, 1024, (uint64_t)p->n1 * 1024,
+                          kSfaCtaHeads, 64, bf16))
+    return DSA_ERR_CUDA;
+  if (!make_tmap_3d_16bit(&tqr, p->query_rope, (uint64_t)d.rows, (uint64_t)p->n1, 64, 128, (uint64_t)p->n1 * 128,
+                          kSfaCtaHeads, 64, bf16))
+    return DSA_ERR_CUDA;
+  if (split > 1) sfa_fwd_sm100_kernel<true><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, tq, tqr, a);
+  else sfa_fwd_sm100_kernel<false><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, tq, tqr, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   if (split > 1) {
     sfa_merge_kernel<<<dim3(d.rows, kSfaHeads / 8), 256, 0, st>>>(d, split, a.part_o, a.part_m, a.part_l, a.is_bf16);

@@ -21,8 +21,8 @@ import os
 import torch
 
 from . import _cabi
-from ._host import (INT64_MAX, current_stream, dtype_code, max_len_from_cumulative, ptr, require_cuda,
-                    seq_tensor, workspace)
+from ._host import (INT64_MAX, current_stream, dtype_code, max_len_from_cumulative, note_launch, ptr,
+                    require_cuda, seq_tensor, workspace)
 
 _RANK_MODES = {"io_dtype": _cabi.RANK_IO_DTYPE, "fp32": _cabi.RANK_FP32}
 _rank_mode = os.environ.get("DSA_LI_RANK_MODE", "io_dtype")
@@ -44,7 +44,7 @@ def set_kernel(kind):
 
 
 def _build_params(query, key, weights, actual_seq_lengths_query, actual_seq_lengths_key, block_table,
-                  layout_query, layout_key, sparse_count, sparse_mode, return_value):
+                  layout_query, layout_key, sparse_count, sparse_mode, return_value, max_seqlen_key=None):
     if layout_query not in ("BSND", "TND"):
         raise ValueError(f"layout_query must be BSND or TND, got {layout_query}")
     if layout_key not in ("BSND", "TND", "PA_BSND"):
@@ -71,9 +71,10 @@ def _build_params(query, key, weights, actual_seq_lengths_query, actual_seq_leng
     seq_q, host_q = seq_tensor(actual_seq_lengths_query, dev)
     seq_k, host_k = seq_tensor(actual_seq_lengths_key, dev)
     # As in the reference, a TND query makes both length arguments cumulative
-    # (lightning_indexer_triton.py:507-509), whatever the key layout is.
+    # (lightning_indexer_triton.py:507-509) for BSND and TND keys.  A paged cache always takes
+    # per-batch key lengths, like the attention operator (sparse_flash_attention_triton.py:1379).
     q_cum = 1 if is_tnd else 0
-    k_cum = 1 if is_tnd else 0
+    k_cum = 1 if (is_tnd and layout_key != "PA_BSND") else 0
     B = seq_q.shape[0] if is_tnd else batch_dim
 
     block_size = max_blocks = 0
@@ -89,7 +90,10 @@ def _build_params(query, key, weights, actual_seq_lengths_query, actual_seq_leng
                 raise ValueError("TND key requires cumulative actual_seq_lengths_key")
             k_cum = 1
         N2 = key.shape[1]
-        s2 = max_len_from_cumulative(host_k, key.shape[0])
+        # Longest key sequence: sizes the score scratch (rows x s2 fp32) and picks the top-k kernel.
+        # With lengths on the device it is unknown without a sync, so the total token count stands
+        # in unless the caller passes max_seqlen_key (as varlen attention interfaces do).
+        s2 = int(max_seqlen_key) if max_seqlen_key is not None else max_len_from_cumulative(host_k, key.shape[0])
     else:
         if key.dim() != 4:
             raise ValueError("PA_BSND key must be [num_blocks, block_size, N2, D]")
@@ -150,6 +154,7 @@ def lightning_indexer_triton(
     pre_tokens=INT64_MAX,
     next_tokens=INT64_MAX,
     return_value=False,
+    max_seqlen_key=None,
 ):
     """Top-`sparse_count` keys per query row of sum_g relu(q_g . k) * w_g.
 
@@ -162,6 +167,9 @@ def lightning_indexer_triton(
         sparse_count: top-k count; sparse_mode: 0 full, 3 rightDownCausal
         pre_tokens / next_tokens: accepted and ignored, as in the reference
         return_value: also return the selected scores (else zeros)
+        max_seqlen_key: (addition) upper bound of the per-sequence key length for a TND key whose
+            cumulative lengths live on the device; without it the total key count T2 is used, which
+            makes the score scratch rows x T2 fp32 and sends every row to the generic top-k kernel
 
     Returns:
         (indices int32, values in the query dtype), shape [B,S1,N2,sparse_count] or
@@ -172,7 +180,7 @@ def lightning_indexer_triton(
         raise ValueError("Only sparse_mode 0 (full) / 3 (rightDownCausal) supported")
     p, keep, idx, val, out_shape = _build_params(
         query, key, weights, actual_seq_lengths_query, actual_seq_lengths_key, block_table,
-        layout_query, layout_key, sparse_count, sparse_mode, return_value)
+        layout_query, layout_key, sparse_count, sparse_mode, return_value, max_seqlen_key)
     dev = query.device
     with torch.cuda.device(dev):
         nbytes = ctypes.c_size_t(0)
@@ -180,6 +188,7 @@ def lightning_indexer_triton(
         ws = workspace(nbytes.value, dev)
         _cabi.check(_cabi.lib.dsa_li_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), current_stream(dev)),
                     "lightning_indexer")
+        note_launch("lightning_indexer", ws, dev)
     del keep
     indices = idx.view(out_shape)
     values = val.view(out_shape) if val is not None else torch.zeros(out_shape, dtype=query.dtype, device=dev)

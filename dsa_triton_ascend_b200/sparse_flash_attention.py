@@ -12,8 +12,8 @@ import ctypes
 import torch
 
 from . import _cabi
-from ._host import (INT64_MAX, current_stream, dtype_code, max_len_from_cumulative, ptr, require_cuda,
-                    seq_tensor, workspace)
+from ._host import (INT64_MAX, current_stream, dtype_code, max_len_from_cumulative, note_launch, ptr,
+                    require_cuda, seq_tensor, workspace)
 
 _VALID_D = (128, 256, 512)
 _D_ROPE = 64
@@ -178,6 +178,7 @@ def sparse_flash_attention_triton(
             ws = workspace(nbytes.value, dev)
             _cabi.check(_cabi.lib.dsa_sfa_forward(ctypes.byref(p), ws.data_ptr(), ws.numel(), current_stream(dev)),
                         "sparse_flash_attention")
+            note_launch("sparse_flash_attention", ws, dev)
     if not return_softmax_lse:
         sm_max = torch.zeros(stat_shape, dtype=torch.float32, device=dev)
         sm_sum = torch.zeros(stat_shape, dtype=torch.float32, device=dev)
