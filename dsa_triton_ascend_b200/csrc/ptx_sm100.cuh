@@ -36,11 +36,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
+#ifdef DSA_EXP_TESTWAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity), "r"(8000u)  // suspend-time hint in ns
       : "memory");
+#endif
   return done != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets the other warps of a CTA leave quickly once
@@ -49,6 +57,9 @@ constexpr uint32_t kWaitPolls = 1u << 20;  // x (up to) 8 us per poll: gives up 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kWaitPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef DSA_EXP_SLEEP
+    __nanosleep(DSA_EXP_SLEEP);
+#endif
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -71,6 +82,17 @@ __device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
 }
 __device__ __forceinline__ void st_cluster_v4(uint32_t raddr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4_b32(uint32_t raddr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Asynchronous 16-byte store into another CTA of the cluster; when the bytes have landed they are
+// counted as transaction bytes on an mbarrier of the destination CTA (no wait on the sender side).
+__device__ __forceinline__ void st_async_v4(uint32_t raddr, uint4 v, uint32_t raddr_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(raddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(raddr_bar)
                : "memory");
 }
 // Arrive on an mbarrier of another CTA of the cluster; orders this thread's earlier (remote) writes.
@@ -100,11 +122,19 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
+#ifdef DSA_EXP_TESTWAIT
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
       "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)  // suspend-time hint in ns
       : "memory");
+#endif
   return done != 0;
 }
 
@@ -117,12 +147,17 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #endif
 }
+// all state spaces (covers rows written into a peer CTA's shared memory)
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < (kWaitPolls << 2); ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
+#ifdef DSA_EXP_SLEEP
+    __nanosleep(DSA_EXP_SLEEP);
+#endif
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -265,6 +300,9 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
 }
 __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
+#ifdef DSA_EXP_NOMMA
+  return;
+#endif
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"

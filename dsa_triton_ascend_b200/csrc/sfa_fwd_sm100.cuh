@@ -49,14 +49,14 @@ constexpr int kSfaHeads = 128;       // heads per CTA pair
 constexpr int kSfaCtaHeads = 64;
 constexpr int kSfaBK = 64;           // keys per tile
 constexpr int kSfaHalfBK = 32;       // keys of a tile each CTA gathers for the score product
-constexpr int kSfaThreads = 640;
+constexpr int kSfaThreads = 768;
 constexpr int kSfaQkLanes = 3;       // QK^T issuers; issuer i owns feature blocks 3i..3i+2 and a partial S
-constexpr int kSfaKWarps = 6;        // warps 0..5: K gather producers, two per issuer
-constexpr int kSfaVWarp = 6;         // V copier
-constexpr int kSfaQWarp = 7;         // Q loader
-constexpr int kSfaQkWarp0 = 8;       // warps 8..10
-constexpr int kSfaPvWarp = 11;
-constexpr int kSfaSoftWarp0 = 16;    // warps 16..19 (12..15 idle)
+constexpr int kSfaKWarps = 9;        // warps 0..8: K gather producers, three per issuer
+constexpr int kSfaQWarp = 9;         // Q loader (warps 10, 11 idle)
+constexpr int kSfaQkWarp0 = 12;      // warps 12..14
+constexpr int kSfaPvWarp = 15;
+constexpr int kSfaCopyWarp0 = 16;    // warps 16..19: V copiers
+constexpr int kSfaSoftWarp0 = 20;    // warps 20..23
 constexpr int kSfaDv = 512;
 constexpr int kSfaMaxSlots = 8192;   // sparse_count * sparse_block_size served by this kernel
 
@@ -77,6 +77,15 @@ constexpr uint32_t kSfaOffBar = kSfaOffX + 3 * 128 * 4;
 constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 512;
 static_assert(kSfaOffK % 1024 == 0 && kSfaOffV % 1024 == 0 && kSfaOffP % 1024 == 0, "operand alignment");
 static_assert(kSfaSmemBytes <= 232448, "shared memory");
+
+// setmaxnreg.inc only ever gets registers that warps of the SAME CTA have released and blocks (for
+// good) until it has them: what the softmax warps ask for must fit into what the others give back.
+constexpr int kSfaLaunchRegs = 80;   // 65536 / 768 threads, rounded down to a multiple of 8
+constexpr int kSfaRegsLow = 56, kSfaRegsHigh = 168;
+static_assert((kSfaRegsHigh - kSfaLaunchRegs) * (kSfaThreads / 32 - kSfaSoftWarp0) <=
+                  (kSfaLaunchRegs - kSfaRegsLow) * kSfaCopyWarp0,
+              "setmaxnreg: more registers requested than released");
+static_assert(kSfaLaunchRegs * kSfaThreads <= 65536, "register file");
 
 constexpr uint32_t kTmO = 0, kTmS = 256;
 constexpr float kSfaRescaleTau = 8.f;  // log2 units: the running reference only moves when exceeded by this
@@ -183,9 +192,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   // K barriers are indexed [slot * 3 + issuer]: every issuer's three feature blocks are handed over
   // and released on their own.
   uint64_t* k_full = bars;         // [6] gather -> QK issuer / relay                 (tx bytes)
-  uint64_t* k_empty = bars + 6;    // [6] blocks read by the issuer's MMAs (commit) and by both CTAs' V copiers -> K producers
+  uint64_t* k_empty = bars + 6;    // [6] blocks read by the issuer's MMAs (commit) and by the four copier warps -> K producers
   uint64_t* k_ready = bars + 12;   // [6] even CTA only: the odd CTA's blocks have landed
-  uint64_t* v_full = bars + 18;    // [2] bulk copies of both CTAs -> PV issuer / relay, V copier (tx bytes)
+  uint64_t* v_full = bars + 18;    // [2] own copier warps (4 arrivals + 1 arming) and the peer's st.async bytes -> PV issuer / relay
   uint64_t* v_empty = bars + 20;   // [2] PV of the tile done -> V copier              (commit, both CTAs)
   uint64_t* v_ready = bars + 22;   // [2] even CTA only: the odd CTA's V slot has landed
   uint64_t* s_full = bars + 24;    // [2] all three partial products done -> softmax   (commit x 3, both CTAs)
@@ -208,17 +217,22 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   const bool misaligned = (ptx::smem_u32(sfa_sm) & 1023u) != 0;
   if (threadIdx.x == 0) {
     for (int i = 0; i < 6; ++i) {
-      ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 3); ptx::mbar_init(&k_ready[i], 1);
+      ptx::mbar_init(&k_full[i], 1); ptx::mbar_init(&k_empty[i], 5); ptx::mbar_init(&k_ready[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&v_full[i], 1); ptx::mbar_init(&v_empty[i], 1); ptx::mbar_init(&v_ready[i], 1);
+      ptx::mbar_init(&v_full[i], 5); ptx::mbar_init(&v_empty[i], 1); ptx::mbar_init(&v_ready[i], 1);
       ptx::mbar_init(&s_full[i], kSfaQkLanes); ptx::mbar_init(&s_empty[i], 8);
       ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
     }
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_ready, 1);
     ptx::mbar_init(q_empty, kSfaQkLanes);
+#ifdef DSA_EXP_PRODONLY
+    ptx::mbar_init(o_free, kSfaKWarps);
+    reinterpret_cast<volatile int*>(xs)[0] = 0; reinterpret_cast<volatile int*>(xs)[1] = 0;
+#else
     ptx::mbar_init(o_free, 8);
+#endif
     ptx::mbar_init(x_bar, 4);
     *abort_flag = misaligned ? 1 : 0;
     ptx::mbar_fence_init();
@@ -239,23 +253,25 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   auto item_tiles = [&](int32_t item) -> int32_t { return (a.nvalid[item].x + kSfaBK - 1) / kSfaBK; };
 
   if (warp < kSfaSoftWarp0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    // registers: kSfaLaunchRegs per thread at launch; producers and issuers give some back, the
+    // softmax warps take them (whole warpgroups of four warps change together)
+    if (warp < kSfaCopyWarp0) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSfaRegsLow));
     if (*abort_flag) {
       // nothing started: fall through to the teardown
     } else if (warp < kSfaKWarps) {
       // ------------------------------------------------------------------ K gather producers
-      // Two warps per QK^T issuer: 8 row groups (4 of this CTA's 32 keys each) x the issuer's 3
-      // column blocks = 24 gather4 loads of 512 bytes per tile, dealt out over the two warps (a
-      // warp issues one such load every ~70 cycles whatever the lane pattern, warps issue in
-      // parallel, the SM's TMA unit takes one every ~18 cycles).
-      const int qi = warp >> 1;                          // the issuer this warp feeds
-      const int gw = warp & 1;
-      const int o = gw + 2 * lane;
+      // Three warps per QK^T issuer: 8 row groups (4 of this CTA's 32 keys each) x the issuer's 3
+      // column blocks = 24 gather4 loads of 512 bytes per tile, dealt out over the three warps.
+      // Measured in this kernel: the lanes of a warp issue one after the other, ~220 cycles per
+      // load; warps issue in parallel until the SM's TMA unit saturates at one load per ~18 cycles
+      // (28 B/clk, bulk copies included) - which is why nothing but these loads goes through it.
+      const int qi = warp / 3;                           // the issuer this warp feeds
+      const int gw = warp - qi * 3;
+      const int o = gw + 3 * lane;
       const bool active = o < 24;
       const int grp = o / 3, blk = 3 * qi + (o - grp * 3);
       const int key0 = (int)rank * kSfaHalfBK + grp * 4;   // first key (within the tile) of this load
       const int32_t x = blk < 8 ? blk * 64 : 0;
-      const CUtensorMap* tm = blk == 8 ? &tmap_kr : &tmap_kn;
       unsigned char* slot0 = k_s + blk * kSfaKBlk + grp * 512;
       uint64_t* full = k_full + qi;                      // slot s: full[s * 3]
       uint64_t* empty = k_empty + qi;
@@ -291,12 +307,29 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         load_rows(nxt, rn);
         const uint32_t s = n_tile & 1, use = n_tile >> 1;
         SFA_PROF(0);
-        if (lane == 0) ok = ptx::mbar_wait_cluster(&empty[s * 3], (use & 1) ^ 1, abort_flag);
+#ifndef DSA_EXP_PRODONLY
+        ok = ptx::mbar_wait_warp(&empty[s * 3], (use & 1) ^ 1, abort_flag);
+#else
+        // timing experiment: no consumer; a slot is re-armed once its previous load has landed
+        if (lane == 0 && use > 0) ok = ptx::mbar_wait(&full[s * 3], (use - 1) & 1, abort_flag);
+#endif
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
         SFA_PROF(1);
         if (gw == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&full[s * 3], kSfaKSub);
-        if (active) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, tm, &full[s * 3], x, rc[0], rc[1], rc[2], rc[3]);
+        __syncwarp();
+        SFA_PROF(3);
+        // the tensor map is named directly in each call (a map chosen through a per-lane pointer
+        // costs an address conversion per load)
+        if (active) {
+#ifdef DSA_EXP_ONEMAP
+          if (blk == 8) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kn, &full[s * 3], 0, rc[0], rc[1], rc[2], rc[3]);
+#else
+          if (blk == 8) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kr, &full[s * 3], 0, rc[0], rc[1], rc[2], rc[3]);
+#endif
+          else ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kn, &full[s * 3], x, rc[0], rc[1], rc[2], rc[3]);
+        }
+        SFA_PROF(4);
         __syncwarp();
         SFA_PROF(2);
         ++n_tile;
@@ -304,54 +337,95 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 #pragma unroll
         for (int i = 0; i < 4; ++i) rc[i] = rn[i];
       }
-      SFA_PROF_STORE(0, lane == 0 && warp == 0);
-    } else if (warp == kSfaVWarp) {
-      // ------------------------------------------------------------------ V copier
-      // The value operand of a tile (all 64 keys x this CTA's 256 value columns) is not gathered
-      // again: every CTA already holds its own 32 keys with all columns in its K slot.  Per tile
-      // eight 4 KB bulk copies (lanes 0..7) move the four column blocks that this CTA owns into
-      // its own V slot and the four that the peer owns into the peer's V slot (distributed shared
-      // memory), rows 32*rank.. of every block.  A K slot may be refilled once the score MMAs AND
-      // these copies have read it: the copier tells its own K producers when its V slot is complete
-      // (its local copies are then done) and the peer's K producers at the same moment (the peer's
-      // copies into this CTA are then done).
-      const uint32_t peer = rank ^ 1u;
-      const int dst_rank = (lane & 4) ? (int)peer : (int)rank;          // lanes 0..3 local, 4..7 to the peer
-      const int pblk = lane & 3;                                        // V block: j = pblk >> 1, h = pblk & 1
-      const int fblk = 4 * (pblk >> 1) + 2 * dst_rank + (pblk & 1);     // feature block holding those columns
-      const uint32_t dst0 = ptx::map_to_rank(v_s + pblk * kSfaVBlk + rank * kSfaKBlk, (uint32_t)dst_rank);
-      const uint32_t bar0 = ptx::map_to_rank(v_full, (uint32_t)dst_rank);
-      const uint32_t k_empty_peer = ptx::map_to_rank(k_empty, peer);
-      uint32_t n_tile = 0;
-      bool ok = true;
-      SFA_PROF_DECL;
-      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
-        const int32_t ntiles = item_tiles(item);
-        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-          const uint32_t b = n_tile & 1, use = n_tile >> 1;
-          SFA_PROF(0);
-          // V slot b is free in both CTAs once the product that read it has completed
-          ok = ptx::mbar_wait_warp(&v_empty[b], (use & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          SFA_PROF(1);
-          if (lane == 0) ptx::mbar_arrive_expect_tx(&v_full[b], kSfaVSlot);
-          ok = ptx::mbar_wait_warp(&k_full[b * 3], use & 1, abort_flag) && ptx::mbar_wait_warp(&k_full[b * 3 + 1], use & 1, abort_flag) &&
-               ptx::mbar_wait_warp(&k_full[b * 3 + 2], use & 1, abort_flag);
-          if (!ok) break;
-          SFA_PROF(2);
-          if (lane < 8)
-            ptx::bulk_copy_to_peer(dst0 + b * kSfaVSlot, k_s + b * kSfaKSlot + fblk * kSfaKBlk, kSfaKBlk, bar0 + b * 8);
-          __syncwarp();
-          SFA_PROF(3);
-          ok = ptx::mbar_wait_cluster_warp(&v_full[b], use & 1, abort_flag);
-          if (!ok) break;
-          SFA_PROF(4);
-          if (lane < 3) ptx::mbar_arrive(&k_empty[b * 3 + lane]);
-          else if (lane < 6) ptx::mbar_arrive_remote_relaxed(k_empty_peer + (b * 3 + lane - 3) * 8, 0u);
-          __syncwarp();
+#ifdef DSA_EXP_PRODONLY
+      // drain: the last loads of both slots must have landed before the CTA may exit
+      if (lane == 0) {
+        for (uint32_t back = 1; back <= 2 && back <= n_tile; ++back) {
+          const uint32_t n = n_tile - back;
+          ptx::mbar_wait(&full[(n & 1) * 3], (n >> 1) & 1, abort_flag);
         }
       }
-      SFA_PROF_STORE(1, lane == 0);
+      __syncwarp();
+      if (lane == 0) { ptx::mbar_arrive(o_free); atomicAdd(reinterpret_cast<int*>(xs) + 1, 1); if (reinterpret_cast<volatile int*>(xs)[1] == kSfaKWarps) *reinterpret_cast<volatile int*>(xs) = 1; }
+#endif
+      SFA_PROF_STORE(0, lane == 0 && warp == 0);
+#ifdef DSA_EXP_PRODONLY
+    } else if (true) {
+#if DSA_EXP_PRODONLY == 2
+      ptx::mbar_wait_warp(o_free, 0, abort_flag);          // o_free: 8 arrivals... re-initialised below to 9
+#elif DSA_EXP_PRODONLY == 3
+      while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500);
+#elif DSA_EXP_PRODONLY >= 4
+      // waits that give up as soon as the producers of this CTA are done (timing experiments only)
+      auto fwait = [&](uint64_t* bar, uint32_t par) -> bool {
+        bool got = true;
+        while (!ptx::mbar_try_wait(bar, par)) { if (*reinterpret_cast<volatile int*>(xs) != 0) { got = false; break; } }
+        return __all_sync(0xffffffffu, got);
+      };
+#endif
+#if DSA_EXP_PRODONLY == 4
+      // one warp per CTA keeps issuing tcgen05.commit (even CTA, multicast) and both wait for it
+      if (warp == 12) {
+        uint32_t ph = 0;
+        while (*reinterpret_cast<volatile int*>(xs) == 0) {
+          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);   // count 3 -> needs 3 commits per phase
+          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);
+          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);
+          __syncwarp();
+          if (!fwait(&s_full[0], ph & 1)) break;
+          ++ph;
+          __nanosleep(200);
+        }
+      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
+#elif DSA_EXP_PRODONLY == 5
+      // four warps ping-pong through shared memory + an mbarrier (like the softmax exchange)
+      if (warp >= 16 && warp < 20) {
+        uint32_t ph = 0;
+        const int L = (warp - 16) * 32 + lane;
+        while (*reinterpret_cast<volatile int*>(xs) == 0) {
+          xm[L] = (float)ph;
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(x_bar);
+          if (!fwait(x_bar, ph & 1)) break;
+          ++ph;
+          if (xm[L ^ 64] < 0.f) break;
+          __nanosleep(200);
+        }
+      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
+#elif DSA_EXP_PRODONLY == 6
+      // the odd CTA's warp 12 keeps sending relaxed remote arrivals to the even CTA's warp 12, which waits for them
+      if (warp == 12) {
+        uint32_t ph = 0;
+        const uint32_t rb = ptx::map_to_rank(q_ready, 0);
+        while (*reinterpret_cast<volatile int*>(xs) == 0) {
+          if (rank != 0) { if (ptx::elect_one()) ptx::mbar_arrive_remote_relaxed(rb, 0u); __syncwarp(); __nanosleep(400); }
+          else { if (!fwait(q_ready, ph & 1)) break; ++ph; }
+        }
+      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
+#elif DSA_EXP_PRODONLY == 8 || DSA_EXP_PRODONLY == 9
+      // idle warps watch the very barriers the gathers complete on (8: five warps, all lanes; 9: one lane of one warp)
+      if ((DSA_EXP_PRODONLY == 8 && (warp == 12 || (warp >= 16 && warp < 20))) || (DSA_EXP_PRODONLY == 9 && warp == 12)) {
+        for (uint32_t n = 0; *reinterpret_cast<volatile int*>(xs) == 0; ++n) {
+          const uint32_t b = n & 1, use = n >> 1;
+          bool got = true;
+          if (DSA_EXP_PRODONLY == 8 || lane == 0) {
+            for (int i = 0; i < 3 && got; ++i)
+              while (!ptx::mbar_try_wait(&k_full[b * 3 + i], use & 1)) { if (*reinterpret_cast<volatile int*>(xs) != 0) { got = false; break; } }
+          }
+          if (!__all_sync(0xffffffffu, got)) break;
+        }
+      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
+#elif DSA_EXP_PRODONLY == 7
+      // four warps keep storing to global memory (epilogue-like, 32-byte stores to rows 1 KB apart)
+      if (warp >= 16 && warp < 20) {
+        const int L = (warp - 16) * 32 + lane;
+        unsigned char* o = (unsigned char*)a.p.out + ((int64_t)(cluster_id * 2 + rank) * 128 + L) * 1024;
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int it = 0;
+        while (*reinterpret_cast<volatile int*>(xs) == 0) { ptx::st_global_v8(o + (it & 31) * 32, w); ++it; if ((it & 31) == 0) __nanosleep(300); }
+      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
+#endif
+#endif
     } else if (warp == kSfaQWarp) {
       // ------------------------------------------------------------------ Q loader
       // Per token: this CTA's 64 heads x 576 features into shared memory (nine 64 x 64 boxes; heads
@@ -375,7 +449,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
               ptx::tma_load_3d(q_s + f * kSfaQBlk, f < 8 ? &tmap_q : &tmap_qr, q_full, f < 8 ? f * 64 : 0, h0, row);
             if (rank != 0) {
               ok = ptx::mbar_wait(q_full, n_tok & 1, abort_flag);
-              if (ok) { ptx::fence_proxy_async_smem(); ptx::mbar_arrive_remote(q_ready_lead); }
+              if (ok) ptx::mbar_arrive_remote_relaxed(q_ready_lead, 0u);
             }
           }
         } else if (hn > 0) {
@@ -392,7 +466,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         ++n_tok;
       }
-    } else if (warp < kSfaPvWarp) {
+    } else if (warp >= kSfaQkWarp0 && warp < kSfaPvWarp) {
       // ------------------------------------------------------------------ QK^T issuers (even CTA) / K relays (odd CTA)
       // Issuer i multiplies feature blocks 3i..3i+2 of every tile into its own partial S; the
       // softmax adds the three partials.  One thread issues a short (N = 64) MMA only every 60-90
@@ -420,10 +494,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           if (!ok) break;
           SFA_PROF(1);
           if (rank != 0) {
-            if (ptx::elect_one()) {
-              ptx::fence_proxy_async_smem();
-              ptx::mbar_arrive_remote(k_ready_lead + kb * 8);
-            }
+            // relaxed: the blocks were written by the TMA unit and are complete once the barrier
+            // says so; nothing of this thread's own has to be published
+            if (ptx::elect_one()) ptx::mbar_arrive_remote_relaxed(k_ready_lead + kb * 8, 0u);
             __syncwarp();
             continue;
           }
@@ -455,6 +528,78 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ++n_tok;
       }
       SFA_PROF_STORE(2, lane == 0 && qi == 0);
+    } else if (warp >= kSfaCopyWarp0) {
+      // ------------------------------------------------------------------ V copiers
+      // The value operand of a tile (all 64 keys x this CTA's 256 value columns) is not gathered
+      // again - the TMA unit is the busiest part of this kernel.  Every CTA already holds its own
+      // 32 keys with all columns in its K slot: these 128 threads copy the four column blocks that
+      // this CTA owns into its own V slot (plain loads and stores) and the four that the peer owns
+      // into the peer's V slot (st.async: the bytes are counted on the peer's barrier when they
+      // land, the sender does not wait), rows 32*rank.. of every block; 16 chunks of 16 bytes per
+      // thread.  Byte offsets inside 4 KB are kept, so the 128-byte swizzle pattern carries over.
+      const int tid = (warp - kSfaCopyWarp0) * 32 + lane;
+      const uint32_t peer = rank ^ 1u;
+      const uint32_t v_peer = ptx::map_to_rank(v_s, peer);
+      const uint32_t v_full_peer = ptx::map_to_rank(v_full, peer);
+      uint32_t n_tile = 0;
+      bool ok = true;
+      SFA_PROF_DECL;
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t ntiles = item_tiles(item);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          SFA_PROF(0);
+          // V slot b is free in both CTAs once the product that read it has completed
+          ok = ptx::mbar_wait_warp(&v_empty[b], (use & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(1);
+          // the peer's half of my V slot: 16 KB of transaction bytes
+#ifdef DSA_EXP_NOCOPY
+          if (tid == 0) ptx::mbar_arrive(&v_full[b]);
+#else
+          if (tid == 0) ptx::mbar_arrive_expect_tx(&v_full[b], kSfaVSlot / 2);
+#endif
+          ok = ptx::mbar_wait_warp(&k_full[b * 3], use & 1, abort_flag) &&
+               ptx::mbar_wait_warp(&k_full[b * 3 + 1], use & 1, abort_flag) &&
+               ptx::mbar_wait_warp(&k_full[b * 3 + 2], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(2);
+          const unsigned char* ksrc = k_s + b * kSfaKSlot;
+          const uint32_t vdst = b * kSfaVSlot + rank * kSfaKBlk;     // rows 32*rank.. of a V block
+#ifndef DSA_EXP_NOCOPY
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            // half 0: the four blocks this CTA owns (local), half 1: the four the peer owns (remote)
+            const int owner = half == 0 ? (int)rank : (int)peer;
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int q = i * 128 + tid;                      // 0..1023: chunk within the four blocks
+              const int pblk = q >> 8, within = q & 255;
+              const int fblk = 4 * (pblk >> 1) + 2 * owner + (pblk & 1);
+              v[i] = *reinterpret_cast<const uint4*>(ksrc + fblk * kSfaKBlk + within * 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int q = i * 128 + tid;
+              const int pblk = q >> 8, within = q & 255;
+              const uint32_t off = vdst + pblk * kSfaVBlk + within * 16;
+              if (half == 0) *reinterpret_cast<uint4*>(v_s + off) = v[i];
+              else ptx::st_async_v4(v_peer + off, v[i], v_full_peer + b * 8);
+            }
+          }
+#endif
+          SFA_PROF(3);
+          // the K slot has been read (the loads have returned): its producers may refill it; the
+          // local rows are made visible to the tensor core's reads before the arrival says so
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane < 3) ptx::mbar_arrive(&k_empty[b * 3 + lane]);
+          if (lane == 0) ptx::mbar_arrive(&v_full[b]);
+          SFA_PROF(4);
+        }
+      }
+      SFA_PROF_STORE(1, tid == 0);
     } else if (warp == kSfaPvWarp) {
       // ------------------------------------------------------------------ PV issuer (even CTA) / V relay (odd CTA)
       uint32_t n_tile = 0, n_tok = 0;
@@ -472,13 +617,15 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
           const uint32_t b = n_tile & 1, use = n_tile >> 1;
           SFA_PROF(0);
-          ok = ptx::mbar_wait_warp(&v_full[b], use & 1, abort_flag);
+          ok = ptx::mbar_wait_cluster_warp(&v_full[b], use & 1, abort_flag);
           if (!ok) break;
           SFA_PROF(1);
           if (rank != 0) {
+            // the peer's rows arrived through the generic proxy: order them before the tensor core's
+            // reads of this CTA's shared memory, then tell the issuer
             if (ptx::elect_one()) {
               ptx::fence_proxy_async_smem();
-              ptx::mbar_arrive_remote(v_ready_lead + b * 8);
+              ptx::mbar_arrive_remote_relaxed(v_ready_lead + b * 8, 0u);
             }
             __syncwarp();
             continue;
@@ -490,6 +637,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           SFA_PROF(3);
           ptx::tc_fence_after();
           if (ptx::elect_one()) {
+            ptx::fence_proxy_async_smem();   // the V rows the peer stored into this CTA (generic proxy)
 #pragma unroll
             for (int ks = 0; ks < kSfaBK / 16; ++ks) {
               const uint64_t ad = ptx::desc_kmajor_sw128(p_addr + b * kSfaPBuf + ks * 32);
@@ -511,8 +659,17 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       SFA_PROF_STORE(3, lane == 0);
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSfaRegsHigh));
+#ifdef DSA_EXP_PRODONLY
+#if DSA_EXP_PRODONLY == 2
+    ptx::mbar_wait_warp(o_free, 0, abort_flag);
+#elif DSA_EXP_PRODONLY >= 3
+    while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500);
+#endif
+    if (false) {
+#else
     if (!*abort_flag) {
+#endif
       // ------------------------------------------------------------------ softmax + epilogue
       const int quarter = warp & 3;
       const int L = quarter * 32 + lane;            // TMEM lane
@@ -583,6 +740,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           SFA_PROF(0);
           ptx::tc_fence_after();
           float sc[kSfaHalfBK];
+#ifdef DSA_EXP_NOSOFT
+          for (int k = 0; k < kSfaHalfBK; ++k) sc[k] = 0.f;
+          if (false)
+#endif
           {
             // the three issuers' partial products
             float s1[kSfaHalfBK], s2[kSfaHalfBK];
@@ -666,6 +827,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             }
             ptx::tmem_st_wait();
           }
+#ifdef DSA_EXP_NOSOFT
+          if (false)
+#endif
           {
             // row hl of the K-major, 128-byte-swizzled A operand: keys half*32 .. +31 are the 16-byte
             // chunks half*4 .. +3 of the row
@@ -867,6 +1031,13 @@ inline int sfa_sm100_device_sms(int dev) {
   n = sm_count[dev].load(std::memory_order_relaxed);
   if (n > 0) return n;
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 2) return 0;
+  // the in-kernel register hand-over is sized for kSfaLaunchRegs registers per thread at launch: a
+  // build that allocates a different number must not run (setmaxnreg.inc could block for good)
+  cudaFuncAttributes fa0, fa1;
+  if (cudaFuncGetAttributes(&fa0, sfa_fwd_sm100_kernel<false>) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa1, sfa_fwd_sm100_kernel<true>) != cudaSuccess ||
+      fa0.numRegs != kSfaLaunchRegs || fa1.numRegs != kSfaLaunchRegs)
+    return 0;
   if (cudaFuncSetAttribute(sfa_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)kSfaSmemBytes) != cudaSuccess ||
       cudaFuncSetAttribute(sfa_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
