@@ -36,19 +36,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-#ifdef DSA_EXP_TESTWAIT
-      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, P;\n\t}\n"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity), "r"(8000u)  // suspend-time hint in ns
       : "memory");
-#endif
   return done != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets the other warps of a CTA leave quickly once
@@ -57,9 +49,6 @@ constexpr uint32_t kWaitPolls = 1u << 20;  // x (up to) 8 us per poll: gives up 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kWaitPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef DSA_EXP_SLEEP
-    __nanosleep(DSA_EXP_SLEEP);
-#endif
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -122,19 +111,11 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-#ifdef DSA_EXP_TESTWAIT
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, P;\n\t}\n"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
       "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)  // suspend-time hint in ns
       : "memory");
-#endif
   return done != 0;
 }
 
@@ -143,9 +124,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 
 // ---- proxies / fences -------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
-#ifndef DSA_EXP_NOFENCE
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
 }
 // all state spaces (covers rows written into a peer CTA's shared memory)
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -155,23 +134,59 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < (kWaitPolls << 2); ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-#ifdef DSA_EXP_SLEEP
-    __nanosleep(DSA_EXP_SLEEP);
-#endif
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
 }
 
-// Warp-wide waits for warps whose next step is warp-collective (tcgen05.ld / st, elect.sync):
-// every lane polls.  (Measured on B200: one polling lane with the result broadcast to the others
-// made the attention kernel 1.7x slower, whichever of try_wait / test_wait / sleep it used.)
+// Warp-wide waits: every lane polls.  Letting one lane poll and handing the result to the others
+// with a shuffle or a warp barrier looks cheaper and is not: measured on B200, the lanes parked at
+// the shuffle resumed ~1400 cycles after the polling lane had seen the barrier flip (whichever of
+// try_wait / test_wait / sleep it used), which made a gather producer's tile 2.6x and the whole
+// attention kernel 1.7x slower.  Must be called by all 32 lanes.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
 }
 __device__ __forceinline__ bool mbar_wait_cluster_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait_cluster(bar, parity, abort_flag));
+}
+
+// Same, for hand-overs that are expected within a few hundred cycles: test_wait never suspends the
+// thread, so the hand-over is seen without a wake-up delay (at the price of issue slots).
+template <bool kCluster>
+__device__ __forceinline__ bool mbar_spin_warp_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = false;
+  for (uint32_t i = 0; i < (kWaitPolls << 6); ++i) {
+    uint32_t done;
+    if (kCluster) {
+      asm volatile(
+          "{\n\t.reg .pred P;\n\t"
+          "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+          "selp.b32 %0, 1, 0, P;\n\t}\n"
+          : "=r"(done)
+          : "r"(smem_u32(bar)), "r"(parity)
+          : "memory");
+    } else {
+      asm volatile(
+          "{\n\t.reg .pred P;\n\t"
+          "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+          "selp.b32 %0, 1, 0, P;\n\t}\n"
+          : "=r"(done)
+          : "r"(smem_u32(bar)), "r"(parity)
+          : "memory");
+    }
+    if (done) { ok = true; break; }
+    if ((i & 1023u) == 1023u && *abort_flag) break;
+  }
+  if (!ok && !*abort_flag) *abort_flag = 1;
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ bool mbar_spin_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_spin_warp_impl<false>(bar, parity, abort_flag);
+}
+__device__ __forceinline__ bool mbar_spin_cluster_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_spin_warp_impl<true>(bar, parity, abort_flag);
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------
@@ -300,9 +315,6 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
 }
 __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
-#ifdef DSA_EXP_NOMMA
-  return;
-#endif
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"

@@ -8,33 +8,45 @@
 // heads 64c..64c+63, i.e. its own rows of S = Q K^T and of O = P V, so the softmax of a row never
 // needs data from the other CTA.  Both contractions are pair MMAs (tcgen05.mma.cta_group::2,
 // M = 128 = 2 x 64 rows): each CTA feeds its own A rows and HALF of the B operand, which the
-// hardware shares between the two tensor cores.  That fixes what each CTA has to gather:
-//   S tile  [128 heads x 64 keys]  : B = K rows, split along the keys  -> CTA c gathers 32 of the
+// hardware shares between the two tensor cores.  That fixes what each CTA needs per 64-key tile:
+//   S tile  [128 heads x 64 keys]  : B = K rows, split along the keys  -> CTA c needs 32 of the
 //                                    tile's 64 keys with all 576 features  (36 KB, K-major)
-//   O       [128 heads x 512 cols] : B = V rows, split along the value columns -> CTA c gathers
+//   O       [128 heads x 512 cols] : B = V rows, split along the value columns -> CTA c needs
 //                                    all 64 keys, columns {c*128.., 256+c*128..} (32 KB, MN-major)
 // (two N = 256 MMAs per 16-key step: the first produces value columns 0..255, the second
 // 256..511).  The two operand blocks of a CTA cannot alias: a pair MMA reads both CTAs at the SAME
 // shared-memory offsets, the score product needs identical features at an offset and the value
-// product identical keys.  Gathers are TMA tile::gather4 loads into the 128-byte-swizzled MMA
-// layout, issued by twelve producer warps from a front-packed list of physical KV rows that a
-// pre-pass kernel writes.
+// product identical keys.
+//
+// Data movement.  Only the K block is gathered from L2: TMA tile::gather4 loads into the
+// 128-byte-swizzled MMA layout, issued by six producer warps from a front-packed list of physical
+// KV rows that a pre-pass kernel writes.  The SM's TMA unit is the scarce resource here (it
+// saturates at one 512-byte gather4 per ~18 cycles, bulk copies included), so the V block is not
+// gathered a second time: four copier warps build it from the K block, which already holds this
+// CTA's 32 keys with all columns - plain loads / stores for the columns this CTA owns, st.async
+// into the peer's shared memory for the columns the peer owns.
 //
 // Accumulator layout of a pair MMA with M = 128 (measured): lanes 0..63 hold a CTA's rows with the
 // first half of N, lanes 64..127 the same rows with the second half.  So TMEM lane L of CTA c
 // belongs to head 64c + (L & 63); for S it holds the tile's keys 32*(L>>6) .. +31, for O the value
-// columns j*256 + 128*(L>>6) .. +127 of MMA j.  The two threads of a head exchange their running
-// maxima and sums through shared memory.
+// columns j*256 + 128*(L>>6) .. +127 of MMA j.
 //
-// Tensor memory per CTA: O 0..255 | S (two buffers) 256..319.
+// Softmax.  Two groups of four warps take alternate tiles (group g: S buffer g, P buffer g), so one
+// tile's exponentials overlap the other's tensor-memory reads, barrier waits and P stores.  The two
+// threads of a head inside a group (the two halves of N) exchange their tile maxima through shared
+// memory.  The reference maximum that the probabilities are scaled by is only moved when a tile
+// exceeds it by more than 2^8 (O is rescaled then, which is rare); it is handed from tile to tile,
+// i.e. from group to group, through shared memory together with the running true maximum.
+//
+// Tensor memory per CTA: O 0..255 | S partials (2 buffers x 3 issuers x 32 columns) 256..447.
 // Shared memory per CTA: Q_c 72 KB (A operand, loaded per token by TMA) | 2 x 36 KB K slots |
-// 2 x 32 KB V slots | 2 x 8 KB P (A operand of the value product, written by the softmax warps).
+// 2 x 32 KB V slots | 2 x 8 KB P (A operand of the value product) | 2.5 KB exchange buffers.
 //
-// Warps (640 threads): 0..5 K producers, 6..11 V producers, 12/13 QK^T issuers (even / odd tiles,
-// two issuing threads keep the tensor pipe fed with the short N = 64 MMAs), 14 PV issuer, 15 Q
-// loader, 16..19 softmax + epilogue.  MMAs are issued by the even CTA only; in the odd CTA the
-// issuer warps relay "my operand has landed" to the even CTA's barriers instead.  All waits are
-// bounded; a wait that gives up sets the status word.
+// Warps (768 threads): 0..5 K gather producers, 6 Q loader, 8..10 QK^T issuers (issuer i owns
+// feature blocks 3i..3i+2 and a partial S: one thread issues a short N = 64 MMA only every 60-90
+// cycles), 11 PV issuer, 12..15 V copiers, 16..19 / 20..23 softmax groups.  MMAs are issued by the
+// even CTA only; in the odd CTA the issuer warps relay "my operand has landed" to the even CTA's
+// barriers instead.  All waits are bounded; a wait that gives up sets the status word.
 #pragma once
 
 #include <atomic>
@@ -50,13 +62,13 @@ constexpr int kSfaCtaHeads = 64;
 constexpr int kSfaBK = 64;           // keys per tile
 constexpr int kSfaHalfBK = 32;       // keys of a tile each CTA gathers for the score product
 constexpr int kSfaThreads = 768;
-constexpr int kSfaQkLanes = 3;       // QK^T issuers; issuer i owns feature blocks 3i..3i+2 and a partial S
-constexpr int kSfaKWarps = 9;        // warps 0..8: K gather producers, three per issuer
-constexpr int kSfaQWarp = 9;         // Q loader (warps 10, 11 idle)
-constexpr int kSfaQkWarp0 = 12;      // warps 12..14
-constexpr int kSfaPvWarp = 15;
-constexpr int kSfaCopyWarp0 = 16;    // warps 16..19: V copiers
-constexpr int kSfaSoftWarp0 = 20;    // warps 20..23
+constexpr int kSfaQkLanes = 3;       // QK^T issuers
+constexpr int kSfaKWarps = 6;        // warps 0..5: two per issuer
+constexpr int kSfaQWarp = 6;         // Q loader (warp 7 idle)
+constexpr int kSfaQkWarp0 = 8;       // warps 8..10
+constexpr int kSfaPvWarp = 11;
+constexpr int kSfaCopyWarp0 = 12;    // warps 12..15
+constexpr int kSfaSoftWarp0 = 16;    // warps 16..19 (group 0), 20..23 (group 1)
 constexpr int kSfaDv = 512;
 constexpr int kSfaMaxSlots = 8192;   // sparse_count * sparse_block_size served by this kernel
 
@@ -72,8 +84,8 @@ constexpr uint32_t kSfaOffQ = 0;
 constexpr uint32_t kSfaOffK = kSfaOffQ + kSfaQBytes;
 constexpr uint32_t kSfaOffV = kSfaOffK + 2 * kSfaKSlot;
 constexpr uint32_t kSfaOffP = kSfaOffV + 2 * kSfaVSlot;
-constexpr uint32_t kSfaOffX = kSfaOffP + 2 * kSfaPBuf;       // float xm[2][128], xs[128]
-constexpr uint32_t kSfaOffBar = kSfaOffX + 3 * 128 * 4;
+constexpr uint32_t kSfaOffX = kSfaOffP + 2 * kSfaPBuf;       // float xm[2][128] | float2 mref[2][64] | float fin[2][64]
+constexpr uint32_t kSfaOffBar = kSfaOffX + 1024 + 1024 + 512;
 constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 512;
 static_assert(kSfaOffK % 1024 == 0 && kSfaOffV % 1024 == 0 && kSfaOffP % 1024 == 0, "operand alignment");
 static_assert(kSfaSmemBytes <= 232448, "shared memory");
@@ -81,8 +93,11 @@ static_assert(kSfaSmemBytes <= 232448, "shared memory");
 // setmaxnreg.inc only ever gets registers that warps of the SAME CTA have released and blocks (for
 // good) until it has them: what the softmax warps ask for must fit into what the others give back.
 constexpr int kSfaLaunchRegs = 80;   // 65536 / 768 threads, rounded down to a multiple of 8
-constexpr int kSfaRegsLow = 56, kSfaRegsHigh = 168;
-static_assert((kSfaRegsHigh - kSfaLaunchRegs) * (kSfaThreads / 32 - kSfaSoftWarp0) <=
+constexpr int kSfaRegsLow = 56;      // warps 0..11
+constexpr int kSfaRegsCopy = 104;    // warps 12..15 (a tile's 16 chunks of 16 bytes sit in registers)
+constexpr int kSfaRegsHigh = 104;    // warps 16..23
+static_assert((kSfaRegsHigh - kSfaLaunchRegs) * (kSfaThreads / 32 - kSfaSoftWarp0) +
+                      (kSfaRegsCopy - kSfaLaunchRegs) * (kSfaSoftWarp0 - kSfaCopyWarp0) <=
                   (kSfaLaunchRegs - kSfaRegsLow) * kSfaCopyWarp0,
               "setmaxnreg: more registers requested than released");
 static_assert(kSfaLaunchRegs * kSfaThreads <= 65536, "register file");
@@ -122,20 +137,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Development aid, compiled only with -DDSA_SFA_PROFILE: cycle sums per role of the first cluster
-// (slot = role * 8 + counter, odd CTA + 64), read back with dsa_debug_sfa_profile().
-#ifdef DSA_SFA_PROFILE
-__device__ long long g_sfa_prof[128];
-#define SFA_PROF_DECL long long pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt = clock64()
-#define SFA_PROF(i) do { const long long pn = clock64(); pacc[i] += pn - pt; pt = pn; } while (0)
-#define SFA_PROF_STORE(role, cond) do { if (blockIdx.x < 2 && (cond)) { \
-    for (int pi = 0; pi < 8; ++pi) g_sfa_prof[(blockIdx.x & 1) * 64 + (role) * 8 + pi] = pacc[pi]; } } while (0)
-#else
-#define SFA_PROF_DECL
-#define SFA_PROF(i)
-#define SFA_PROF_STORE(role, cond)
-#endif
-
 // Pre-pass: one warp per query row.  Writes the physical KV rows of the slots that take part, in
 // slot order, and their count.  A slot whose paged block is absent inside the valid length takes
 // part as a zero row, like the reference's un-paged cache
@@ -174,6 +175,20 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __rest
         make_int2(max(0, min(part_keys, n - lane * part_keys)), (int32_t)((int64_t)row * slots + lane * part_keys));
 }
 
+// Development aid, compiled only with -DDSA_SFA_PROFILE: cycle sums per role of the first cluster
+// (slot = role * 8 + counter, odd CTA + 64), read back with dsa_debug_sfa_profile().
+#ifdef DSA_SFA_PROFILE
+__device__ long long g_sfa_prof[128];
+#define SFA_PROF_DECL long long pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt = clock64()
+#define SFA_PROF(i) do { const long long pn = clock64(); pacc[i] += pn - pt; pt = pn; } while (0)
+#define SFA_PROF_STORE(role, cond) do { if (blockIdx.x < 2 && (cond)) { \
+    for (int pi = 0; pi < 8; ++pi) g_sfa_prof[(blockIdx.x & 1) * 64 + (role) * 8 + pi] = pacc[pi]; } } while (0)
+#else
+#define SFA_PROF_DECL
+#define SFA_PROF(i)
+#define SFA_PROF_STORE(role, cond)
+#endif
+
 // kSplit: work items are parts of rows (split-KV) and leave fp32 partials; compiled apart so that the
 // prefill instantiation carries none of it.
 template <bool kSplit>
@@ -186,29 +201,36 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   unsigned char* k_s = sfa_sm + kSfaOffK;
   unsigned char* v_s = sfa_sm + kSfaOffV;
   unsigned char* p_s = sfa_sm + kSfaOffP;
-  float* xm = reinterpret_cast<float*>(sfa_sm + kSfaOffX);   // [2][128] running-maximum exchange
-  float* xs = xm + 256;                                       // [128] row-sum exchange
+  float* xm = reinterpret_cast<float*>(sfa_sm + kSfaOffX);     // [2 groups][128] exchange between the halves of a head
+  float2* mref = reinterpret_cast<float2*>(xm + 256);           // [2 groups][64] (reference, true maximum) after the group's latest tile
+  float* fin = reinterpret_cast<float*>(mref + 128);            // [2 groups][64] row sums of a group at the end of a token
   uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
   // K barriers are indexed [slot * 3 + issuer]: every issuer's three feature blocks are handed over
   // and released on their own.
-  uint64_t* k_full = bars;         // [6] gather -> QK issuer / relay                 (tx bytes)
+  uint64_t* k_full = bars;         // [6] gather -> QK issuer / relay, copiers              (tx bytes)
   uint64_t* k_empty = bars + 6;    // [6] blocks read by the issuer's MMAs (commit) and by the four copier warps -> K producers
   uint64_t* k_ready = bars + 12;   // [6] even CTA only: the odd CTA's blocks have landed
   uint64_t* v_full = bars + 18;    // [2] own copier warps (4 arrivals + 1 arming) and the peer's st.async bytes -> PV issuer / relay
-  uint64_t* v_empty = bars + 20;   // [2] PV of the tile done -> V copier              (commit, both CTAs)
-  uint64_t* v_ready = bars + 22;   // [2] even CTA only: the odd CTA's V slot has landed
-  uint64_t* s_full = bars + 24;    // [2] all three partial products done -> softmax   (commit x 3, both CTAs)
-  uint64_t* s_empty = bars + 26;   // [2] even CTA only: softmax warps of both CTAs hold S in registers
+  uint64_t* v_empty = bars + 20;   // [2] PV of the tile done -> copiers                     (commit, both CTAs)
+  uint64_t* v_ready = bars + 22;   // [2] even CTA only: the odd CTA's V slot is complete
+  uint64_t* s_full = bars + 24;    // [2] all three partial products done -> softmax group   (commit x 3, both CTAs)
+  uint64_t* s_empty = bars + 26;   // [2] even CTA only: the group's warps of both CTAs hold S in registers
   uint64_t* p_full = bars + 28;    // [2] even CTA only: P stored (O rescaled) in both CTAs
-  uint64_t* p_empty = bars + 30;   // [2] PV done -> softmax                           (commit, both CTAs)
+  uint64_t* p_empty = bars + 30;   // [2] PV done -> softmax                                 (commit, both CTAs)
   uint64_t* q_full = bars + 32;    // this CTA's Q has landed (tx bytes)
   uint64_t* q_ready = bars + 33;   // even CTA only: the odd CTA's Q has landed
-  uint64_t* q_empty = bars + 34;   // all QK issuers are through with the token        (commit x 3, both CTAs)
+  uint64_t* q_empty = bars + 34;   // all QK issuers are through with the token              (commit x 3, both CTAs)
   uint64_t* o_free = bars + 35;    // even CTA only: epilogue warps of both CTAs have read O
-  uint64_t* x_bar = bars + 36;     // softmax warps: exchange buffer written
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 37);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 38);
-  static_assert(39 * 8 <= 512, "barrier area");
+  // The two halves of a head sit in warps q and q + 2 of a group ("pair" q & 1): the per-tile
+  // exchange and the hand-over of the reference maximum only involve that pair.
+  uint64_t* x_bar = bars + 36;     // [group * 2 + pair] xm written (2 warps)
+  uint64_t* xr_bar = bars + 40;    // [group * 2 + pair] xm read, it may be written again (2 warps)
+  uint64_t* m_bar = bars + 44;     // [group * 2 + pair] mref written for the group's latest tile (2 warps)
+  uint64_t* e_bar = bars + 48;     // both groups: fin written
+  uint64_t* er_bar = bars + 49;    // both groups: fin read
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 50);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 51);
+  static_assert(52 * 8 <= 512, "barrier area");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -224,16 +246,15 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       ptx::mbar_init(&s_full[i], kSfaQkLanes); ptx::mbar_init(&s_empty[i], 8);
       ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
     }
+    for (int i = 0; i < 4; ++i) {
+      ptx::mbar_init(&x_bar[i], 2); ptx::mbar_init(&xr_bar[i], 2); ptx::mbar_init(&m_bar[i], 2);
+    }
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_ready, 1);
     ptx::mbar_init(q_empty, kSfaQkLanes);
-#ifdef DSA_EXP_PRODONLY
-    ptx::mbar_init(o_free, kSfaKWarps);
-    reinterpret_cast<volatile int*>(xs)[0] = 0; reinterpret_cast<volatile int*>(xs)[1] = 0;
-#else
-    ptx::mbar_init(o_free, 8);
-#endif
-    ptx::mbar_init(x_bar, 4);
+    ptx::mbar_init(o_free, 16);
+    ptx::mbar_init(e_bar, 8);
+    ptx::mbar_init(er_bar, 8);
     *abort_flag = misaligned ? 1 : 0;
     ptx::mbar_fence_init();
   }
@@ -252,22 +273,23 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   const int32_t n1 = a.p.n1;                   // real heads (<= 128); rows past them carry zero queries
   auto item_tiles = [&](int32_t item) -> int32_t { return (a.nvalid[item].x + kSfaBK - 1) / kSfaBK; };
 
-  if (warp < kSfaSoftWarp0) {
-    // registers: kSfaLaunchRegs per thread at launch; producers and issuers give some back, the
-    // softmax warps take them (whole warpgroups of four warps change together)
-    if (warp < kSfaCopyWarp0) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSfaRegsLow));
+  // Registers: kSfaLaunchRegs per thread at launch; producers and issuers give some back, the
+  // copier and softmax warps take them (whole warpgroups of four warps change together).  Each
+  // class of roles sits in its own branch, right under its setmaxnreg: the compiler budgets a
+  // branch by the setmaxnreg that dominates it.
+  if (warp < kSfaCopyWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSfaRegsLow));
     if (*abort_flag) {
       // nothing started: fall through to the teardown
     } else if (warp < kSfaKWarps) {
       // ------------------------------------------------------------------ K gather producers
-      // Three warps per QK^T issuer: 8 row groups (4 of this CTA's 32 keys each) x the issuer's 3
-      // column blocks = 24 gather4 loads of 512 bytes per tile, dealt out over the three warps.
-      // Measured in this kernel: the lanes of a warp issue one after the other, ~220 cycles per
-      // load; warps issue in parallel until the SM's TMA unit saturates at one load per ~18 cycles
-      // (28 B/clk, bulk copies included) - which is why nothing but these loads goes through it.
-      const int qi = warp / 3;                           // the issuer this warp feeds
-      const int gw = warp - qi * 3;
-      const int o = gw + 3 * lane;
+      // Two warps per QK^T issuer: 8 row groups (4 of this CTA's 32 keys each) x the issuer's 3
+      // column blocks = 24 gather4 loads of 512 bytes per tile, dealt out over the two warps.  The
+      // lanes of a warp issue one after the other (~100 cycles per load), warps issue in parallel
+      // until the SM's TMA unit saturates at one load per ~18 cycles.
+      const int qi = warp >> 1;                          // the issuer this warp feeds
+      const int gw = warp & 1;
+      const int o = gw + 2 * lane;
       const bool active = o < 24;
       const int grp = o / 3, blk = 3 * qi + (o - grp * 3);
       const int key0 = (int)rank * kSfaHalfBK + grp * 4;   // first key (within the tile) of this load
@@ -307,29 +329,19 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         load_rows(nxt, rn);
         const uint32_t s = n_tile & 1, use = n_tile >> 1;
         SFA_PROF(0);
-#ifndef DSA_EXP_PRODONLY
-        ok = ptx::mbar_wait_warp(&empty[s * 3], (use & 1) ^ 1, abort_flag);
-#else
-        // timing experiment: no consumer; a slot is re-armed once its previous load has landed
-        if (lane == 0 && use > 0) ok = ptx::mbar_wait(&full[s * 3], (use - 1) & 1, abort_flag);
-#endif
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        // every lane polls (see ptx::mbar_wait_warp): the gather below is issued for the lanes one
+        // after the other and must find the warp converged.  Like every wait of this kernel it
+        // spins without suspending: waking from a suspended try_wait costs hundreds of cycles at
+        // every hand-over (826 vs 640 TFLOP/s on a 4096-token, top-2048 case).
+        ok = ptx::mbar_spin_warp(&empty[s * 3], (use & 1) ^ 1, abort_flag);
         if (!ok) break;
         SFA_PROF(1);
         if (gw == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&full[s * 3], kSfaKSub);
         __syncwarp();
-        SFA_PROF(3);
-        // the tensor map is named directly in each call (a map chosen through a per-lane pointer
-        // costs an address conversion per load)
         if (active) {
-#ifdef DSA_EXP_ONEMAP
-          if (blk == 8) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kn, &full[s * 3], 0, rc[0], rc[1], rc[2], rc[3]);
-#else
           if (blk == 8) ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kr, &full[s * 3], 0, rc[0], rc[1], rc[2], rc[3]);
-#endif
           else ptx::tma_gather4_2d(slot0 + s * kSfaKSlot, &tmap_kn, &full[s * 3], x, rc[0], rc[1], rc[2], rc[3]);
         }
-        SFA_PROF(4);
         __syncwarp();
         SFA_PROF(2);
         ++n_tile;
@@ -337,95 +349,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 #pragma unroll
         for (int i = 0; i < 4; ++i) rc[i] = rn[i];
       }
-#ifdef DSA_EXP_PRODONLY
-      // drain: the last loads of both slots must have landed before the CTA may exit
-      if (lane == 0) {
-        for (uint32_t back = 1; back <= 2 && back <= n_tile; ++back) {
-          const uint32_t n = n_tile - back;
-          ptx::mbar_wait(&full[(n & 1) * 3], (n >> 1) & 1, abort_flag);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) { ptx::mbar_arrive(o_free); atomicAdd(reinterpret_cast<int*>(xs) + 1, 1); if (reinterpret_cast<volatile int*>(xs)[1] == kSfaKWarps) *reinterpret_cast<volatile int*>(xs) = 1; }
-#endif
       SFA_PROF_STORE(0, lane == 0 && warp == 0);
-#ifdef DSA_EXP_PRODONLY
-    } else if (true) {
-#if DSA_EXP_PRODONLY == 2
-      ptx::mbar_wait_warp(o_free, 0, abort_flag);          // o_free: 8 arrivals... re-initialised below to 9
-#elif DSA_EXP_PRODONLY == 3
-      while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500);
-#elif DSA_EXP_PRODONLY >= 4
-      // waits that give up as soon as the producers of this CTA are done (timing experiments only)
-      auto fwait = [&](uint64_t* bar, uint32_t par) -> bool {
-        bool got = true;
-        while (!ptx::mbar_try_wait(bar, par)) { if (*reinterpret_cast<volatile int*>(xs) != 0) { got = false; break; } }
-        return __all_sync(0xffffffffu, got);
-      };
-#endif
-#if DSA_EXP_PRODONLY == 4
-      // one warp per CTA keeps issuing tcgen05.commit (even CTA, multicast) and both wait for it
-      if (warp == 12) {
-        uint32_t ph = 0;
-        while (*reinterpret_cast<volatile int*>(xs) == 0) {
-          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);   // count 3 -> needs 3 commits per phase
-          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);
-          if (rank == 0 && ptx::elect_one()) ptx::mma_commit_pair(&s_full[0]);
-          __syncwarp();
-          if (!fwait(&s_full[0], ph & 1)) break;
-          ++ph;
-          __nanosleep(200);
-        }
-      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
-#elif DSA_EXP_PRODONLY == 5
-      // four warps ping-pong through shared memory + an mbarrier (like the softmax exchange)
-      if (warp >= 16 && warp < 20) {
-        uint32_t ph = 0;
-        const int L = (warp - 16) * 32 + lane;
-        while (*reinterpret_cast<volatile int*>(xs) == 0) {
-          xm[L] = (float)ph;
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(x_bar);
-          if (!fwait(x_bar, ph & 1)) break;
-          ++ph;
-          if (xm[L ^ 64] < 0.f) break;
-          __nanosleep(200);
-        }
-      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
-#elif DSA_EXP_PRODONLY == 6
-      // the odd CTA's warp 12 keeps sending relaxed remote arrivals to the even CTA's warp 12, which waits for them
-      if (warp == 12) {
-        uint32_t ph = 0;
-        const uint32_t rb = ptx::map_to_rank(q_ready, 0);
-        while (*reinterpret_cast<volatile int*>(xs) == 0) {
-          if (rank != 0) { if (ptx::elect_one()) ptx::mbar_arrive_remote_relaxed(rb, 0u); __syncwarp(); __nanosleep(400); }
-          else { if (!fwait(q_ready, ph & 1)) break; ++ph; }
-        }
-      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
-#elif DSA_EXP_PRODONLY == 8 || DSA_EXP_PRODONLY == 9
-      // idle warps watch the very barriers the gathers complete on (8: five warps, all lanes; 9: one lane of one warp)
-      if ((DSA_EXP_PRODONLY == 8 && (warp == 12 || (warp >= 16 && warp < 20))) || (DSA_EXP_PRODONLY == 9 && warp == 12)) {
-        for (uint32_t n = 0; *reinterpret_cast<volatile int*>(xs) == 0; ++n) {
-          const uint32_t b = n & 1, use = n >> 1;
-          bool got = true;
-          if (DSA_EXP_PRODONLY == 8 || lane == 0) {
-            for (int i = 0; i < 3 && got; ++i)
-              while (!ptx::mbar_try_wait(&k_full[b * 3 + i], use & 1)) { if (*reinterpret_cast<volatile int*>(xs) != 0) { got = false; break; } }
-          }
-          if (!__all_sync(0xffffffffu, got)) break;
-        }
-      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
-#elif DSA_EXP_PRODONLY == 7
-      // four warps keep storing to global memory (epilogue-like, 32-byte stores to rows 1 KB apart)
-      if (warp >= 16 && warp < 20) {
-        const int L = (warp - 16) * 32 + lane;
-        unsigned char* o = (unsigned char*)a.p.out + ((int64_t)(cluster_id * 2 + rank) * 128 + L) * 1024;
-        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        int it = 0;
-        while (*reinterpret_cast<volatile int*>(xs) == 0) { ptx::st_global_v8(o + (it & 31) * 32, w); ++it; if ((it & 31) == 0) __nanosleep(300); }
-      } else { while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500); }
-#endif
-#endif
     } else if (warp == kSfaQWarp) {
       // ------------------------------------------------------------------ Q loader
       // Per token: this CTA's 64 heads x 576 features into shared memory (nine 64 x 64 boxes; heads
@@ -469,9 +393,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
     } else if (warp >= kSfaQkWarp0 && warp < kSfaPvWarp) {
       // ------------------------------------------------------------------ QK^T issuers (even CTA) / K relays (odd CTA)
       // Issuer i multiplies feature blocks 3i..3i+2 of every tile into its own partial S; the
-      // softmax adds the three partials.  One thread issues a short (N = 64) MMA only every 60-90
-      // cycles, three keep the tensor pipe busy.  The loop is warp-uniform (every lane waits) and
-      // only the MMA and the commits are issued by one elected lane.
+      // softmax adds the three partials.  The loop is warp-uniform (every lane waits) and only the
+      // MMAs and the commits are issued by one elected lane.
       const uint32_t qi = warp - kSfaQkWarp0;
       uint32_t n_tile = 0, n_tok = 0;
       bool ok = true;
@@ -484,13 +407,13 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         if (ntiles == 0) continue;
         SFA_PROF(0);
         if (rank == 0) {
-          ok = ptx::mbar_wait_warp(q_full, n_tok & 1, abort_flag) && ptx::mbar_wait_cluster_warp(q_ready, n_tok & 1, abort_flag);
+          ok = ptx::mbar_spin_warp(q_full, n_tok & 1, abort_flag) && ptx::mbar_spin_cluster_warp(q_ready, n_tok & 1, abort_flag);
         }
         SFA_PROF(5);
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
           const uint32_t b = n_tile & 1, use = n_tile >> 1, kb = b * kSfaQkLanes + qi;
           SFA_PROF(0);
-          ok = ptx::mbar_wait_warp(&k_full[kb], use & 1, abort_flag);
+          ok = ptx::mbar_spin_warp(&k_full[kb], use & 1, abort_flag);
           if (!ok) break;
           SFA_PROF(1);
           if (rank != 0) {
@@ -500,9 +423,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             __syncwarp();
             continue;
           }
-          ok = ptx::mbar_wait_cluster_warp(&k_ready[kb], use & 1, abort_flag);
+          ok = ptx::mbar_spin_cluster_warp(&k_ready[kb], use & 1, abort_flag);
           SFA_PROF(2);
-          ok = ok && ptx::mbar_wait_cluster_warp(&s_empty[b], (use & 1) ^ 1, abort_flag);
+          ok = ok && ptx::mbar_spin_cluster_warp(&s_empty[b], (use & 1) ^ 1, abort_flag);
           if (!ok) break;
           SFA_PROF(3);
           ptx::tc_fence_after();
@@ -528,78 +451,6 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         ++n_tok;
       }
       SFA_PROF_STORE(2, lane == 0 && qi == 0);
-    } else if (warp >= kSfaCopyWarp0) {
-      // ------------------------------------------------------------------ V copiers
-      // The value operand of a tile (all 64 keys x this CTA's 256 value columns) is not gathered
-      // again - the TMA unit is the busiest part of this kernel.  Every CTA already holds its own
-      // 32 keys with all columns in its K slot: these 128 threads copy the four column blocks that
-      // this CTA owns into its own V slot (plain loads and stores) and the four that the peer owns
-      // into the peer's V slot (st.async: the bytes are counted on the peer's barrier when they
-      // land, the sender does not wait), rows 32*rank.. of every block; 16 chunks of 16 bytes per
-      // thread.  Byte offsets inside 4 KB are kept, so the 128-byte swizzle pattern carries over.
-      const int tid = (warp - kSfaCopyWarp0) * 32 + lane;
-      const uint32_t peer = rank ^ 1u;
-      const uint32_t v_peer = ptx::map_to_rank(v_s, peer);
-      const uint32_t v_full_peer = ptx::map_to_rank(v_full, peer);
-      uint32_t n_tile = 0;
-      bool ok = true;
-      SFA_PROF_DECL;
-      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
-        const int32_t ntiles = item_tiles(item);
-        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-          const uint32_t b = n_tile & 1, use = n_tile >> 1;
-          SFA_PROF(0);
-          // V slot b is free in both CTAs once the product that read it has completed
-          ok = ptx::mbar_wait_warp(&v_empty[b], (use & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          SFA_PROF(1);
-          // the peer's half of my V slot: 16 KB of transaction bytes
-#ifdef DSA_EXP_NOCOPY
-          if (tid == 0) ptx::mbar_arrive(&v_full[b]);
-#else
-          if (tid == 0) ptx::mbar_arrive_expect_tx(&v_full[b], kSfaVSlot / 2);
-#endif
-          ok = ptx::mbar_wait_warp(&k_full[b * 3], use & 1, abort_flag) &&
-               ptx::mbar_wait_warp(&k_full[b * 3 + 1], use & 1, abort_flag) &&
-               ptx::mbar_wait_warp(&k_full[b * 3 + 2], use & 1, abort_flag);
-          if (!ok) break;
-          SFA_PROF(2);
-          const unsigned char* ksrc = k_s + b * kSfaKSlot;
-          const uint32_t vdst = b * kSfaVSlot + rank * kSfaKBlk;     // rows 32*rank.. of a V block
-#ifndef DSA_EXP_NOCOPY
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            // half 0: the four blocks this CTA owns (local), half 1: the four the peer owns (remote)
-            const int owner = half == 0 ? (int)rank : (int)peer;
-            uint4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int q = i * 128 + tid;                      // 0..1023: chunk within the four blocks
-              const int pblk = q >> 8, within = q & 255;
-              const int fblk = 4 * (pblk >> 1) + 2 * owner + (pblk & 1);
-              v[i] = *reinterpret_cast<const uint4*>(ksrc + fblk * kSfaKBlk + within * 16);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int q = i * 128 + tid;
-              const int pblk = q >> 8, within = q & 255;
-              const uint32_t off = vdst + pblk * kSfaVBlk + within * 16;
-              if (half == 0) *reinterpret_cast<uint4*>(v_s + off) = v[i];
-              else ptx::st_async_v4(v_peer + off, v[i], v_full_peer + b * 8);
-            }
-          }
-#endif
-          SFA_PROF(3);
-          // the K slot has been read (the loads have returned): its producers may refill it; the
-          // local rows are made visible to the tensor core's reads before the arrival says so
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane < 3) ptx::mbar_arrive(&k_empty[b * 3 + lane]);
-          if (lane == 0) ptx::mbar_arrive(&v_full[b]);
-          SFA_PROF(4);
-        }
-      }
-      SFA_PROF_STORE(1, tid == 0);
     } else if (warp == kSfaPvWarp) {
       // ------------------------------------------------------------------ PV issuer (even CTA) / V relay (odd CTA)
       uint32_t n_tile = 0, n_tok = 0;
@@ -612,12 +463,12 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         if (ntiles == 0) continue;
         // the previous token's O has been read out in both CTAs
         SFA_PROF(0);
-        if (rank == 0) ok = ptx::mbar_wait_cluster_warp(o_free, (n_tok & 1) ^ 1, abort_flag);
+        if (rank == 0) ok = ptx::mbar_spin_cluster_warp(o_free, (n_tok & 1) ^ 1, abort_flag);
         SFA_PROF(5);
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
           const uint32_t b = n_tile & 1, use = n_tile >> 1;
           SFA_PROF(0);
-          ok = ptx::mbar_wait_cluster_warp(&v_full[b], use & 1, abort_flag);
+          ok = ptx::mbar_spin_cluster_warp(&v_full[b], use & 1, abort_flag);
           if (!ok) break;
           SFA_PROF(1);
           if (rank != 0) {
@@ -630,9 +481,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             __syncwarp();
             continue;
           }
-          ok = ptx::mbar_wait_cluster_warp(&v_ready[b], use & 1, abort_flag);
+          ok = ptx::mbar_spin_cluster_warp(&v_ready[b], use & 1, abort_flag);
           SFA_PROF(2);
-          ok = ok && ptx::mbar_wait_cluster_warp(&p_full[b], use & 1, abort_flag);
+          ok = ok && ptx::mbar_spin_cluster_warp(&p_full[b], use & 1, abort_flag);
           if (!ok) break;
           SFA_PROF(3);
           ptx::tc_fence_after();
@@ -658,33 +509,100 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       }
       SFA_PROF_STORE(3, lane == 0);
     }
+  } else if (warp < kSfaSoftWarp0) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSfaRegsCopy));
+    if (!*abort_flag) {
+      // ------------------------------------------------------------------ V copiers
+      // These 128 threads copy the four column blocks of the K slot that this CTA owns as value
+      // columns into its own V slot (plain loads and stores) and the four that the peer owns into
+      // the peer's V slot (st.async: the bytes are counted on the peer's barrier when they land,
+      // the sender does not wait), rows 32*rank.. of every block; 16 chunks of 16 bytes per thread.
+      // Byte offsets inside 4 KB are kept, so the 128-byte swizzle pattern carries over.
+      const int tid = (warp - kSfaCopyWarp0) * 32 + lane;
+      const uint32_t peer = rank ^ 1u;
+      const uint32_t v_peer = ptx::map_to_rank(v_s, peer);
+      const uint32_t v_full_peer = ptx::map_to_rank(v_full, peer);
+      uint32_t n_tile = 0;
+      bool ok = true;
+      SFA_PROF_DECL;
+      for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
+        const int32_t ntiles = item_tiles(item);
+        for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
+          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          SFA_PROF(0);
+          ok = ptx::mbar_spin_warp(&k_full[b * 3], use & 1, abort_flag) &&
+               ptx::mbar_spin_warp(&k_full[b * 3 + 1], use & 1, abort_flag) &&
+               ptx::mbar_spin_warp(&k_full[b * 3 + 2], use & 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(1);
+          // The tile's 16 chunks go into registers first and the K slot is handed back at once: its
+          // refill must not wait for the V slot, which is only free when the value product two
+          // tiles back has completed (the registers act as a third V stage).
+          const unsigned char* ksrc = k_s + b * kSfaKSlot;
+          uint4 v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // i < 8: the four blocks this CTA owns (local copy), i >= 8: the four the peer owns (remote)
+            const int owner = i < 8 ? (int)rank : (int)peer;
+            const int q = (i & 7) * 128 + tid;                  // 0..1023: chunk within the four blocks
+            const int pblk = q >> 8, within = q & 255;
+            const int fblk = 4 * (pblk >> 1) + 2 * owner + (pblk & 1);
+            v[i] = *reinterpret_cast<const uint4*>(ksrc + fblk * kSfaKBlk + within * 16);
+          }
+          // The slot goes back to the TMA unit: reads through the generic proxy (the loads above)
+          // and the writes of the next gather through the async proxy are only ordered by a proxy
+          // fence.  Without it the gather was seen to overtake these loads (outputs changed from
+          // run to run once the hand-overs of this kernel got fast).
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane < 3) ptx::mbar_arrive(&k_empty[b * 3 + lane]);
+          SFA_PROF(2);
+          // V slot b is free in both CTAs once the product that read it has completed
+          ok = ptx::mbar_spin_warp(&v_empty[b], (use & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          SFA_PROF(3);
+          // the peer's half of my V slot: 16 KB of transaction bytes
+          if (tid == 0) ptx::mbar_arrive_expect_tx(&v_full[b], kSfaVSlot / 2);
+          const uint32_t vdst = b * kSfaVSlot + rank * kSfaKBlk;     // rows 32*rank.. of a V block
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int q = (i & 7) * 128 + tid;
+            const int pblk = q >> 8, within = q & 255;
+            const uint32_t off = vdst + pblk * kSfaVBlk + within * 16;
+            if (i >= 8) ptx::st_async_v4(v_peer + off, v[i], v_full_peer + b * 8);
+            else *reinterpret_cast<uint4*>(v_s + off) = v[i];
+          }
+          // the local rows are made visible to the tensor core's reads before the arrival says so
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&v_full[b]);
+          SFA_PROF(4);
+        }
+      }
+      SFA_PROF_STORE(1, tid == 0);
+    }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSfaRegsHigh));
-#ifdef DSA_EXP_PRODONLY
-#if DSA_EXP_PRODONLY == 2
-    ptx::mbar_wait_warp(o_free, 0, abort_flag);
-#elif DSA_EXP_PRODONLY >= 3
-    while (*reinterpret_cast<volatile int*>(xs) == 0) __nanosleep(500);
-#endif
-    if (false) {
-#else
     if (!*abort_flag) {
-#endif
       // ------------------------------------------------------------------ softmax + epilogue
+      const int g = (warp - kSfaSoftWarp0) >> 2;    // group: takes the tiles with (tile number & 1) == g
       const int quarter = warp & 3;
       const int L = quarter * 32 + lane;            // TMEM lane
       const int hl = L & 63, half = L >> 6;         // head within this CTA; which half of N this lane holds
       const int32_t hg = (int32_t)rank * kSfaCtaHeads + hl;
       const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-      const uint32_t s_empty_lead = ptx::map_to_rank(s_empty, 0);
-      const uint32_t p_full_lead = ptx::map_to_rank(p_full, 0);
+      const uint32_t s_empty_lead = ptx::map_to_rank(&s_empty[g], 0);
+      const uint32_t p_full_lead = ptx::map_to_rank(&p_full[g], 0);
       const uint32_t o_free_lead = ptx::map_to_rank(o_free, 0);
-      uint32_t n_tile = 0, n_x = 0;
+      float* xmg = xm + g * 128;
+      const int gp = g * 2 + (quarter & 1);         // this warp's pair
+      const int gp_other = (g ^ 1) * 2 + (quarter & 1);
+      uint32_t n_tile = 0, n_tok = 0, n_x = 0;
       bool ok = true;
       SFA_PROF_DECL;
       // waits are warp-wide: the tcgen05 loads / stores that follow are warp-collective and must
       // never run with part of a warp gone
-      auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool { return ptx::mbar_wait_warp(bar, parity, abort_flag); };
+      auto wait_w = [&](uint64_t* bar, uint32_t parity) -> bool { return ptx::mbar_spin_warp(bar, parity, abort_flag); };
       // One arrival per warp on a barrier of the even CTA.  From the odd CTA it is a relaxed remote
       // arrival: a cluster-scope release costs ~1000 cycles here, and what the arrival announces has
       // already been made visible by the fences before it (tcgen05.wait + tcgen05 fence for tensor
@@ -696,66 +614,70 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           else ptx::mbar_arrive_remote_relaxed(remote, 0u);
         }
       };
-      // value of the head's other thread (lane L ^ 64, another warp) through shared memory
-      auto exchange = [&](float* buf, float v, float& other) -> bool {
-        buf[L] = v;
+      // Value of the head's other thread in this group (lane L ^ 64, another warp) through shared
+      // memory.  The buffer is written again only after everybody has read it (xr_bar).
+      auto exchange = [&](float v, float& other) -> bool {
+        bool got = n_x == 0 || ptx::mbar_spin_warp(&xr_bar[gp], (n_x - 1) & 1, abort_flag);
+        xmg[L] = v;
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(x_bar);
-        const bool got = wait_w(x_bar, n_x & 1);
+        if (lane == 0) ptx::mbar_arrive(&x_bar[gp]);
+        got = ptx::mbar_spin_warp(&x_bar[gp], n_x & 1, abort_flag) && got;
+        other = xmg[L ^ 64];
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&xr_bar[gp]);
         ++n_x;
-        other = buf[L ^ 64];
         return got;
       };
       for (int32_t item = cluster_id; item < a.items && ok; item += n_clusters) {
         const int32_t nvalid = a.nvalid[item].x;
         const int32_t ntiles = (nvalid + kSfaBK - 1) / kSfaBK;
         const int32_t row = kSplit ? item / a.split : item;
-        // this lane's output columns: j * 256 + half * 128 + 0..127 for j = 0, 1
-        unsigned char* out_row = (unsigned char*)a.p.out + (((int64_t)row * n1 + hg) * kSfaDv + half * 128) * 2;
-        float* part_row = kSplit ? a.part_o + ((int64_t)item * kSfaHeads + hg) * kSfaDv + half * 128 : nullptr;
+        // this lane's output columns: group g stores the columns of MMA j = g, g * 256 + half * 128 + 0..127
+        const int col0 = g * 256 + half * 128;
+        unsigned char* out_row = (unsigned char*)a.p.out + (((int64_t)row * n1 + hg) * kSfaDv + col0) * 2;
+        float* part_row = kSplit ? a.part_o + ((int64_t)item * kSfaHeads + hg) * kSfaDv + col0 : nullptr;
         if (ntiles == 0) {
           if constexpr (kSplit) {
             // an empty part: the merge skips it
-            if (half == 0) { a.part_m[(int64_t)item * kSfaHeads + hg] = 0.f; a.part_l[(int64_t)item * kSfaHeads + hg] = 0.f; }
+            if (g == 0 && half == 0) { a.part_m[(int64_t)item * kSfaHeads + hg] = 0.f; a.part_l[(int64_t)item * kSfaHeads + hg] = 0.f; }
           } else if (hg < n1) {
             // nothing visible: zeros in all three outputs
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-              for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(out_row + j * 512)[c] = make_uint4(0, 0, 0, 0);
-            if (half == 0 && a.p.return_lse) {
+            for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+            if (g == 0 && half == 0 && a.p.return_lse) {
               a.p.softmax_max[(int64_t)row * n1 + hg] = 0.f;
               a.p.softmax_sum[(int64_t)row * n1 + hg] = 0.f;
             }
           }
           continue;
         }
-        float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f, l_tot = 0.f;
+        // this thread's share of the row sum, relative to the reference m_cur of its latest tile
+        float m_cur = -INFINITY, l = 0.f, l_grp = 0.f;
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
-          const uint32_t b = n_tile & 1, use = n_tile >> 1;
+          if ((int)(n_tile & 1u) != g) continue;
+          const uint32_t use = n_tile >> 1;
           const int32_t cnt = min(kSfaBK, nvalid - t * kSfaBK) - half * kSfaHalfBK;   // valid keys among this lane's 32
           SFA_PROF(7);
-          ok = wait_w(&s_full[b], use & 1);
+          ok = wait_w(&s_full[g], use & 1);
           if (!ok) break;
           SFA_PROF(0);
           ptx::tc_fence_after();
           float sc[kSfaHalfBK];
-#ifdef DSA_EXP_NOSOFT
-          for (int k = 0; k < kSfaHalfBK; ++k) sc[k] = 0.f;
-          if (false)
-#endif
           {
             // the three issuers' partial products
-            float s1[kSfaHalfBK], s2[kSfaHalfBK];
-            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes) * 32, reinterpret_cast<uint32_t*>(sc));
-            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes + 1) * 32, reinterpret_cast<uint32_t*>(s1));
-            ptx::tmem_ld_x32(lane_addr + kTmS + (b * kSfaQkLanes + 2) * 32, reinterpret_cast<uint32_t*>(s2));
+            float s1[kSfaHalfBK];
+            ptx::tmem_ld_x32(lane_addr + kTmS + (g * kSfaQkLanes) * 32, reinterpret_cast<uint32_t*>(sc));
+            ptx::tmem_ld_x32(lane_addr + kTmS + (g * kSfaQkLanes + 1) * 32, reinterpret_cast<uint32_t*>(s1));
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] = (sc[k] + s1[k]) + s2[k];
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] += s1[k];
+            ptx::tmem_ld_x32(lane_addr + kTmS + (g * kSfaQkLanes + 2) * 32, reinterpret_cast<uint32_t*>(s1));
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < kSfaHalfBK; ++k) sc[k] += s1[k];
           }
           ptx::tc_fence_before();
-          signal_lead(&s_empty[b], s_empty_lead + b * 8);
+          signal_lead(&s_empty[g], s_empty_lead);
           SFA_PROF(1);
           // ---- softmax in the log2 domain; keys past `cnt` are padding
           if (cnt >= kSfaHalfBK) {
@@ -773,47 +695,59 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           }
           float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
           SFA_PROF(2);
-          ok = exchange(xm + b * 128, mx, mx_other);
+          ok = exchange(mx, mx_other);
           if (!ok) break;
-          SFA_PROF(3);
           mx = fmaxf(mx, mx_other);       // the tile's maximum for this head (the first half always has a valid key)
-          m_true = fmaxf(m_true, mx);
-          float alpha = 1.f;
+          // ---- the reference maximum comes from the previous tile, i.e. from the other group
+          float m_new = mx, mt_new = mx, alpha = 1.f;
           bool rescale = false;
-          if (t == 0) {
-            m_ref = mx;
-          } else if (mx > m_ref + kSfaRescaleTau) {
-            alpha = ex2(m_ref - mx);
-            m_ref = mx;
-            rescale = true;
+          if (t > 0) {
+            const uint32_t prev = n_tile - 1;
+            ok = ptx::mbar_spin_warp(&m_bar[gp_other], (prev >> 1) & 1, abort_flag);
+            if (!ok) break;
+            const float2 mp = mref[(g ^ 1) * 64 + hl];
+            mt_new = fmaxf(mp.y, mx);
+            if (mx > mp.x + kSfaRescaleTau) {
+              alpha = ex2(mp.x - mx);     // O holds sums relative to the old reference
+              rescale = true;
+            } else {
+              m_new = mp.x;
+            }
           }
+          // both warps of the pair arrive: the arrival also says "I have read the other group's
+          // entry", which that group overwrites at its next tile
+          if (half == 0) mref[g * 64 + hl] = make_float2(m_new, mt_new);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&m_bar[gp]);
+          SFA_PROF(3);
+          if (m_cur != m_new) { l *= ex2(m_cur - m_new); m_cur = m_new; }   // (l is 0 while m_cur is -inf)
           float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int k = 0; k < kSfaHalfBK; k += 4) {
-            sc[k] = ex2(sc[k] - m_ref); sc[k + 1] = ex2(sc[k + 1] - m_ref);
-            sc[k + 2] = ex2(sc[k + 2] - m_ref); sc[k + 3] = ex2(sc[k + 3] - m_ref);
+            sc[k] = ex2(sc[k] - m_new); sc[k + 1] = ex2(sc[k + 1] - m_new);
+            sc[k + 2] = ex2(sc[k + 2] - m_new); sc[k + 3] = ex2(sc[k + 3] - m_new);
             sum4[0] += sc[k]; sum4[1] += sc[k + 1]; sum4[2] += sc[k + 2]; sum4[3] += sc[k + 3];
           }
-          l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+          l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
           if (ntiles == 1) {
             // a single tile holds the whole row: normalise before rounding, as the golden does
             float l_other;
-            ok = exchange(xs, l, l_other);
+            ok = exchange(l, l_other);
             if (!ok) break;
-            l_tot = l + l_other;
-            const float inv = 1.f / l_tot;
+            l_grp = l + l_other;
+            const float inv = 1.f / l_grp;
 #pragma unroll
             for (int k = 0; k < kSfaHalfBK; ++k) sc[k] *= inv;
           }
           // ---- P (and, rarely, a rescaled O) once the product that last read this P buffer has finished
           SFA_PROF(2);
-          ok = wait_w(&p_empty[b], (use & 1) ^ 1);
+          ok = wait_w(&p_empty[g], (use & 1) ^ 1);
           if (!ok) break;
           SFA_PROF(4);
           if (__any_sync(0xffffffffu, rescale)) {
             // O must be quiescent: the previous tile's product (other P buffer) has to be complete too
             const uint32_t prev = n_tile - 1;
-            ok = wait_w(&p_empty[prev & 1], (prev >> 1) & 1);
+            ok = wait_w(&p_empty[g ^ 1], (prev >> 1) & 1);
             if (!ok) break;
             ptx::tc_fence_after();
 #pragma unroll 1
@@ -827,13 +761,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             }
             ptx::tmem_st_wait();
           }
-#ifdef DSA_EXP_NOSOFT
-          if (false)
-#endif
           {
             // row hl of the K-major, 128-byte-swizzled A operand: keys half*32 .. +31 are the 16-byte
             // chunks half*4 .. +3 of the row
-            unsigned char* prow = p_s + b * kSfaPBuf + hl * 128;
+            unsigned char* prow = p_s + g * kSfaPBuf + hl * 128;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               uint4 w;
@@ -846,37 +777,60 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           }
           ptx::fence_proxy_async_smem();
           ptx::tc_fence_before();
-          signal_lead(&p_full[b], p_full_lead + b * 8);
+          signal_lead(&p_full[g], p_full_lead);
           SFA_PROF(5);
         }
         if (!ok) break;
         SFA_PROF(7);
-        // ---- epilogue: wait for the last product, normalise, store
+        // ---- end of the token: final reference and true maximum (from the group of the last tile),
+        // row sum over the four threads of the head (two halves x two groups)
+        const uint32_t last = n_tile - 1;
+        float m_fin, mt_fin;
         {
-          const uint32_t last = n_tile - 1;
-          ok = wait_w(&p_empty[last & 1], (last >> 1) & 1);
+          ok = wait_w(&m_bar[(last & 1) * 2 + (quarter & 1)], (last >> 1) & 1);
           if (!ok) break;
+          const float2 mf = mref[(last & 1) * 64 + hl];
+          m_fin = mf.x; mt_fin = mf.y;
         }
-        ptx::tc_fence_after();
-        if (ntiles > 1) {
+        float l_tot;
+        if (ntiles == 1) {
+          // already normalised inside the tile's group; the group without a tile contributes nothing
+          if ((int)(last & 1u) != g) l_grp = 0.f;
+        } else {
+          const float ls = l * ex2(m_cur - m_fin);      // 0 for a thread whose group had no tile (m_cur = -inf, l = 0)
           float l_other;
-          ok = exchange(xs, l, l_other);
+          ok = exchange(m_cur == -INFINITY ? 0.f : ls, l_other);
           if (!ok) break;
-          l_tot = l + l_other;
+          l_grp = (m_cur == -INFINITY ? 0.f : ls) + l_other;
         }
+        {
+          ok = n_tok == 0 || wait_w(er_bar, (n_tok - 1) & 1);
+          if (!ok) break;
+          if (half == 0) fin[g * 64 + hl] = l_grp;
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(e_bar);
+          ok = wait_w(e_bar, n_tok & 1);
+          if (!ok) break;
+          l_tot = l_grp + fin[(g ^ 1) * 64 + hl];
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(er_bar);
+        }
+        // ---- epilogue: wait for the last product, normalise, store this group's 128 columns
+        ok = wait_w(&p_empty[last & 1], (last >> 1) & 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
         const float inv = ntiles == 1 ? 1.f : 1.f / l_tot;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          // c = j * 4 + chunk: accumulator columns c*32 .. +31 = value columns j*256 + half*128 + chunk*32 ..
+        for (int c = 0; c < 4; ++c) {
+          // accumulator columns g*128 + c*32 .. +31 = value columns g*256 + half*128 + c*32 ..
           uint32_t o[32];
-          ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
+          ptx::tmem_ld_x32(lane_addr + kTmO + g * 128 + c * 32, o);
           ptx::tmem_ld_wait();
-          const int col = (c >> 2) * 256 + (c & 3) * 32;   // relative to half * 128
           if constexpr (kSplit) {
             // split-KV: the normalised partial output stays fp32 for the merge
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              reinterpret_cast<float4*>(part_row + col)[i] =
+              reinterpret_cast<float4*>(part_row + c * 32)[i] =
                   make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
                               __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
           } else {
@@ -886,26 +840,27 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
               w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, a.is_bf16);
             // whole 32-byte sectors per store: a lane's row is 1 KB away from its neighbour's
             if (hg < n1) {
-              ptx::st_global_v8(out_row + col * 2, w);
-              ptx::st_global_v8(out_row + col * 2 + 32, w + 8);
+              ptx::st_global_v8(out_row + c * 64, w);
+              ptx::st_global_v8(out_row + c * 64 + 32, w + 8);
             }
           }
         }
         ptx::tc_fence_before();
         signal_lead(o_free, o_free_lead);
         SFA_PROF(6);
-        if (half == 0) {
+        if (g == 0 && half == 0) {
           // max of the scaled scores and sum of exp(score - max), back from the log2 domain
           if constexpr (kSplit) {
-            a.part_m[(int64_t)item * kSfaHeads + hg] = m_true * 0.6931471805599453f;
-            a.part_l[(int64_t)item * kSfaHeads + hg] = l_tot * ex2(m_ref - m_true);
+            a.part_m[(int64_t)item * kSfaHeads + hg] = mt_fin * 0.6931471805599453f;
+            a.part_l[(int64_t)item * kSfaHeads + hg] = l_tot * ex2(m_fin - mt_fin);
           } else if (a.p.return_lse && hg < n1) {
-            a.p.softmax_max[(int64_t)row * n1 + hg] = m_true * 0.6931471805599453f;
-            a.p.softmax_sum[(int64_t)row * n1 + hg] = l_tot * ex2(m_ref - m_true);
+            a.p.softmax_max[(int64_t)row * n1 + hg] = mt_fin * 0.6931471805599453f;
+            a.p.softmax_sum[(int64_t)row * n1 + hg] = l_tot * ex2(m_fin - mt_fin);
           }
         }
+        ++n_tok;
       }
-      SFA_PROF_STORE(4, threadIdx.x == kSfaSoftWarp0 * 32);
+      SFA_PROF_STORE(4 + g, (warp & 3) == 0 && lane == 0);
     }
   }
 
@@ -1077,9 +1032,6 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.part_l = reinterpret_cast<float*>((char*)scratch + w.part_l);
   a.part_o = reinterpret_cast<float*>((char*)scratch + w.part_o);
   int clusters = sms / 2;
-#ifdef DSA_SFA_MAX_CLUSTERS
-  clusters = DSA_SFA_MAX_CLUSTERS;
-#endif
   if (clusters > a.items) clusters = a.items;
   CUtensorMap tkn, tkr, tq, tqr;
   if (!make_tmap_gather4_16bit(&tkn, p->key, (uint64_t)p->key_rows, 512, 1024, 64, bf16)) return DSA_ERR_CUDA;

@@ -112,6 +112,14 @@ def test_config5_full_size_sampled_sequences():
         block_size=bs)
     torch.cuda.synchronize()
 
+    # bitwise repeatable at full size (128 rows x 32 tiles keep every ring of the kernel busy)
+    for _ in range(3):
+        out2, smax2, ssum2 = sparse_flash_attention_triton(
+            q, kv_cache, kv_cache, idx, scale_value=scale, block_table=table, actual_seq_lengths_kv=lens_l,
+            query_rope=qr, key_rope=kr_cache, layout_kv="PA_BSND", sparse_mode=3, return_softmax_lse=True,
+            block_size=bs)
+        assert torch.equal(out2, out) and torch.equal(smax2, smax) and torch.equal(ssum2, ssum)
+
     # every row: 2048 distinct positions inside the causal window, values descending, sum >= 1
     lens_t = torch.tensor(lens_l, device="cuda")
     limit = (lens_t[:, None] - S1 + torch.arange(S1, device="cuda")[None, :] + 1)[:, :, None, None]
