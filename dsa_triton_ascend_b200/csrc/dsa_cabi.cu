@@ -38,6 +38,10 @@ static int li_validate(const DsaLiParams* p) {
   if (p->layout_k == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
   if (p->layout_k == DSA_LAYOUT_PA_BSND && (!p->block_table || p->block_size < 1 || p->max_blocks < 1 || !p->seq_k))
     return DSA_ERR_VALUE;
+  // a paged sequence cannot be longer than its row of the block table (the score scratch and the
+  // key tiles are sized from s2; positions past the table would never be written)
+  if (p->layout_k == DSA_LAYOUT_PA_BSND && (int64_t)p->s2 > (int64_t)p->max_blocks * p->block_size) return DSA_ERR_VALUE;
+  if (p->key_rows < 0) return DSA_ERR_VALUE;
   if (p->phases < 1 || p->phases > DSA_PHASE_ALL) return DSA_ERR_VALUE;
   if (p->kernel < DSA_KERNEL_AUTO || p->kernel > DSA_KERNEL_TENSOR) return DSA_ERR_VALUE;
   return DSA_OK;
@@ -56,6 +60,7 @@ static LiDev li_dev(const DsaLiParams* p) {
   d.seq.batch = p->batch; d.seq.s1 = p->s1; d.seq.s2 = p->s2;
   d.seq.block_size = p->block_size; d.seq.max_blocks = p->max_blocks;
   d.seq.sparse_mode = p->sparse_mode;
+  d.seq.key_rows = p->key_rows;
   d.query = p->query; d.key = p->key; d.weights = p->weights;
   d.out_indices = p->out_indices; d.out_values = p->out_values;
   d.dtype_w = p->dtype_w; d.n1 = p->n1; d.n2 = p->n2; d.d = p->d;
@@ -80,6 +85,7 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       int rc = li_sm100_launch(p, d, scores, ld, status, st);
       if (rc != DSA_OK) return rc;
     } else if (p->s2 > 0) {
+      if ((p->s2 + kSimtKeys - 1) / kSimtKeys > 65535) return DSA_ERR_TOO_LARGE;   // key tiles ride on grid.y
       dim3 grid((unsigned)rown, (unsigned)((p->s2 + kSimtKeys - 1) / kSimtKeys), 1);
       li_score_simt_kernel<T><<<grid, kSimtKeys, 0, st>>>(d, scores, ld);
       if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
@@ -151,6 +157,7 @@ static SfaDev sfa_dev(const DsaSfaParams* p) {
   d.seq.batch = p->batch; d.seq.s1 = p->s1; d.seq.s2 = p->s2;
   d.seq.block_size = p->block_size; d.seq.max_blocks = p->max_blocks;
   d.seq.sparse_mode = p->sparse_mode;
+  d.seq.key_rows = p->key_rows;
   d.query = p->query; d.query_rope = p->query_rope; d.key = p->key; d.key_rope = p->key_rope;
   d.sparse_indices = p->sparse_indices;
   d.out = p->out; d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
@@ -175,6 +182,22 @@ static int sfa_launch_simt(const DsaSfaParams* p, cudaStream_t st) {
   sfa_fwd_simt_kernel<T><<<grid, kSfaSimtThreads, smem, st>>>(d);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   return DSA_OK;
+}
+
+// A wait that nothing satisfies, with a short limit: one thread waits on an mbarrier that no one
+// ever arrives on (no copy or MMA is in flight), gives up and reports it the way the tensor-core
+// kernels do (status word 1).  Used to test the failure path end to end without faulting a GPU.
+__global__ void selftest_wait_timeout_kernel(int32_t* status, uint32_t polls) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    abort_flag = 0;
+    ptx::mbar_fence_init();
+    bool got = false;
+    for (uint32_t i = 0; i < polls && !got; ++i) got = ptx::mbar_try_wait(&bar, 0);
+    if (!got) atomicExch(status, 1);
+  }
 }
 
 }  // namespace dsa
@@ -307,6 +330,14 @@ int dsa_debug_sfa_profile(long long* out) {
   return cudaMemcpyFromSymbol(out, g_sfa_prof, sizeof(long long) * 128) == cudaSuccess ? DSA_OK : DSA_ERR_CUDA;
 }
 #endif
+
+int dsa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < kWorkspaceHeader || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  selftest_wait_timeout_kernel<<<1, 32, 0, cs>>>((int32_t*)workspace, 64u);   // 64 polls of up to 8 us
+  return cudaGetLastError() == cudaSuccess ? DSA_OK : DSA_ERR_CUDA;
+}
 
 int dsa_read_device_status(const void* workspace, void* stream) {
   if (!workspace) return DSA_ERR_NULL;

@@ -24,6 +24,7 @@ struct SeqDesc {
   int32_t batch, s1, s2;
   int32_t block_size, max_blocks;
   int32_t sparse_mode;
+  int64_t key_rows;   // physical key rows behind the key pointer (0: unknown, no check)
 };
 
 // Everything a kernel needs to know about one query row.
@@ -74,16 +75,22 @@ __device__ __forceinline__ RowInfo row_info(const SeqDesc& s, int32_t row) {
   return r;
 }
 
-// Physical key row of logical position `p` of sequence r.b; -1 when a paged block is absent.
+// Physical key row of logical position `p` of sequence r.b; -1 (the callers read a zero row) when a
+// paged block is absent or when the row would lie outside the key tensor: a stale block-table entry
+// or cumulative lengths that overrun the tensor must not become an out-of-bounds read.
 __device__ __forceinline__ int64_t key_row(const SeqDesc& s, const RowInfo& r, int32_t p) {
+  int64_t row;
   if (s.layout_k == DSA_LAYOUT_PA_BSND) {
     int32_t blk_i = p / s.block_size;
     if (blk_i >= s.max_blocks) return -1;
     int32_t blk = s.block_table[(int64_t)r.b * s.max_blocks + blk_i];
     if (blk < 0) return -1;
-    return (int64_t)blk * s.block_size + (p - blk_i * s.block_size);
+    row = (int64_t)blk * s.block_size + (p - blk_i * s.block_size);
+  } else {
+    row = r.key_base + p;
   }
-  return r.key_base + p;
+  if (s.key_rows > 0 && row >= s.key_rows) return -1;
+  return row;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

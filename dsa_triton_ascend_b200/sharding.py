@@ -113,3 +113,85 @@ def sparse_flash_attention_rows(query, key, sparse_indices, query_rope, key_rope
     return sparse_flash_attention_triton(
         query[:, r0:r1], key, key, sparse_indices[:, r0:r1], actual_seq_lengths_query=lq,
         actual_seq_lengths_kv=lk, query_rope=query_rope[:, r0:r1], key_rope=key_rope, **kw)
+
+
+# ---- TND batches: contiguous token ranges -----------------------------------------------------------
+def tnd_token_slices(cum_q: Sequence[int], cum_k: Sequence[int], world: int, cap: int = 0,
+                     align: int = 8) -> List[Tuple[int, int]]:
+    """Split the T1 tokens of a TND batch into `world` contiguous ranges of nearly equal causal work
+    (visible keys per token, clipped at `cap` for top-k attention).  Boundaries are multiples of
+    `align` tokens."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    per_tok = []
+    pq = pk = 0
+    for cq, ck in zip(cum_q, cum_k):
+        aq, ak = int(cq) - pq, int(ck) - pk
+        for s in range(aq):
+            v = min(max(ak - aq + s + 1, 0), ak)
+            per_tok.append(min(v, cap) if cap > 0 else v)
+        pq, pk = int(cq), int(ck)
+    total_tok, total = len(per_tok), sum(per_tok)
+    bounds, acc, r = [0], 0, 0
+    for i in range(1, world):
+        target = total * i / world
+        while r < total_tok and acc + per_tok[r] / 2 < target:
+            acc += per_tok[r]
+            r += 1
+        b = max(min(total_tok, (r + align // 2) // align * align), bounds[-1])
+        bounds.append(b)
+        acc, r = sum(per_tok[:b]), b
+    bounds.append(total_tok)
+    return [(bounds[i], bounds[i + 1]) for i in range(world)]
+
+
+def tnd_slice(cum_q: Sequence[int], cum_k: Sequence[int], t0: int, t1: int):
+    """Tokens [t0, t1) of a TND batch as a stand-alone TND problem.
+
+    Returns (cum_q', cum_k', key_ranges): the cumulative lengths of the sequences the range touches
+    and, per such sequence, the rows [k0, k1) of the packed key tensor it needs.  A sequence cut at
+    its end keeps act_k' = act_k - (act_q - r1) keys (see the module docstring), so the keys of the
+    slice are the concatenation of those row ranges rather than a view of the full key tensor."""
+    if not (0 <= t0 <= t1 <= (int(cum_q[-1]) if len(cum_q) else 0)):
+        raise ValueError("token range outside the batch")
+    out_q, out_k, ranges = [], [], []
+    pq = pk = 0
+    for cq, ck in zip(cum_q, cum_k):
+        cq, ck = int(cq), int(ck)
+        lo, hi = max(t0, pq), min(t1, cq)
+        if hi > lo:
+            q_, k_ = slice_lengths(cq - pq, ck - pk, lo - pq, hi - pq)
+            out_q.append((out_q[-1] if out_q else 0) + q_)
+            out_k.append((out_k[-1] if out_k else 0) + k_)
+            ranges.append((pk, pk + k_))
+        pq, pk = cq, ck
+    return out_q, out_k, ranges
+
+
+def _cat_rows(t, ranges):
+    import torch
+    if len(ranges) == 1:
+        return t[ranges[0][0]:ranges[0][1]]
+    return torch.cat([t[a:b] for a, b in ranges], dim=0)
+
+
+def lightning_indexer_tokens(query, key, weights, cum_q: Sequence[int], cum_k: Sequence[int], t0: int,
+                             t1: int, **kw):
+    """lightning_indexer_triton on tokens [t0, t1) of a TND batch (TND query and key).  Returns what
+    the full call returns for those tokens (indices are positions inside each token's own sequence)."""
+    from .lightning_indexer import lightning_indexer_triton
+    cq, ck, ranges = tnd_slice(cum_q, cum_k, t0, t1)
+    return lightning_indexer_triton(query[t0:t1], _cat_rows(key, ranges), weights[t0:t1],
+                                    actual_seq_lengths_query=cq, actual_seq_lengths_key=ck,
+                                    layout_query="TND", layout_key="TND", **kw)
+
+
+def sparse_flash_attention_tokens(query, key, sparse_indices, query_rope, key_rope, cum_q: Sequence[int],
+                                  cum_k: Sequence[int], t0: int, t1: int, **kw):
+    """sparse_flash_attention_triton on tokens [t0, t1) of a TND batch (TND query and KV)."""
+    from .sparse_flash_attention import sparse_flash_attention_triton
+    cq, ck, ranges = tnd_slice(cum_q, cum_k, t0, t1)
+    k = _cat_rows(key, ranges)
+    return sparse_flash_attention_triton(
+        query[t0:t1], k, k, sparse_indices[t0:t1], actual_seq_lengths_query=cq, actual_seq_lengths_kv=ck,
+        query_rope=query_rope[t0:t1], key_rope=_cat_rows(key_rope, ranges), layout_query="TND", layout_kv="TND", **kw)

@@ -170,6 +170,13 @@ const char* dsa_status_string(int status);
 /* Synchronises `stream` and returns the device status word stored at the start of a
  * workspace: DSA_OK, or DSA_ERR_DEVICE_WAIT when a bounded in-kernel wait gave up. */
 int dsa_read_device_status(const void* workspace, void* stream);
+/* Self-test of the failure path (no counterpart in the reference, which reports nothing from the
+ * device): enqueues a one-thread kernel that waits, with a limit of about half a millisecond, on a
+ * barrier nothing ever signals, gives up and leaves the status word set - exactly what a tensor-core
+ * kernel does when one of its bounded waits runs out.  dsa_read_device_status(workspace) then
+ * returns DSA_ERR_DEVICE_WAIT; the device context stays usable.  `workspace`: >= 256 bytes,
+ * 256-byte aligned. */
+int dsa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, void* stream);
 /* 1 when dsa_*_forward would take the tcgen05 path for these parameters, else 0. */
 int dsa_li_uses_tensor_path(const DsaLiParams* p);
 int dsa_sfa_uses_tensor_path(const DsaSfaParams* p);

@@ -93,11 +93,8 @@ def test_sfa_tensor_path_equals_portable_on_random_problems(seed):
             out[kind] = [host(t) for t in sfa.sparse_flash_attention_triton(*args, **kw)]
         finally:
             sfa.set_kernel("auto")
-    if layout == "PA_BSND" and seed % 2:
-        # an absent block inside the valid length: the portable kernel reads zeros (like the
-        # reference's un-paging), the tensor path drops the slot; compare only finiteness there
-        assert all(np.isfinite(a).all() for a in out["tensor"])
-        return
+    # (odd seeds with a paged cache have absent blocks inside the valid length: both paths read such
+    # a slot as a zero row that takes part, like the reference's un-paging)
     sfa_acceptance_rule(*out["tensor"], *out["portable"])
 
 
