@@ -8,13 +8,15 @@ One step = one pass of the hot path over one synthetic batch:
   * attention: TND, sequence lengths 8192/4096/2048/1024 (15360 tokens), 128 heads, D=512+64,
                bf16, top-k 2048 token-wise, mode 3, indices taken from an indexer run over the
                same token layout (done once, outside the timed region), softmax stats returned.
-`value` is attention forward TFLOP/s over all ranks (valid query-key pairs x 128 heads x
-2*(576+512) flop); the indexer's query-tokens/s (score + top-k) is reported beside it.  Every
-rank works on its own seeded batch (weak scaling, no collective on the data path); the timed
-region is bracketed by a barrier and a device synchronise, timed with CUDA events on the launch
-stream, max over ranks.  `e2e` repeats the step through the public Python operators with
-pinned HOST buffers: host->device copies of every input and device->host copies of every result
-are inside its timed region.
+`value` is attention forward TFLOP/s of the whole job (valid query-key pairs x 128 heads x
+2*(576+512) flop / the slowest rank's time); the indexer's query-tokens/s (score + top-k) is
+reported beside it.  The inputs are the seeded tensors of dsa_triton_ascend_b200.synthetic
+(numpy RandomState(2) / RandomState(3)).  With N GPUs the SAME problem is split (strong
+scaling): indexer rows and attention tokens in contiguous ranges balanced by causal work, keys
+replicated, no collective on the data path; the timed region is bracketed by a barrier and a
+device synchronise, timed with CUDA events on the launch stream, max over ranks.  `e2e` repeats
+the step through the public Python operators with pinned HOST buffers: host->device copies of
+every input and device->host copies of every result are inside its timed region.
 
 `--impl reference` times the CPU implementation of the same path (the numpy restatement of the
 reference goldens under oracle/, run over all host cores) on a bounded sample of the same
@@ -127,46 +129,44 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-def make_gpu_batch(torch, seed, lens, quick):
-    """Synthetic batch resident in HBM: N(0,1) bf16 activations, fp32 weights N(0,1)/8."""
-    g = torch.Generator(device="cuda").manual_seed(seed)
-    bf = torch.bfloat16
-    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
-    S = lens[0]
-    T = sum(lens)
-    b = {}
-    b["li_q"] = rn(1, S, LI_HEADS, LI_D).to(bf)
-    b["li_k"] = rn(1, S, 1, LI_D).to(bf)
-    b["li_w"] = rn(1, S, LI_HEADS) / 8
-    # indexer inputs over the attention batch's token layout (only used to make the indices)
-    iq = rn(T, LI_HEADS, LI_D).to(bf)
-    ik = rn(T, 1, LI_D).to(bf)
-    iw = rn(T, LI_HEADS) / 8
-    b["q"] = torch.empty(T, SFA_HEADS, SFA_D, dtype=bf, device="cuda")
-    for i in range(0, T, 2048):  # chunked: keeps the fp32 staging buffer small
-        b["q"][i:i + 2048] = rn(min(2048, T - i), SFA_HEADS, SFA_D).to(bf)
-    b["qr"] = rn(T, SFA_HEADS, SFA_DR).to(bf)
-    b["k"] = rn(T, 1, SFA_D).to(bf)
-    b["kr"] = rn(T, 1, SFA_DR).to(bf)
-    cu = np.cumsum(lens).tolist()
-    b["cu"] = cu
-    from dsa_triton_ascend_b200 import lightning_indexer_triton
-    idx, _ = lightning_indexer_triton(iq, ik, iw, actual_seq_lengths_query=cu, actual_seq_lengths_key=cu,
-                                      layout_query="TND", layout_key="TND", sparse_count=TOPK, sparse_mode=3)
-    b["idx"] = idx.contiguous()
-    del iq, ik, iw
-    torch.cuda.synchronize()
-    return b
+def bind_to_gpu_numa_node(index):
+    """Restrict this process to the CPUs NVML reports as local to GPU `index` (a read-only query),
+    so that pinned host buffers land on that GPU's NUMA node.  Returns the CPU count or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cpus = [w * 64 + b for w, m in enumerate(words) for b in range(64) if (int(m) >> b) & 1]
+        cpus = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
+def pct(xs):
+    xs = np.asarray(xs, np.float64)
+    return {"mean": float(xs.mean()), "median": float(np.median(xs)), "p20": float(np.percentile(xs, 20)),
+            "p80": float(np.percentile(xs, 80))}
 
 
 def decode_c5(torch, rank, world, flush, iters=5):
     """Configuration 5 (decode): lightning_indexer then sparse_flash_attention over paged caches,
-    B=64 sequences split over the ranks, S1=2, KV lengths uniform in [16384, 65536], block 128.
-    Reported beside the headline numbers; the indexer here is bound by reading the index-K cache."""
+    B=64 sequences dealt out over the ranks by cached length (sharding.sequence_shards), S1=2, KV
+    lengths uniform in [16384, 65536] from RandomState(4), block 128.  Reported beside the headline
+    numbers; the indexer here is bound by reading the index-K cache."""
     from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
-    B, S1, bs, K = max(1, 64 // world), 2, 128, TOPK
+    from dsa_triton_ascend_b200.sharding import sequence_shards
+    S1, bs, K = 2, 128, TOPK
+    all_lens = np.random.RandomState(4).randint(16384, 65537, size=64)
+    mine = sequence_shards(all_lens.tolist(), world)[rank]
+    lens = all_lens[mine]
+    B = len(mine)
     rng = np.random.RandomState(4000 + rank)
-    lens = rng.randint(16384, 65537, size=B)
     need = [int(-(-L // bs)) for L in lens]
     nblk, max_blocks = sum(need), max(need)
     perm = rng.permutation(nblk)
@@ -250,45 +250,69 @@ def decode_c5(torch, rank, world, flush, iters=5):
     graph_ms = float(np.median(t_g))
     ik_bytes = float(sum(lens_l)) * LI_D * 2                     # index-K rows the indexer must read
     gathered = float(B * S1 * K) * (SFA_D + SFA_DR) * 2          # KV rows the attention gathers
-    return {"workload": "B=%d S1=2 L~U[16384,65536] paged block 128, LI 64x128 -> top-%d -> SFA 128x(512+64)" % (B, K),
+    return {"workload": "64 sequences over %d rank(s) (%d here), S1=2, L~U[16384,65536] paged block 128, "
+                        "LI 64x128 -> top-%d -> SFA 128x(512+64)" % (world, B, K),
             "li_ms": li_ms, "sfa_ms": sfa_ms, "step_ms": li_ms + sfa_ms, "graph_replay_step_ms": graph_ms,
-            "li_index_k_GBps": ik_bytes / (li_ms * 1e-3) / 1e9, "sfa_gather_GBps": gathered / (sfa_ms * 1e-3) / 1e9,
-            "tokens_per_s": B * S1 / ((li_ms + sfa_ms) * 1e-3) * world}
+            "li_index_k_GBps": ik_bytes / (li_ms * 1e-3) / 1e9, "sfa_gather_GBps": gathered / (sfa_ms * 1e-3) / 1e9}
 
 
 def run_gpu(args):
+    import ctypes
     import torch
     import torch.distributed as dist
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
+    numa_cpus = bind_to_gpu_numa_node(local)          # before any pinned allocation
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    from dsa_triton_ascend_b200 import lightning_indexer_triton, sparse_flash_attention_triton
-    from dsa_triton_ascend_b200 import _cabi
+    from dsa_triton_ascend_b200 import _cabi, lightning_indexer_triton, sparse_flash_attention_triton, synthetic
+    from dsa_triton_ascend_b200.sharding import (row_slices, slice_lengths, tnd_slice, tnd_token_slices)
     import dsa_triton_ascend_b200.lightning_indexer as li_mod
 
-    lens = [L // args.scale for L in SEQ_LENS]
-    topk = TOPK // args.scale
-    globals()["TOPK"] = topk
-    batch = make_gpu_batch(torch, 1000 + rank, lens, args.quick)
-    S, T = lens[0], sum(lens)
-    scale = 1.0 / np.sqrt(SFA_D + SFA_DR)
+    # ---- the seeded problem (host), this rank's share of it (device)
+    c3 = synthetic.config3(None, args.scale)
+    c4 = synthetic.config4(None, args.scale)
+    S, topk = c3["S"], c3["sparse_count"]
+    lens, cum, T = c4["lens"], c4["cum"], c4["T"]
+    scale = c4["scale"]
     flops_sfa, _ = sfa_flops(lens, topk)
     flops_li, _ = li_flops(S)
+    r0, r1 = row_slices(S, S, world)[rank]                                   # indexer rows of this rank
+    t0, t1 = tnd_token_slices(cum, cum, world, cap=topk)[rank]               # attention tokens of this rank
+    cq, ck, kranges = tnd_slice(cum, cum, t0, t1)
+    my_li_pairs = sum(s + 1 for s in range(r0, r1))
+    my_sfa_pairs = 0
+    pq = 0
+    for cqe, L in zip(cum, lens):
+        for t in range(max(t0, pq), min(t1, cqe)):
+            my_sfa_pairs += min(topk, t - pq + 1)
+        pq = cqe
+    dev = lambda x: x.cuda(non_blocking=False)
+    cat = lambda t: torch.cat([t[a:b] for a, b in kranges], dim=0) if len(kranges) != 1 else t[kranges[0][0]:kranges[0][1]]
+    li_lq, li_lk = slice_lengths(S, S, r0, r1)
+    b = {"li_q": dev(c3["q"][:, r0:r1]), "li_k": dev(c3["k"]), "li_w": dev(c3["w"][:, r0:r1]),
+         "q": dev(c4["q"][t0:t1]), "qr": dev(c4["qr"][t0:t1]), "k": dev(cat(c4["k"])), "kr": dev(cat(c4["kr"]))}
+    # the attention's indices come from the indexer over the same tokens (once, outside the timed region)
+    idx, _ = lightning_indexer_triton(dev(c4["qi"][t0:t1]), dev(cat(c4["ki"])), dev(c4["wi"][t0:t1]),
+                                      actual_seq_lengths_query=cq, actual_seq_lengths_key=ck, layout_query="TND",
+                                      layout_key="TND", sparse_count=topk, sparse_mode=3,
+                                      max_seqlen_key=max(lens))
+    b["idx"] = idx.contiguous()
+    torch.cuda.synchronize()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def li_step():
-        return lightning_indexer_triton(batch["li_q"], batch["li_k"], batch["li_w"], sparse_count=topk, sparse_mode=3)
+        return lightning_indexer_triton(b["li_q"], b["li_k"], b["li_w"], actual_seq_lengths_query=[li_lq],
+                                        actual_seq_lengths_key=[li_lk], sparse_count=topk, sparse_mode=3)
 
     def sfa_step():
         return sparse_flash_attention_triton(
-            batch["q"], batch["k"], batch["k"], batch["idx"], scale_value=scale,
-            actual_seq_lengths_query=batch["cu"], actual_seq_lengths_kv=batch["cu"],
-            query_rope=batch["qr"], key_rope=batch["kr"], layout_query="TND", layout_kv="TND",
+            b["q"], b["k"], b["k"], b["idx"], scale_value=scale, actual_seq_lengths_query=cq,
+            actual_seq_lengths_kv=ck, query_rope=b["qr"], key_rope=b["kr"], layout_query="TND", layout_kv="TND",
             sparse_mode=3, return_softmax_lse=True)
 
     def barrier():
@@ -297,32 +321,36 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        li_step()
-        sfa_step()
+        li_out = li_step()
+        sfa_out = sfa_step()
     barrier()
 
     sampler = ClockSampler(local)
     sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
+    launches0 = int(_cabi.lib.dsa_kernel_launch_count())
     t_wall = time.perf_counter()
     for s in range(args.steps):
         flush.fill_(s & 0xFF)  # evict L2 between timed iterations
         ev[s][0].record()
-        li_step()
+        li_out = li_step()
         ev[s][1].record()
-        sfa_step()
+        sfa_out = sfa_step()
         ev[s][2].record()
     barrier()
     t_wall = time.perf_counter() - t_wall
+    launches = int(_cabi.lib.dsa_kernel_launch_count()) - launches0
     clocks = sampler.stop()
-    li_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    sfa_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    li_all = [e[0].elapsed_time(e[1]) for e in ev]
+    sfa_all = [e[1].elapsed_time(e[2]) for e in ev]
+    li_ms, sfa_ms = float(np.mean(li_all)), float(np.mean(sfa_all))
+    from dsa_triton_ascend_b200 import check_status
+    check_status()
 
     # score / top-k split of the indexer (same inputs, phases launched separately)
-    p, keep, _, _, _ = li_mod._build_params(batch["li_q"], batch["li_k"], batch["li_w"], None, None, None,
+    p, keep, _, _, _ = li_mod._build_params(b["li_q"], b["li_k"], b["li_w"], [li_lq], [li_lk], None,
                                             "BSND", "BSND", topk, 3, False)
-    import ctypes
     nbytes = ctypes.c_size_t(0)
     _cabi.check(_cabi.lib.dsa_li_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)), "li")
     ws = torch.empty(nbytes.value, dtype=torch.uint8, device="cuda")
@@ -342,24 +370,32 @@ def run_gpu(args):
             if i >= args.warmup:
                 times.append(a.elapsed_time(b_))
         phase_ms[name] = float(np.mean(times))
-    del keep
+    del keep, ws
 
     # ---- end to end through the public operators with pinned HOST buffers.  Rows are independent,
     # so the step is run as a pipeline over row chunks: chunk i+1 is uploaded and chunk i-1 is
     # downloaded (separate copy streams, PCIe is full duplex) while chunk i computes.  The small
     # key tensors are uploaded once per step; every byte of input and output crosses PCIe inside
     # the timed region.
-    from dsa_triton_ascend_b200.sharding import slice_lengths
-    host_in = {k: v.cpu().pin_memory() for k, v in batch.items() if hasattr(v, "cpu")}
-    out_h = torch.empty(batch["q"].shape, dtype=torch.bfloat16).pin_memory()
-    st_h = torch.empty((2, T, SFA_HEADS), dtype=torch.float32).pin_memory()
-    idx_h = torch.empty((S, 1, topk), dtype=torch.int32).pin_memory()
-    h2d = sum(host_in[k].numel() * host_in[k].element_size() for k in host_in)
+    host_in = {k_: v.cpu().pin_memory() for k_, v in b.items()}
+    n_tok, n_row = t1 - t0, r1 - r0
+    out_h = torch.empty((n_tok, SFA_HEADS, SFA_D), dtype=torch.bfloat16).pin_memory()
+    st_h = torch.empty((2, n_tok, SFA_HEADS), dtype=torch.float32).pin_memory()
+    idx_h = torch.empty((n_row, 1, topk), dtype=torch.int32).pin_memory()
+    h2d = sum(host_in[k_].numel() * host_in[k_].element_size() for k_ in host_in)
     d2h = out_h.numel() * 2 + st_h.numel() * 4 + idx_h.numel() * 4
     chunk = max(256, 1024 // args.scale)
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     comp = torch.cuda.current_stream()
-    seq_start = [0] + batch["cu"][:-1]
+    # this rank's attention tokens as (local token range, sequence key range, row range in the sequence, lengths)
+    pieces, pq, pk, loc = [], 0, 0, 0
+    for cqe, cke in zip(cq, ck):
+        Lq, Lk = cqe - pq, cke - pk
+        for a0 in range(0, Lq, chunk):
+            a1 = min(Lq, a0 + chunk)
+            pieces.append((loc + a0, loc + a1, pk, cke) + slice_lengths(Lq, Lk, a0, a1))
+        loc += Lq
+        pq, pk = cqe, cke
 
     def upload(t, keep):
         with torch.cuda.stream(s_in):
@@ -373,47 +409,43 @@ def run_gpu(args):
         # indexer: key + per-chunk query rows / weights in, indices out
         lik = upload(host_in["li_k"], keep)
         k_d, kr_d = upload(host_in["k"], keep), upload(host_in["kr"], keep)
-        for r0 in range(0, S, 2 * chunk):
-            r1 = min(S, r0 + 2 * chunk)
-            q_c = upload(host_in["li_q"][:, r0:r1], keep)
-            w_c = upload(host_in["li_w"][:, r0:r1], keep)
-            ev = torch.cuda.Event()
-            ev.record(s_in)
-            comp.wait_event(ev)
-            lq, lk = slice_lengths(S, S, r0, r1)
+        for a0 in range(0, n_row, 2 * chunk):
+            a1 = min(n_row, a0 + 2 * chunk)
+            q_c = upload(host_in["li_q"][:, a0:a1], keep)
+            w_c = upload(host_in["li_w"][:, a0:a1], keep)
+            e_ = torch.cuda.Event()
+            e_.record(s_in)
+            comp.wait_event(e_)
+            lq, lk = slice_lengths(li_lq, li_lk, a0, a1)
             i_c, _ = lightning_indexer_triton(q_c, lik, w_c, actual_seq_lengths_query=[lq],
                                               actual_seq_lengths_key=[lk], sparse_count=topk, sparse_mode=3)
-            ev2 = torch.cuda.Event()
-            ev2.record(comp)
-            s_out.wait_event(ev2)
+            e2 = torch.cuda.Event()
+            e2.record(comp)
+            s_out.wait_event(e2)
             with torch.cuda.stream(s_out):
-                idx_h[r0:r1].copy_(i_c[0], non_blocking=True)
+                idx_h[a0:a1].copy_(i_c[0], non_blocking=True)
             i_c.record_stream(s_out)
         # attention: one sequence at a time, rows in chunks
-        for b, L in enumerate(lens):
-            t0 = seq_start[b]
-            for r0 in range(0, L, chunk):
-                r1 = min(L, r0 + chunk)
-                sl = slice(t0 + r0, t0 + r1)
-                q_c, qr_c = upload(host_in["q"][sl], keep), upload(host_in["qr"][sl], keep)
-                i_c = upload(host_in["idx"][sl], keep)
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-                comp.wait_event(ev)
-                lq, lk = slice_lengths(L, L, r0, r1)
-                o, m, s_ = sparse_flash_attention_triton(
-                    q_c[None], k_d[t0:t0 + L][None], None, i_c[None], scale_value=scale,
-                    actual_seq_lengths_query=[lq], actual_seq_lengths_kv=[lk], query_rope=qr_c[None],
-                    key_rope=kr_d[t0:t0 + L][None], sparse_mode=3, return_softmax_lse=True)
-                ev2 = torch.cuda.Event()
-                ev2.record(comp)
-                s_out.wait_event(ev2)
-                with torch.cuda.stream(s_out):
-                    out_h[sl].copy_(o[0], non_blocking=True)
-                    st_h[0, sl].copy_(m[0, 0], non_blocking=True)
-                    st_h[1, sl].copy_(s_[0, 0], non_blocking=True)
-                for t_ in (o, m, s_):
-                    t_.record_stream(s_out)
+        for (l0, l1, k0, k1, lq, lk) in pieces:
+            sl = slice(l0, l1)
+            q_c, qr_c = upload(host_in["q"][sl], keep), upload(host_in["qr"][sl], keep)
+            i_c = upload(host_in["idx"][sl], keep)
+            e_ = torch.cuda.Event()
+            e_.record(s_in)
+            comp.wait_event(e_)
+            o, m, s_ = sparse_flash_attention_triton(
+                q_c[None], k_d[k0:k1][None], None, i_c[None], scale_value=scale,
+                actual_seq_lengths_query=[lq], actual_seq_lengths_kv=[lk], query_rope=qr_c[None],
+                key_rope=kr_d[k0:k1][None], sparse_mode=3, return_softmax_lse=True)
+            e2 = torch.cuda.Event()
+            e2.record(comp)
+            s_out.wait_event(e2)
+            with torch.cuda.stream(s_out):
+                out_h[sl].copy_(o[0], non_blocking=True)
+                st_h[0, sl].copy_(m[0, 0], non_blocking=True)
+                st_h[1, sl].copy_(s_[0, 0], non_blocking=True)
+            for t_ in (o, m, s_):
+                t_.record_stream(s_out)
         comp.wait_stream(s_out)
         comp.wait_stream(s_in)
 
@@ -428,77 +460,131 @@ def run_gpu(args):
     barrier()
     e2e_ms = a.elapsed_time(b_) / e2e_steps
 
-    def reduce_max(x):
+    def gather(x):
         if world == 1:
-            return x
+            return [float(x)]
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        allr = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allr, t)
+        return [float(v.item()) for v in allr]
 
-    # per-rank device times and clocks (the headline uses the slowest rank)
-    per_rank = None
-    if world > 1:
-        mine = torch.tensor([li_ms, sfa_ms, e2e_ms, float(clocks.get("sm_mhz") or 0.0),
-                             float(len(clocks.get("reasons") or []))], dtype=torch.float64, device="cuda")
-        allr = [torch.zeros_like(mine) for _ in range(world)]
-        dist.all_gather(allr, mine)
-        per_rank = {"li_ms": [float(t[0]) for t in allr], "sfa_ms": [float(t[1]) for t in allr],
-                    "e2e_ms": [float(t[2]) for t in allr], "sm_mhz": [float(t[3]) for t in allr],
-                    "throttle_reasons": [int(t[4]) for t in allr]}
-    li_ms, sfa_ms, e2e_ms = reduce_max(li_ms), reduce_max(sfa_ms), reduce_max(e2e_ms)
+    # per-rank device times, work shares and clocks (the headline uses the slowest rank)
+    per_rank = {"li_ms": gather(li_ms), "sfa_ms": gather(sfa_ms), "e2e_ms": gather(e2e_ms),
+                "sfa_pairs": gather(my_sfa_pairs), "li_pairs": gather(my_li_pairs),
+                "h2d_GBps": gather((h2d) / (e2e_ms * 1e-3) / 1e9), "d2h_GBps": gather(d2h / (e2e_ms * 1e-3) / 1e9),
+                "sm_mhz": gather(float(clocks.get("sm_mhz") or 0.0)),
+                "throttle_reasons": gather(float(len(clocks.get("reasons") or []))),
+                "numa_cpus": gather(float(numa_cpus or 0))}
+    h2d_tot, d2h_tot = sum(gather(h2d)), sum(gather(d2h))
+    launches_tot = int(sum(gather(launches)))
+    li_max, sfa_max, e2e_max = max(per_rank["li_ms"]), max(per_rank["sfa_ms"]), max(per_rank["e2e_ms"])
+    step_max = max(x + y for x, y in zip(per_rank["li_ms"], per_rank["sfa_ms"]))
     pk = peaks()
-    topk_bytes = float(li_flops(S)[1]) * 4.0 + float(S) * topk * 4.0
-    sfa_tf = flops_sfa / (sfa_ms * 1e-3) / 1e12
-    tensor_sfa = bool(getattr(run_gpu, "_sfa_tensor", False))
+    sfa_tf = flops_sfa / (sfa_max * 1e-3) / 1e12                  # whole job
+    sfa_tf_gpu = (my_sfa_pairs * SFA_HEADS * 2.0 * (2 * SFA_D + SFA_DR)) / (sfa_ms * 1e-3) / 1e12   # this GPU's kernel
+    li_score_tf = (my_li_pairs * LI_HEADS * 2.0 * LI_D) / (phase_ms["score"] * 1e-3) / 1e12
+    topk_bytes = float(my_li_pairs) * 4.0 + float(n_row) * topk * 4.0
+    workload = "LI B=1 S=%d N1=64 D=128 k=%d + SFA TND lens=%s N1=128 D=512+64 topk=%d, mode 3" % (S, topk, lens, topk)
     line = {
-        "metric": METRIC, "value": sfa_tf * world, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": li_ms + sfa_ms, "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": sfa_tf, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_max, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "LI B=1 S=%d N1=64 D=128 k=%d + SFA TND lens=%s N1=128 D=512+64 topk=%d, mode 3"
-                               % (S, topk, lens, topk),
-                   "l2": "256 MiB buffer written between timed iterations; inputs (q 1.9 GiB) exceed L2",
-                   "quick": bool(args.quick)},
-        "li_topk_qtok_per_s": S / (li_ms * 1e-3) * world,
-        "li_ms": li_ms, "li_score_ms": phase_ms["score"], "li_topk_ms": phase_ms["topk"],
-        "li_score_tflops": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
-        "sfa_ms": sfa_ms, "sfa_tflops_per_gpu": sfa_tf,
+        "config": {"workload": workload, "quick": bool(args.quick)},
+        "l2": "256 MiB buffer written between timed iterations; inputs (q 1.9 GiB at one GPU) exceed L2",
+        "inputs": "dsa_triton_ascend_b200.synthetic: numpy RandomState(2) indexer / RandomState(3) attention, "
+                  "bf16; N GPUs split the same problem by causal work, keys replicated",
+        "li_topk_qtok_per_s": S / (li_max * 1e-3),
+        "li_ms": li_max, "li_score_ms": phase_ms["score"], "li_topk_ms": phase_ms["topk"],
+        "li_topk_share": phase_ms["topk"] / (phase_ms["score"] + phase_ms["topk"]),
+        "li_score_tflops": li_score_tf,
+        "sfa_ms": sfa_max, "sfa_tflops_per_gpu": sfa_tf_gpu,
+        "timing": {"sfa_ms": pct(sfa_all), "li_ms": pct(li_all), "note": "this rank's steps; value uses the mean"},
+        "shard_imbalance": {"sfa_max_over_mean": sfa_max / float(np.mean(per_rank["sfa_ms"])),
+                            "li_max_over_mean": li_max / float(np.mean(per_rank["li_ms"]))},
         "li_tensor_path": tensor_li,
-        "roofline": {"bound": "tensor", "achieved": sfa_tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": sfa_tf / pk["bf16_tflops"],
-                     # dram read + write of sfa_fwd_sm100_kernel per launch: ncu capture of the 1/4-size
-                     # workload (3840 tokens: 1.0435 GB) scaled by the token count (q and out dominate)
-                     "traffic": 1.0435e9 * T / 3840.0, "kernel": "sfa_fwd_sm100_kernel",
-                     "peak_source": pk["source"] + " (burst bf16 GEMM)"},
-        "roofline_li_score": {"bound": "tensor", "achieved": flops_li / (phase_ms["score"] * 1e-3) / 1e12,
-                              "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                              "frac": flops_li / (phase_ms["score"] * 1e-3) / 1e12 / pk["bf16_tflops"]},
+        "roofline": {"bound": "tensor", "achieved": sfa_tf_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": sfa_tf_gpu / pk["bf16_tflops"],
+                     # dram read + write of sfa_fwd_sm100_kernel per launch: q + out dominate and grow with
+                     # the token count; ncu capture of a 3840-token case (1.0435 GB) scaled by tokens
+                     "traffic": 1.0435e9 * n_tok / 3840.0, "kernel": "sfa_fwd_sm100_kernel",
+                     "peak_source": pk["source"] + " (burst bf16 GEMM)",
+                     "frac_of_sustained": sfa_tf_gpu / pk["bf16_tflops_sustained"]},
+        "roofline_li_score": {"bound": "tensor", "achieved": li_score_tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                              "frac": li_score_tf / pk["bf16_tflops"]},
         # top-k: reads every visible fp32 score once, writes k int32 indices per row
         "roofline_li_topk": {"bound": "hbm", "achieved": topk_bytes / (phase_ms["topk"] * 1e-3) / 1e9,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": topk_bytes / (phase_ms["topk"] * 1e-3) / 1e9 / pk["hbm_gbs"],
                              "note": "instruction-bound (ordered selection), not memory-bound"},
-        "e2e": {"value": flops_sfa / (e2e_ms * 1e-3) / 1e12 * world, "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "li_topk_qtok_per_s": S / (e2e_ms * 1e-3) * world},
-        "gpu_launches": 4 * args.steps,  # li_score, top-k, sfa_compact, sfa_fwd per step
+        "e2e": {"value": flops_sfa / (e2e_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_max,
+                "h2d_bytes_per_step": int(h2d_tot), "d2h_bytes_per_step": int(d2h_tot),
+                "li_topk_qtok_per_s": S / (e2e_max * 1e-3)},
+        "gpu_launches": launches_tot,
         "clocks": clocks, "wall_s": t_wall,
     }
-    if per_rank is not None:
+    if world > 1:
         line["per_rank"] = per_rank
+    else:
+        line["host_GBps"] = {"h2d": per_rank["h2d_GBps"][0], "d2h": per_rank["d2h_GBps"][0], "numa_cpus": numa_cpus}
+    if rank == 0 and not args.no_cpu:
+        # the CPU leg also checks rows of the TIMED outputs of this rank against the oracle
+        line["verified_rows"] = verify_rows(torch, c3, c4, r0, r1, t0, t1, li_out, sfa_out, b["idx"], topk)
+        if world == 1:
+            line["cpu_baseline"] = cpu_reference(sample_s=args.cpu_seconds, procs=1, lens=lens, topk=topk)
     if args.scale == 1 and not args.quick and not args.no_decode:
         del host_in, out_h
         dec = decode_c5(torch, rank, world, flush)
-        dec["step_ms"] = reduce_max(dec["step_ms"])
+        steps = gather(dec["step_ms"])
+        graphs = gather(dec["graph_replay_step_ms"])
+        dec["step_ms"], dec["graph_replay_step_ms"] = max(steps), max(graphs)
+        dec["tokens_per_s"] = 64 * 2 / (max(steps) * 1e-3)
+        dec["per_rank_step_ms"] = steps
         dec["roofline_li"] = {"bound": "hbm", "achieved": dec["li_index_k_GBps"], "peak": pk["hbm_gbs"],
                               "unit": "GB/s", "frac": dec["li_index_k_GBps"] / pk["hbm_gbs"],
-                              "note": "index-K cache bytes / indexer time (score + top-k)"}
+                              "note": "this rank's index-K cache bytes / indexer time (score + top-k)"}
         line["decode_c5"] = dec
-    if rank == 0 and world == 1 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_reference(sample_s=args.cpu_seconds, procs=1, lens=lens, topk=topk)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def verify_rows(torch, c3, c4, r0, r1, t0, t1, li_out, sfa_out, idx_dev, topk):
+    """Part of the CPU leg: a few rows of the outputs the timed region produced, against the oracle
+    (reference rule for the indexer, atol = rtol = 2e-2 / 1e-3 for the attention).  Returns the
+    number of rows checked; raises on a mismatch."""
+    from oracle import lightning_indexer_oracle, sparse_flash_attention_oracle
+    from oracle.compare import li_reference_rule, sfa_acceptance_rule
+    f32 = lambda t: t.detach().float().cpu().numpy()
+    S = c3["S"]
+    n = 0
+    rows = sorted(set(int(x) for x in np.linspace(r0, r1 - 1, 3)))
+    ri, _ = lightning_indexer_oracle(f32(c3["q"]), f32(c3["k"]), f32(c3["w"]), [S], [S], sparse_count=topk,
+                                     sparse_mode=3, return_value=False, rows=[(0, s) for s in rows])
+    got = li_out[0].detach().cpu().numpy()
+    for s in rows:
+        a_, b_ = got[0, s - r0, 0], ri[0, s, 0]
+        assert ((a_ >= 0) == (b_ >= 0)).all() and (a_ == b_).mean() >= 0.97, "indexer row %d differs from the oracle" % s
+        n += 1
+    cum, lens = c4["cum"], c4["lens"]
+    out, smax, ssum = sfa_out
+    idx_h = idx_dev.detach().cpu().numpy()
+    for t in sorted(set(int(x) for x in np.linspace(t0, t1 - 1, 3))):
+        bseq = int(np.searchsorted(cum, t, side="right"))
+        s0 = 0 if bseq == 0 else int(cum[bseq - 1])
+        s, L = t - s0, lens[bseq]
+        qq = np.zeros((1, L, SFA_HEADS, SFA_D), np.float32)
+        qq[0, s] = f32(c4["q"][t])
+        qqr = np.zeros((1, L, SFA_HEADS, SFA_DR), np.float32)
+        qqr[0, s] = f32(c4["qr"][t])
+        ii = np.full((1, L, 1, topk), -1, np.int32)
+        ii[0, s] = idx_h[t - t0]
+        ref = sparse_flash_attention_oracle(qq, f32(c4["k"][s0:s0 + L])[None], ii, qqr, f32(c4["kr"][s0:s0 + L])[None],
+                                            c4["scale"], [L], [L], sparse_mode=3, dtype="bf16", rows=[(0, s)])
+        sfa_acceptance_rule(f32(out[t - t0]), f32(smax[0, t - t0]), f32(ssum[0, t - t0]), ref[0][0, s], ref[1][0, 0, s],
+                            ref[2][0, 0, s])
+        n += 1
+    return n
 
 
 # ----------------------------------------------------------------------------------------------
@@ -613,9 +699,10 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": int(args.gpus),
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": flops / (v * 1e12) * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "LI B=1 S=%d N1=64 D=128 k=%d + SFA TND lens=%s N1=128 D=512+64 topk=%d, mode 3"
                                % (lens[0], topk, lens, topk), "quick": bool(args.quick)},
+        "sample": last["sample"],
         "li_topk_qtok_per_s": last["li_topk_qtok_per_s"],
         "cpu_baseline": dict(last, value=v),
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -62,6 +62,7 @@ EXPORTS = (
     "dsa_li_workspace_bytes", "dsa_li_forward", "dsa_li_uses_tensor_path",
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
     "dsa_li_forward_static", "dsa_li_static_scratch_bytes", "dsa_selftest_wait_timeout",
+    "dsa_kernel_launch_count",
 )
 
 
@@ -90,6 +91,7 @@ def _load():
     lib.dsa_li_static_scratch_bytes.restype = _c.c_size_t
     lib.dsa_selftest_wait_timeout.argtypes = [_c.c_void_p, _c.c_size_t, _c.c_void_p]
     lib.dsa_selftest_wait_timeout.restype = _c.c_int
+    lib.dsa_kernel_launch_count.restype = _c.c_ulonglong
     return lib
 
 

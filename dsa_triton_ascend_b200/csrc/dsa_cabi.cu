@@ -89,6 +89,7 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       dim3 grid((unsigned)rown, (unsigned)((p->s2 + kSimtKeys - 1) / kSimtKeys), 1);
       li_score_simt_kernel<T><<<grid, kSimtKeys, 0, st>>>(d, scores, ld);
       if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+      count_launch();
     }
   }
   if (p->phases & DSA_PHASE_TOPK) {
@@ -121,6 +122,7 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       }
     }
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
   }
   return DSA_OK;
 }
@@ -181,6 +183,7 @@ static int sfa_launch_simt(const DsaSfaParams* p, cudaStream_t st) {
   dim3 grid((unsigned)d.rows, gy, 1);
   sfa_fwd_simt_kernel<T><<<grid, kSfaSimtThreads, smem, st>>>(d);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
   return DSA_OK;
 }
 
@@ -206,7 +209,9 @@ using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 2; }
+int dsa_abi_version(void) { return 3; }
+
+unsigned long long dsa_kernel_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
 const char* dsa_status_string(int status) {
   switch (status) {

@@ -12,7 +12,16 @@
 
 #include "../../include/dsa_b200.h"
 
+#include <atomic>
+
 namespace dsa {
+
+// Kernels this library has launched in this process (read by dsa_kernel_launch_count()).
+inline std::atomic<unsigned long long>& launch_counter() {
+  static std::atomic<unsigned long long> n{0};
+  return n;
+}
+inline void count_launch(unsigned k = 1) { launch_counter().fetch_add(k, std::memory_order_relaxed); }
 
 // Sequence description shared by both operators (device copy of the ABI struct fields).
 struct SeqDesc {

@@ -22,6 +22,9 @@
 // epilogue (TMEM lane quarter = warp % 4, column half = (warp - 2) / 4).
 #pragma once
 
+#include <atomic>
+#include <mutex>
+
 #include "li_score_simt.cuh"
 #include "ptx_sm100.cuh"
 
@@ -455,17 +458,23 @@ inline bool li_sm100_eligible(const DsaLiParams* p) {
 
 inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, int64_t ld, int32_t* status,
                            cudaStream_t st) {
-  static int sm_count[64] = {0};
+  // SM count per device, set up once per device (safe from several host threads)
+  static std::atomic<int> sm_count[64];
+  static std::mutex setup_lock;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DSA_ERR_CUDA;
-  if (sm_count[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return DSA_ERR_CUDA;
-    if (cudaFuncSetAttribute(li_score_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLiSmemBytes) !=
-        cudaSuccess)
-      return DSA_ERR_CUDA;
-    sm_count[dev] = n;
+  if (sm_count[dev].load(std::memory_order_acquire) == 0) {
+    std::lock_guard<std::mutex> g(setup_lock);
+    if (sm_count[dev].load(std::memory_order_relaxed) == 0) {
+      int n = 0;
+      if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return DSA_ERR_CUDA;
+      if (cudaFuncSetAttribute(li_score_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)kLiSmemBytes) != cudaSuccess)
+        return DSA_ERR_CUDA;
+      sm_count[dev].store(n, std::memory_order_release);
+    }
   }
+  const int sms = sm_count[dev].load(std::memory_order_relaxed);
   const bool bf16 = p->dtype_qk == DSA_DTYPE_BF16;
   CUtensorMap tq, tk;
   const bool tnd = p->layout_q == DSA_LAYOUT_TND;
@@ -490,10 +499,10 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   const int32_t tiles_max = (int32_t)((keys_max + kLiKeys - 1) / kLiKeys);
   a.nchunks = 1;
   a.chunk_tiles = tiles_max > 0 ? tiles_max : 1;
-  if (groups < 2 * sm_count[dev] && tiles_max > 1) {
+  if (groups < 2 * sms && tiles_max > 1) {
     // static assignment: many small chunks (>= 8 tiles each) even out sequences of unequal length;
     // about eight items per SM measured best on 64 sequences of 16K-64K keys (28 tiles per chunk)
-    int32_t want = (8 * sm_count[dev] + groups - 1) / groups;
+    int32_t want = (8 * sms + groups - 1) / groups;
     if (want > tiles_max) want = tiles_max;
     a.chunk_tiles = (tiles_max + want - 1) / want;
     if (a.chunk_tiles < 8) a.chunk_tiles = tiles_max < 8 ? tiles_max : 8;
@@ -506,9 +515,10 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   a.krow_oob = (int32_t)p->key_rows;
   a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
   a.idesc_n128 = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 128, 0, 0);
-  const int grid = a.items < sm_count[dev] ? a.items : sm_count[dev];
+  const int grid = a.items < sms ? a.items : sms;
   li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
   return DSA_OK;
 }
 

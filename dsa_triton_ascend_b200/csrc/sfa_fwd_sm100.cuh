@@ -1016,6 +1016,7 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + w.key_list);
   sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
   SfaSm100Args a;
   a.p = d;
   a.status = status;
@@ -1045,9 +1046,11 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   if (split > 1) sfa_fwd_sm100_kernel<true><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, tq, tqr, a);
   else sfa_fwd_sm100_kernel<false><<<clusters * 2, kSfaThreads, kSfaSmemBytes, st>>>(tkn, tkr, tq, tqr, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
   if (split > 1) {
     sfa_merge_kernel<<<dim3(d.rows, kSfaHeads / 8), 256, 0, st>>>(d, split, a.part_o, a.part_m, a.part_l, a.is_bf16);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
   }
   return DSA_OK;
 }

@@ -180,6 +180,9 @@ int dsa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, void* str
 /* 1 when dsa_*_forward would take the tcgen05 path for these parameters, else 0. */
 int dsa_li_uses_tensor_path(const DsaLiParams* p);
 int dsa_sfa_uses_tensor_path(const DsaSfaParams* p);
+/* Number of CUDA kernels this library has launched in this process so far (all devices, all
+ * entry points; memsets are not kernels).  No counterpart in the reference. */
+unsigned long long dsa_kernel_launch_count(void);
 /* ABI version of this header. */
 int dsa_abi_version(void);
 

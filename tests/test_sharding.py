@@ -137,3 +137,43 @@ def test_two_gloo_ranks_decode_their_own_sequences(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_decode_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "ok_decode").exists()
+
+
+def test_tnd_token_slices_cover_balance_and_reproduce_the_full_problem():
+    """Token ranges of a TND batch (the configuration-4 split): they cover every token once, are
+    balanced by clipped causal work, and each range run as a stand-alone TND problem (its own
+    cumulative lengths, the key rows it needs) reproduces the rows of the full problem."""
+    from dsa_triton_ascend_b200.sharding import tnd_slice, tnd_token_slices
+    from oracle import layouts
+    lens = [8192, 4096, 2048, 1024]
+    cum = np.cumsum(lens).tolist()
+    for world in (2, 4, 8):
+        sl = tnd_token_slices(cum, cum, world, cap=2048)
+        assert sl[0][0] == 0 and sl[-1][1] == cum[-1] and all(a[1] == b[0] for a, b in zip(sl, sl[1:]))
+        work = []
+        for t0, t1 in sl:
+            cq, ck, ranges = tnd_slice(cum, cum, t0, t1)
+            assert (cq[-1] if cq else 0) == t1 - t0 and len(cq) == len(ck) == len(ranges)
+            tot, pq, pk = 0, 0, 0
+            for a, b in zip(cq, ck):
+                tot += causal_work(a - pq, b - pk, 0, a - pq, 2048)
+                pq, pk = a, b
+            work.append(tot)
+        assert sum(work) == sum(causal_work(L, L, 0, L, 2048) for L in lens)
+        assert max(work) <= 1.05 * sum(work) / world, work
+    # a small batch through the oracle: slices that cut through sequences
+    lens = [37, 12, 25]
+    cum = np.cumsum(lens).tolist()
+    T, N1, D, K = cum[-1], 8, 64, 8
+    rng = np.random.RandomState(11)
+    from oracle.inputs import round_io
+    q = round_io(rng.randn(T, N1, D).astype(np.float32), "bf16")
+    k = round_io(rng.randn(T, 1, D).astype(np.float32), "bf16")
+    w = rng.randn(T, N1).astype(np.float32)
+    full_i, full_v = layouts.li_oracle_tnd(q, k, w, cum, cum, sparse_count=K, sparse_mode=3, return_value=True)
+    for t0, t1 in tnd_token_slices(cum, cum, 3, align=1):
+        cq, ck, ranges = tnd_slice(cum, cum, t0, t1)
+        ks = np.concatenate([k[a:b] for a, b in ranges], axis=0)
+        i, v = layouts.li_oracle_tnd(q[t0:t1], ks, w[t0:t1], cq, ck, sparse_count=K, sparse_mode=3, return_value=True)
+        np.testing.assert_array_equal(i, full_i[t0:t1])
+        np.testing.assert_array_equal(v, full_v[t0:t1])
