@@ -275,7 +275,7 @@ def run_gpu(args):
 
     # ---- the seeded problem (host), this rank's share of it (device)
     c3 = synthetic.config3(None, args.scale)
-    c4 = synthetic.config4(None, args.scale)
+    c4 = synthetic.config4(None, args.scale, args.lens)
     S, topk = c3["S"], c3["sparse_count"]
     lens, cum, T = c4["lens"], c4["cum"], c4["T"]
     scale = c4["scale"]
@@ -450,15 +450,18 @@ def run_gpu(args):
         comp.wait_stream(s_in)
 
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_step()
-    barrier()
-    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(e2e_steps):
+    if args.no_e2e:
+        e2e_ms = 1e30
+    else:
         e2e_step()
-    b_.record()
-    barrier()
-    e2e_ms = a.elapsed_time(b_) / e2e_steps
+        barrier()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b_.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b_) / e2e_steps
 
     def gather(x):
         if world == 1:
@@ -522,6 +525,9 @@ def run_gpu(args):
         "gpu_launches": launches_tot,
         "clocks": clocks, "wall_s": t_wall,
     }
+    if args.no_e2e:
+        line["e2e"] = None
+        per_rank.pop("e2e_ms")
     if world > 1:
         line["per_rank"] = per_rank
     else:
@@ -720,13 +726,16 @@ def main():
     ap.add_argument("--quick", action="store_true", help="1/8-size workload (debugging only; not a bench value)")
     ap.add_argument("--scale", type=int, default=1,
                     help="divide sequence lengths and top-k by this (profiling captures; not a bench value)")
+    ap.add_argument("--lens", type=lambda v: [int(x) for x in v.split(",")], default=None,
+                    help="attention sequence lengths instead of 8192,4096,2048,1024 (profiling captures; not a bench value)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the configuration-5 (paged decode) side measurement")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.quick:
         args.scale = max(args.scale, 8)
-    args.quick = args.scale > 1
+    args.quick = args.scale > 1 or args.lens is not None
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -7,7 +7,9 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libdsa_b200.so")
+# DSA_B200_LIB points at another build of the same library (e.g. one compiled with
+# -DDSA_SFA_PROFILE for csrc/probes/sfa_role_cycles.py); there is still no fallback.
+LIB_PATH = os.environ.get("DSA_B200_LIB") or os.path.join(_HERE, "csrc", "libdsa_b200.so")
 
 LAYOUTS = {"BSND": 0, "TND": 1, "PA_BSND": 2}
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2

@@ -48,10 +48,11 @@ def config3(device=None, scale=1):
     return dict(q=q, k=k, w=w, S=S, sparse_count=c["sparse_count"] // scale, sparse_mode=3)
 
 
-def config4(device=None, scale=1):
-    """Attention at the prefill shape (TND) plus the indexer inputs its indices come from."""
+def config4(device=None, scale=1, lens=None):
+    """Attention at the prefill shape (TND) plus the indexer inputs its indices come from.
+    `lens` overrides the sequence lengths (profiling captures on a part of the batch)."""
     c = CONFIG4
-    lens = [L // scale for L in c["lens"]]
+    lens = [L // scale for L in (lens or c["lens"])]
     T = sum(lens)
     rng = np.random.RandomState(c["seed"])
     bf = torch.bfloat16
