@@ -1,17 +1,21 @@
-"""B200-native (sm_100a) DeepSeek-Sparse-Attention forward hot path.
+"""B200-native (sm_100a) DeepSeek-Sparse-Attention hot path.
 
-Public API = the two operators of WhFanatic/dsa_triton_ascend with unchanged signatures:
-`lightning_indexer_triton` / `LightningIndexerTriton` and `sparse_flash_attention_triton` /
-`SparseFlashAttentionTriton`.  Both are thin wrappers over the C-ABI CUDA library built from
+Public API = the operators of WhFanatic/dsa_triton_ascend with unchanged signatures:
+`lightning_indexer_triton` / `LightningIndexerTriton`, `sparse_flash_attention_triton` /
+`SparseFlashAttentionTriton` and the attention backward `sparse_flash_attention_grad_triton` /
+`SparseFlashAttentionGradTriton`.  All are thin wrappers over the C-ABI CUDA library built from
 `dsa_triton_ascend_b200/csrc` (declared in `include/dsa_b200.h`).  `check_status()` (an
 addition) reports a device-side wait that ran out in the latest call of either operator.
 """
 from ._host import check_status  # noqa: F401
 from .lightning_indexer import LightningIndexerTriton, lightning_indexer_triton  # noqa: F401
 from .sparse_flash_attention import SparseFlashAttentionTriton, sparse_flash_attention_triton  # noqa: F401
+from .sparse_flash_attention_grad import (SparseFlashAttentionGradTriton,  # noqa: F401
+                                          sparse_flash_attention_grad_triton)
 
 __all__ = [
     "lightning_indexer_triton", "LightningIndexerTriton",
     "sparse_flash_attention_triton", "SparseFlashAttentionTriton",
+    "sparse_flash_attention_grad_triton", "SparseFlashAttentionGradTriton",
     "check_status",
 ]

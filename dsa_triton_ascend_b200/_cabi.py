@@ -59,12 +59,31 @@ class DsaSfaParams(_c.Structure):
     ]
 
 
+class DsaSfaGradParams(_c.Structure):
+    _fields_ = [
+        ("struct_size", _c.c_uint32), ("kernel", _c.c_int32),
+        ("query", _c.c_void_p), ("query_rope", _c.c_void_p), ("key", _c.c_void_p), ("key_rope", _c.c_void_p),
+        ("sparse_indices", _c.c_void_p), ("d_out", _c.c_void_p), ("out", _c.c_void_p),
+        ("softmax_max", _c.c_void_p), ("softmax_sum", _c.c_void_p),
+        ("seq_q", _c.c_void_p), ("seq_k", _c.c_void_p),
+        ("d_query", _c.c_void_p), ("d_query_rope", _c.c_void_p),
+        ("d_key", _c.c_void_p), ("d_key_rope", _c.c_void_p), ("d_value", _c.c_void_p),
+        ("layout_q", _c.c_int32), ("layout_kv", _c.c_int32), ("dtype", _c.c_int32),
+        ("seq_q_cumulative", _c.c_int32), ("seq_k_cumulative", _c.c_int32),
+        ("batch", _c.c_int32), ("s1", _c.c_int32), ("s2", _c.c_int32),
+        ("n1", _c.c_int32), ("d", _c.c_int32), ("d_rope", _c.c_int32),
+        ("sparse_count", _c.c_int32), ("sparse_block_size", _c.c_int32), ("sparse_mode", _c.c_int32),
+        ("scale", _c.c_float),
+        ("key_rows", _c.c_int64),
+    ]
+
+
 EXPORTS = (
     "dsa_abi_version", "dsa_status_string", "dsa_read_device_status",
     "dsa_li_workspace_bytes", "dsa_li_forward", "dsa_li_uses_tensor_path",
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
     "dsa_li_forward_static", "dsa_li_static_scratch_bytes", "dsa_selftest_wait_timeout",
-    "dsa_kernel_launch_count",
+    "dsa_kernel_launch_count", "dsa_sfa_grad_workspace_bytes", "dsa_sfa_grad",
 )
 
 
@@ -88,6 +107,10 @@ def _load():
         f = getattr(lib, f"dsa_{name}_uses_tensor_path")
         f.argtypes = [_c.POINTER(ptype)]
         f.restype = _c.c_int
+    lib.dsa_sfa_grad_workspace_bytes.argtypes = [_c.POINTER(DsaSfaGradParams), _c.POINTER(_c.c_size_t)]
+    lib.dsa_sfa_grad_workspace_bytes.restype = _c.c_int
+    lib.dsa_sfa_grad.argtypes = [_c.POINTER(DsaSfaGradParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
+    lib.dsa_sfa_grad.restype = _c.c_int
     lib.dsa_li_forward_static.argtypes = [_c.POINTER(DsaLiParams), _c.c_void_p]
     lib.dsa_li_forward_static.restype = _c.c_int
     lib.dsa_li_static_scratch_bytes.restype = _c.c_size_t

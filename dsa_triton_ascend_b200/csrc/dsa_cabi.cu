@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 #include "../../include/dsa_b200.h"
 #include "dsa_common.cuh"
 #include "li_score_simt.cuh"
@@ -11,6 +13,7 @@
 #include "li_topk.cuh"
 #include "sfa_fwd_simt.cuh"
 #include "sfa_fwd_sm100.cuh"
+#include "sfa_bwd_simt.cuh"
 
 namespace dsa {
 
@@ -203,13 +206,82 @@ __global__ void selftest_wait_timeout_kernel(int32_t* status, uint32_t polls) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Attention backward: validation and launch
+// ---------------------------------------------------------------------------------------------
+static int sfa_grad_validate(const DsaSfaGradParams* p) {
+  if (p == nullptr) return DSA_ERR_NULL;
+  if (p->struct_size != sizeof(DsaSfaGradParams)) return DSA_ERR_STRUCT;
+  if (!p->query || !p->query_rope || !p->key || !p->key_rope || !p->sparse_indices || !p->d_out || !p->out ||
+      !p->softmax_max || !p->softmax_sum || !p->d_query || !p->d_query_rope || !p->d_key || !p->d_key_rope ||
+      !p->d_value)
+    return DSA_ERR_NULL;
+  if (p->layout_q != DSA_LAYOUT_BSND && p->layout_q != DSA_LAYOUT_TND) return DSA_ERR_VALUE;
+  if (p->layout_kv != DSA_LAYOUT_BSND && p->layout_kv != DSA_LAYOUT_TND) return DSA_ERR_VALUE;
+  if (p->dtype != DSA_DTYPE_BF16 && p->dtype != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
+  // shape guards of sparse_flash_attention_grad_triton.py:587-594 (head count relaxed to any n1 >= 1)
+  if (p->d != 128 && p->d != 256 && p->d != 512) return DSA_ERR_VALUE;
+  if (p->d_rope != 64) return DSA_ERR_VALUE;
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 0 || p->n1 < 1) return DSA_ERR_VALUE;
+  if (p->sparse_mode != 0 && p->sparse_mode != 3) return DSA_ERR_VALUE;  // :552-553
+  const int bs = p->sparse_block_size;
+  if (bs < 1 || bs > 128 || (bs & (bs - 1)) != 0) return DSA_ERR_VALUE;  // :560-562
+  if (p->sparse_count < 1 || p->key_rows < 0) return DSA_ERR_VALUE;
+  if (p->layout_q == DSA_LAYOUT_TND && (!p->seq_q || !p->seq_q_cumulative)) return DSA_ERR_VALUE;
+  if (p->layout_kv == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
+  if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE) return DSA_ERR_UNSUPPORTED;
+  return DSA_OK;
+}
+
+template <typename T>
+static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t st) {
+  SfaGradDev d;
+  d.seq.seq_q = p->seq_q; d.seq.seq_k = p->seq_k; d.seq.block_table = nullptr;
+  d.seq.layout_q = p->layout_q; d.seq.layout_k = p->layout_kv;
+  d.seq.seq_q_cum = p->seq_q_cumulative; d.seq.seq_k_cum = p->seq_k_cumulative;
+  d.seq.batch = p->batch; d.seq.s1 = p->s1; d.seq.s2 = p->s2;
+  d.seq.block_size = 0; d.seq.max_blocks = 0;
+  d.seq.sparse_mode = p->sparse_mode;
+  d.seq.key_rows = p->key_rows;
+  d.query = p->query; d.query_rope = p->query_rope; d.key = p->key; d.key_rope = p->key_rope;
+  d.sparse_indices = p->sparse_indices;
+  d.d_out = p->d_out; d.out = p->out; d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
+  d.d_query = p->d_query; d.d_query_rope = p->d_query_rope;
+  d.dk_acc = acc;
+  d.dv_acc = acc + p->key_rows * (p->d + p->d_rope);
+  d.rows = p->layout_q == DSA_LAYOUT_TND ? p->s1 : p->batch * p->s1;
+  d.n1 = p->n1; d.d = p->d; d.d_rope = p->d_rope;
+  d.sparse_count = p->sparse_count; d.sparse_block_size = p->sparse_block_size;
+  d.scale = p->scale;
+  if (d.rows > 0) {
+    const size_t smem = sfa_grad_smem_bytes(p->d, p->d_rope, sizeof(T));
+    if (cudaFuncSetAttribute(sfa_bwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DSA_ERR_CUDA;
+    const unsigned gy = (unsigned)((p->n1 + kSfaGradHeads - 1) / kSfaGradHeads);
+    dim3 grid((unsigned)d.rows, gy, 1);
+    sfa_bwd_simt_kernel<T><<<grid, kSfaGradThreads, smem, st>>>(d);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
+  }
+  if (p->key_rows > 0) {
+    const int64_t total = p->key_rows * (int64_t)(2 * p->d + p->d_rope);
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 16);
+    sfa_bwd_finalize_kernel<T><<<blocks, 256, 0, st>>>(d.dk_acc, d.dv_acc, (T*)p->d_key, (T*)p->d_key_rope,
+                                                      (T*)p->d_value, p->key_rows, p->d, p->d_rope);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
+  }
+  return DSA_OK;
+}
+
 }  // namespace dsa
 
 using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 3; }
+int dsa_abi_version(void) { return 4; }
 
 unsigned long long dsa_kernel_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -285,6 +357,30 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
   }
   if (p->dtype == DSA_DTYPE_BF16) return sfa_launch_simt<__nv_bfloat16>(p, cs);
   return sfa_launch_simt<__half>(p, cs);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention backward
+// ---------------------------------------------------------------------------------------------
+int dsa_sfa_grad_workspace_bytes(const DsaSfaGradParams* p, size_t* out_bytes) {
+  int st = sfa_grad_validate(p);
+  if (st != DSA_OK) return st;
+  if (!out_bytes) return DSA_ERR_NULL;
+  *out_bytes = kWorkspaceHeader + (size_t)p->key_rows * (size_t)(2 * p->d + p->d_rope) * sizeof(float);
+  return DSA_OK;
+}
+
+int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = sfa_grad_validate(p);
+  if (st != DSA_OK) return st;
+  size_t need = 0;
+  dsa_sfa_grad_workspace_bytes(p, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, need, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  float* acc = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
+  if (p->dtype == DSA_DTYPE_BF16) return sfa_grad_launch<__nv_bfloat16>(p, acc, cs);
+  return sfa_grad_launch<__half>(p, acc, cs);
 }
 
 // ---------------------------------------------------------------------------------------------

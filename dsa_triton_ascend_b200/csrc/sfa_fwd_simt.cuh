@@ -31,15 +31,18 @@ constexpr int kSfaSimtPad = 8;      // elements of row padding (keeps 16-byte lo
 
 // Validity and physical row of slot j of a query row (sparse_flash_attention_triton.py:465,
 // 1036-1051): returns the logical token or -1.
-__device__ __forceinline__ int32_t sfa_slot_token(const SfaDev& p, const RowInfo& ri, const int32_t* idx_row,
-                                                  int32_t j) {
-  const int32_t bs = p.sparse_block_size;
+__device__ __forceinline__ int32_t sfa_slot_token(const SeqDesc& seq, int32_t bs, const RowInfo& ri,
+                                                  const int32_t* idx_row, int32_t j) {
   const int32_t id = idx_row[j / bs];
   if (id < 0) return -1;
   const int64_t tok = (int64_t)id * bs + (j % bs);
   if (tok >= ri.threshold || tok >= ri.act_k) return -1;
-  if (p.seq.layout_k != DSA_LAYOUT_PA_BSND && tok >= p.seq.s2) return -1;
+  if (seq.layout_k != DSA_LAYOUT_PA_BSND && tok >= seq.s2) return -1;
   return (int32_t)tok;
+}
+__device__ __forceinline__ int32_t sfa_slot_token(const SfaDev& p, const RowInfo& ri, const int32_t* idx_row,
+                                                  int32_t j) {
+  return sfa_slot_token(p.seq, p.sparse_block_size, ri, idx_row, j);
 }
 
 // grid = (rows, ceil(n1 / 16)); block = 256 threads.

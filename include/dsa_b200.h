@@ -138,6 +138,51 @@ int dsa_sfa_workspace_bytes(const DsaSfaParams* p, size_t* out_bytes);
 int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * sparse_flash_attention backward - replaces `_sfa_grad_core`
+ * (sparse_flash_attention_grad_triton.py:385-493) behind `sparse_flash_attention_grad_triton`
+ * (:499-680).  Inputs are the forward operands, the gradient of the attention output, the
+ * forward output and its softmax statistics; the five gradients have the shapes and dtype of
+ * query, key, value (= key), query_rope, key_rope.  d_key holds the QK path and d_value the
+ * PV path separately, as in the reference (a caller that shares key and value adds them).
+ * Layouts BSND and TND (query and key/value); paged caches are not differentiated, as in the
+ * reference.  The scatter-add over keys uses fp32 atomics in the workspace, so the last place
+ * of d_key / d_value / d_key_rope can vary between runs (the reference refuses
+ * deterministic=True for the same reason, :558-559).
+ */
+typedef struct DsaSfaGradParams {
+  uint32_t struct_size; /* sizeof(DsaSfaGradParams) */
+  int32_t kernel;       /* DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE */
+  const void* query;      /* [rows, n1, d]      */
+  const void* query_rope; /* [rows, n1, d_rope] */
+  const void* key;        /* BSND [batch, s2, 1, d] | TND [T2, 1, d] */
+  const void* key_rope;
+  const int32_t* sparse_indices; /* [rows, 1, sparse_count] */
+  const void* d_out;      /* [rows, n1, d] */
+  const void* out;        /* [rows, n1, d] */
+  const float* softmax_max; /* [rows, n1] (BSND view [batch,1,s1,n1], TND view [1,T1,n1]) */
+  const float* softmax_sum;
+  const int32_t* seq_q;
+  const int32_t* seq_k;
+  void* d_query;      /* [rows, n1, d]      */
+  void* d_query_rope; /* [rows, n1, d_rope] */
+  void* d_key;        /* [key_rows, d]      */
+  void* d_key_rope;   /* [key_rows, d_rope] */
+  void* d_value;      /* [key_rows, d]      */
+  int32_t layout_q, layout_kv, dtype;
+  int32_t seq_q_cumulative, seq_k_cumulative;
+  int32_t batch, s1, s2, n1, d, d_rope;
+  int32_t sparse_count, sparse_block_size, sparse_mode;
+  float scale;
+  int64_t key_rows; /* batch*s2 (BSND) or T2 (TND) */
+} DsaSfaGradParams;
+
+/* Workspace: a status header plus fp32 accumulators key_rows * (2*d + d_rope) * 4 bytes. */
+int dsa_sfa_grad_workspace_bytes(const DsaSfaGradParams* p, size_t* out_bytes);
+/* Enqueue the backward on `stream`: clears the accumulators, runs the gradient kernel and the
+ * conversion of the accumulators to the io dtype. */
+int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * dsa_li_forward_static - the indexer without a caller workspace and without any allocation.
  * (No counterpart in the reference; added for hosts described below.)
  *

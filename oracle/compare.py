@@ -5,6 +5,8 @@ Two families:
     equality, boundary-tie tolerance for set differences, banded relative error on the
     selected values) and test_sfa_triton.py:88-123 (percentage of elements inside
     rtol/atol, no outlier with relative error >= 10);
+    (test_sfa_grad_triton.py:89-121 for the backward: rtol 6e-2 / atol 5e-2 in bf16, 3e-2 / 2e-2 in
+    fp16, atol scaled by sqrt(S1) for the scatter-added gradients, 99.5 % inside);
   * the stricter acceptance rules of this build: positional index equality wherever
     the fp32 gap between the k-th and (k+1)-th score exceeds 1e-3 relative; attention
     output within atol = rtol = 2e-2 (bf16) and softmax statistics within 1e-3 relative.
@@ -86,3 +88,26 @@ def sfa_acceptance_rule(out, smax, ssum, ref_out, ref_smax, ref_ssum, tol_out=2e
         bad = ~np.isclose(x, y, rtol=tol_stat, atol=tol_stat * 1e-2)
         assert not bad.any(), f"{name}: {bad.sum()} elements outside {tol_stat} relative, " \
                               f"max |diff| {np.abs(x - y).max():.4e}"
+
+
+def sfa_grad_reference_rule(a, b, dtype="bf16", scale=1.0):
+    """True when gradient `a` is close to `b` in the sense of test_sfa_grad_triton.py:89-121."""
+    rtol = 6e-2 if dtype == "bf16" else 3e-2
+    atol = (5e-2 if dtype == "bf16" else 2e-2) * scale
+    return sfa_reference_rule(a, b, dtype, pct_thd=99.5, rtol=rtol, atol=atol)
+
+
+def sfa_grad_acceptance_rule(a, b, dtype="bf16", name="gradient", ulps=2.0, noise=2e-6):
+    """Stricter rule of this build for a gradient given the SAME forward state as the checker: every
+    element within `ulps` units in the last place of the io dtype (taken at the larger magnitude of
+    the two), plus `noise` times the largest magnitude of the tensor for fp32 sums that cancel."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    assert a.shape == b.shape, f"{name}: shape {a.shape} vs {b.shape}"
+    assert np.isfinite(a).all(), f"{name}: non-finite values"
+    mag = np.maximum(np.maximum(np.abs(a), np.abs(b)).astype(np.float64), 1e-30)
+    e = np.floor(np.log2(mag))
+    ulp = 2.0 ** (e - 7) if dtype == "bf16" else np.maximum(2.0 ** (e - 10), 2.0 ** -24)
+    tol = ulps * ulp + noise * float(np.abs(b).max())
+    bad = np.abs(a.astype(np.float64) - b) > tol
+    assert not bad.any(), f"{name}: {bad.sum()} of {bad.size} elements more than {ulps} ulp apart, " \
+                          f"max |diff| {np.abs(a - b).max():.4e} at |ref| max {np.abs(b).max():.4e}"

@@ -59,6 +59,22 @@ def sfa_inputs(seed, B, S1, S2, N1, D=512, Dr=64, dtype="bf16"):
     kr = draw(B, S2, 1, Dr)
     return q, k, qr, kr
 
+def sfa_grad_inputs(seed, B, S1, S2, N1, D=512, Dr=64, dtype="bf16"):
+    """q, k, v (drawn, unused), q_rope, k_rope, d_out in the order and with the 0.3 scale of the
+    reference's backward tests (test_sfa_grad_triton.py:73-86)."""
+    rng = np.random.RandomState(seed)
+
+    def draw(*shape):
+        return round_io(rng.randn(*shape).astype(np.float32) * np.float32(0.3), dtype)
+
+    q = draw(B, S1, N1, D)
+    k = draw(B, S2, 1, D)
+    draw(B, S2, 1, D)
+    qr = draw(B, S1, N1, Dr)
+    kr = draw(B, S2, 1, Dr)
+    do = draw(B, S1, N1, D)
+    return q, k, qr, kr, do
+
 
 # The two CPU-sized configurations of the benchmark specification.
 def config1():

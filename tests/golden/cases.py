@@ -1,7 +1,8 @@
 """Case table shared by the fixture generator and the parity tests.
 
 Shapes follow the reference's own parametrisations (test_li_triton.py:143-163,
-test_sfa_triton.py:129-140) plus the two CPU-sized benchmark configurations.
+test_sfa_triton.py:129-140, test_sfa_grad_triton.py:126-138) plus the two CPU-sized benchmark
+configurations.
 """
 
 # name -> dict(seed, B, S1, S2, N1, N2, D, k, dtype, mode, act_q, act_k)
@@ -40,6 +41,22 @@ SFA_CASES = {
                             act_q=[24, 10, 3], act_k=[192, 7, 100]),
 }
 
+# backward cases: same keys as SFA_CASES (shapes of test_sfa_grad_triton.py:126-138, plus a full-mode
+# and a ragged case)
+SFA_GRAD_CASES = {
+    "sfa_grad_tiny":        dict(seed=51, B=1, S1=4, S2=128, N1=8, D=512, k=64, block=1, mode=3, dtype="bf16"),
+    "sfa_grad_multi_batch": dict(seed=52, B=2, S1=16, S2=256, N1=16, D=128, k=128, block=1, mode=3, dtype="fp16"),
+    "sfa_grad_block2":      dict(seed=53, B=1, S1=8, S2=128, N1=8, D=256, k=32, block=2, mode=3, dtype="bf16"),
+    "sfa_grad_block4":      dict(seed=54, B=1, S1=8, S2=256, N1=16, D=512, k=32, block=4, mode=3, dtype="fp16"),
+    "sfa_grad_single_row":  dict(seed=55, B=1, S1=1, S2=128, N1=8, D=128, k=16, block=1, mode=3, dtype="bf16"),
+    "sfa_grad_one_head":    dict(seed=56, B=1, S1=4, S2=128, N1=1, D=512, k=64, block=1, mode=3, dtype="bf16"),
+    "sfa_grad_heads128":    dict(seed=57, B=1, S1=4, S2=128, N1=128, D=256, k=64, block=1, mode=3, dtype="bf16"),
+    "sfa_grad_topk2048":    dict(seed=58, B=1, S1=4, S2=2048, N1=8, D=128, k=2048, block=1, mode=3, dtype="fp16"),
+    "sfa_grad_full_mode":   dict(seed=59, B=1, S1=4, S2=128, N1=8, D=256, k=64, block=1, mode=0, dtype="fp16"),
+    "sfa_grad_ragged":      dict(seed=60, B=3, S1=24, S2=192, N1=16, D=512, k=96, block=1, mode=3, dtype="bf16",
+                                 act_q=[24, 10, 3], act_k=[192, 7, 100]),
+}
+
 
 def li_case_inputs(name):
     """Seeded inputs of one LI case: (q, k, w, act_q, act_k, spec)."""
@@ -64,6 +81,20 @@ def sfa_case_inputs(name):
                          act_q, act_k)
     scale = 1.0 / np.sqrt(c["D"] + 64.0)
     return q, k, qr, kr, idx, act_q, act_k, scale, c
+
+def sfa_grad_case_inputs(name):
+    """Seeded inputs of one backward case:
+    (q, k, q_rope, k_rope, d_out, idx, act_q, act_k, scale, spec)."""
+    import numpy as np
+    from oracle.inputs import sfa_grad_inputs, sparse_indices
+    c = SFA_GRAD_CASES[name]
+    q, k, qr, kr, do = sfa_grad_inputs(c["seed"], c["B"], c["S1"], c["S2"], c["N1"], c["D"], 64, c["dtype"])
+    act_q = np.asarray(c.get("act_q", [c["S1"]] * c["B"]), dtype=np.int32)
+    act_k = np.asarray(c.get("act_k", [c["S2"]] * c["B"]), dtype=np.int32)
+    idx = sparse_indices(c["seed"] + 1000, c["B"], c["S1"], c["S2"], c["k"], c["block"], c["mode"],
+                         act_q, act_k)
+    scale = 1.0 / np.sqrt(c["D"] + 64.0)
+    return q, k, qr, kr, do, idx, act_q, act_k, scale, c
 
 
 def case_rows(c, act_q):

@@ -2,10 +2,12 @@
 
 Run in a container that has the reference checkout:
     python tests/golden/make_golden.py /path/to/reference
-It imports lightning_indexer_numpy.lightning_indexer_golden_bsnd and
-sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd from that checkout, runs
-them on the seeded inputs of tests/golden/cases.py and stores only the outputs (inputs are
-regenerated from the seeds).  For cases with `rows_every` only the listed rows are kept.
+It imports lightning_indexer_numpy.lightning_indexer_golden_bsnd,
+sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd and
+sparse_flash_attention_grad_numpy.sparse_flash_attention_grad_golden_bsnd from that checkout,
+runs them on the seeded inputs of tests/golden/cases.py and stores only the outputs (inputs
+are regenerated from the seeds; the backward cases take their forward state from the forward
+golden).  For cases with `rows_every` only the listed rows are kept.
 The stored arrays pin the numpy restatement under oracle/ (tests/test_oracle_golden.py).
 """
 import os
@@ -16,13 +18,15 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from tests.golden.cases import LI_CASES, SFA_CASES, case_rows, li_case_inputs, sfa_case_inputs  # noqa: E402
+from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, case_rows, li_case_inputs,  # noqa: E402
+                                sfa_case_inputs, sfa_grad_case_inputs)
 
 
 def main(ref_dir):
     sys.path.insert(0, ref_dir)
     import lightning_indexer_numpy as ref_li
     import sparse_flash_attention_numpy as ref_sfa
+    import sparse_flash_attention_grad_numpy as ref_grad
 
     for name in LI_CASES:
         q, k, w, act_q, act_k, c = li_case_inputs(name)
@@ -63,6 +67,20 @@ def main(ref_dir):
             out=o[sel[:, 0], sel[:, 1]].astype(np.float16 if c["dtype"] == "fp16" else np.float32),
             smax=smax[sel[:, 0], 0, sel[:, 1]], ssum=ssum[sel[:, 0], 0, sel[:, 1]])
         print(name, o.shape, len(rows))
+
+    for name in SFA_GRAD_CASES:
+        q, k, qr, kr, do, idx, act_q, act_k, scale, c = sfa_grad_case_inputs(name)
+        dt = ref_sfa.BF16 if c["dtype"] == "bf16" else np.float16
+        o, smax, ssum = ref_sfa.sparse_flash_attention_golden_bsnd(
+            q, k, k, idx, qr, kr, scale, act_q, act_k, sparse_block_size=c["block"],
+            sparse_mode=c["mode"], return_softmax_lse=True, dtype=dt)
+        grads = ref_grad.sparse_flash_attention_grad_golden_bsnd(
+            q, k, k, idx, do, o, smax, ssum, qr, kr, scale, act_q, act_k,
+            sparse_block_size=c["block"], sparse_mode=c["mode"], dtype=dt)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"),
+                            **{n: g.astype(np.float32) for n, g in
+                               zip(("d_query", "d_key", "d_value", "d_query_rope", "d_key_rope"), grads)})
+        print(name, [g.shape for g in grads])
 
 
 def _row_mask(shape, sel):

@@ -28,15 +28,18 @@ def test_library_exports_every_declared_symbol():
 
 def test_ctypes_structs_match_the_c_header():
     from dsa_triton_ascend_b200 import _cabi
-    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu\\n",' \
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
           'sizeof(DsaLiParams),sizeof(DsaSfaParams),offsetof(DsaLiParams,phases),' \
-          'offsetof(DsaSfaParams,scale),offsetof(DsaLiParams,out_indices));return 0;}\n'
+          'offsetof(DsaSfaParams,scale),offsetof(DsaLiParams,out_indices),sizeof(DsaSfaGradParams),' \
+          'offsetof(DsaSfaGradParams,d_value),offsetof(DsaSfaGradParams,key_rows));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "t.c")
         open(c, "w").write(src)
         exe = os.path.join(d, "t")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
-        li, sfa, off_ph, off_sc, off_oi = map(int, subprocess.check_output([exe]).split())
+        li, sfa, off_ph, off_sc, off_oi, grad, off_dv, off_kr = map(int, subprocess.check_output([exe]).split())
+    assert grad == ctypes.sizeof(_cabi.DsaSfaGradParams)
+    assert off_dv == _cabi.DsaSfaGradParams.d_value.offset and off_kr == _cabi.DsaSfaGradParams.key_rows.offset
     assert li == ctypes.sizeof(_cabi.DsaLiParams) and sfa == ctypes.sizeof(_cabi.DsaSfaParams)
     assert off_ph == _cabi.DsaLiParams.phases.offset
     assert off_sc == _cabi.DsaSfaParams.scale.offset
@@ -112,6 +115,53 @@ def test_sfa_shape_guards_raise_value_error():
     q, k, qr, kr, si = _sfa_args(N2=2)
     with pytest.raises(ValueError):
         sparse_flash_attention_triton(q, k, k, si, query_rope=qr, key_rope=kr)
+
+
+def test_sfa_grad_guards_raise_value_error_like_the_reference():
+    """test_sfa_grad_triton.py:307-340 (test_guards): every unsupported interface knob raises at the
+    host gate, before any tensor is touched; plus the shape guards of
+    sparse_flash_attention_grad_triton.py:587-594 and the ABI's own validation."""
+    from dsa_triton_ascend_b200 import SparseFlashAttentionGradTriton, _cabi, sparse_flash_attention_grad_triton as gfn
+    q, k, qr, kr, si = _sfa_args()
+    do = out = q
+    smax = torch.zeros(1, 1, 4, 8)
+    ssum = torch.ones(1, 1, 4, 8)
+
+    def call(**kw):
+        base = dict(scale_value=1.0 / 24.0, query_rope=qr, key_rope=kr, sparse_mode=3)
+        base.update(kw)
+        return gfn(q, k, k, si, do, out, smax, ssum, **base)
+
+    for kw in (dict(pre_tokens=0), dict(next_tokens=0), dict(sparse_mode=1), dict(deterministic=True),
+               dict(sparse_block_size=3), dict(query_rope=None), dict(layout="PA_BSND")):
+        with pytest.raises(ValueError):
+            call(**kw)
+    for bad in (dict(D=192), dict(Dr=32), dict(N2=2)):
+        q2, k2, qr2, kr2, si2 = _sfa_args(**bad)
+        with pytest.raises(ValueError):
+            gfn(q2, k2, k2, si2, q2, q2, smax, ssum, query_rope=qr2, key_rope=kr2)
+    with pytest.raises(ValueError):  # statistics of the wrong shape
+        gfn(q, k, k, si, do, out, smax[:, :, :2], ssum, query_rope=qr, key_rope=kr)
+    with pytest.raises(RuntimeError):  # CPU tensors: there is no CPU path
+        SparseFlashAttentionGradTriton(scale_value=1.0)(q, k, k, si, do, out, smax, ssum, query_rope=qr, key_rope=kr)
+    n = ctypes.c_size_t(0)
+    g = _cabi.DsaSfaGradParams()
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -2
+    g.struct_size = ctypes.sizeof(g)
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -1
+    for f in ("query", "query_rope", "key", "key_rope", "sparse_indices", "d_out", "out", "softmax_max",
+              "softmax_sum", "d_query", "d_query_rope", "d_key", "d_key_rope", "d_value"):
+        setattr(g, f, 256)
+    g.batch, g.s1, g.s2, g.n1, g.d, g.d_rope = 1, 4, 64, 8, 512, 64
+    g.sparse_count, g.sparse_block_size, g.sparse_mode, g.key_rows = 16, 1, 3, 64
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
+    assert n.value == 256 + 64 * (2 * 512 + 64) * 4
+    g.layout_kv = 2                                   # paged caches are not differentiated
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -3
+    g.layout_kv, g.kernel = 0, 2                      # there is no tensor-core backward
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -5
+    g.kernel = 0
+    assert _cabi.lib.dsa_sfa_grad(ctypes.byref(g), None, 0, None) == -4
 
 
 def test_li_guards_raise_value_error_like_the_reference():

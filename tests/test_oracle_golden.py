@@ -2,16 +2,20 @@
 
 tests/golden/*.npz were produced by tests/golden/make_golden.py from
 lightning_indexer_numpy.lightning_indexer_golden_bsnd and
-sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd on the seeded inputs of
-tests/golden/cases.py; the restatement has to reproduce them bit for bit.
+sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd (and, for the backward cases,
+sparse_flash_attention_grad_numpy.sparse_flash_attention_grad_golden_bsnd) on the seeded inputs
+of tests/golden/cases.py; the forward restatements have to reproduce them bit for bit, the
+backward one to the last place of the io dtype.
 """
 import os
 
 import numpy as np
 import pytest
 
-from oracle import lightning_indexer_oracle, sparse_flash_attention_oracle
-from tests.golden.cases import LI_CASES, SFA_CASES, li_case_inputs, sfa_case_inputs
+from oracle import (lightning_indexer_oracle, sparse_flash_attention_grad_oracle,
+                    sparse_flash_attention_oracle)
+from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, li_case_inputs, sfa_case_inputs,
+                                sfa_grad_case_inputs)
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -48,6 +52,39 @@ def test_sfa_oracle_matches_reference_golden(name):
     np.testing.assert_array_equal(out[sel[:, 0], sel[:, 1]], g["out"].astype(np.float32))
     np.testing.assert_array_equal(smax[sel[:, 0], 0, sel[:, 1]], g["smax"])
     np.testing.assert_array_equal(ssum[sel[:, 0], 0, sel[:, 1]], g["ssum"])
+
+def _ulp(x, dtype):
+    """Spacing of the io dtype at |x| (bf16: 8 mantissa bits, fp16: 11; fp16 subnormal floor)."""
+    a = np.maximum(np.abs(x).astype(np.float64), 1e-30)
+    e = np.floor(np.log2(a))
+    return np.where(dtype == "bf16", 2.0 ** (e - 7), np.maximum(2.0 ** (e - 10), 2.0 ** -24))
+
+
+@pytest.mark.parametrize("name", sorted(SFA_GRAD_CASES))
+def test_sfa_grad_oracle_matches_reference_golden(name):
+    """The forward state comes from the forward oracle (bit-identical to the forward golden that the
+    fixture generator used).  The backward restatement sums the same fp32 terms as the golden in
+    another order (matrix products instead of a per-head loop), so results agree except where the
+    two fp32 sums round to neighbouring io-dtype values: at most one unit in the last place apart
+    (plus the fp32 noise of sums that cancel), and equal on nearly every element."""
+    q, k, qr, kr, do, idx, act_q, act_k, scale, c = sfa_grad_case_inputs(name)
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    out, smax, ssum = sparse_flash_attention_oracle(
+        q, k, idx, qr, kr, scale, act_q, act_k, sparse_block_size=c["block"], sparse_mode=c["mode"],
+        return_softmax_lse=True, dtype=c["dtype"])
+    got = sparse_flash_attention_grad_oracle(
+        q, k, idx, do, out, smax, ssum, qr, kr, scale, act_q, act_k, sparse_block_size=c["block"],
+        sparse_mode=c["mode"], dtype=c["dtype"])
+    for n, a in zip(("d_query", "d_key", "d_value", "d_query_rope", "d_key_rope"), got):
+        b = g[n]
+        assert a.shape == b.shape, n
+        noise = 1e-6 * np.abs(b).max()
+        assert (np.abs(a - b) <= _ulp(b, c["dtype"]) + noise).all(), f"{n}: more than one ulp apart"
+        assert (a == b).mean() >= 0.98, f"{n}: {(a == b).mean():.4f} equal"
+    # rows the golden never visits (past the valid query length) stay exactly zero
+    for b_ in range(c["B"]):
+        assert (got[0][b_, int(act_q[b_]):] == 0).all() and (got[3][b_, int(act_q[b_]):] == 0).all()
+        assert (got[1][b_, int(act_k[b_]):] == 0).all() and (got[2][b_, int(act_k[b_]):] == 0).all()
 
 
 def test_li_oracle_layout_adapters_roundtrip():
