@@ -102,10 +102,10 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       const int e = p->sparse_count <= kTopkThreads ? 1 : (p->sparse_count <= 2 * kTopkThreads ? 2 : 4);
 #define DSA_TOPK_FAST(R, E) li_topk_fast_kernel<T, R, E><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld)
       if (rank16) {
-        // io-dtype ranking: counting (radix) kernel
-        if (e == 1) li_topk_radix_kernel<T, 1><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
-        else if (e == 2) li_topk_radix_kernel<T, 2><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
-        else li_topk_radix_kernel<T, 4><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+        // io-dtype ranking: one histogram on a linear scale selects and orders
+        if (e == 1) li_topk_bins_kernel<T, 1><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+        else if (e == 2) li_topk_bins_kernel<T, 2><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+        else li_topk_bins_kernel<T, 4><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
       }
       else { if (e == 1) DSA_TOPK_FAST(false, 1); else if (e == 2) DSA_TOPK_FAST(false, 2); else DSA_TOPK_FAST(false, 4); }
 #undef DSA_TOPK_FAST
@@ -425,6 +425,12 @@ int dsa_li_forward_static(const DsaLiParams* p, void* stream) {
   return li_launch<__half>(p, scores, cs);
 }
 
+#ifdef DSA_TOPK_PROFILE
+// Development aid (see li_topk.cuh): cycles per phase of one top-k CTA.
+int dsa_debug_topk_profile(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_topk_prof, sizeof(long long) * 16) == cudaSuccess ? DSA_OK : DSA_ERR_CUDA;
+}
+#endif
 #ifdef DSA_SFA_PROFILE
 // development builds only: the attention kernel's cycle counters (128 values)
 int dsa_debug_sfa_profile(long long* out) {

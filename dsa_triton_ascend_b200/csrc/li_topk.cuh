@@ -10,6 +10,8 @@
 
 #include "li_score_simt.cuh"
 
+#include <type_traits>
+
 namespace dsa {
 
 constexpr int kTopkThreads = 512;
@@ -436,68 +438,96 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_fast_kernel(LiDev p, con
 }
 
 // ------------------------------------------------------------------------------------------------
-// Radix path (io-dtype ranking, rows of up to 8192 visible keys, sparse_count <= 2048).
-// The rank key has only 16 bits, so the whole job is done with counting instead of comparing:
-//   1. threshold: two 256-bin histograms (high byte, then low byte inside the chosen bin), filled
-//      with warp-aggregated adds (__match_any_sync) because nearly all scores share a few bins;
-//   2. ordered compaction: per (round, warp) counts of "key > T" and "key == T" elements are
-//      prefix-summed in position order, which both places the survivors in ascending position
-//      and cuts the ties at the threshold to the first `need` positions without any search;
-//   3. stable LSD radix sort of the <= 2048 survivors on the key, kSortBits bits per pass, descending;
-//      passes over bit groups in which all survivors agree are skipped (usually 1-2 of the 4).
-//      Equal keys keep their ascending position order, which is the required tie-break.
+// Bin path (io-dtype ranking, rows of up to 8192 visible keys, sparse_count <= 2048): selection and
+// ordering from ONE histogram of the row on a linear scale of the score.
+//
+// Every key gets a bin b = floor((hi - x) / width), 4096 bins over [mean - 3 s, mean + 5 s] of the
+// row (s = 1.25 x the mean absolute deviation, which a few outliers barely move; values outside are
+// clamped to the end bins).  The bin is monotone in the score, so with bin 0 the best:
+//   * the exclusive prefix sum of the bin counts is, for every bin, the output slot at which its
+//     members start, and the bin in which the prefix crosses sparse_count holds the threshold;
+//   * members of the bins before that one all survive; of the crossing bin the `need` best survive,
+//     found by ranking its few members against each other (bisection on the composite when the bin
+//     is large);
+//   * survivors are dropped into their bin's slot range in arrival order (one shared-memory add),
+//     and each then finds its final slot by counting the members of its own bin that precede it in
+//     (key descending, position ascending) order.  Bins hold a handful of members (2048 survivors
+//     over ~2000 bins), so this costs a few compares per survivor instead of the 2-4 counting
+//     passes over all survivors of a radix sort.
+// Rows whose scores pile into few bins (all equal, or a scale dominated by outliers) stay correct:
+// bins of more than kBinSmall members are ordered by whole warps, members x members.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_tot /*[16]*/, uint32_t* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t inc = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-    if (lane >= o) inc += t;
-  }
-  if (lane == 31) warp_tot[warp] = inc;
-  __syncthreads();
-  uint32_t base = 0, all = 0;
-#pragma unroll
-  for (int w = 0; w < kTopkThreads / 32; ++w) {
-    const uint32_t t = warp_tot[w];
-    if (w < warp) base += t;
-    all += t;
-  }
-  if (total) *total = all;
-  __syncthreads();   // warp_tot may be reused right away
-  return base + inc - v;
+// Development aid, compiled only with -DDSA_TOPK_PROFILE: cycles per phase of one CTA (the row at
+// three quarters of the grid), read back with dsa_debug_topk_profile().
+#ifdef DSA_TOPK_PROFILE
+__device__ long long g_topk_prof[16];
+#define TOPK_PROF_DECL long long tp_t = clock64(); int tp_i = 0
+#define TOPK_PROF() do { if (threadIdx.x == 0 && blockIdx.x == (gridDim.x / 4) * 3) { \
+    const long long tp_n = clock64(); g_topk_prof[tp_i] = tp_n - tp_t; tp_t = tp_n; } ++tp_i; } while (0)
+#else
+#define TOPK_PROF_DECL
+#define TOPK_PROF()
+#endif
+
+constexpr int kBinCount = 4096;
+constexpr int kBinSmall = 16;    // bins up to this size are ordered by their own members
+constexpr int kBinSide = 128;    // crossing bins up to this size are cut by ranking, larger ones by bisection
+constexpr int kBinBigList = 128; // a row has at most 2048 / 17 = 120 bins above kBinSmall
+
+template <typename T>
+__device__ __forceinline__ T key16_bits(uint32_t k16) {
+  const uint16_t h = (k16 & 0x8000u) ? (uint16_t)(k16 & 0x7FFFu) : (uint16_t)(~k16);
+  return *reinterpret_cast<const T*>(&h);
 }
 
-// Mask of the lanes whose kBits-bit digit equals this lane's (one ballot per bit; cheaper than a match).
-template <int kBits>
-__device__ __forceinline__ uint32_t same_digit(uint32_t d) {
-  uint32_t m = 0xffffffffu;
-#pragma unroll
-  for (int b = 0; b < kBits; ++b) {
-    const uint32_t v = __ballot_sync(0xffffffffu, (d >> b) & 1u);
-    m &= ((d >> b) & 1u) ? v : ~v;
-  }
-  return m;
+__device__ __forceinline__ int32_t score_bin(float x, float hi, float inv_w) {
+  return min(max(__float2int_rd((hi - x) * inv_w), 0), kBinCount - 1);
 }
-constexpr int kSortBits = 4;                       // digit width of the survivor sort
-constexpr int kSortBins = 1 << kSortBits;
-constexpr int kSortPasses = (16 + kSortBits - 1) / kSortBits;
+
+// Sums of two floats per thread, returned to every thread (same summation order everywhere).
+__device__ __forceinline__ float2 block_sum2_f32(float u, float v, float2* part /*[16]*/) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    u += __shfl_xor_sync(0xffffffffu, u, o);
+    v += __shfl_xor_sync(0xffffffffu, v, o);
+  }
+  if (lane == 0) part[threadIdx.x >> 5] = make_float2(u, v);
+  __syncthreads();
+  float2 t = part[lane & (kTopkThreads / 32 - 1)];
+#pragma unroll
+  for (int o = kTopkThreads / 64; o > 0; o >>= 1) {
+    t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
+    t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
+  }
+  return t;
+}
+
+// Rank key of a score already rounded to the io dtype (same order as rank_key<T, true>).
+template <typename T>
+__device__ __forceinline__ uint32_t rank_key_of(T r) {
+  uint16_t h = *reinterpret_cast<uint16_t*>(&r);
+  if ((h & 0x7FFFu) == 0) h = 0;
+  return (h & 0x8000u) ? (uint32_t)(uint16_t)(~h) : (uint32_t)(h | 0x8000u);
+}
 
 template <typename T, int E>
-__global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p, const float* __restrict__ scores,
-                                                                     int64_t ld) {
+__global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, const float* __restrict__ scores,
+                                                                    int64_t ld) {
   constexpr int P2 = kTopkThreads * E;
   constexpr int NW = kTopkThreads / 32;
-  __shared__ uint32_t buf[2][P2];
-  constexpr int TN = kSortBins * E * NW;          // (digit, round, warp) counters of a sort pass
-  __shared__ uint32_t tab[TN < 512 ? 512 : TN];   // also holds the 2 x 256 compaction counters
-  __shared__ uint32_t hist[256];
+  __shared__ __align__(16) uint32_t hist[kBinCount];   // counts, then slot cursors
+  __shared__ uint32_t buf[P2];                         // survivors by bin, any order inside a bin
+  __shared__ uint16_t bbin[P2];                        // their bins
+  __shared__ uint32_t outs[P2];                        // survivors in output order
+  __shared__ uint32_t side[kBinSide];                  // members of the crossing bin
+  __shared__ uint32_t biglist[kBinBigList];
+  __shared__ float2 part[NW];
   __shared__ uint32_t warp_tot[NW];
-  __shared__ uint32_t sh_a, sh_b, sh_c, sh_diff, sh_ref;
+  __shared__ uint32_t counters[40];
+  __shared__ uint32_t sh_bstar, sh_need, sh_cstar, sh_base, sh_side, sh_big;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t lt = (1u << lane) - 1u;
   const int32_t rown = blockIdx.x;
   const int32_t row = rown / p.n2;
   const RowInfo ri = row_info(p.seq, row);
@@ -514,68 +544,81 @@ __global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p,
     return;
   }
   const float* s = scores + (int64_t)rown * ld;
-  // rounds (of 512 positions) that hold visible keys; the per-key loops below skip the rest
-  const int rounds = (n + kTopkThreads - 1) / kTopkThreads;
-  uint32_t key[kTopkFastKeys];
-#pragma unroll
-  for (int j = 0; j < kTopkFastKeys; ++j) {
-    const int pos = j * kTopkThreads + tid;
-    key[j] = (j < rounds && pos < n) ? rank_key<T, true>(s[pos]) : 0u;   // real keys are >= 1
-  }
+  TOPK_PROF_DECL;
 
-  // ---- 1. threshold key T, number of keys above it and of ties to keep
-  uint32_t thr = 0, need = 0;
-  if (n > K) {
-    uint32_t remaining = (uint32_t)K, hi = 0;
-#pragma unroll 1
-    for (int level = 0; level < 2; ++level) {
-      if (tid < 256) hist[tid] = 0;
-      __syncthreads();
+  // ---- 1. scale of the row from a sample of up to 512 scores spread over it: centre = their mean,
+  // spread = mean distance of a sample from its neighbouring sample (for normal scores 1.13 sigma;
+  // a few outliers barely move it)
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(hist);
+    h4[2 * tid] = make_uint4(0, 0, 0, 0);
+    h4[2 * tid + 1] = make_uint4(0, 0, 0, 0);
+  }
+  if (tid < 40) counters[tid] = 0;
+  if (tid == 0) { sh_bstar = kBinCount; sh_need = 0; sh_cstar = 0; sh_base = 0; sh_side = 0; sh_big = 0; }
+  float hi, inv_w;
+  {
+    const int ns = min(n, kTopkThreads);
+    const bool in = tid < ns;
+    const int sp = n > kTopkThreads ? (int)(((int64_t)tid * n) >> 9) : tid;
+    const float x = in ? round_io<T>(s[sp]) : 0.f;
+    const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+    const float dv = (in && (tid ^ 1) < ns) ? fabsf(x - other) : 0.f;
+    const float2 tot = block_sum2_f32(x, dv, part);
+    const float mean = tot.x / (float)ns;
+    const float sdev = 0.9f * (tot.y / (float)ns);
+    hi = mean + 5.f * sdev;
+    inv_w = sdev > 0.f ? (float)kBinCount / (8.f * sdev) : 0.f;
+    if (!(fabsf(hi) <= 3.0e38f) || !(inv_w <= 3.0e38f)) { hi = 0.f; inv_w = 0.f; }   // infinities / NaN in the sample
+  }
+  TOPK_PROF();   // 0: scale
+
+  // ---- 2. load, bin, count.  Thread t holds positions 4 * (g * 512 + t) .. + 3 for g = 0..3
+  // (16-byte loads; rows start 16-byte aligned and are padded to a multiple of 4 scores).
+  // The io dtype is coarser than the bins wherever scores are large, so equal keys (ties, ordered by
+  // position) would pile into one bin with empty bins behind it.  The next lower value of the dtype
+  // lies 2^(e - mantissa bits) below a score of exponent e (half that below a positive power of
+  // two); where that distance is two bins or more, the key moves down the scale by up to 63/64 of it
+  // in proportion to its position.  Keys never reach a lower key's bin offset, equal keys stay in
+  // position order: the bin is still monotone in (key descending, position ascending).
+  constexpr int kMantBits = std::is_same<T, __half>::value ? 10 : 7;
+  const float gap_scale = inv_w * (1.f / (float)(1 << kMantBits));
+  const float tid4 = (float)(4 * tid);
+  uint32_t key[kTopkFastKeys];   // key16 | bin << 16; 0 = no key at this position
 #pragma unroll
-      for (int j = 0; j < kTopkFastKeys; ++j) {
-        if (j >= rounds) break;
-        const bool in = key[j] != 0 && (level == 0 || (key[j] >> 8) == hi);
-        const uint32_t d = level == 0 ? (key[j] >> 8) : (key[j] & 255u);
-        if (level == 0) {
-          // high byte: nearly all keys share a few values, so add once per group of equal values
-          const uint32_t vm = __ballot_sync(0xffffffffu, in);
-          const uint32_t m = __match_any_sync(0xffffffffu, d) & vm;
-          if (in && (m & lt) == 0) atomicAdd(&hist[255 - d], __popc(m));
-        } else if (in) {
-          atomicAdd(&hist[255 - d], 1u);   // low byte inside the chosen bin: spread over the bins
-        }
+  for (int g = 0; g < kTopkFastKeys / 4; ++g) {
+    const int pos0 = 4 * (g * kTopkThreads + tid);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (pos0 < n) v = *reinterpret_cast<const float4*>(s + pos0);
+    const float xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      key[4 * g + u] = 0u;
+      if (pos0 + u < n) {
+        const T r = from_f32<T>(xs[u]);
+        const float x = to_f32<T>(r);
+        // equal keys are spread over the bins up to the next lower key in position order
+        const uint32_t xb = __float_as_uint(x);
+        const float gap = __uint_as_float(xb & 0x7F800000u) * (((xb & 0x807FFFFFu) == 0u) ? 0.5f * gap_scale : gap_scale);
+        const float off = gap >= 2.f ? gap * ((tid4 + (float)(4 * g * kTopkThreads + u)) * (63.f / (64.f * 8192.f))) : 0.f;
+        const int32_t b = min(max(__float2int_rd((hi - x) * inv_w + off), 0), kBinCount - 1);
+        atomicAdd(&hist[b], 1u);
+        key[4 * g + u] = rank_key_of<T>(r) | ((uint32_t)b << 16);
       }
-      __syncthreads();
-      const uint32_t cnt = tid < 256 ? hist[tid] : 0;
-      const uint32_t below = block_exclusive_scan(cnt, warp_tot, nullptr);
-      if (tid < 256 && below < remaining && remaining <= below + cnt) { sh_a = 255 - tid; sh_b = below; }
-      __syncthreads();
-      if (level == 0) hi = sh_a; else thr = (hi << 8) | sh_a;
-      remaining -= sh_b;
-      __syncthreads();
     }
-    need = remaining;   // ties at the threshold that still fit
-  } else {
-    thr = 0;            // every real key is above 0: everything is kept
-  }
-
-  // ---- 2. ordered compaction through per (round, warp) counters
-  uint32_t* cnt_g = tab;          // [16 rounds][16 warps]
-  uint32_t* cnt_e = tab + 256;
-#pragma unroll
-  for (int j = 0; j < kTopkFastKeys; ++j) {
-    uint32_t g = 0, e = 0;
-    if (j < rounds) {
-      g = __ballot_sync(0xffffffffu, key[j] > thr);
-      e = __ballot_sync(0xffffffffu, thr != 0 && key[j] == thr);
-    }
-    if (lane == 0) { cnt_g[j * NW + warp] = __popc(g); cnt_e[j * NW + warp] = __popc(e); }
   }
   __syncthreads();
+  TOPK_PROF();   // 1: load + histogram
+
+  // ---- 2. slot at which every bin starts; the bin in which the count crosses K
   {
-    // threads 0..255 scan the "above" counters, 256..511 the "tie" counters (both in position order)
-    const uint32_t v = tab[tid];
-    uint32_t inc = v;
+    uint4* h4 = reinterpret_cast<uint4*>(hist);
+    uint4 a = h4[2 * tid], c = h4[2 * tid + 1];
+    uint32_t cnt[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+    uint32_t sum = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sum += cnt[q];
+    uint32_t inc = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -583,100 +626,149 @@ __global__ void __launch_bounds__(kTopkThreads, 2) li_topk_radix_kernel(LiDev p,
     }
     if (lane == 31) warp_tot[warp] = inc;
     __syncthreads();
-    uint32_t base = 0;
-    const int w0 = warp < 8 ? 0 : 8;
-    for (int w = w0; w < warp; ++w) base += warp_tot[w];
-    if (tid == 0) {
-      uint32_t g = 0;
-      for (int w = 0; w < 8; ++w) g += warp_tot[w];
-      sh_c = g;   // number of keys above the threshold
-      sh_diff = 0;
-      sh_ref = thr ? thr : key[0];   // some key that is kept (position 0 is always visible)
+    uint32_t run = inc - sum;
+    {
+      // exclusive prefix of the 16 warp totals, by shuffles inside every warp
+      const uint32_t wt = warp_tot[lane & (NW - 1)];
+      uint32_t winc = wt;
+#pragma unroll
+      for (int o = 1; o < NW; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, winc, o);
+        if ((lane & (NW - 1)) >= o) winc += t;
+      }
+      run += __shfl_sync(0xffffffffu, winc - wt, warp);
     }
-    __syncthreads();
-    tab[tid] = base + inc - v;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t c0 = cnt[q];
+      if (run < (uint32_t)K && (uint32_t)K <= run + c0) {   // the K-th best key lies in this bin
+        sh_bstar = 8 * tid + q; sh_base = run; sh_need = (uint32_t)K - run; sh_cstar = c0;
+      }
+      cnt[q] = run;
+      run += c0;
+    }
+    h4[2 * tid] = make_uint4(cnt[0], cnt[1], cnt[2], cnt[3]);
+    h4[2 * tid + 1] = make_uint4(cnt[4], cnt[5], cnt[6], cnt[7]);
   }
   __syncthreads();
-  const uint32_t n_gt = sh_c, ref = sh_ref;
-  uint32_t diff = 0;   // bits in which some kept key differs from `ref`
+  // bins before `bstar` survive whole, bins after it not at all (no crossing: fewer than K keys);
+  // of the crossing bin the `need` best survive
+  const uint32_t bstar = sh_bstar, need = sh_need, cstar = sh_cstar, base_star = sh_base;
+  const bool side_cut = cstar <= (uint32_t)kBinSide;
+  TOPK_PROF();   // 2: scan
+
+  // ---- 3. a large crossing bin is cut by bisection: largest C with count(members >= C) >= need.
+  // (A small one goes to `side` below and is ranked there.)
+  uint32_t cut = 0u;
+  if (bstar < (uint32_t)kBinCount && !side_cut) {
+    uint32_t lo = 1u, hi_c = 0xFFFFFFFFu;
+    int slot = 0;
+#pragma unroll 1
+    for (int it = 0; it < 32 && lo < hi_c; ++it, ++slot) {
+      const uint32_t mid = lo + ((hi_c - lo) >> 1) + ((hi_c - lo) & 1u);
+      uint32_t c = 0;
+#pragma unroll
+      for (int j = 0; j < kTopkFastKeys; ++j) {
+        const uint32_t pos = 4 * ((j >> 2) * kTopkThreads + tid) + (j & 3);
+        const uint32_t comp = (key[j] << 16) | (0xFFFFu - pos);
+        c += (key[j] & 0xFFFFu) != 0u && (key[j] >> 16) == bstar && comp >= mid;
+      }
+      const uint32_t total = block_count(c, &counters[slot]);
+      if (total >= need) lo = mid; else hi_c = mid - 1u;
+    }
+    cut = lo;
+  }
+
+  // ---- 4. survivors into their bin's slot range (arrival order inside a bin)
 #pragma unroll
   for (int j = 0; j < kTopkFastKeys; ++j) {
-    if (j >= rounds) break;
-    const uint32_t pos = j * kTopkThreads + tid;
-    const uint32_t entry = (key[j] << 16) | pos;
-    const bool is_g = key[j] > thr, is_e = thr != 0 && key[j] == thr;
-    const uint32_t g = __ballot_sync(0xffffffffu, is_g);
-    const uint32_t e = __ballot_sync(0xffffffffu, is_e);
-    if (is_g) {
-      buf[0][cnt_g[j * NW + warp] + __popc(g & lt)] = entry;
-      diff |= key[j] ^ ref;
-    } else if (is_e) {
-      const uint32_t ord = cnt_e[j * NW + warp] + __popc(e & lt);
-      if (ord < need) buf[0][n_gt + ord] = entry;
+    const uint32_t b = key[j] >> 16;
+    const uint32_t pos = 4 * ((j >> 2) * kTopkThreads + tid) + (j & 3);
+    const uint32_t comp = (key[j] << 16) | (0xFFFFu - pos);
+    if ((key[j] & 0xFFFFu) != 0u && b <= bstar) {
+      if (b < bstar || (!side_cut && comp >= cut)) {
+        const uint32_t slot = atomicAdd(&hist[b], 1u);
+        if (slot < (uint32_t)P2) { buf[slot] = comp; bbin[slot] = (uint16_t)b; }
+      } else if (side_cut) {
+        side[atomicAdd(&sh_side, 1u)] = comp;
+      }
     }
   }
-  diff = __reduce_or_sync(0xffffffffu, diff);
-  if (lane == 0 && diff) atomicOr(&sh_diff, diff);
-  for (int i = nsel + tid; i < P2; i += kTopkThreads) buf[0][i] = 0x0000FFFFu;   // padding: key 0 sorts last
   __syncthreads();
-  const uint32_t differing = sh_diff & 0xFFFFu;
+  TOPK_PROF();   // 3: scatter
 
-  // ---- 3. stable LSD radix sort on the key, descending (digit' = bins - 1 - digit); digits of
-  // kSortBits = 4 bits: measured 0.475 ms on 8192 x 8192, k = 2048 against 0.51 (5 bits) and 0.60 (6 bits)
-  int cur = 0;
-#pragma unroll 1
-  for (int g = 0; g < kSortPasses; ++g) {
-    if (((differing >> (kSortBits * g)) & (kSortBins - 1u)) == 0) continue;
-    for (int i = tid; i < TN; i += kTopkThreads) tab[i] = 0;
-    __syncthreads();
-    uint32_t ent[E], rk[E], dg[E];
+  // ---- 5. order inside each bin: final slot = bin start + members that precede this one
+  {
+    uint32_t mine[E], st[E], cn[E];
 #pragma unroll
     for (int r = 0; r < E; ++r) {
-      ent[r] = buf[cur][r * kTopkThreads + tid];
-      dg[r] = (kSortBins - 1u) - ((ent[r] >> (16 + kSortBits * g)) & (kSortBins - 1u));
-      const uint32_t m = same_digit<kSortBits>(dg[r]);
-      rk[r] = __popc(m & lt);
-      if (rk[r] == 0) tab[(dg[r] * E + r) * NW + warp] = __popc(m);
-    }
-    __syncthreads();
-    {
-      // exclusive scan of the (digit, round, warp) counters
-      constexpr int PER = (TN + kTopkThreads - 1) / kTopkThreads;
-      uint32_t loc[PER], sum = 0;
-#pragma unroll
-      for (int q = 0; q < PER; ++q) {
-        loc[q] = tid * PER + q < TN ? tab[tid * PER + q] : 0u;
-        sum += loc[q];
-      }
-      uint32_t base = block_exclusive_scan(sum, warp_tot, nullptr);
-#pragma unroll
-      for (int q = 0; q < PER; ++q) {
-        if (tid * PER + q < TN) tab[tid * PER + q] = base;
-        base += loc[q];
+      const int e = r * kTopkThreads + tid;
+      mine[r] = 0u; st[r] = 0u; cn[r] = 0u;
+      if (e < nsel && (!side_cut || (uint32_t)e < base_star || bstar == (uint32_t)kBinCount)) {
+        mine[r] = buf[e];
+        const int32_t b = bbin[e];
+        st[r] = b ? hist[b - 1] : 0u;
+        cn[r] = min(hist[b], (uint32_t)nsel) - st[r];
+        if (cn[r] > (uint32_t)kBinSmall) {
+          if ((uint32_t)e == st[r]) {
+            const uint32_t i = atomicAdd(&sh_big, 1u);
+            if (i < (uint32_t)kBinBigList) biglist[i] = (uint32_t)b;
+          }
+          cn[r] = 0u;
+        }
       }
     }
-    __syncthreads();
 #pragma unroll
-    for (int r = 0; r < E; ++r) buf[cur ^ 1][tab[(dg[r] * E + r) * NW + warp] + rk[r]] = ent[r];
-    __syncthreads();
-    cur ^= 1;
+    for (int r = 0; r < E; ++r) {
+      if (cn[r] != 0u) {
+        uint32_t rank = 0;
+        for (uint32_t q = st[r]; q < st[r] + cn[r]; ++q) rank += buf[q] > mine[r];
+        outs[st[r] + rank] = mine[r];
+      }
+    }
+    // the crossing bin: its members rank each other; the first `need` fill the last slots
+    if (side_cut && (uint32_t)tid < cstar) {
+      const uint32_t m = side[tid];
+      uint32_t rank = 0;
+      for (uint32_t q = 0; q < cstar; ++q) rank += side[q] > m;
+      if (rank < need) outs[base_star + rank] = m;
+    }
   }
+  __syncthreads();
+  TOPK_PROF();   // 4: order inside small bins
+  {
+    const uint32_t nbig = min(sh_big, (uint32_t)kBinBigList);
+    for (uint32_t i = 0; i < nbig; ++i) {
+      const uint32_t b = biglist[i];
+      const uint32_t st = b ? hist[b - 1] : 0u;
+      const uint32_t en = min(hist[b], (uint32_t)nsel);
+      const uint32_t c = en - st;
+      const bool shared_bin = c > 256u;                  // a large bin is split over all warps
+      if (!shared_bin && (i % NW) != (uint32_t)warp) continue;
+      for (uint32_t m0 = st + (shared_bin ? 32u * warp : 0u); m0 < en; m0 += shared_bin ? 32u * NW : 32u) {
+        const uint32_t m = m0 + lane;
+        const uint32_t mine = m < en ? buf[m] : 0u;
+        uint32_t rank = 0;
+        for (uint32_t q = st; q < en; ++q) rank += buf[q] > mine;
+        if (m < en) outs[st + rank] = mine;
+      }
+    }
+    if (nbig) __syncthreads();
+  }
+  TOPK_PROF();   // 5: large bins
 
-  // ---- 4. emit
+  // ---- 6. emit: positions and values come out of the composites
   for (int i = tid; i < K; i += kTopkThreads) {
     if (i < nsel) {
-      const uint32_t e = buf[cur][i];
-      oi[i] = (int32_t)(e & 0xFFFFu);
-      if (ov) {
-        const uint32_t k16 = e >> 16;
-        const uint16_t h = (k16 & 0x8000u) ? (uint16_t)(k16 & 0x7FFFu) : (uint16_t)(~k16);
-        ov[i] = *reinterpret_cast<const T*>(&h);
-      }
+      const uint32_t e = outs[i];
+      oi[i] = (int32_t)(0xFFFFu - (e & 0xFFFFu));
+      if (ov) ov[i] = key16_bits<T>(e >> 16);
     } else {
       oi[i] = -1;
       if (ov) ov[i] = from_f32<T>(0.f);
     }
   }
+  TOPK_PROF();   // 6: emit
 }
 
 }  // namespace dsa
