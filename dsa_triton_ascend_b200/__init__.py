@@ -2,8 +2,9 @@
 
 Public API = the operators of WhFanatic/dsa_triton_ascend with unchanged signatures:
 `lightning_indexer_triton` / `LightningIndexerTriton`, `sparse_flash_attention_triton` /
-`SparseFlashAttentionTriton` and the attention backward `sparse_flash_attention_grad_triton` /
-`SparseFlashAttentionGradTriton`.  All are thin wrappers over the C-ABI CUDA library built from
+`SparseFlashAttentionTriton`, the attention backward `sparse_flash_attention_grad_triton` /
+`SparseFlashAttentionGradTriton` and the indexer's KL-loss backward
+`sparse_lightning_indexer_grad_kl_loss_triton` / `SparseLightningIndexerGradKLLossTriton`.  All are thin wrappers over the C-ABI CUDA library built from
 `dsa_triton_ascend_b200/csrc` (declared in `include/dsa_b200.h`).  `check_status()` (an
 addition) reports a device-side wait that ran out in the latest call of either operator.
 """
@@ -12,10 +13,13 @@ from .lightning_indexer import LightningIndexerTriton, lightning_indexer_triton 
 from .sparse_flash_attention import SparseFlashAttentionTriton, sparse_flash_attention_triton  # noqa: F401
 from .sparse_flash_attention_grad import (SparseFlashAttentionGradTriton,  # noqa: F401
                                           sparse_flash_attention_grad_triton)
+from .sparse_lightning_indexer_grad_kl_loss import (SparseLightningIndexerGradKLLossTriton,  # noqa: F401
+                                                     sparse_lightning_indexer_grad_kl_loss_triton)
 
 __all__ = [
     "lightning_indexer_triton", "LightningIndexerTriton",
     "sparse_flash_attention_triton", "SparseFlashAttentionTriton",
     "sparse_flash_attention_grad_triton", "SparseFlashAttentionGradTriton",
+    "sparse_lightning_indexer_grad_kl_loss_triton", "SparseLightningIndexerGradKLLossTriton",
     "check_status",
 ]

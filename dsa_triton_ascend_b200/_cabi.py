@@ -77,6 +77,22 @@ class DsaSfaGradParams(_c.Structure):
         ("key_rows", _c.c_int64),
     ]
 
+class DsaSliGradParams(_c.Structure):
+    _fields_ = [
+        ("struct_size", _c.c_uint32), ("kernel", _c.c_int32),
+        ("query", _c.c_void_p), ("query_rope", _c.c_void_p), ("key", _c.c_void_p), ("key_rope", _c.c_void_p),
+        ("query_index", _c.c_void_p), ("key_index", _c.c_void_p), ("weights", _c.c_void_p),
+        ("sparse_indices", _c.c_void_p), ("softmax_max", _c.c_void_p), ("softmax_sum", _c.c_void_p),
+        ("seq_q", _c.c_void_p), ("seq_k", _c.c_void_p),
+        ("d_query_index", _c.c_void_p), ("d_key_index", _c.c_void_p), ("d_weights", _c.c_void_p),
+        ("loss", _c.c_void_p),
+        ("dtype", _c.c_int32), ("dtype_w", _c.c_int32),
+        ("batch", _c.c_int32), ("s1", _c.c_int32), ("s2", _c.c_int32), ("n1", _c.c_int32),
+        ("d", _c.c_int32), ("d_rope", _c.c_int32), ("g", _c.c_int32), ("d_idx", _c.c_int32),
+        ("topk", _c.c_int32),
+        ("scale", _c.c_float),
+    ]
+
 
 EXPORTS = (
     "dsa_abi_version", "dsa_status_string", "dsa_read_device_status",
@@ -84,6 +100,7 @@ EXPORTS = (
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
     "dsa_li_forward_static", "dsa_li_static_scratch_bytes", "dsa_selftest_wait_timeout",
     "dsa_kernel_launch_count", "dsa_sfa_grad_workspace_bytes", "dsa_sfa_grad",
+    "dsa_sli_grad_workspace_bytes", "dsa_sli_grad",
 )
 
 
@@ -111,6 +128,10 @@ def _load():
     lib.dsa_sfa_grad_workspace_bytes.restype = _c.c_int
     lib.dsa_sfa_grad.argtypes = [_c.POINTER(DsaSfaGradParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
     lib.dsa_sfa_grad.restype = _c.c_int
+    lib.dsa_sli_grad_workspace_bytes.argtypes = [_c.POINTER(DsaSliGradParams), _c.POINTER(_c.c_size_t)]
+    lib.dsa_sli_grad_workspace_bytes.restype = _c.c_int
+    lib.dsa_sli_grad.argtypes = [_c.POINTER(DsaSliGradParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
+    lib.dsa_sli_grad.restype = _c.c_int
     lib.dsa_li_forward_static.argtypes = [_c.POINTER(DsaLiParams), _c.c_void_p]
     lib.dsa_li_forward_static.restype = _c.c_int
     lib.dsa_li_static_scratch_bytes.restype = _c.c_size_t

@@ -14,6 +14,7 @@
 #include "sfa_fwd_simt.cuh"
 #include "sfa_fwd_sm100.cuh"
 #include "sfa_bwd_simt.cuh"
+#include "sli_grad_simt.cuh"
 
 namespace dsa {
 
@@ -275,13 +276,78 @@ static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t s
   return DSA_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Indexer KL-loss backward: validation and launch
+// ---------------------------------------------------------------------------------------------
+static int sli_grad_validate(const DsaSliGradParams* p) {
+  if (p == nullptr) return DSA_ERR_NULL;
+  if (p->struct_size != sizeof(DsaSliGradParams)) return DSA_ERR_STRUCT;
+  if (!p->query || !p->key || !p->query_index || !p->key_index || !p->weights || !p->sparse_indices ||
+      !p->softmax_max || !p->softmax_sum || !p->d_query_index || !p->d_key_index || !p->d_weights || !p->loss)
+    return DSA_ERR_NULL;
+  if (p->d_rope != 0 && (!p->query_rope || !p->key_rope)) return DSA_ERR_NULL;
+  if (p->dtype != DSA_DTYPE_BF16 && p->dtype != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
+  if (p->dtype_w < DSA_DTYPE_BF16 || p->dtype_w > DSA_DTYPE_FP32) return DSA_ERR_VALUE;
+  // shapes the reference is specified for (test_sli_grad_kl_loss_triton.py:43-45), any head counts
+  if (p->d != 128 && p->d != 256 && p->d != 512) return DSA_ERR_VALUE;
+  if (p->d_idx != 128 && p->d_idx != 256 && p->d_idx != 512) return DSA_ERR_VALUE;
+  if (p->d_rope != 0 && p->d_rope != 64) return DSA_ERR_VALUE;
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 1 || p->n1 < 1 || p->g < 1 || p->topk < 1) return DSA_ERR_VALUE;
+  if (p->topk > 8192) return DSA_ERR_TOO_LARGE;   // p and I of a row live in shared memory
+  if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE) return DSA_ERR_UNSUPPORTED;
+  return DSA_OK;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+template <typename T>
+static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st) {
+  SliGradDev d;
+  const int64_t rows = (int64_t)p->batch * p->s1;
+  const int64_t key_elems = (int64_t)p->batch * p->s2 * p->d_idx;
+  d.query = p->query; d.query_rope = p->d_rope ? p->query_rope : nullptr;
+  d.key = p->key; d.key_rope = p->d_rope ? p->key_rope : nullptr;
+  d.query_index = p->query_index; d.key_index = p->key_index; d.weights = p->weights;
+  d.sparse_indices = p->sparse_indices; d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
+  d.act_q = p->seq_q; d.act_k = p->seq_k;
+  d.d_query_index = p->d_query_index; d.d_weights = p->d_weights; d.d_key_index = p->d_key_index; d.loss = p->loss;
+  d.di = reinterpret_cast<float*>(ws);
+  d.loss_parts = reinterpret_cast<float*>(ws + align256((size_t)rows * p->topk * 4));
+  d.dki_acc = reinterpret_cast<float*>((char*)d.loss_parts + align256((size_t)rows * 4));
+  d.batch = p->batch; d.s1 = p->s1; d.s2 = p->s2; d.n1 = p->n1; d.d = p->d; d.d_rope = p->d_rope;
+  d.g = p->g; d.d_idx = p->d_idx; d.topk = p->topk; d.dtype_w = p->dtype_w;
+  d.scale = p->scale;
+  if (cudaMemsetAsync(d.dki_acc, 0, (size_t)key_elems * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
+  if (rows > 0) {
+    const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
+    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * p->topk * 4;
+    const size_t smem_b = (size_t)(kSliHeads + kSliKeys) * (p->d_idx + kSliPad) * sizeof(T);
+    if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
+            cudaSuccess)
+      return DSA_ERR_CUDA;
+    sli_teacher_kernel<T><<<(unsigned)rows, kSliThreads, smem_a, st>>>(d, stride);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    dim3 grid((unsigned)rows, (unsigned)((p->g + kSliHeads - 1) / kSliHeads), 1);
+    sli_grad_kernel<T><<<grid, kSliThreads, smem_b, st>>>(d);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch(2);
+  }
+  const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>((key_elems + 255) / 256, 148 * 16));
+  sli_finalize_kernel<T><<<blocks, 256, 0, st>>>(d, key_elems, (int32_t)rows);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
+  return DSA_OK;
+}
 }  // namespace dsa
 
 using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 4; }
+int dsa_abi_version(void) { return 5; }
 
 unsigned long long dsa_kernel_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -381,6 +447,30 @@ int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_by
   float* acc = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
   if (p->dtype == DSA_DTYPE_BF16) return sfa_grad_launch<__nv_bfloat16>(p, acc, cs);
   return sfa_grad_launch<__half>(p, acc, cs);
+}
+
+int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes) {
+  int st = sli_grad_validate(p);
+  if (st != DSA_OK) return st;
+  if (!out_bytes) return DSA_ERR_NULL;
+  const size_t rows = (size_t)p->batch * p->s1;
+  *out_bytes = kWorkspaceHeader + align256(rows * p->topk * 4) + align256(rows * 4) +
+               (size_t)p->batch * p->s2 * p->d_idx * 4;
+  return DSA_OK;
+}
+
+int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = sli_grad_validate(p);
+  if (st != DSA_OK) return st;
+  size_t need = 0;
+  dsa_sli_grad_workspace_bytes(p, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  if ((int64_t)p->batch * p->s1 > 0x7FFFFFFF) return DSA_ERR_TOO_LARGE;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  char* ws = (char*)workspace + kWorkspaceHeader;
+  if (p->dtype == DSA_DTYPE_BF16) return sli_grad_launch<__nv_bfloat16>(p, ws, cs);
+  return sli_grad_launch<__half>(p, ws, cs);
 }
 
 // ---------------------------------------------------------------------------------------------

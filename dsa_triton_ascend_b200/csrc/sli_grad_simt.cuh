@@ -1,0 +1,351 @@
+// Portable (CUDA-core) backward of the sparse lightning indexer under the KL loss against the
+// attention distribution (sparse_lightning_indexer_grad_kl_loss_triton.py:25-327, golden
+// sli_grad_kl_loss_numpy.py:16-156).  Per query row with n used slots and idx = its sparse
+// indices clipped to [0, S2):
+//     p[k]  = mean_h exp((q[h].k[idx k] + qr[h].kr[idx k]) * scale - max[h]) / (sum[h] + 1e-8)
+//     I[k]  = sum_g w[g] relu(qi[g].ki[idx k]);  sI = softmax_k(I);  dI = sI - p
+//     loss += sum_k max(p,1e-8) (log max(p,1e-8) - log max(sI,1e-8))
+//     dW[g] = sum_k dI[k] relu[g,k];   ds[g,k] = dI[k] w[g] [relu[g,k] > 0]
+//     dQI[g] = sum_k ds[g,k] ki[idx k];   dKI[idx k] += sum_g ds[g,k] qi[g]
+// The reference runs all stages in one program per row and keeps ReLU values, gathered index keys,
+// p, I and dI in global scratch tensors between them (:385-400).  Here the first kernel produces dI and
+// the row's loss term (p and I live in shared memory); the second, one block per (row, 16 index
+// heads), recomputes the index scores it needs instead of reading a [rows, G, topK] ReLU cache,
+// accumulates dQI / dW in registers and adds dKI into an fp32 accumulator with 16-byte reductions; a
+// third converts the accumulator and sums the loss terms in a fixed order.
+#pragma once
+
+#include "dsa_common.cuh"
+#include "sfa_bwd_simt.cuh"
+
+namespace dsa {
+
+struct SliGradDev {
+  const void* query;        // [rows, n1, d]
+  const void* query_rope;   // [rows, n1, d_rope] or null (d_rope 0)
+  const void* key;          // [batch * s2, d]
+  const void* key_rope;     // [batch * s2, d_rope] or null
+  const void* query_index;  // [rows, g, d_idx]
+  const void* key_index;    // [batch * s2, d_idx]
+  const void* weights;      // [rows, g], dtype_w
+  const int32_t* sparse_indices;   // [rows, topk]
+  const float* softmax_max;        // [rows, n1]
+  const float* softmax_sum;
+  const int32_t* act_q;     // [batch] or null
+  const int32_t* act_k;
+  void* d_query_index;      // [rows, g, d_idx]
+  void* d_weights;          // [rows, g], dtype_w
+  void* d_key_index;        // [batch * s2, d_idx]
+  float* loss;              // [1]
+  float* di;                // [rows, topk]  scratch
+  float* loss_parts;        // [rows]        scratch
+  float* dki_acc;           // [batch * s2, d_idx] scratch, zeroed by the caller
+  int32_t batch, s1, s2, n1, d, d_rope, g, d_idx, topk, dtype_w;
+  float scale;
+};
+
+constexpr int kSliHeads = 16;
+constexpr int kSliKeys = 32;
+constexpr int kSliThreads = 256;
+constexpr int kSliPad = 8;
+constexpr float kSliEps = 1e-8f;
+
+__device__ __forceinline__ int32_t sli_row_slots(const SliGradDev& p, int32_t row, int32_t* b_out) {
+  const int32_t b = row / p.s1, pos = row - b * p.s1;
+  const int32_t aq = p.act_q ? p.act_q[b] : p.s1;
+  const int32_t ak = p.act_k ? p.act_k[b] : p.s2;
+  *b_out = b;
+  if (pos >= aq) return 0;
+  return min(min(p.topk, p.s2), max(ak - aq + pos + 1, 0));   // :72-74
+}
+
+__device__ __forceinline__ void store_weight(void* w, int32_t dtype_w, int64_t i, float v) {
+  if (dtype_w == DSA_DTYPE_FP32) ((float*)w)[i] = v;
+  else if (dtype_w == DSA_DTYPE_FP16) ((__half*)w)[i] = __float2half_rn(v);
+  else ((__nv_bfloat16*)w)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float sli_block_reduce(float v, float* red /*[8]*/, bool is_max) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float t = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, t) : v + t;
+  }
+  __syncthreads();   // `red` may still be read from an earlier reduction
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < kSliThreads / 32; ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+  return r;
+}
+
+// Stages `heads` rows of width `wa` (+ `wb` from a second tensor) into shared memory, zero past `have`.
+template <typename T>
+__device__ __forceinline__ void sli_stage_heads(T* dst, int stride, const T* a, int wa, const T* b, int wb, int h0,
+                                                int have) {
+  const int w = wa + wb;
+  for (int i = threadIdx.x; i < kSliHeads * w; i += kSliThreads) {
+    const int h = i / w, c = i - h * w;
+    T v = from_f32<T>(0.f);
+    if (h0 + h < have) v = c < wa ? a[(int64_t)(h0 + h) * wa + c] : b[(int64_t)(h0 + h) * wb + (c - wa)];
+    dst[h * stride + c] = v;
+  }
+}
+
+// Gathers the rows idx_s[0..32) (16-byte chunks) of one or two key tensors into shared memory.
+template <typename T>
+__device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, int wa, const T* b, int wb,
+                                                const int64_t* rows_s) {
+  const int ca = wa / 8, cb = wb / 8, ct = ca + cb;
+  for (int i = threadIdx.x; i < kSliKeys * ct; i += kSliThreads) {
+    const int k = i / ct, c = i - k * ct;
+    const int64_t r = rows_s[k];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r >= 0) v = c < ca ? reinterpret_cast<const uint4*>(a + r * wa)[c] : reinterpret_cast<const uint4*>(b + r * wb)[c - ca];
+    *reinterpret_cast<uint4*>(&dst[k * stride + c * 8]) = v;
+  }
+}
+
+// Dot products of key `lane` with heads `warp` and `warp + 8` over `w` columns.
+template <typename T>
+__device__ __forceinline__ void sli_dots(const T* qs, const T* ks, int stride, int w, float* s0, float* s1) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint4* kp = reinterpret_cast<const uint4*>(&ks[lane * stride]);
+  const uint4* q0 = reinterpret_cast<const uint4*>(&qs[warp * stride]);
+  const uint4* q1 = reinterpret_cast<const uint4*>(&qs[(warp + 8) * stride]);
+  float a0 = 0.f, a1 = 0.f;
+  for (int c = 0; c < w / 8; ++c) {
+    const uint4 kv = kp[c], a = q0[c], b = q1[c];
+    const T* kk = reinterpret_cast<const T*>(&kv);
+    const T* aa = reinterpret_cast<const T*>(&a);
+    const T* bb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float kf = to_f32<T>(kk[e]);
+      a0 = fmaf(kf, to_f32<T>(aa[e]), a0);
+      a1 = fmaf(kf, to_f32<T>(bb[e]), a1);
+    }
+  }
+  *s0 = a0;
+  *s1 = a1;
+}
+
+// grid = rows; block = 256.  dynamic smem: (16 + 32) * stride elements of T, then 2 * topk floats.
+template <typename T>
+__global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, int stride) {
+  extern __shared__ __align__(16) unsigned char sli_smem[];
+  T* qs = reinterpret_cast<T*>(sli_smem);
+  T* ks = qs + kSliHeads * stride;
+  float* p_s = reinterpret_cast<float*>(ks + kSliKeys * stride);
+  float* i_s = p_s + p.topk;
+  __shared__ float red_s[kSliThreads / 32][kSliKeys];
+  __shared__ float red8[kSliThreads / 32];
+  __shared__ int64_t rows_s[kSliKeys];
+  __shared__ float max_s[kSliHeads], inv_s[kSliHeads], w_s[kSliHeads];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t row = blockIdx.x;
+  int32_t b;
+  const int32_t n = sli_row_slots(p, row, &b);
+  if (n == 0) {
+    if (tid == 0) p.loss_parts[row] = 0.f;
+    return;
+  }
+  const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.topk;
+  const T* q = (const T*)p.query + (int64_t)row * p.n1 * p.d;
+  const T* qr = p.d_rope ? (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope : nullptr;
+  const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
+
+  for (int phase = 0; phase < 2; ++phase) {          // 0: attention distribution p, 1: index scores I
+    const int heads = phase == 0 ? p.n1 : p.g;
+    const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
+    for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
+      __syncthreads();
+      if (tid < kSliKeys) {
+        const int32_t j = j0 + tid;
+        rows_s[tid] = j < n ? (int64_t)b * p.s2 + min(max(idx_row[j], 0), p.s2 - 1) : -1;   // :96
+      }
+      __syncthreads();
+      if (phase == 0) sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s);
+      else sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+      float acc = 0.f;
+      for (int h0 = 0; h0 < heads; h0 += kSliHeads) {
+        __syncthreads();
+        if (phase == 0) sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, heads);
+        else sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, heads);
+        if (tid < kSliHeads) {
+          const int h = h0 + tid;
+          if (phase == 0) {
+            max_s[tid] = h < heads ? p.softmax_max[(int64_t)row * p.n1 + h] : 0.f;
+            inv_s[tid] = h < heads ? 1.f / (p.softmax_sum[(int64_t)row * p.n1 + h] + kSliEps) : 0.f;
+          } else {
+            w_s[tid] = h < heads ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
+          }
+        }
+        __syncthreads();
+        float s0, s1;
+        sli_dots<T>(qs, ks, stride, w, &s0, &s1);
+        float part;
+        if (phase == 0) {
+          part = (h0 + warp < heads ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
+                 (h0 + warp + 8 < heads ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
+        } else {
+          part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
+        }
+        red_s[warp][lane] = part;
+        __syncthreads();
+        if (tid < kSliKeys) {
+#pragma unroll
+          for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
+        }
+      }
+      if (tid < kSliKeys && j0 + tid < n) {
+        if (phase == 0) p_s[j0 + tid] = acc * (1.f / (float)p.n1);
+        else i_s[j0 + tid] = acc;
+      }
+    }
+  }
+  __syncthreads();
+
+  // softmax of the index scores, dI, the row's KL term (:95-116)
+  float m = -INFINITY;
+  for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, i_s[k]);
+  m = sli_block_reduce(m, red8, true);
+  float se = 0.f;
+  for (int k = tid; k < n; k += kSliThreads) se += expf(i_s[k] - m);
+  se = sli_block_reduce(se, red8, false);
+  const float inv = 1.f / (se + kSliEps);
+  float kl = 0.f;
+  float* di = p.di + (int64_t)row * p.topk;
+  for (int k = tid; k < n; k += kSliThreads) {
+    const float si = expf(i_s[k] - m) * inv, pk = p_s[k];
+    di[k] = si - pk;
+    const float pc = fmaxf(pk, kSliEps), sc = fmaxf(si, kSliEps);
+    kl += pc * (logf(pc) - logf(sc));
+  }
+  kl = sli_block_reduce(kl, red8, false);
+  if (tid == 0) p.loss_parts[row] = kl;
+}
+
+// grid = (rows, ceil(g / 16)); block = 256.  dynamic smem: (16 + 32) * (d_idx + pad) elements of T.
+template <typename T>
+__global__ void __launch_bounds__(kSliThreads) sli_grad_kernel(SliGradDev p) {
+  extern __shared__ __align__(16) unsigned char sli_smem[];
+  const int stride = p.d_idx + kSliPad;
+  T* qs = reinterpret_cast<T*>(sli_smem);
+  T* ks = qs + kSliHeads * stride;
+  __shared__ float dss[kSliHeads][kSliKeys + 1];
+  __shared__ float di_s[kSliKeys], w_s[kSliHeads];
+  __shared__ int64_t rows_s[kSliKeys];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t row = blockIdx.x;
+  const int32_t h0 = blockIdx.y * kSliHeads;
+  int32_t b;
+  const int32_t n = sli_row_slots(p, row, &b);
+  const int ah = tid >> 4, ac = (tid & 15) * 2;   // dQI accumulator: head ah, columns ac + 32 j (+1)
+  const int nq = p.d_idx / 32;
+  float acc[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+  float dw0 = 0.f, dw1 = 0.f;
+
+  if (n > 0) {
+    const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
+    sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, p.g);
+    if (tid < kSliHeads) w_s[tid] = h0 + tid < p.g ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h0 + tid) : 0.f;
+    const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.topk;
+    const float* di = p.di + (int64_t)row * p.topk;
+    const int gq = p.d_idx / 4;
+    for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
+      __syncthreads();
+      if (tid < kSliKeys) {
+        const int32_t j = j0 + tid;
+        rows_s[tid] = j < n ? (int64_t)b * p.s2 + min(max(idx_row[j], 0), p.s2 - 1) : -1;
+        di_s[tid] = j < n ? di[j] : 0.f;
+      }
+      __syncthreads();
+      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+      __syncthreads();
+      {
+        float s0, s1;
+        sli_dots<T>(qs, ks, stride, p.d_idx, &s0, &s1);
+        const float dk = di_s[lane];
+        dw0 = fmaf(dk, fmaxf(s0, 0.f), dw0);
+        dw1 = fmaf(dk, fmaxf(s1, 0.f), dw1);
+        dss[warp][lane] = s0 > 0.f ? dk * w_s[warp] : 0.f;
+        dss[warp + 8][lane] = s1 > 0.f ? dk * w_s[warp + 8] : 0.f;
+      }
+      __syncthreads();
+      for (int k = 0; k < kSliKeys; ++k) {
+        const float w = dss[ah][k];
+        if (w == 0.f) continue;
+        const T* kr_ = &ks[k * stride + ac];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j < nq) {
+            acc[2 * j] = fmaf(w, to_f32<T>(kr_[32 * j]), acc[2 * j]);
+            acc[2 * j + 1] = fmaf(w, to_f32<T>(kr_[32 * j + 1]), acc[2 * j + 1]);
+          }
+        }
+      }
+      for (int u = tid; u < kSliKeys * gq; u += kSliThreads) {
+        const int k = u / gq, g4 = u - k * gq;
+        const int64_t r = rows_s[k];
+        if (r < 0) continue;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+        for (int h = 0; h < kSliHeads; ++h) {
+          const float w = dss[h][k];
+          const uint2 v = *reinterpret_cast<const uint2*>(&qs[h * stride + 4 * g4]);
+          const T* e = reinterpret_cast<const T*>(&v);
+          a0 = fmaf(w, to_f32<T>(e[0]), a0); a1 = fmaf(w, to_f32<T>(e[1]), a1);
+          a2 = fmaf(w, to_f32<T>(e[2]), a2); a3 = fmaf(w, to_f32<T>(e[3]), a3);
+        }
+        red_add_v4(p.dki_acc + r * p.d_idx + 4 * g4, a0, a1, a2, a3);
+      }
+    }
+  }
+  // dW (sum over the keys a lane saw) and dQI of this head chunk; zeros for unused rows
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    dw0 += __shfl_xor_sync(0xffffffffu, dw0, o);
+    dw1 += __shfl_xor_sync(0xffffffffu, dw1, o);
+  }
+  if (lane == 0) {
+    if (h0 + warp < p.g) store_weight(p.d_weights, p.dtype_w, (int64_t)row * p.g + h0 + warp, dw0);
+    if (h0 + warp + 8 < p.g) store_weight(p.d_weights, p.dtype_w, (int64_t)row * p.g + h0 + warp + 8, dw1);
+  }
+  if (h0 + ah < p.g) {
+    T* dst = (T*)p.d_query_index + ((int64_t)row * p.g + h0 + ah) * p.d_idx + ac;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < nq) {
+        dst[32 * j] = from_f32<T>(acc[2 * j]);
+        dst[32 * j + 1] = from_f32<T>(acc[2 * j + 1]);
+      }
+    }
+  }
+}
+
+// fp32 accumulator -> d_key_index; block 0 also adds up the rows' loss terms in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256) sli_finalize_kernel(SliGradDev p, int64_t total, int32_t rows) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    ((T*)p.d_key_index)[i] = from_f32<T>(p.dki_acc[i]);
+  if (blockIdx.x == 0) {
+    __shared__ float red[256];
+    float s = 0.f;
+    for (int r = threadIdx.x; r < rows; r += 256) s += p.loss_parts[r];
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+      if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) p.loss[0] = red[0];
+  }
+}
+
+}  // namespace dsa

@@ -183,6 +183,46 @@ int dsa_sfa_grad_workspace_bytes(const DsaSfaGradParams* p, size_t* out_bytes);
 int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Backward of the sparse lightning indexer under the KL loss against the attention distribution -
+ * replaces `_sparse_lightning_indexer_grad_kl_loss_core`
+ * (sparse_lightning_indexer_grad_kl_loss_triton.py:331-443) behind
+ * `sparse_lightning_indexer_grad_kl_loss_triton` (:496-580).  BSND, rightDownCausal, one key head.
+ * Inputs: the attention operands (query / key with optional 64-wide rope parts), the indexer
+ * operands (query_index, key_index, weights), the sparse indices and the softmax statistics of the
+ * dense causal attention forward.  Outputs: d_query_index, d_key_index (dtype of the index tensors),
+ * d_weights (dtype of weights) and the fp32 loss (one element).  d_key_index is a scatter-add with
+ * fp32 atomics: its last place can vary between runs.
+ */
+typedef struct DsaSliGradParams {
+  uint32_t struct_size; /* sizeof(DsaSliGradParams) */
+  int32_t kernel;       /* DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE */
+  const void* query;       /* [batch, s1, n1, d]      */
+  const void* query_rope;  /* [batch, s1, n1, d_rope] or NULL with d_rope = 0 */
+  const void* key;         /* [batch, s2, 1, d]       */
+  const void* key_rope;    /* [batch, s2, 1, d_rope] or NULL */
+  const void* query_index; /* [batch, s1, g, d_idx]   */
+  const void* key_index;   /* [batch, s2, 1, d_idx]   */
+  const void* weights;     /* [batch, s1, g], dtype_w */
+  const int32_t* sparse_indices; /* [batch, s1, 1, topk] */
+  const float* softmax_max;      /* [batch, 1, s1, n1] */
+  const float* softmax_sum;
+  const int32_t* seq_q; /* [batch] valid query lengths or NULL */
+  const int32_t* seq_k; /* [batch] valid key lengths or NULL   */
+  void* d_query_index;  /* [batch, s1, g, d_idx] */
+  void* d_key_index;    /* [batch, s2, 1, d_idx] */
+  void* d_weights;      /* [batch, s1, g], dtype_w */
+  float* loss;          /* [1] */
+  int32_t dtype, dtype_w;
+  int32_t batch, s1, s2, n1, d, d_rope, g, d_idx, topk;
+  float scale;
+} DsaSliGradParams;
+
+/* Workspace: status header + fp32 scratch (dI [rows, topk], one loss term per row, the d_key_index
+ * accumulator [batch * s2, d_idx]). */
+int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes);
+int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * dsa_li_forward_static - the indexer without a caller workspace and without any allocation.
  * (No counterpart in the reference; added for hosts described below.)
  *

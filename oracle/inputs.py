@@ -75,6 +75,31 @@ def sfa_grad_inputs(seed, B, S1, S2, N1, D=512, Dr=64, dtype="bf16"):
     do = draw(B, S1, N1, D)
     return q, k, qr, kr, do
 
+def sli_grad_inputs(seed, B, S1, S2, N1, D, G, Di, topk, pattern="causal_random", Dr=64, dtype="fp16"):
+    """q, k, q_rope, k_rope, q_index, k_index, |w| drawn in the order of the reference's backward
+    tests (test_sli_grad_kl_loss_triton.py:82-94), then sparse indices of the given pattern
+    (:96-131): "random" anywhere in [0, S2), "causal_random" distinct positions inside each row's
+    causal window (zero-padded), "causal_continuous" 0..n-1, "repeated" alternating 0 / 7."""
+    rng = np.random.RandomState(seed)
+    draw = lambda *shape: round_io(rng.randn(*shape).astype(np.float32), dtype)   # noqa: E731
+    q, k = draw(B, S1, N1, D), draw(B, S2, 1, D)
+    qr, kr = draw(B, S1, N1, Dr), draw(B, S2, 1, Dr)
+    qi, ki = draw(B, S1, G, Di), draw(B, S2, 1, Di)
+    w = np.abs(draw(B, S1, G))
+    si = np.zeros((B, S1, 1, topk), np.int32)
+    if pattern == "random":
+        si = rng.randint(0, S2, (B, S1, 1, topk)).astype(np.int32)
+    elif pattern == "repeated":
+        si[..., 1::2] = min(S2 - 1, 7)
+    else:
+        for b in range(B):
+            for s1 in range(S1):
+                visible = min(max(S2 - S1 + s1 + 1, 1), S2)
+                n = min(topk, visible)
+                si[b, s1, 0, :n] = (rng.choice(visible, size=n, replace=False) if pattern == "causal_random"
+                                    else np.arange(n))
+    return q, k, qr, kr, qi, ki, w, si
+
 
 # The two CPU-sized configurations of the benchmark specification.
 def config1():

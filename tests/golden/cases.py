@@ -57,6 +57,17 @@ SFA_GRAD_CASES = {
                                  act_q=[24, 10, 3], act_k=[192, 7, 100]),
 }
 
+# indexer KL-loss backward: shapes of test_sli_grad_kl_loss_triton.py:17-20,46-64 scaled to what the
+# numpy golden finishes in seconds; pattern = how sparse_indices are drawn (:96-131)
+SLI_GRAD_CASES = {
+    "sli_grad_strict":   dict(seed=61, B=1, S1=4, S2=1024, N1=64, D=512, G=16, Di=128, k=512, pattern="causal_random"),
+    "sli_grad_small":    dict(seed=62, B=2, S1=6, S2=256, N1=32, D=128, G=32, Di=128, k=128, pattern="causal_random"),
+    "sli_grad_heads128": dict(seed=63, B=1, S1=3, S2=384, N1=128, D=256, G=128, Di=128, k=256, pattern="causal_random"),
+    "sli_grad_random":   dict(seed=64, B=1, S1=5, S2=300, N1=32, D=512, G=8, Di=256, k=200, pattern="random"),
+    "sli_grad_repeated": dict(seed=65, B=1, S1=4, S2=128, N1=32, D=128, G=64, Di=128, k=96, pattern="repeated"),
+    "sli_grad_k_gt_s2":  dict(seed=66, B=1, S1=8, S2=48, N1=32, D=256, G=16, Di=512, k=64, pattern="causal_continuous"),
+}
+
 
 def li_case_inputs(name):
     """Seeded inputs of one LI case: (q, k, w, act_q, act_k, spec)."""
@@ -95,6 +106,16 @@ def sfa_grad_case_inputs(name):
                          act_q, act_k)
     scale = 1.0 / np.sqrt(c["D"] + 64.0)
     return q, k, qr, kr, do, idx, act_q, act_k, scale, c
+
+def sli_grad_case_inputs(name):
+    """Seeded inputs of one indexer-loss backward case:
+    (q, k, qr, kr, qi, ki, w, si, scale, spec); fp16-rounded fp32 arrays."""
+    import numpy as np
+    from oracle.inputs import sli_grad_inputs
+    c = SLI_GRAD_CASES[name]
+    arrs = sli_grad_inputs(c["seed"], c["B"], c["S1"], c["S2"], c["N1"], c["D"], c["G"], c["Di"], c["k"],
+                           c["pattern"])
+    return arrs + (1.0 / np.sqrt(float(c["D"])), c)
 
 
 def case_rows(c, act_q):

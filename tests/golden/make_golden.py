@@ -7,7 +7,8 @@ sparse_flash_attention_numpy.sparse_flash_attention_golden_bsnd and
 sparse_flash_attention_grad_numpy.sparse_flash_attention_grad_golden_bsnd from that checkout,
 runs them on the seeded inputs of tests/golden/cases.py and stores only the outputs (inputs
 are regenerated from the seeds; the backward cases take their forward state from the forward
-golden).  For cases with `rows_every` only the listed rows are kept.
+golden).  sli_grad_kl_loss_numpy.py (numpy_reference and _compute_sm_stats, both plain numpy) imports
+mindspore at module level only to set a context; an empty stand-in module satisfies that import.  For cases with `rows_every` only the listed rows are kept.
 The stored arrays pin the numpy restatement under oracle/ (tests/test_oracle_golden.py).
 """
 import os
@@ -18,8 +19,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, case_rows, li_case_inputs,  # noqa: E402
-                                sfa_case_inputs, sfa_grad_case_inputs)
+from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES, case_rows,  # noqa: E402
+                                li_case_inputs, sfa_case_inputs, sfa_grad_case_inputs, sli_grad_case_inputs)
 
 
 def main(ref_dir):
@@ -81,6 +82,21 @@ def main(ref_dir):
                             **{n: g.astype(np.float32) for n, g in
                                zip(("d_query", "d_key", "d_value", "d_query_rope", "d_key_rope"), grads)})
         print(name, [g.shape for g in grads])
+
+    import types
+    if "mindspore" not in sys.modules:
+        stub = types.ModuleType("mindspore")
+        stub.GRAPH_MODE = 0
+        stub.set_context = lambda **kw: None
+        sys.modules["mindspore"] = stub
+    import sli_grad_kl_loss_numpy as ref_sli
+    for name in SLI_GRAD_CASES:
+        q, k, qr, kr, qi, ki, w, si, scale, c = sli_grad_case_inputs(name)
+        sm_max, sm_sum = ref_sli._compute_sm_stats(q, k, qr, kr, scale)
+        res = ref_sli.numpy_reference(q, k, qr, kr, qi, ki, w, si, sm_max, sm_sum, scale)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), sm_max=sm_max, sm_sum=sm_sum,
+                            **{n: res[n].astype(np.float32) for n in ("dQueryIndex", "dKeyIndex", "dW", "loss")})
+        print(name, float(res["loss"][0]), res["dKeyIndex"].shape)
 
 
 def _row_mask(shape, sel):

@@ -28,16 +28,19 @@ def test_library_exports_every_declared_symbol():
 
 def test_ctypes_structs_match_the_c_header():
     from dsa_triton_ascend_b200 import _cabi
-    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
           'sizeof(DsaLiParams),sizeof(DsaSfaParams),offsetof(DsaLiParams,phases),' \
           'offsetof(DsaSfaParams,scale),offsetof(DsaLiParams,out_indices),sizeof(DsaSfaGradParams),' \
-          'offsetof(DsaSfaGradParams,d_value),offsetof(DsaSfaGradParams,key_rows));return 0;}\n'
+          'offsetof(DsaSfaGradParams,d_value),offsetof(DsaSfaGradParams,key_rows),sizeof(DsaSliGradParams),' \
+          'offsetof(DsaSliGradParams,scale));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "t.c")
         open(c, "w").write(src)
         exe = os.path.join(d, "t")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
-        li, sfa, off_ph, off_sc, off_oi, grad, off_dv, off_kr = map(int, subprocess.check_output([exe]).split())
+        li, sfa, off_ph, off_sc, off_oi, grad, off_dv, off_kr, sli, off_ss = map(
+            int, subprocess.check_output([exe]).split())
+    assert sli == ctypes.sizeof(_cabi.DsaSliGradParams) and off_ss == _cabi.DsaSliGradParams.scale.offset
     assert grad == ctypes.sizeof(_cabi.DsaSfaGradParams)
     assert off_dv == _cabi.DsaSfaGradParams.d_value.offset and off_kr == _cabi.DsaSfaGradParams.key_rows.offset
     assert li == ctypes.sizeof(_cabi.DsaLiParams) and sfa == ctypes.sizeof(_cabi.DsaSfaParams)
@@ -162,6 +165,45 @@ def test_sfa_grad_guards_raise_value_error_like_the_reference():
     assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -5
     g.kernel = 0
     assert _cabi.lib.dsa_sfa_grad(ctypes.byref(g), None, 0, None) == -4
+
+
+def test_sli_grad_guards_and_abi_validation():
+    """sparse_lightning_indexer_grad_kl_loss_triton.py:511-515 (layout / sparse_mode / one key head) and
+    the ABI's own checks, without a GPU."""
+    from dsa_triton_ascend_b200 import _cabi, sparse_lightning_indexer_grad_kl_loss_triton as fn
+    hf = torch.float16
+    q, k = torch.zeros(1, 4, 32, 128, dtype=hf), torch.zeros(1, 64, 1, 128, dtype=hf)
+    qi, ki = torch.zeros(1, 4, 8, 128, dtype=hf), torch.zeros(1, 64, 1, 128, dtype=hf)
+    w, si = torch.zeros(1, 4, 8, dtype=hf), torch.zeros(1, 4, 1, 16, dtype=torch.int32)
+    mx, sm = torch.zeros(1, 1, 4, 32), torch.ones(1, 1, 4, 32)
+    for kw in (dict(layout="TND"), dict(sparse_mode=0)):
+        with pytest.raises(ValueError):
+            fn(q, k, qi, ki, w, si, mx, sm, **kw)
+    with pytest.raises(ValueError):
+        fn(q, k, qi, ki, w, si.repeat(1, 1, 2, 1), mx, sm)
+    with pytest.raises(ValueError):
+        fn(q, k, qi[..., :96], ki[..., :96], w, si, mx, sm)
+    with pytest.raises(ValueError):
+        fn(q, k, qi, ki, w, si, mx[..., :8], sm)
+    with pytest.raises(RuntimeError):   # CPU tensors: there is no CPU path
+        fn(q, k, qi, ki, w, si, mx, sm)
+    n = ctypes.c_size_t(0)
+    g = _cabi.DsaSliGradParams()
+    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -2
+    g.struct_size = ctypes.sizeof(g)
+    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -1
+    for f in ("query", "key", "query_index", "key_index", "weights", "sparse_indices", "softmax_max", "softmax_sum",
+              "d_query_index", "d_key_index", "d_weights", "loss"):
+        setattr(g, f, 256)
+    g.batch, g.s1, g.s2, g.n1, g.d, g.d_rope, g.g, g.d_idx, g.topk = 1, 4, 64, 32, 128, 0, 8, 128, 16
+    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
+    assert n.value == 256 + 256 + 256 + 64 * 128 * 4
+    g.d_rope = 64                                   # rope width given but no rope tensors
+    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -1
+    g.d_rope, g.topk = 0, 10000
+    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -8
+    g.topk = 16
+    assert _cabi.lib.dsa_sli_grad(ctypes.byref(g), None, 0, None) == -4
 
 
 def test_li_guards_raise_value_error_like_the_reference():

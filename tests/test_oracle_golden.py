@@ -12,10 +12,10 @@ import os
 import numpy as np
 import pytest
 
-from oracle import (lightning_indexer_oracle, sparse_flash_attention_grad_oracle,
+from oracle import (lightning_indexer_oracle, sli_grad_kl_loss_oracle, sparse_flash_attention_grad_oracle,
                     sparse_flash_attention_oracle)
-from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, li_case_inputs, sfa_case_inputs,
-                                sfa_grad_case_inputs)
+from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES, li_case_inputs,
+                                sfa_case_inputs, sfa_grad_case_inputs, sli_grad_case_inputs)
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -85,6 +85,25 @@ def test_sfa_grad_oracle_matches_reference_golden(name):
     for b_ in range(c["B"]):
         assert (got[0][b_, int(act_q[b_]):] == 0).all() and (got[3][b_, int(act_q[b_]):] == 0).all()
         assert (got[1][b_, int(act_k[b_]):] == 0).all() and (got[2][b_, int(act_k[b_]):] == 0).all()
+
+@pytest.mark.parametrize("name", sorted(SLI_GRAD_CASES))
+def test_sli_grad_oracle_matches_reference_golden(name):
+    """sli_grad_kl_loss_numpy.numpy_reference returns un-rounded fp32 results; the restatement does the
+    same sums with the heads of a row batched into matrix products, so the two agree to fp32
+    summation noise: 2e-5 of each tensor's largest magnitude.  The statistics stored beside the
+    outputs (the golden file's own `_compute_sm_stats`, which rounds scores to fp16 first) also pin
+    `oracle.sli_grad_oracle.softmax_stats` to within that rounding."""
+    from oracle.sli_grad_oracle import softmax_stats
+    q, k, qr, kr, qi, ki, w, si, scale, c = sli_grad_case_inputs(name)
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    got = sli_grad_kl_loss_oracle(q, k, qr, kr, qi, ki, w, si, g["sm_max"], g["sm_sum"], scale)
+    for n in ("dQueryIndex", "dKeyIndex", "dW", "loss"):
+        a, b = got[n], g[n]
+        assert a.shape == b.shape, n
+        assert np.abs(a - b).max() <= 2e-5 * max(np.abs(b).max(), 1e-3), f"{n}: {np.abs(a - b).max()}"
+    m, s_ = softmax_stats(q, k, qr, kr, scale)
+    np.testing.assert_allclose(m, g["sm_max"], rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(np.log(s_), np.log(g["sm_sum"]), rtol=0, atol=2e-2)
 
 
 def test_li_oracle_layout_adapters_roundtrip():
