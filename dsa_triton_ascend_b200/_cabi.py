@@ -91,6 +91,19 @@ class DsaSliGradParams(_c.Structure):
         ("d", _c.c_int32), ("d_rope", _c.c_int32), ("g", _c.c_int32), ("d_idx", _c.c_int32),
         ("topk", _c.c_int32),
         ("scale", _c.c_float),
+        ("dense", _c.c_int32), ("n2", _c.c_int32),
+        ("softmax_max_index", _c.c_void_p), ("softmax_sum_index", _c.c_void_p),
+    ]
+
+
+class DsaDenseLseParams(_c.Structure):
+    _fields_ = [
+        ("struct_size", _c.c_uint32), ("reserved", _c.c_int32),
+        ("query_index", _c.c_void_p), ("key_index", _c.c_void_p), ("weights", _c.c_void_p),
+        ("seq_q", _c.c_void_p), ("seq_k", _c.c_void_p),
+        ("softmax_max_index", _c.c_void_p), ("softmax_sum_index", _c.c_void_p),
+        ("dtype", _c.c_int32), ("dtype_w", _c.c_int32),
+        ("batch", _c.c_int32), ("s1", _c.c_int32), ("s2", _c.c_int32), ("g", _c.c_int32), ("d_idx", _c.c_int32),
     ]
 
 
@@ -100,7 +113,7 @@ EXPORTS = (
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
     "dsa_li_forward_static", "dsa_li_static_scratch_bytes", "dsa_selftest_wait_timeout",
     "dsa_kernel_launch_count", "dsa_sfa_grad_workspace_bytes", "dsa_sfa_grad",
-    "dsa_sli_grad_workspace_bytes", "dsa_sli_grad",
+    "dsa_sli_grad_workspace_bytes", "dsa_sli_grad", "dsa_dense_li_lse",
 )
 
 
@@ -132,6 +145,8 @@ def _load():
     lib.dsa_sli_grad_workspace_bytes.restype = _c.c_int
     lib.dsa_sli_grad.argtypes = [_c.POINTER(DsaSliGradParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
     lib.dsa_sli_grad.restype = _c.c_int
+    lib.dsa_dense_li_lse.argtypes = [_c.POINTER(DsaDenseLseParams), _c.c_void_p]
+    lib.dsa_dense_li_lse.restype = _c.c_int
     lib.dsa_li_forward_static.argtypes = [_c.POINTER(DsaLiParams), _c.c_void_p]
     lib.dsa_li_forward_static.restype = _c.c_int
     lib.dsa_li_static_scratch_bytes.restype = _c.c_size_t

@@ -280,11 +280,14 @@ static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t s
 // ---------------------------------------------------------------------------------------------
 // Indexer KL-loss backward: validation and launch
 // ---------------------------------------------------------------------------------------------
+// Slots per query row: topk for the sparse operator, every key for the dense one.
+static int64_t sli_slots(const DsaSliGradParams* p) { return p->dense ? p->s2 : p->topk; }
+
 static int sli_grad_validate(const DsaSliGradParams* p) {
   if (p == nullptr) return DSA_ERR_NULL;
   if (p->struct_size != sizeof(DsaSliGradParams)) return DSA_ERR_STRUCT;
-  if (!p->query || !p->key || !p->query_index || !p->key_index || !p->weights || !p->sparse_indices ||
-      !p->softmax_max || !p->softmax_sum || !p->d_query_index || !p->d_key_index || !p->d_weights || !p->loss)
+  if (!p->query || !p->key || !p->query_index || !p->key_index || !p->weights ||
+      (!p->dense && !p->sparse_indices) || !p->softmax_max || !p->softmax_sum || !p->d_query_index || !p->d_key_index || !p->d_weights || !p->loss)
     return DSA_ERR_NULL;
   if (p->d_rope != 0 && (!p->query_rope || !p->key_rope)) return DSA_ERR_NULL;
   if (p->dtype != DSA_DTYPE_BF16 && p->dtype != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
@@ -293,8 +296,15 @@ static int sli_grad_validate(const DsaSliGradParams* p) {
   if (p->d != 128 && p->d != 256 && p->d != 512) return DSA_ERR_VALUE;
   if (p->d_idx != 128 && p->d_idx != 256 && p->d_idx != 512) return DSA_ERR_VALUE;
   if (p->d_rope != 0 && p->d_rope != 64) return DSA_ERR_VALUE;
-  if (p->batch < 1 || p->s1 < 0 || p->s2 < 1 || p->n1 < 1 || p->g < 1 || p->topk < 1) return DSA_ERR_VALUE;
-  if (p->topk > 8192) return DSA_ERR_TOO_LARGE;   // p and I of a row live in shared memory
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 1 || p->n1 < 1 || p->g < 1) return DSA_ERR_VALUE;
+  if (p->dense) {
+    if (p->n2 < 1 || p->n1 % p->n2 != 0) return DSA_ERR_VALUE;
+    if ((p->softmax_max_index == nullptr) != (p->softmax_sum_index == nullptr)) return DSA_ERR_NULL;
+  } else {
+    if (p->n2 != 1 && p->n2 != 0) return DSA_ERR_VALUE;
+    if (p->topk < 1) return DSA_ERR_VALUE;
+  }
+  if (sli_slots(p) > 8192) return DSA_ERR_TOO_LARGE;   // p and I of a row live in shared memory
   if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE) return DSA_ERR_UNSUPPORTED;
   return DSA_OK;
 }
@@ -309,19 +319,27 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   d.query = p->query; d.query_rope = p->d_rope ? p->query_rope : nullptr;
   d.key = p->key; d.key_rope = p->d_rope ? p->key_rope : nullptr;
   d.query_index = p->query_index; d.key_index = p->key_index; d.weights = p->weights;
-  d.sparse_indices = p->sparse_indices; d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
+  d.sparse_indices = p->dense ? nullptr : p->sparse_indices;
+  d.softmax_max = p->softmax_max; d.softmax_sum = p->softmax_sum;
   d.act_q = p->seq_q; d.act_k = p->seq_k;
+  const int32_t slots = (int32_t)sli_slots(p);
   d.d_query_index = p->d_query_index; d.d_weights = p->d_weights; d.d_key_index = p->d_key_index; d.loss = p->loss;
   d.di = reinterpret_cast<float*>(ws);
-  d.loss_parts = reinterpret_cast<float*>(ws + align256((size_t)rows * p->topk * 4));
-  d.dki_acc = reinterpret_cast<float*>((char*)d.loss_parts + align256((size_t)rows * 4));
-  d.batch = p->batch; d.s1 = p->s1; d.s2 = p->s2; d.n1 = p->n1; d.d = p->d; d.d_rope = p->d_rope;
-  d.g = p->g; d.d_idx = p->d_idx; d.topk = p->topk; d.dtype_w = p->dtype_w;
+  d.loss_parts = reinterpret_cast<float*>(ws + align256((size_t)rows * slots * 4));
+  float* stats = reinterpret_cast<float*>((char*)d.loss_parts + align256((size_t)rows * 4));
+  d.dki_acc = reinterpret_cast<float*>((char*)stats + align256((size_t)rows * 8));
+  d.stats_given = (p->dense && p->softmax_max_index) ? 1 : 0;
+  d.index_max = d.stats_given ? const_cast<float*>(p->softmax_max_index) : stats;
+  d.index_sum = d.stats_given ? const_cast<float*>(p->softmax_sum_index) : stats + rows;
+  d.lse_only = 0;
+  d.batch = p->batch; d.s1 = p->s1; d.s2 = p->s2; d.n1 = p->n1; d.n2 = p->dense ? p->n2 : 1;
+  d.d = p->d; d.d_rope = p->d_rope;
+  d.g = p->g; d.d_idx = p->d_idx; d.topk = slots; d.dtype_w = p->dtype_w;
   d.scale = p->scale;
   if (cudaMemsetAsync(d.dki_acc, 0, (size_t)key_elems * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
   if (rows > 0) {
     const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
-    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * p->topk * 4;
+    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * slots * 4;
     const size_t smem_b = (size_t)(kSliHeads + kSliKeys) * (p->d_idx + kSliPad) * sizeof(T);
     if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
@@ -341,13 +359,33 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   count_launch();
   return DSA_OK;
 }
+template <typename T>
+static int dense_lse_launch(const DsaDenseLseParams* p, cudaStream_t st) {
+  SliGradDev d = {};
+  d.query_index = p->query_index; d.key_index = p->key_index; d.weights = p->weights;
+  d.act_q = p->seq_q; d.act_k = p->seq_k;
+  d.index_max = p->softmax_max_index; d.index_sum = p->softmax_sum_index;
+  d.batch = p->batch; d.s1 = p->s1; d.s2 = p->s2; d.n1 = 1; d.n2 = 1; d.g = p->g; d.d_idx = p->d_idx;
+  d.topk = p->s2; d.dtype_w = p->dtype_w; d.lse_only = 1;
+  const int64_t rows = (int64_t)p->batch * p->s1;
+  if (rows == 0) return DSA_OK;
+  const int stride = p->d_idx + kSliPad;
+  const size_t smem = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * p->s2 * 4;
+  if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return DSA_ERR_CUDA;
+  sli_teacher_kernel<T><<<(unsigned)rows, kSliThreads, smem, st>>>(d, stride);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch();
+  return DSA_OK;
+}
+
 }  // namespace dsa
 
 using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 5; }
+int dsa_abi_version(void) { return 6; }
 
 unsigned long long dsa_kernel_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -449,13 +487,28 @@ int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_by
   return sfa_grad_launch<__half>(p, acc, cs);
 }
 
+int dsa_dense_li_lse(const DsaDenseLseParams* p, void* stream) {
+  if (p == nullptr) return DSA_ERR_NULL;
+  if (p->struct_size != sizeof(DsaDenseLseParams)) return DSA_ERR_STRUCT;
+  if (!p->query_index || !p->key_index || !p->weights || !p->softmax_max_index || !p->softmax_sum_index)
+    return DSA_ERR_NULL;
+  if (p->dtype != DSA_DTYPE_BF16 && p->dtype != DSA_DTYPE_FP16) return DSA_ERR_VALUE;
+  if (p->dtype_w < DSA_DTYPE_BF16 || p->dtype_w > DSA_DTYPE_FP32) return DSA_ERR_VALUE;
+  if (p->d_idx != 128 && p->d_idx != 256 && p->d_idx != 512) return DSA_ERR_VALUE;
+  if (p->batch < 1 || p->s1 < 0 || p->s2 < 1 || p->g < 1) return DSA_ERR_VALUE;
+  if (p->s2 > 8192) return DSA_ERR_TOO_LARGE;
+  if ((int64_t)p->batch * p->s1 > 0x7FFFFFFF) return DSA_ERR_TOO_LARGE;
+  if (p->dtype == DSA_DTYPE_BF16) return dense_lse_launch<__nv_bfloat16>(p, (cudaStream_t)stream);
+  return dense_lse_launch<__half>(p, (cudaStream_t)stream);
+}
+
 int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes) {
   int st = sli_grad_validate(p);
   if (st != DSA_OK) return st;
   if (!out_bytes) return DSA_ERR_NULL;
   const size_t rows = (size_t)p->batch * p->s1;
-  *out_bytes = kWorkspaceHeader + align256(rows * p->topk * 4) + align256(rows * 4) +
-               (size_t)p->batch * p->s2 * p->d_idx * 4;
+  *out_bytes = kWorkspaceHeader + align256(rows * (size_t)sli_slots(p) * 4) + align256(rows * 4) +
+               align256(rows * 8) + (size_t)p->batch * p->s2 * p->d_idx * 4;
   return DSA_OK;
 }
 

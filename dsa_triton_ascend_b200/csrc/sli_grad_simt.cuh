@@ -13,6 +13,11 @@
 // heads), recomputes the index scores it needs instead of reading a [rows, G, topK] ReLU cache,
 // accumulates dQI / dW in registers and adds dKI into an fp32 accumulator with 16-byte reductions; a
 // third converts the accumulator and sums the loss terms in a fixed order.
+//
+// The same kernels serve the dense operator (dense_loss_backward_triton.py:130-341: every causally
+// visible key 0..n-1 instead of selected ones, attention keys with n2 heads, the student distribution
+// normalised with index statistics given from outside) and, stopped after the index scores, the
+// dense softmax-LSE helper (:344-420).
 #pragma once
 
 #include "dsa_common.cuh"
@@ -28,9 +33,11 @@ struct SliGradDev {
   const void* query_index;  // [rows, g, d_idx]
   const void* key_index;    // [batch * s2, d_idx]
   const void* weights;      // [rows, g], dtype_w
-  const int32_t* sparse_indices;   // [rows, topk]
-  const float* softmax_max;        // [rows, n1]
+  const int32_t* sparse_indices;   // [rows, topk]; null: dense, slot j is key j
+  const float* softmax_max;        // [batch, n2, s1, n1 / n2]
   const float* softmax_sum;
+  float* index_max;                // [rows] dense: index statistics (read when stats_given, else written)
+  float* index_sum;
   const int32_t* act_q;     // [batch] or null
   const int32_t* act_k;
   void* d_query_index;      // [rows, g, d_idx]
@@ -40,7 +47,9 @@ struct SliGradDev {
   float* di;                // [rows, topk]  scratch
   float* loss_parts;        // [rows]        scratch
   float* dki_acc;           // [batch * s2, d_idx] scratch, zeroed by the caller
-  int32_t batch, s1, s2, n1, d, d_rope, g, d_idx, topk, dtype_w;
+  int32_t batch, s1, s2, n1, n2, d, d_rope, g, d_idx, topk, dtype_w;
+  int32_t stats_given;   // dense: index_max / index_sum come from the caller
+  int32_t lse_only;      // dense: stop after the index statistics
   float scale;
 };
 
@@ -56,7 +65,14 @@ __device__ __forceinline__ int32_t sli_row_slots(const SliGradDev& p, int32_t ro
   const int32_t ak = p.act_k ? p.act_k[b] : p.s2;
   *b_out = b;
   if (pos >= aq) return 0;
-  return min(min(p.topk, p.s2), max(ak - aq + pos + 1, 0));   // :72-74
+  const int32_t vis = max(ak - aq + pos + 1, 0);
+  if (p.sparse_indices == nullptr) return min(min(vis, ak), p.s2);   // dense: every visible key
+  return min(min(p.topk, p.s2), vis);   // :72-74
+}
+
+// Key position of slot j of a row: the clipped sparse index (:96), or j itself for the dense operator.
+__device__ __forceinline__ int32_t sli_slot_key(const SliGradDev& p, const int32_t* idx_row, int32_t j) {
+  return idx_row ? min(max(idx_row[j], 0), p.s2 - 1) : j;
 }
 
 __device__ __forceinline__ void store_weight(void* w, int32_t dtype_w, int64_t i, float v) {
@@ -94,13 +110,14 @@ __device__ __forceinline__ void sli_stage_heads(T* dst, int stride, const T* a, 
 }
 
 // Gathers the rows idx_s[0..32) (16-byte chunks) of one or two key tensors into shared memory.
+// Row rows_s[k] of a tensor with `nh` heads per position is row rows_s[k] * nh + head.
 template <typename T>
 __device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, int wa, const T* b, int wb,
-                                                const int64_t* rows_s) {
+                                                const int64_t* rows_s, int nh = 1, int head = 0) {
   const int ca = wa / 8, cb = wb / 8, ct = ca + cb;
   for (int i = threadIdx.x; i < kSliKeys * ct; i += kSliThreads) {
     const int k = i / ct, c = i - k * ct;
-    const int64_t r = rows_s[k];
+    const int64_t r = rows_s[k] < 0 ? -1 : rows_s[k] * nh + head;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r >= 0) v = c < ca ? reinterpret_cast<const uint4*>(a + r * wa)[c] : reinterpret_cast<const uint4*>(b + r * wb)[c - ca];
     *reinterpret_cast<uint4*>(&dst[k * stride + c * 8]) = v;
@@ -148,56 +165,70 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
   const int32_t row = blockIdx.x;
   int32_t b;
   const int32_t n = sli_row_slots(p, row, &b);
+  const bool dense = p.sparse_indices == nullptr;
   if (n == 0) {
-    if (tid == 0) p.loss_parts[row] = 0.f;
+    if (tid == 0) {
+      if (!p.lse_only) p.loss_parts[row] = 0.f;
+      if (dense && !p.stats_given) { p.index_max[row] = -INFINITY; p.index_sum[row] = 0.f; }
+    }
     return;
   }
-  const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.topk;
+  const int32_t pos = row - b * p.s1;
+  const int32_t* idx_row = dense ? nullptr : p.sparse_indices + (int64_t)row * p.topk;
   const T* q = (const T*)p.query + (int64_t)row * p.n1 * p.d;
   const T* qr = p.d_rope ? (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope : nullptr;
   const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
+  const int grp = p.n1 / p.n2;   // query heads per attention key head
 
-  for (int phase = 0; phase < 2; ++phase) {          // 0: attention distribution p, 1: index scores I
-    const int heads = phase == 0 ? p.n1 : p.g;
+  for (int phase = p.lse_only ? 1 : 0; phase < 2; ++phase) {   // 0: attention distribution p, 1: index scores I
     const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
+    const int kv_heads = phase == 0 ? p.n2 : 1;
+    const int per_kv = phase == 0 ? grp : p.g;
     for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
       __syncthreads();
       if (tid < kSliKeys) {
         const int32_t j = j0 + tid;
-        rows_s[tid] = j < n ? (int64_t)b * p.s2 + min(max(idx_row[j], 0), p.s2 - 1) : -1;   // :96
+        rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
       }
-      __syncthreads();
-      if (phase == 0) sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s);
-      else sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
       float acc = 0.f;
-      for (int h0 = 0; h0 < heads; h0 += kSliHeads) {
-        __syncthreads();
-        if (phase == 0) sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, heads);
-        else sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, heads);
-        if (tid < kSliHeads) {
-          const int h = h0 + tid;
-          if (phase == 0) {
-            max_s[tid] = h < heads ? p.softmax_max[(int64_t)row * p.n1 + h] : 0.f;
-            inv_s[tid] = h < heads ? 1.f / (p.softmax_sum[(int64_t)row * p.n1 + h] + kSliEps) : 0.f;
-          } else {
-            w_s[tid] = h < heads ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
+      for (int kv = 0; kv < kv_heads; ++kv) {
+        __syncthreads();   // rows_s written; the previous key head's dot products are done with ks
+        if (phase == 0)
+          sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
+        else
+          sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+        const int h_end = (kv + 1) * per_kv;
+        for (int h0 = kv * per_kv; h0 < h_end; h0 += kSliHeads) {
+          __syncthreads();
+          if (phase == 0) sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, h_end);
+          else sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, h_end);
+          if (tid < kSliHeads) {
+            const int h = h0 + tid;
+            if (phase == 0) {
+              // statistics are [batch, n2, s1, grp]
+              const int64_t si = (((int64_t)b * p.n2 + kv) * p.s1 + pos) * grp + (h - kv * grp);
+              max_s[tid] = h < h_end ? p.softmax_max[si] : 0.f;
+              inv_s[tid] = h < h_end ? 1.f / (p.softmax_sum[si] + kSliEps) : 0.f;
+            } else {
+              w_s[tid] = h < h_end ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
+            }
           }
-        }
-        __syncthreads();
-        float s0, s1;
-        sli_dots<T>(qs, ks, stride, w, &s0, &s1);
-        float part;
-        if (phase == 0) {
-          part = (h0 + warp < heads ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
-                 (h0 + warp + 8 < heads ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
-        } else {
-          part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
-        }
-        red_s[warp][lane] = part;
-        __syncthreads();
-        if (tid < kSliKeys) {
+          __syncthreads();
+          float s0, s1;
+          sli_dots<T>(qs, ks, stride, w, &s0, &s1);
+          float part;
+          if (phase == 0) {
+            part = (h0 + warp < h_end ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
+                   (h0 + warp + 8 < h_end ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
+          } else {
+            part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
+          }
+          red_s[warp][lane] = part;
+          __syncthreads();
+          if (tid < kSliKeys) {
 #pragma unroll
-          for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
+            for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
+          }
         }
       }
       if (tid < kSliKeys && j0 + tid < n) {
@@ -208,16 +239,30 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
   }
   __syncthreads();
 
-  // softmax of the index scores, dI, the row's KL term (:95-116)
-  float m = -INFINITY;
-  for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, i_s[k]);
-  m = sli_block_reduce(m, red8, true);
-  float se = 0.f;
-  for (int k = tid; k < n; k += kSliThreads) se += expf(i_s[k] - m);
-  se = sli_block_reduce(se, red8, false);
-  const float inv = 1.f / (se + kSliEps);
-  float kl = 0.f;
+  // student distribution: softmax of the index scores (:95-103), or, for the dense operator, the
+  // scores normalised with the index statistics (dense_loss_backward_triton.py:300-312)
+  float m, se;
+  if (dense && p.stats_given) {
+    m = p.index_max[row];
+    se = p.index_sum[row];
+  } else {
+    m = -INFINITY;
+    for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, i_s[k]);
+    m = sli_block_reduce(m, red8, true);
+    se = 0.f;
+    for (int k = tid; k < n; k += kSliThreads) se += expf(i_s[k] - m);
+    se = sli_block_reduce(se, red8, false);
+    if (dense && tid == 0) { p.index_max[row] = m; p.index_sum[row] = se; }
+  }
+  if (p.lse_only) return;
   float* di = p.di + (int64_t)row * p.topk;
+  if (dense && !(se > 0.f)) {           // the reference skips such rows: no gradient, no loss
+    for (int k = tid; k < n; k += kSliThreads) di[k] = 0.f;
+    if (tid == 0) p.loss_parts[row] = 0.f;
+    return;
+  }
+  const float inv = dense ? 1.f / fmaxf(se, kSliEps) : 1.f / (se + kSliEps);
+  float kl = 0.f;
   for (int k = tid; k < n; k += kSliThreads) {
     const float si = expf(i_s[k] - m) * inv, pk = p_s[k];
     di[k] = si - pk;
@@ -255,14 +300,14 @@ __global__ void __launch_bounds__(kSliThreads) sli_grad_kernel(SliGradDev p) {
     const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
     sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, p.g);
     if (tid < kSliHeads) w_s[tid] = h0 + tid < p.g ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h0 + tid) : 0.f;
-    const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.topk;
+    const int32_t* idx_row = p.sparse_indices ? p.sparse_indices + (int64_t)row * p.topk : nullptr;
     const float* di = p.di + (int64_t)row * p.topk;
     const int gq = p.d_idx / 4;
     for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
       __syncthreads();
       if (tid < kSliKeys) {
         const int32_t j = j0 + tid;
-        rows_s[tid] = j < n ? (int64_t)b * p.s2 + min(max(idx_row[j], 0), p.s2 - 1) : -1;
+        rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
         di_s[tid] = j < n ? di[j] : 0.f;
       }
       __syncthreads();

@@ -192,6 +192,14 @@ int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_by
  * dense causal attention forward.  Outputs: d_query_index, d_key_index (dtype of the index tensors),
  * d_weights (dtype of weights) and the fp32 loss (one element).  d_key_index is a scatter-add with
  * fp32 atomics: its last place can vary between runs.
+ *
+ * With dense = 1 the same entry point is the dense operator, replacing
+ * `_dense_loss_backward_with_index_core` / `_dense_loss_backward_core`
+ * (dense_loss_backward_triton.py:423-598) behind `dense_loss_backward_triton` (:708-770): every
+ * causally visible key takes part (sparse_indices is ignored and may be NULL, topk is ignored), the
+ * attention key may have n2 heads (key [batch, s2, n2, d], statistics [batch, n2, s1, n1 / n2]) and
+ * the student distribution is normalised with softmax_max_index / softmax_sum_index ([batch * s1]
+ * fp32, as dsa_dense_li_lse produces them); when those are NULL they are computed internally.
  */
 typedef struct DsaSliGradParams {
   uint32_t struct_size; /* sizeof(DsaSliGradParams) */
@@ -215,12 +223,38 @@ typedef struct DsaSliGradParams {
   int32_t dtype, dtype_w;
   int32_t batch, s1, s2, n1, d, d_rope, g, d_idx, topk;
   float scale;
+  int32_t dense;                  /* 0: sparse operator, 1: dense operator */
+  int32_t n2;                     /* attention key heads (1 for the sparse operator) */
+  const float* softmax_max_index; /* dense: [batch * s1] or NULL */
+  const float* softmax_sum_index;
 } DsaSliGradParams;
 
 /* Workspace: status header + fp32 scratch (dI [rows, topk], one loss term per row, the d_key_index
  * accumulator [batch * s2, d_idx]). */
 int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes);
 int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Dense lightning-indexer softmax statistics - replaces `_dense_index_stats_core`
+ * (dense_loss_backward_triton.py:344-420) behind `npu_dense_lightning_indexer_softmax_lse_triton`
+ * (:773-802): per query row the maximum and the sum of exponentials over the causally visible keys
+ * of I[k] = sum_g w[g] relu(query_index[g] . key_index[k]); -inf / 0 for rows that see no key.
+ * No workspace.
+ */
+typedef struct DsaDenseLseParams {
+  uint32_t struct_size; /* sizeof(DsaDenseLseParams) */
+  int32_t reserved;
+  const void* query_index; /* [batch, s1, g, d_idx] */
+  const void* key_index;   /* [batch, s2, 1, d_idx] */
+  const void* weights;     /* [batch, s1, g], dtype_w */
+  const int32_t* seq_q;    /* [batch] or NULL */
+  const int32_t* seq_k;
+  float* softmax_max_index; /* [batch * s1] */
+  float* softmax_sum_index;
+  int32_t dtype, dtype_w;
+  int32_t batch, s1, s2, g, d_idx;
+} DsaDenseLseParams;
+int dsa_dense_li_lse(const DsaDenseLseParams* p, void* stream);
 
 /*
  * dsa_li_forward_static - the indexer without a caller workspace and without any allocation.

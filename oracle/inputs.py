@@ -100,6 +100,17 @@ def sli_grad_inputs(seed, B, S1, S2, N1, D, G, Di, topk, pattern="causal_random"
                                     else np.arange(n))
     return q, k, qr, kr, qi, ki, w, si
 
+def dense_loss_inputs(seed, B, S1, S2, N1, N2, D, G, Di, Dr=64, dtype="fp16"):
+    """q, k, q_rope, k_rope, q_index, k_index, |w| in the order of the reference's dense-loss tests
+    (test_dense_loss_backward_triton.py:169-178); the attention key has N2 heads."""
+    rng = np.random.RandomState(seed)
+    draw = lambda *shape: round_io(rng.randn(*shape).astype(np.float32), dtype)   # noqa: E731
+    q, k = draw(B, S1, N1, D), draw(B, S2, N2, D)
+    qr, kr = draw(B, S1, N1, Dr), draw(B, S2, N2, Dr)
+    qi, ki = draw(B, S1, G, Di), draw(B, S2, 1, Di)
+    w = np.abs(draw(B, S1, G))
+    return q, k, qr, kr, qi, ki, w
+
 
 # The two CPU-sized configurations of the benchmark specification.
 def config1():

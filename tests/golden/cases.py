@@ -68,6 +68,14 @@ SLI_GRAD_CASES = {
     "sli_grad_k_gt_s2":  dict(seed=66, B=1, S1=8, S2=48, N1=32, D=256, G=16, Di=512, k=64, pattern="causal_continuous"),
 }
 
+# dense indexer LSE + KL-loss backward (test_dense_loss_backward_triton.py:20-58); N2 = key heads
+DENSE_LOSS_CASES = {
+    "dense_loss_core":    dict(seed=71, B=1, S1=2, S2=64, N1=32, N2=32, D=128, G=32, Di=128),
+    "dense_loss_tail":    dict(seed=72, B=1, S1=3, S2=96, N1=32, N2=32, D=256, G=64, Di=256),
+    "dense_loss_mqa":     dict(seed=73, B=1, S1=3, S2=128, N1=64, N2=1, D=512, G=128, Di=256),
+    "dense_loss_gqa":     dict(seed=74, B=2, S1=5, S2=80, N1=32, N2=8, D=128, G=32, Di=128),
+}
+
 
 def li_case_inputs(name):
     """Seeded inputs of one LI case: (q, k, w, act_q, act_k, spec)."""
@@ -116,6 +124,14 @@ def sli_grad_case_inputs(name):
     arrs = sli_grad_inputs(c["seed"], c["B"], c["S1"], c["S2"], c["N1"], c["D"], c["G"], c["Di"], c["k"],
                            c["pattern"])
     return arrs + (1.0 / np.sqrt(float(c["D"])), c)
+
+def dense_loss_case_inputs(name):
+    """Seeded inputs of one dense-loss case: (q, k, qr, kr, qi, ki, w, scale, spec)."""
+    import numpy as np
+    from oracle.inputs import dense_loss_inputs
+    c = DENSE_LOSS_CASES[name]
+    arrs = dense_loss_inputs(c["seed"], c["B"], c["S1"], c["S2"], c["N1"], c["N2"], c["D"], c["G"], c["Di"])
+    return arrs + (1.0 / np.sqrt(c["D"] + 64.0), c)
 
 
 def case_rows(c, act_q):

@@ -8,7 +8,11 @@ sparse_flash_attention_grad_numpy.sparse_flash_attention_grad_golden_bsnd from t
 runs them on the seeded inputs of tests/golden/cases.py and stores only the outputs (inputs
 are regenerated from the seeds; the backward cases take their forward state from the forward
 golden).  sli_grad_kl_loss_numpy.py (numpy_reference and _compute_sm_stats, both plain numpy) imports
-mindspore at module level only to set a context; an empty stand-in module satisfies that import.  For cases with `rows_every` only the listed rows are kept.
+mindspore at module level only to set a context; an empty stand-in module satisfies that import.
+The dense-loss baselines live in the reference's test module (test_dense_loss_backward_triton.py:
+_dense_indexer_lse_numpy, _compute_softmax_stats, _dense_loss_backward_numpy); they take and return
+mindspore tensors only to call .asnumpy() on them, so the stand-in's Tensor is a thin holder of a
+numpy array.  For cases with `rows_every` only the listed rows are kept.
 The stored arrays pin the numpy restatement under oracle/ (tests/test_oracle_golden.py).
 """
 import os
@@ -19,8 +23,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES, case_rows,  # noqa: E402
-                                li_case_inputs, sfa_case_inputs, sfa_grad_case_inputs, sli_grad_case_inputs)
+from tests.golden.cases import (DENSE_LOSS_CASES, LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES,  # noqa: E402
+                                case_rows, dense_loss_case_inputs, li_case_inputs, sfa_case_inputs,
+                                sfa_grad_case_inputs, sli_grad_case_inputs)
 
 
 def main(ref_dir):
@@ -88,6 +93,17 @@ def main(ref_dir):
         stub = types.ModuleType("mindspore")
         stub.GRAPH_MODE = 0
         stub.set_context = lambda **kw: None
+        stub.float16, stub.bfloat16, stub.float32 = "float16", "bfloat16", "float32"
+
+        class _Holder:
+            def __init__(self, a, dtype=None):
+                self.a = np.asarray(a)
+                self.shape = self.a.shape
+
+            def asnumpy(self):
+                return self.a
+
+        stub.Tensor = _Holder
         sys.modules["mindspore"] = stub
     import sli_grad_kl_loss_numpy as ref_sli
     for name in SLI_GRAD_CASES:
@@ -97,6 +113,18 @@ def main(ref_dir):
         np.savez_compressed(os.path.join(HERE, name + ".npz"), sm_max=sm_max, sm_sum=sm_sum,
                             **{n: res[n].astype(np.float32) for n in ("dQueryIndex", "dKeyIndex", "dW", "loss")})
         print(name, float(res["loss"][0]), res["dKeyIndex"].shape)
+    import test_dense_loss_backward_triton as ref_dense
+    T = sys.modules["mindspore"].Tensor
+    for name in DENSE_LOSS_CASES:
+        q, k, qr, kr, qi, ki, w, scale, c = dense_loss_case_inputs(name)
+        mx_i, sm_i = ref_dense._dense_indexer_lse_numpy(T(qi), T(ki), T(w))
+        mx, sm = ref_dense._compute_softmax_stats(T(q), T(k), T(qr), T(kr), scale)
+        res = ref_dense._dense_loss_backward_numpy(T(q), T(k), T(qr), T(kr), T(qi), T(ki), T(w), mx, sm, mx_i, sm_i, scale)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), sm_max=mx.asnumpy(), sm_sum=sm.asnumpy(),
+                            max_index=mx_i.asnumpy(), sum_index=sm_i.asnumpy(),
+                            **{n: r.asnumpy().astype(np.float32) for n, r in
+                               zip(("dQueryIndex", "dKeyIndex", "dW", "loss"), res)})
+        print(name, float(res[3].asnumpy()[0]))
 
 
 def _row_mask(shape, sel):

@@ -28,18 +28,21 @@ def test_library_exports_every_declared_symbol():
 
 def test_ctypes_structs_match_the_c_header():
     from dsa_triton_ascend_b200 import _cabi
-    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsa_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",' \
           'sizeof(DsaLiParams),sizeof(DsaSfaParams),offsetof(DsaLiParams,phases),' \
           'offsetof(DsaSfaParams,scale),offsetof(DsaLiParams,out_indices),sizeof(DsaSfaGradParams),' \
           'offsetof(DsaSfaGradParams,d_value),offsetof(DsaSfaGradParams,key_rows),sizeof(DsaSliGradParams),' \
-          'offsetof(DsaSliGradParams,scale));return 0;}\n'
+          'offsetof(DsaSliGradParams,scale),sizeof(DsaDenseLseParams),' \
+          'offsetof(DsaSliGradParams,softmax_sum_index));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "t.c")
         open(c, "w").write(src)
         exe = os.path.join(d, "t")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
-        li, sfa, off_ph, off_sc, off_oi, grad, off_dv, off_kr, sli, off_ss = map(
+        li, sfa, off_ph, off_sc, off_oi, grad, off_dv, off_kr, sli, off_ss, lse, off_si = map(
             int, subprocess.check_output([exe]).split())
+    assert lse == ctypes.sizeof(_cabi.DsaDenseLseParams)
+    assert off_si == _cabi.DsaSliGradParams.softmax_sum_index.offset
     assert sli == ctypes.sizeof(_cabi.DsaSliGradParams) and off_ss == _cabi.DsaSliGradParams.scale.offset
     assert grad == ctypes.sizeof(_cabi.DsaSfaGradParams)
     assert off_dv == _cabi.DsaSfaGradParams.d_value.offset and off_kr == _cabi.DsaSfaGradParams.key_rows.offset
@@ -197,7 +200,7 @@ def test_sli_grad_guards_and_abi_validation():
         setattr(g, f, 256)
     g.batch, g.s1, g.s2, g.n1, g.d, g.d_rope, g.g, g.d_idx, g.topk = 1, 4, 64, 32, 128, 0, 8, 128, 16
     assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
-    assert n.value == 256 + 256 + 256 + 64 * 128 * 4
+    assert n.value == 256 + 256 + 256 + 256 + 64 * 128 * 4
     g.d_rope = 64                                   # rope width given but no rope tensors
     assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -1
     g.d_rope, g.topk = 0, 10000
@@ -235,3 +238,44 @@ def test_product_package_never_imports_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read().replace("numpy golden", ""), f
+
+
+def test_dense_loss_guards_raise_like_the_reference():
+    """dense_loss_backward_triton.py:599-705: layout / sparse_mode / window guards, shape and dtype
+    checks, statistics given together; and the LSE entry point's ABI validation."""
+    from dsa_triton_ascend_b200 import _cabi, dense_lightning_indexer_softmax_lse_triton as lse
+    from dsa_triton_ascend_b200 import dense_loss_backward_triton as fn
+    hf = torch.float16
+    q, k = torch.zeros(1, 2, 32, 128, dtype=hf), torch.zeros(1, 64, 32, 128, dtype=hf)
+    qi, ki, w = torch.zeros(1, 2, 32, 128, dtype=hf), torch.zeros(1, 64, 1, 128, dtype=hf), torch.zeros(1, 2, 32, dtype=hf)
+    mx, sm = torch.zeros(1, 32, 2, 1), torch.ones(1, 32, 2, 1)
+    for kw in (dict(layout="TND"), dict(sparse_mode=0), dict(pre_tokens=0), dict(next_tokens=0)):
+        with pytest.raises(ValueError):
+            fn(q, k, qi, ki, w, mx, sm, **kw)
+        with pytest.raises(ValueError):
+            lse(qi, ki, w, **kw)
+    with pytest.raises(ValueError):
+        fn(q, k[:, :, :5], qi, ki, w, mx, sm)                       # N1 not divisible by N2
+    with pytest.raises(ValueError):
+        fn(q, k, qi, ki, w, mx[:, :1], sm)                          # statistics of the wrong shape
+    with pytest.raises(ValueError):
+        fn(q, k, qi, ki, w, mx, sm, softmax_max_index=torch.zeros(1, 1, 2))      # only one of the pair
+    with pytest.raises(TypeError):
+        fn(q, k, qi, ki, w, mx.half(), sm)
+    with pytest.raises(TypeError):
+        fn(q, k, qi.bfloat16(), ki.bfloat16(), w, mx, sm)
+    with pytest.raises(ValueError):
+        fn(q, k, qi, ki, w, mx, sm, query_rope=torch.zeros(1, 2, 32, 64, dtype=hf))
+    with pytest.raises(ValueError):
+        lse(qi[..., :96], ki[..., :96], w)
+    with pytest.raises(RuntimeError):   # CPU tensors: there is no CPU path
+        lse(qi, ki, w)
+    p = _cabi.DsaDenseLseParams()
+    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -2
+    p.struct_size = ctypes.sizeof(p)
+    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -1
+    p.query_index = p.key_index = p.weights = p.softmax_max_index = p.softmax_sum_index = 256
+    p.batch, p.s1, p.s2, p.g, p.d_idx = 1, 2, 100000, 32, 128
+    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -8
+    p.s2, p.d_idx = 64, 100
+    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -3

@@ -12,10 +12,11 @@ import os
 import numpy as np
 import pytest
 
-from oracle import (lightning_indexer_oracle, sli_grad_kl_loss_oracle, sparse_flash_attention_grad_oracle,
-                    sparse_flash_attention_oracle)
-from tests.golden.cases import (LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES, li_case_inputs,
-                                sfa_case_inputs, sfa_grad_case_inputs, sli_grad_case_inputs)
+from oracle import (dense_indexer_lse_oracle, dense_loss_backward_oracle, lightning_indexer_oracle,
+                    sli_grad_kl_loss_oracle, sparse_flash_attention_grad_oracle, sparse_flash_attention_oracle)
+from tests.golden.cases import (DENSE_LOSS_CASES, LI_CASES, SFA_CASES, SFA_GRAD_CASES, SLI_GRAD_CASES,
+                                dense_loss_case_inputs, li_case_inputs, sfa_case_inputs, sfa_grad_case_inputs,
+                                sli_grad_case_inputs)
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -104,6 +105,28 @@ def test_sli_grad_oracle_matches_reference_golden(name):
     m, s_ = softmax_stats(q, k, qr, kr, scale)
     np.testing.assert_allclose(m, g["sm_max"], rtol=2e-3, atol=2e-3)
     np.testing.assert_allclose(np.log(s_), np.log(g["sm_sum"]), rtol=0, atol=2e-2)
+
+@pytest.mark.parametrize("name", sorted(DENSE_LOSS_CASES))
+def test_dense_loss_oracle_matches_reference_baselines(name):
+    """Fixtures: outputs of the numpy baselines in the reference's own test module
+    (_dense_indexer_lse_numpy, _compute_softmax_stats, _dense_loss_backward_numpy).  The restatement
+    batches the heads of a row into matrix products: agreement to fp32 summation noise, which the
+    exponential of index scores in the hundreds amplifies to a few 1e-4 of a tensor's magnitude."""
+    from oracle.dense_loss_oracle import dense_softmax_stats
+    q, k, qr, kr, qi, ki, w, scale, c = dense_loss_case_inputs(name)
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    mx_i, sm_i = dense_indexer_lse_oracle(qi, ki, w)
+    np.testing.assert_allclose(mx_i, g["max_index"], rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(sm_i, g["sum_index"], rtol=1e-4)
+    mx, sm = dense_softmax_stats(q, k, qr, kr, scale)
+    np.testing.assert_allclose(mx, g["sm_max"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(sm, g["sm_sum"], rtol=1e-4)
+    got = dense_loss_backward_oracle(q, k, qr, kr, qi, ki, w, g["sm_max"], g["sm_sum"], g["max_index"],
+                                     g["sum_index"], scale)
+    for n in ("dQueryIndex", "dKeyIndex", "dW", "loss"):
+        a, b = got[n], g[n]
+        assert a.shape == b.shape, n
+        assert np.abs(a - b).max() <= 3e-4 * max(np.abs(b).max(), 1e-3), f"{n}: {np.abs(a - b).max()}"
 
 
 def test_li_oracle_layout_adapters_roundtrip():
