@@ -154,6 +154,76 @@ def pct(xs):
             "p80": float(np.percentile(xs, 80))}
 
 
+def training_side(torch, flush, iters=3):
+    """The three backward operators of the path at the shapes the reference's perf scripts time
+    (perf_sfa_grad_triton.py:23, perf_sli_grad_kl_loss_triton.py:97, perf_dense_loss_backward_triton.py:18),
+    seeded normal inputs x 0.3, causal random indices.  CUDA-core kernels: reported beside the
+    headline numbers, median of `iters` calls, algorithmic flops = 2 x multiply-adds of the
+    contractions over the valid (row, key) pairs."""
+    from dsa_triton_ascend_b200 import (dense_lightning_indexer_softmax_lse_triton, dense_loss_backward_triton,
+                                        sparse_flash_attention_grad_triton, sparse_flash_attention_triton,
+                                        sparse_lightning_indexer_grad_kl_loss_triton)
+    g = torch.Generator(device="cuda").manual_seed(77)
+    bf = torch.bfloat16
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g, device="cuda") * 0.3).to(bf)
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(iters):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts))
+
+    out = {}
+    # attention backward: B, S1, S2, N1, top-k = 1, 512, 4096, 64, 2048 (D 512 + 64)
+    S1, S2, N1, K, D, Dr = 512, 4096, 64, 2048, 512, 64
+    q, k, qr, kr, do = rnd(1, S1, N1, D), rnd(1, S2, 1, D), rnd(1, S1, N1, Dr), rnd(1, S2, 1, Dr), rnd(1, S1, N1, D)
+    idx = torch.full((S1, K), -1, dtype=torch.int32, device="cuda")
+    vis = S2 - S1 + torch.arange(S1, device="cuda") + 1
+    idx[:] = torch.arange(K, device="cuda", dtype=torch.int32)[None, :]      # the first K visible keys of a row
+    idx = idx.masked_fill(torch.arange(K, device="cuda")[None, :] >= vis[:, None], -1).view(1, S1, 1, K)
+    pairs = int((idx >= 0).sum())
+    sc = 1.0 / float(np.sqrt(D + Dr))
+    o, mx, sm = sparse_flash_attention_triton(q, k, k, idx, scale_value=sc, query_rope=qr, key_rope=kr, sparse_mode=3,
+                                              return_softmax_lse=True)
+    ms = timed(lambda: sparse_flash_attention_grad_triton(q, k, k, idx, do, o, mx, sm, scale_value=sc, query_rope=qr,
+                                                          key_rope=kr, sparse_mode=3))
+    fl = pairs * N1 * 2 * ((D + Dr) * 3 + D * 2)
+    out["sfa_grad"] = {"shape": "B1 S1 512 S2 4096 N1 64 k 2048 D 512+64", "ms": ms, "tflops": fl / ms / 1e9}
+    # sparse indexer KL-loss backward: 1, 512, 4096, 64, 512, 64, 128, 2048
+    G, Di = 64, 128
+    qi, ki, w = rnd(1, S1, G, Di), rnd(1, S2, 1, Di), rnd(1, S1, G).abs()
+    idx_c = idx.clamp_min(0)
+    ms = timed(lambda: sparse_lightning_indexer_grad_kl_loss_triton(q, k, qi, ki, w, idx_c, mx, sm, query_rope=qr,
+                                                                    key_rope=kr, scale_value=sc))
+    fl = pairs * 2 * (N1 * (D + Dr) + G * Di * 4)
+    out["sli_grad_kl_loss"] = {"shape": "B1 S1 512 S2 4096 N1 64 D 512+64 G 64 Di 128 k 2048", "ms": ms,
+                               "tflops": fl / ms / 1e9}
+    # dense indexer loss backward: 1, 512, 4096, 64, 64, 128, 64, 128 (MHA keys)
+    N2, D2 = 64, 128
+    q2, k2, qr2, kr2 = rnd(1, S1, N1, D2), rnd(1, S2, N2, D2), rnd(1, S1, N1, Dr), rnd(1, S2, N2, Dr)
+    mx2 = torch.zeros(1, N2, S1, 1, device="cuda")
+    sm2 = torch.full((1, N2, S1, 1), float(S2), device="cuda")
+    lse = dense_lightning_indexer_softmax_lse_triton(qi, ki, w)
+    ms_lse = timed(lambda: dense_lightning_indexer_softmax_lse_triton(qi, ki, w))
+    ms = timed(lambda: dense_loss_backward_triton(q2, k2, qi, ki, w, mx2, sm2, lse[0], lse[1], 1.0 / float(np.sqrt(D2 + Dr)),
+                                                  query_rope=qr2, key_rope=kr2))
+    dpairs = int(vis.sum())
+    fl = dpairs * 2 * (N1 * (D2 + Dr) + G * Di * 4)
+    out["dense_loss_backward"] = {"shape": "B1 S1 512 S2 4096 N1 64 N2 64 D 128+64 G 64 Di 128", "ms": ms,
+                                  "tflops": fl / ms / 1e9, "softmax_lse_ms": ms_lse}
+    return out
+
+
 def decode_c5(torch, rank, world, flush, iters=5):
     """Configuration 5 (decode): lightning_indexer then sparse_flash_attention over paged caches,
     B=64 sequences dealt out over the ranks by cached length (sharding.sequence_shards), S1=2, KV
@@ -549,6 +619,8 @@ def run_gpu(args):
                               "unit": "GB/s", "frac": dec["li_index_k_GBps"] / pk["hbm_gbs"],
                               "note": "this rank's index-K cache bytes / indexer time (score + top-k)"}
         line["decode_c5"] = dec
+    if rank == 0 and args.scale == 1 and not args.quick and not args.no_training:
+        line["training_side"] = training_side(torch, flush)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -731,6 +803,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the configuration-5 (paged decode) side measurement")
+    ap.add_argument("--no-training", action="store_true", help="skip the backward operators' side measurement")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.quick:

@@ -45,10 +45,10 @@ __device__ __forceinline__ int32_t sfa_slot_token(const SfaDev& p, const RowInfo
   return sfa_slot_token(p.seq, p.sparse_block_size, ri, idx_row, j);
 }
 
-// grid = (rows, ceil(n1 / 16)); block = 256 threads.
+// One query row, 16 heads starting at h0, by one block of 256 threads.
 // dynamic smem: (16 + 32) * (d + d_rope + pad) elements of T.
 template <typename T>
-__global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p) {
+__device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, int32_t h0) {
   extern __shared__ __align__(16) unsigned char sfa_smem[];
   const int32_t dq = p.d + p.d_rope;
   const int32_t stride = dq + kSfaSimtPad;
@@ -62,8 +62,6 @@ __global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p)
   __shared__ int64_t krow_s[kSfaSimtKeys];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int32_t row = blockIdx.x;
-  const int32_t h0 = blockIdx.y * kSfaSimtHeads;
   const RowInfo ri = row_info(p.seq, row);
   const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
 
@@ -245,6 +243,25 @@ __global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p)
       p.softmax_max[(int64_t)row * p.n1 + h0 + tid] = lt > 0.f ? m_s[tid] : 0.f;
       p.softmax_sum[(int64_t)row * p.n1 + h0 + tid] = lt > 0.f ? lt : 0.f;
     }
+  }
+}
+
+// grid = (rows, ceil(n1 / 16)); block = 256 threads.
+template <typename T>
+__global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p) {
+  sfa_fwd_simt_row<T>(p, (int32_t)blockIdx.x, (int32_t)blockIdx.y * kSfaSimtHeads);
+}
+
+// Recomputes the rows marked in `redo` (rows whose scores outgrew the tensor-core kernel's fixed
+// reference maximum; normally none).  Any grid; blocks walk over (row, head chunk) pairs.
+template <typename T>
+__global__ void __launch_bounds__(kSfaSimtThreads) sfa_redo_kernel(SfaDev p, const int32_t* __restrict__ redo) {
+  const int32_t chunks = (p.n1 + kSfaSimtHeads - 1) / kSfaSimtHeads;
+  for (int64_t i = blockIdx.x; i < (int64_t)p.rows * chunks; i += gridDim.x) {
+    const int32_t row = (int32_t)(i / chunks);
+    if (redo[row] == 0) continue;
+    __syncthreads();   // the previous row's shared state is no longer read
+    sfa_fwd_simt_row<T>(p, row, (int32_t)(i - (int64_t)row * chunks) * kSfaSimtHeads);
   }
 }
 

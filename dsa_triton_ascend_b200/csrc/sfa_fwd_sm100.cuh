@@ -32,11 +32,14 @@
 // columns j*256 + 128*(L>>6) .. +127 of MMA j.
 //
 // Softmax.  Two groups of four warps take alternate tiles (group g: S buffer g, P buffer g), so one
-// tile's exponentials overlap the other's tensor-memory reads, barrier waits and P stores.  The two
-// threads of a head inside a group (the two halves of N) exchange their tile maxima through shared
-// memory.  The reference maximum that the probabilities are scaled by is only moved when a tile
-// exceeds it by more than 2^8 (O is rescaled then, which is rare); it is handed from tile to tile,
-// i.e. from group to group, through shared memory together with the running true maximum.
+// tile's exponentials overlap the other's tensor-memory reads, barrier waits and P stores.  The
+// probabilities of a row are scaled by ONE reference maximum, that of the row's first tile (its two
+// halves exchanged through shared memory once per token): later tiles neither exchange anything
+// nor wait for the tile before them, and O is never rescaled.  P may then exceed 1; a row whose
+// later scores exceed the reference by more than a guard (2^60 for bf16, 2^12 for fp16: P and the
+// fp32 sums stay finite) is marked and recomputed afterwards by the portable kernel
+// (sfa_redo_kernel), which is exact for any input.  The true maximum and the row sum, which the
+// softmax statistics need, are kept per thread and combined at the end of the token.
 //
 // Tensor memory per CTA: O 0..255 | S partials (2 buffers x 3 issuers x 32 columns) 256..447.
 // Shared memory per CTA: Q_c 72 KB (A operand, loaded per token by TMA) | 2 x 36 KB K slots |
@@ -49,6 +52,7 @@
 // barriers instead.  All waits are bounded; a wait that gives up sets the status word.
 #pragma once
 
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 
@@ -84,8 +88,8 @@ constexpr uint32_t kSfaOffQ = 0;
 constexpr uint32_t kSfaOffK = kSfaOffQ + kSfaQBytes;
 constexpr uint32_t kSfaOffV = kSfaOffK + 2 * kSfaKSlot;
 constexpr uint32_t kSfaOffP = kSfaOffV + 2 * kSfaVSlot;
-constexpr uint32_t kSfaOffX = kSfaOffP + 2 * kSfaPBuf;       // float xm[2][128] | float2 mref[2][64] | float fin[2][64]
-constexpr uint32_t kSfaOffBar = kSfaOffX + 1024 + 1024 + 512;
+constexpr uint32_t kSfaOffX = kSfaOffP + 2 * kSfaPBuf;       // float xm[2][128] | float mref[64] (+ pad) | float2 fin[2][64]
+constexpr uint32_t kSfaOffBar = kSfaOffX + 1024 + 512 + 1024;
 constexpr uint32_t kSfaSmemBytes = kSfaOffBar + 512;
 static_assert(kSfaOffK % 1024 == 0 && kSfaOffV % 1024 == 0 && kSfaOffP % 1024 == 0, "operand alignment");
 static_assert(kSfaSmemBytes <= 232448, "shared memory");
@@ -103,7 +107,10 @@ static_assert((kSfaRegsHigh - kSfaLaunchRegs) * (kSfaThreads / 32 - kSfaSoftWarp
 static_assert(kSfaLaunchRegs * kSfaThreads <= 65536, "register file");
 
 constexpr uint32_t kTmO = 0, kTmS = 256;
-constexpr float kSfaRescaleTau = 8.f;  // log2 units: the running reference only moves when exceeded by this
+// The reference maximum of a row is fixed by its first tile; a later score may exceed it by this many
+// log2 units before the row is handed to the portable kernel (P must stay finite in the io dtype and
+// the fp32 sums of up to 8192 of them far from overflow).
+constexpr float kSfaGuardBf16 = 60.f, kSfaGuardFp16 = 12.f;
 
 struct SfaSm100Args {
   SfaDev p;
@@ -121,6 +128,7 @@ struct SfaSm100Args {
   float* part_o;            // [items, 128, 512] fp32 (split > 1)
   float* part_m;            // [items, 128] maximum of the scaled scores of the part (natural log units)
   float* part_l;            // [items, 128] sum of exp(score - maximum); 0 marks an empty part
+  int32_t* redo;            // [rows] set when a row's scores outgrew the guard: sfa_redo_kernel recomputes it
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -144,10 +152,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
 // KV rows), which the gather loads as zeros.
 __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __restrict__ nvalid,
                                                           int32_t* __restrict__ key_list, int32_t split,
-                                                          int32_t part_keys, int32_t oob_row) {
+                                                          int32_t part_keys, int32_t oob_row,
+                                                          int32_t* __restrict__ redo) {
   const int lane = threadIdx.x & 31;
   const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
+  if (lane == 0) redo[row] = 0;
   const RowInfo ri = row_info(p.seq, row);
   const int32_t slots = p.sparse_count * p.sparse_block_size;
   const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.sparse_count;
@@ -202,8 +212,8 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   unsigned char* v_s = sfa_sm + kSfaOffV;
   unsigned char* p_s = sfa_sm + kSfaOffP;
   float* xm = reinterpret_cast<float*>(sfa_sm + kSfaOffX);     // [2 groups][128] exchange between the halves of a head
-  float2* mref = reinterpret_cast<float2*>(xm + 256);           // [2 groups][64] (reference, true maximum) after the group's latest tile
-  float* fin = reinterpret_cast<float*>(mref + 128);            // [2 groups][64] row sums of a group at the end of a token
+  float* mref = xm + 256;                                       // [64] the token's reference maximum per head (from its first tile)
+  float2* fin = reinterpret_cast<float2*>(xm + 256 + 128);      // [2 groups][64] (row sum, true maximum) of a group at the end of a token
   uint64_t* bars = reinterpret_cast<uint64_t*>(sfa_sm + kSfaOffBar);
   // K barriers are indexed [slot * 3 + issuer]: every issuer's three feature blocks are handed over
   // and released on their own.
@@ -215,17 +225,17 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
   uint64_t* v_ready = bars + 22;   // [2] even CTA only: the odd CTA's V slot is complete
   uint64_t* s_full = bars + 24;    // [2] all three partial products done -> softmax group   (commit x 3, both CTAs)
   uint64_t* s_empty = bars + 26;   // [2] even CTA only: the group's warps of both CTAs hold S in registers
-  uint64_t* p_full = bars + 28;    // [2] even CTA only: P stored (O rescaled) in both CTAs
+  uint64_t* p_full = bars + 28;    // [2] even CTA only: P stored in both CTAs
   uint64_t* p_empty = bars + 30;   // [2] PV done -> softmax                                 (commit, both CTAs)
   uint64_t* q_full = bars + 32;    // this CTA's Q has landed (tx bytes)
   uint64_t* q_ready = bars + 33;   // even CTA only: the odd CTA's Q has landed
   uint64_t* q_empty = bars + 34;   // all QK issuers are through with the token              (commit x 3, both CTAs)
   uint64_t* o_free = bars + 35;    // even CTA only: epilogue warps of both CTAs have read O
-  // The two halves of a head sit in warps q and q + 2 of a group ("pair" q & 1): the per-tile
-  // exchange and the hand-over of the reference maximum only involve that pair.
+  // The two halves of a head sit in warps q and q + 2 of a group ("pair" q & 1): exchanges between
+  // them (first tile of a token, end of a token) only involve that pair.
   uint64_t* x_bar = bars + 36;     // [group * 2 + pair] xm written (2 warps)
   uint64_t* xr_bar = bars + 40;    // [group * 2 + pair] xm read, it may be written again (2 warps)
-  uint64_t* m_bar = bars + 44;     // [group * 2 + pair] mref written for the group's latest tile (2 warps)
+  uint64_t* m_bar = bars + 44;     // [pair] mref written for the token (the 2 warps of the pair in the group of its first tile)
   uint64_t* e_bar = bars + 48;     // both groups: fin written
   uint64_t* er_bar = bars + 49;    // both groups: fin read
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 50);
@@ -247,8 +257,9 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       ptx::mbar_init(&p_full[i], 8); ptx::mbar_init(&p_empty[i], 1);
     }
     for (int i = 0; i < 4; ++i) {
-      ptx::mbar_init(&x_bar[i], 2); ptx::mbar_init(&xr_bar[i], 2); ptx::mbar_init(&m_bar[i], 2);
+      ptx::mbar_init(&x_bar[i], 2); ptx::mbar_init(&xr_bar[i], 2);
     }
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(&m_bar[i], 2);
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_ready, 1);
     ptx::mbar_init(q_empty, kSfaQkLanes);
@@ -308,13 +319,19 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         }
         return TilePos{a.items, 0, 0, 0, 0};
       };
+      // (the four keys of a load are consecutive entries of the list: one 16-byte load when the
+      // row's list starts on a 16-byte boundary, except in a row's last tile, where keys past the
+      // end re-read the tile's first key and are masked by the softmax)
       auto load_rows = [&](const TilePos& tp, int32_t* r) {
-        const int32_t* list = a.key_list + tp.off;
+        if (!active || tp.item >= a.items) { r[0] = r[1] = r[2] = r[3] = 0; return; }
+        const int32_t* list = a.key_list + tp.off + tp.t * kSfaBK;
+        if ((tp.t + 1) * kSfaBK <= tp.nvalid && (tp.off & 3) == 0) {
+          const int4 v = *reinterpret_cast<const int4*>(list + key0);
+          r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+        } else {
+          const int32_t left = tp.nvalid - tp.t * kSfaBK;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int32_t k = tp.t * kSfaBK + key0 + i;
-          // keys past the end of the row re-read the tile's first key (masked by the softmax)
-          r[i] = (active && tp.item < a.items) ? list[k < tp.nvalid ? k : tp.t * kSfaBK] : 0;
+          for (int i = 0; i < 4; ++i) r[i] = list[key0 + i < left ? key0 + i : 0];
         }
       };
       uint32_t n_tile = 0;
@@ -596,7 +613,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
       const uint32_t o_free_lead = ptx::map_to_rank(o_free, 0);
       float* xmg = xm + g * 128;
       const int gp = g * 2 + (quarter & 1);         // this warp's pair
-      const int gp_other = (g ^ 1) * 2 + (quarter & 1);
+      const float guard = a.is_bf16 ? kSfaGuardBf16 : kSfaGuardFp16;
       uint32_t n_tile = 0, n_tok = 0, n_x = 0;
       bool ok = true;
       SFA_PROF_DECL;
@@ -651,8 +668,13 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           }
           continue;
         }
-        // this thread's share of the row sum, relative to the reference m_cur of its latest tile
-        float m_cur = -INFINITY, l = 0.f, l_grp = 0.f;
+        // This thread's share of the row sum, relative to the token's reference maximum m_ref = the
+        // maximum of the row's FIRST tile.  Later tiles use it as it is: nothing is exchanged per
+        // tile and no tile waits for the one before it; O is never rescaled.  P = 2^(s - m_ref) may
+        // exceed 1, which the io dtype and the fp32 sums hold up to the guard; a row that outgrows it
+        // is recomputed by the portable kernel afterwards (sfa_redo_kernel).
+        float m_ref = 0.f, mt = -INFINITY, l = 0.f, l_grp = 0.f;
+        bool have_ref = false, outgrown = false;
         for (int32_t t = 0; t < ntiles && ok; ++t, ++n_tile) {
           if ((int)(n_tile & 1u) != g) continue;
           const uint32_t use = n_tile >> 1;
@@ -693,39 +715,36 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
             mx4[0] = fmaxf(mx4[0], sc[k]); mx4[1] = fmaxf(mx4[1], sc[k + 1]);
             mx4[2] = fmaxf(mx4[2], sc[k + 2]); mx4[3] = fmaxf(mx4[3], sc[k + 3]);
           }
-          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          mt = fmaxf(mt, mx);
           SFA_PROF(2);
-          ok = exchange(mx, mx_other);
-          if (!ok) break;
-          mx = fmaxf(mx, mx_other);       // the tile's maximum for this head (the first half always has a valid key)
-          // ---- the reference maximum comes from the previous tile, i.e. from the other group
-          float m_new = mx, mt_new = mx, alpha = 1.f;
-          bool rescale = false;
-          if (t > 0) {
-            const uint32_t prev = n_tile - 1;
-            ok = ptx::mbar_spin_warp(&m_bar[gp_other], (prev >> 1) & 1, abort_flag);
+          if (t == 0) {
+            // the row's first tile fixes the reference: its maximum over both halves (the first half
+            // always has a valid key), published for the other group
+            float mx_other;
+            ok = exchange(mx, mx_other);
             if (!ok) break;
-            const float2 mp = mref[(g ^ 1) * 64 + hl];
-            mt_new = fmaxf(mp.y, mx);
-            if (mx > mp.x + kSfaRescaleTau) {
-              alpha = ex2(mp.x - mx);     // O holds sums relative to the old reference
-              rescale = true;
-            } else {
-              m_new = mp.x;
-            }
+            m_ref = fmaxf(mx, mx_other);
+            // (everybody has read the previous token's entry: they arrive on er_bar after reading it)
+            ok = n_tok == 0 || wait_w(er_bar, (n_tok - 1) & 1);
+            if (!ok) break;
+            if (half == 0) mref[hl] = m_ref;
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&m_bar[quarter & 1]);
+            have_ref = true;
+          } else if (!have_ref) {
+            ok = wait_w(&m_bar[quarter & 1], n_tok & 1);
+            if (!ok) break;
+            m_ref = mref[hl];
+            have_ref = true;
           }
-          // both warps of the pair arrive: the arrival also says "I have read the other group's
-          // entry", which that group overwrites at its next tile
-          if (half == 0) mref[g * 64 + hl] = make_float2(m_new, mt_new);
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&m_bar[gp]);
+          outgrown = outgrown || mx > m_ref + guard;
           SFA_PROF(3);
-          if (m_cur != m_new) { l *= ex2(m_cur - m_new); m_cur = m_new; }   // (l is 0 while m_cur is -inf)
           float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int k = 0; k < kSfaHalfBK; k += 4) {
-            sc[k] = ex2(sc[k] - m_new); sc[k + 1] = ex2(sc[k + 1] - m_new);
-            sc[k + 2] = ex2(sc[k + 2] - m_new); sc[k + 3] = ex2(sc[k + 3] - m_new);
+            sc[k] = ex2(sc[k] - m_ref); sc[k + 1] = ex2(sc[k + 1] - m_ref);
+            sc[k + 2] = ex2(sc[k + 2] - m_ref); sc[k + 3] = ex2(sc[k + 3] - m_ref);
             sum4[0] += sc[k]; sum4[1] += sc[k + 1]; sum4[2] += sc[k + 2]; sum4[3] += sc[k + 3];
           }
           l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
@@ -739,28 +758,11 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
 #pragma unroll
             for (int k = 0; k < kSfaHalfBK; ++k) sc[k] *= inv;
           }
-          // ---- P (and, rarely, a rescaled O) once the product that last read this P buffer has finished
+          // ---- P once the product that last read this P buffer has finished
           SFA_PROF(2);
           ok = wait_w(&p_empty[g], (use & 1) ^ 1);
           if (!ok) break;
           SFA_PROF(4);
-          if (__any_sync(0xffffffffu, rescale)) {
-            // O must be quiescent: the previous tile's product (other P buffer) has to be complete too
-            const uint32_t prev = n_tile - 1;
-            ok = wait_w(&p_empty[g ^ 1], (prev >> 1) & 1);
-            if (!ok) break;
-            ptx::tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
-              uint32_t o[32];
-              ptx::tmem_ld_x32(lane_addr + kTmO + c * 32, o);
-              ptx::tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              ptx::tmem_st_x32(lane_addr + kTmO + c * 32, o);
-            }
-            ptx::tmem_st_wait();
-          }
           {
             // row hl of the K-major, 128-byte-swizzled A operand: keys half*32 .. +31 are the 16-byte
             // chunks half*4 .. +3 of the row
@@ -782,39 +784,37 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
         }
         if (!ok) break;
         SFA_PROF(7);
-        // ---- end of the token: final reference and true maximum (from the group of the last tile),
-        // row sum over the four threads of the head (two halves x two groups)
+        // ---- end of the token: row sum and true maximum over the four threads of the head (two
+        // halves x two groups); a group without a tile contributes 0 / -inf
         const uint32_t last = n_tile - 1;
-        float m_fin, mt_fin;
+        float l_tot, mt_fin;
         {
-          ok = wait_w(&m_bar[(last & 1) * 2 + (quarter & 1)], (last >> 1) & 1);
+          float l_other, mt_other;
+          if (ntiles > 1) {
+            ok = exchange(l, l_other);
+            if (!ok) break;
+            l_grp = l + l_other;
+          } else if ((int)(last & 1u) != g) {
+            l_grp = 0.f;                                   // (the tile's group normalised inside the tile)
+          }
+          ok = exchange(mt, mt_other);
           if (!ok) break;
-          const float2 mf = mref[(last & 1) * 64 + hl];
-          m_fin = mf.x; mt_fin = mf.y;
-        }
-        float l_tot;
-        if (ntiles == 1) {
-          // already normalised inside the tile's group; the group without a tile contributes nothing
-          if ((int)(last & 1u) != g) l_grp = 0.f;
-        } else {
-          const float ls = l * ex2(m_cur - m_fin);      // 0 for a thread whose group had no tile (m_cur = -inf, l = 0)
-          float l_other;
-          ok = exchange(m_cur == -INFINITY ? 0.f : ls, l_other);
-          if (!ok) break;
-          l_grp = (m_cur == -INFINITY ? 0.f : ls) + l_other;
-        }
-        {
+          const float mt_grp = fmaxf(mt, mt_other);
           ok = n_tok == 0 || wait_w(er_bar, (n_tok - 1) & 1);
           if (!ok) break;
-          if (half == 0) fin[g * 64 + hl] = l_grp;
+          if (half == 0) fin[g * 64 + hl] = make_float2(l_grp, mt_grp);
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(e_bar);
           ok = wait_w(e_bar, n_tok & 1);
           if (!ok) break;
-          l_tot = l_grp + fin[(g ^ 1) * 64 + hl];
+          const float2 fo = fin[(g ^ 1) * 64 + hl];
+          l_tot = l_grp + fo.x;
+          mt_fin = fmaxf(mt_grp, fo.y);
+          m_ref = mref[hl];                                // (a group without a tile has not read it yet)
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(er_bar);
         }
+        if (outgrown && hg < n1) a.redo[row] = 1;
         // ---- epilogue: wait for the last product, normalise, store this group's 128 columns
         ok = wait_w(&p_empty[last & 1], (last >> 1) & 1);
         if (!ok) break;
@@ -852,10 +852,10 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           // max of the scaled scores and sum of exp(score - max), back from the log2 domain
           if constexpr (kSplit) {
             a.part_m[(int64_t)item * kSfaHeads + hg] = mt_fin * 0.6931471805599453f;
-            a.part_l[(int64_t)item * kSfaHeads + hg] = l_tot * ex2(m_fin - mt_fin);
+            a.part_l[(int64_t)item * kSfaHeads + hg] = l_tot * ex2(m_ref - mt_fin);
           } else if (a.p.return_lse && hg < n1) {
             a.p.softmax_max[(int64_t)row * n1 + hg] = mt_fin * 0.6931471805599453f;
-            a.p.softmax_sum[(int64_t)row * n1 + hg] = l_tot * ex2(m_fin - mt_fin);
+            a.p.softmax_sum[(int64_t)row * n1 + hg] = l_tot * ex2(m_ref - mt_fin);
           }
         }
         ++n_tok;
@@ -952,16 +952,17 @@ inline int32_t sfa_sm100_part_keys(int64_t slots, int32_t split) {
   return (int32_t)(((tiles + split - 1) / split) * kSfaBK);
 }
 
-// Workspace beyond the header: nvalid[rows * split], key_list[rows * slots], and for split > 1 the
-// partial maxima, sums and outputs.
-struct SfaWsLayout { size_t nvalid, key_list, part_m, part_l, part_o, total; };
+// Workspace beyond the header: nvalid[rows * split], key_list[rows * slots], redo[rows], and for
+// split > 1 the partial maxima, sums and outputs.
+struct SfaWsLayout { size_t nvalid, key_list, redo, part_m, part_l, part_o, total; };
 inline SfaWsLayout sfa_sm100_ws_layout(int64_t rows, int64_t slots) {
   const int32_t split = sfa_sm100_split(rows, slots);
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   SfaWsLayout w;
   w.nvalid = 0;
   w.key_list = up((size_t)rows * split * 8);
-  w.part_m = w.key_list + up((size_t)rows * slots * 4);
+  w.redo = w.key_list + up((size_t)rows * slots * 4);
+  w.part_m = w.redo + up((size_t)rows * 4);
   const size_t stats = split > 1 ? up((size_t)rows * split * kSfaHeads * 4) : 0;
   w.part_l = w.part_m + stats;
   w.part_o = w.part_l + stats;
@@ -998,6 +999,11 @@ inline int sfa_sm100_device_sms(int dev) {
       cudaFuncSetAttribute(sfa_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)kSfaSmemBytes) != cudaSuccess)
     return 0;
+  const int redo_smem = (kSfaSimtHeads + kSfaSimtKeys) * (512 + 64 + kSfaSimtPad) * 2;
+  if (cudaFuncSetAttribute(sfa_redo_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, redo_smem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(sfa_redo_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, redo_smem) != cudaSuccess)
+    return 0;
   sm_count[dev].store(n, std::memory_order_release);
   return n;
 }
@@ -1014,7 +1020,8 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   const int32_t part_keys = split > 1 ? sfa_sm100_part_keys(slots, split) : (int32_t)((slots + kSfaBK - 1) / kSfaBK) * kSfaBK;
   int2* nvalid = reinterpret_cast<int2*>((char*)scratch + w.nvalid);
   int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + w.key_list);
-  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows);
+  int32_t* redo = reinterpret_cast<int32_t*>((char*)scratch + w.redo);
+  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows, redo);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   count_launch();
   SfaSm100Args a;
@@ -1032,6 +1039,7 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.part_m = reinterpret_cast<float*>((char*)scratch + w.part_m);
   a.part_l = reinterpret_cast<float*>((char*)scratch + w.part_l);
   a.part_o = reinterpret_cast<float*>((char*)scratch + w.part_o);
+  a.redo = redo;
   int clusters = sms / 2;
   if (clusters > a.items) clusters = a.items;
   CUtensorMap tkn, tkr, tq, tqr;
@@ -1049,6 +1057,16 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   count_launch();
   if (split > 1) {
     sfa_merge_kernel<<<dim3(d.rows, kSfaHeads / 8), 256, 0, st>>>(d, split, a.part_o, a.part_m, a.part_l, a.is_bf16);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
+  }
+  {
+    // rows whose scores outgrew the fixed reference maximum (normally none) are redone exactly
+    const size_t smem = (size_t)(kSfaSimtHeads + kSfaSimtKeys) * (p->d + p->d_rope + kSfaSimtPad) * 2;
+    const int64_t work = (int64_t)d.rows * ((p->n1 + kSfaSimtHeads - 1) / kSfaSimtHeads);
+    const unsigned blocks = (unsigned)std::min<int64_t>(work, (int64_t)sms * 2);
+    if (bf16) sfa_redo_kernel<__nv_bfloat16><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo);
+    else sfa_redo_kernel<__half><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     count_launch();
   }

@@ -339,3 +339,42 @@ def test_sfa_split_kv_for_few_rows_matches_oracle(B, S1, S2, K):
     finally:
         sfa.set_kernel("auto")
     sfa_acceptance_rule(*(host(t) for t in got2), *(host(t) for t in want2))
+
+
+@pytest.mark.parametrize("dtype,boost,K", [("bf16", 160.0, 256), ("fp16", 40.0, 256), ("bf16", 160.0, 2048)])
+def test_sfa_rows_whose_scores_outgrow_the_first_tile_are_exact(dtype, boost, K):
+    """The tensor-core kernel scales a row's probabilities by the maximum of the row's FIRST 64 keys
+    and hands rows whose later scores exceed it by more than the guard (2^60 in bf16, 2^12 in fp16) to
+    the portable kernel.  Rows built to do that - scores that climb by tens of natural units after
+    the first tile - and rows that climb by less (handled in place) must both match the oracle; rows
+    whose first tile holds the maximum are the ordinary case."""
+    sfa = _sfa()
+    rng = np.random.RandomState(17)
+    B, S1, S2, N1, D = 1, 6, K + 64, 64, 512
+    q = rng.randn(B, S1, N1, D).astype(np.float32) * 0.05
+    k = rng.randn(B, S2, 1, D).astype(np.float32) * 0.05
+    qr = rng.randn(B, S1, N1, 64).astype(np.float32) * 0.05
+    kr = rng.randn(B, S2, 1, 64).astype(np.float32) * 0.05
+    q[..., 0] = 8.0                                   # score = 8 * k[..., 0] / 24 + small terms
+    climb = np.zeros(S2, np.float32)
+    climb[64:] = np.linspace(boost * 0.25, boost, S2 - 64)       # natural units x 3: up to boost / 3
+    k[0, :, 0, 0] = climb
+    q, k, qr, kr = (round_io(x, dtype) for x in (q, k, qr, kr))
+    idx = np.full((B, S1, 1, K), -1, np.int32)
+    idx[0, 0, 0] = np.arange(K)                        # first tile low, then climbing: outgrows the guard
+    idx[0, 1, 0] = np.arange(K)[::-1] + 64             # first tile already holds the maximum
+    idx[0, 2, 0] = np.arange(K) // 4                   # climbs slowly (duplicates): stays inside the guard in bf16
+    idx[0, 3, 0, :100] = np.arange(100) + 30           # short row crossing the step
+    idx[0, 4, 0, :64] = np.arange(64)                  # a single tile
+    idx[0, 5, 0] = np.arange(K) + 32
+    scale = 1.0 / 24.0
+    dt = tdtype(dtype)
+    ref = sparse_flash_attention_oracle(q, k, idx, qr, kr, scale, [S1], [S2], sparse_mode=0, dtype=dtype)
+    sfa.set_kernel("tensor")
+    try:
+        got = sfa.sparse_flash_attention_triton(dev(q, dt), dev(k, dt), dev(k, dt), dev(idx), scale_value=scale,
+                                                query_rope=dev(qr, dt), key_rope=dev(kr, dt), sparse_mode=0,
+                                                return_softmax_lse=True)
+    finally:
+        sfa.set_kernel("auto")
+    _compare(host(got[0]), host(got[1]), host(got[2]), ref[0], ref[1], ref[2], dtype)
