@@ -252,16 +252,17 @@ __global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p)
   sfa_fwd_simt_row<T>(p, (int32_t)blockIdx.x, (int32_t)blockIdx.y * kSfaSimtHeads);
 }
 
-// Recomputes the rows marked in `redo` (rows whose scores outgrew the tensor-core kernel's fixed
-// reference maximum; normally none).  Any grid; blocks walk over (row, head chunk) pairs.
+// Recomputes the rows listed in redo_list[0 .. *redo_count) (rows whose scores outgrew the
+// tensor-core kernel's fixed reference maximum; normally none, and then every block leaves after
+// one load).  Any grid; blocks walk over (listed row, head chunk) pairs.
 template <typename T>
-__global__ void __launch_bounds__(kSfaSimtThreads) sfa_redo_kernel(SfaDev p, const int32_t* __restrict__ redo) {
+__global__ void __launch_bounds__(kSfaSimtThreads) sfa_redo_kernel(SfaDev p, const int32_t* __restrict__ redo_list,
+                                                                   const int32_t* __restrict__ redo_count) {
   const int32_t chunks = (p.n1 + kSfaSimtHeads - 1) / kSfaSimtHeads;
-  for (int64_t i = blockIdx.x; i < (int64_t)p.rows * chunks; i += gridDim.x) {
-    const int32_t row = (int32_t)(i / chunks);
-    if (redo[row] == 0) continue;
+  const int64_t work = (int64_t)min(*redo_count, p.rows) * chunks;
+  for (int64_t i = blockIdx.x; i < work; i += gridDim.x) {
     __syncthreads();   // the previous row's shared state is no longer read
-    sfa_fwd_simt_row<T>(p, row, (int32_t)(i - (int64_t)row * chunks) * kSfaSimtHeads);
+    sfa_fwd_simt_row<T>(p, redo_list[i / chunks], (int32_t)(i % chunks) * kSfaSimtHeads);
   }
 }
 

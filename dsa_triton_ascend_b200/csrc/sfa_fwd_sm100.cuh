@@ -128,7 +128,10 @@ struct SfaSm100Args {
   float* part_o;            // [items, 128, 512] fp32 (split > 1)
   float* part_m;            // [items, 128] maximum of the scaled scores of the part (natural log units)
   float* part_l;            // [items, 128] sum of exp(score - maximum); 0 marks an empty part
-  int32_t* redo;            // [rows] set when a row's scores outgrew the guard: sfa_redo_kernel recomputes it
+  // rows whose scores outgrew the guard: flag per row (set once), list and count for sfa_redo_kernel
+  int32_t* redo;            // [rows]
+  int32_t* redo_list;       // [rows]
+  int32_t* redo_count;      // [1]
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -153,9 +156,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
 __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __restrict__ nvalid,
                                                           int32_t* __restrict__ key_list, int32_t split,
                                                           int32_t part_keys, int32_t oob_row,
-                                                          int32_t* __restrict__ redo) {
+                                                          int32_t* __restrict__ redo,
+                                                          int32_t* __restrict__ redo_count) {
   const int lane = threadIdx.x & 31;
   const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *redo_count = 0;
   if (row >= p.rows) return;
   if (lane == 0) redo[row] = 0;
   const RowInfo ri = row_info(p.seq, row);
@@ -814,7 +819,7 @@ sfa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kn, const __grid_c
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(er_bar);
         }
-        if (outgrown && hg < n1) a.redo[row] = 1;
+        if (outgrown && hg < n1 && atomicExch(&a.redo[row], 1) == 0) a.redo_list[atomicAdd(a.redo_count, 1)] = row;
         // ---- epilogue: wait for the last product, normalise, store this group's 128 columns
         ok = wait_w(&p_empty[last & 1], (last >> 1) & 1);
         if (!ok) break;
@@ -952,9 +957,9 @@ inline int32_t sfa_sm100_part_keys(int64_t slots, int32_t split) {
   return (int32_t)(((tiles + split - 1) / split) * kSfaBK);
 }
 
-// Workspace beyond the header: nvalid[rows * split], key_list[rows * slots], redo[rows], and for
-// split > 1 the partial maxima, sums and outputs.
-struct SfaWsLayout { size_t nvalid, key_list, redo, part_m, part_l, part_o, total; };
+// Workspace beyond the header: nvalid[rows * split], key_list[rows * slots], the redo flags, list
+// and count, and for split > 1 the partial maxima, sums and outputs.
+struct SfaWsLayout { size_t nvalid, key_list, redo, redo_list, redo_count, part_m, part_l, part_o, total; };
 inline SfaWsLayout sfa_sm100_ws_layout(int64_t rows, int64_t slots) {
   const int32_t split = sfa_sm100_split(rows, slots);
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
@@ -962,7 +967,9 @@ inline SfaWsLayout sfa_sm100_ws_layout(int64_t rows, int64_t slots) {
   w.nvalid = 0;
   w.key_list = up((size_t)rows * split * 8);
   w.redo = w.key_list + up((size_t)rows * slots * 4);
-  w.part_m = w.redo + up((size_t)rows * 4);
+  w.redo_list = w.redo + up((size_t)rows * 4);
+  w.redo_count = w.redo_list + up((size_t)rows * 4);
+  w.part_m = w.redo_count + 256;
   const size_t stats = split > 1 ? up((size_t)rows * split * kSfaHeads * 4) : 0;
   w.part_l = w.part_m + stats;
   w.part_o = w.part_l + stats;
@@ -1021,7 +1028,10 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   int2* nvalid = reinterpret_cast<int2*>((char*)scratch + w.nvalid);
   int32_t* key_list = reinterpret_cast<int32_t*>((char*)scratch + w.key_list);
   int32_t* redo = reinterpret_cast<int32_t*>((char*)scratch + w.redo);
-  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows, redo);
+  int32_t* redo_list = reinterpret_cast<int32_t*>((char*)scratch + w.redo_list);
+  int32_t* redo_count = reinterpret_cast<int32_t*>((char*)scratch + w.redo_count);
+  sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows, redo,
+                                                      redo_count);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   count_launch();
   SfaSm100Args a;
@@ -1040,6 +1050,8 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   a.part_l = reinterpret_cast<float*>((char*)scratch + w.part_l);
   a.part_o = reinterpret_cast<float*>((char*)scratch + w.part_o);
   a.redo = redo;
+  a.redo_list = redo_list;
+  a.redo_count = redo_count;
   int clusters = sms / 2;
   if (clusters > a.items) clusters = a.items;
   CUtensorMap tkn, tkr, tq, tqr;
@@ -1065,8 +1077,8 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
     const size_t smem = (size_t)(kSfaSimtHeads + kSfaSimtKeys) * (p->d + p->d_rope + kSfaSimtPad) * 2;
     const int64_t work = (int64_t)d.rows * ((p->n1 + kSfaSimtHeads - 1) / kSfaSimtHeads);
     const unsigned blocks = (unsigned)std::min<int64_t>(work, (int64_t)sms * 2);
-    if (bf16) sfa_redo_kernel<__nv_bfloat16><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo);
-    else sfa_redo_kernel<__half><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo);
+    if (bf16) sfa_redo_kernel<__nv_bfloat16><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo_list, redo_count);
+    else sfa_redo_kernel<__half><<<blocks, kSfaSimtThreads, smem, st>>>(d, redo_list, redo_count);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     count_launch();
   }
