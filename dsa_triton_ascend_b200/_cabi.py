@@ -113,7 +113,7 @@ EXPORTS = (
     "dsa_sfa_workspace_bytes", "dsa_sfa_forward", "dsa_sfa_uses_tensor_path",
     "dsa_li_forward_static", "dsa_li_static_scratch_bytes", "dsa_selftest_wait_timeout",
     "dsa_kernel_launch_count", "dsa_sfa_grad_workspace_bytes", "dsa_sfa_grad",
-    "dsa_sli_grad_workspace_bytes", "dsa_sli_grad", "dsa_dense_li_lse",
+    "dsa_sli_grad_workspace_bytes", "dsa_sli_grad", "dsa_dense_li_lse_workspace_bytes", "dsa_dense_li_lse",
 )
 
 
@@ -145,7 +145,9 @@ def _load():
     lib.dsa_sli_grad_workspace_bytes.restype = _c.c_int
     lib.dsa_sli_grad.argtypes = [_c.POINTER(DsaSliGradParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
     lib.dsa_sli_grad.restype = _c.c_int
-    lib.dsa_dense_li_lse.argtypes = [_c.POINTER(DsaDenseLseParams), _c.c_void_p]
+    lib.dsa_dense_li_lse_workspace_bytes.argtypes = [_c.POINTER(DsaDenseLseParams), _c.POINTER(_c.c_size_t)]
+    lib.dsa_dense_li_lse_workspace_bytes.restype = _c.c_int
+    lib.dsa_dense_li_lse.argtypes = [_c.POINTER(DsaDenseLseParams), _c.c_void_p, _c.c_size_t, _c.c_void_p]
     lib.dsa_dense_li_lse.restype = _c.c_int
     lib.dsa_li_forward_static.argtypes = [_c.POINTER(DsaLiParams), _c.c_void_p]
     lib.dsa_li_forward_static.restype = _c.c_int

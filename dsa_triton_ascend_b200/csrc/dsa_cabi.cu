@@ -304,7 +304,6 @@ static int sli_grad_validate(const DsaSliGradParams* p) {
     if (p->n2 != 1 && p->n2 != 0) return DSA_ERR_VALUE;
     if (p->topk < 1) return DSA_ERR_VALUE;
   }
-  if (sli_slots(p) > 8192) return DSA_ERR_TOO_LARGE;   // p and I of a row live in shared memory
   if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE) return DSA_ERR_UNSUPPORTED;
   return DSA_OK;
 }
@@ -324,8 +323,10 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   d.act_q = p->seq_q; d.act_k = p->seq_k;
   const int32_t slots = (int32_t)sli_slots(p);
   d.d_query_index = p->d_query_index; d.d_weights = p->d_weights; d.d_key_index = p->d_key_index; d.loss = p->loss;
+  const size_t buf_bytes = align256((size_t)rows * slots * 4);
   d.di = reinterpret_cast<float*>(ws);
-  d.loss_parts = reinterpret_cast<float*>(ws + align256((size_t)rows * slots * 4));
+  d.p_buf = reinterpret_cast<float*>(ws + buf_bytes);
+  d.loss_parts = reinterpret_cast<float*>(ws + 2 * buf_bytes);
   float* stats = reinterpret_cast<float*>((char*)d.loss_parts + align256((size_t)rows * 4));
   d.dki_acc = reinterpret_cast<float*>((char*)stats + align256((size_t)rows * 8));
   d.stats_given = (p->dense && p->softmax_max_index) ? 1 : 0;
@@ -337,21 +338,25 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   d.g = p->g; d.d_idx = p->d_idx; d.topk = slots; d.dtype_w = p->dtype_w;
   d.scale = p->scale;
   if (cudaMemsetAsync(d.dki_acc, 0, (size_t)key_elems * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
+  if (rows > 0 && cudaMemsetAsync(d.di, 0, 2 * buf_bytes, st) != cudaSuccess) return DSA_ERR_CUDA;
   if (rows > 0) {
     const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
-    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * slots * 4;
+    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T);
     const size_t smem_b = (size_t)(kSliHeads + kSliKeys) * (p->d_idx + kSliPad) * sizeof(T);
     if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
         cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
             cudaSuccess)
       return DSA_ERR_CUDA;
-    sli_teacher_kernel<T><<<(unsigned)rows, kSliThreads, smem_a, st>>>(d, stride);
+    dim3 grid_t((unsigned)rows, (unsigned)(sli_att_chunks(d.n1, d.n2) + sli_idx_chunks(d.g)), 1);
+    sli_teacher_kernel<T><<<grid_t, kSliThreads, smem_a, st>>>(d, stride);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
-    dim3 grid((unsigned)rows, (unsigned)((p->g + kSliHeads - 1) / kSliHeads), 1);
+    sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(d.g), 1);
     sli_grad_kernel<T><<<grid, kSliThreads, smem_b, st>>>(d);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
-    count_launch(2);
+    count_launch(3);
   }
   const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>((key_elems + 255) / 256, 148 * 16));
   sli_finalize_kernel<T><<<blocks, 256, 0, st>>>(d, key_elems, (int32_t)rows);
@@ -360,7 +365,7 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   return DSA_OK;
 }
 template <typename T>
-static int dense_lse_launch(const DsaDenseLseParams* p, cudaStream_t st) {
+static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, cudaStream_t st) {
   SliGradDev d = {};
   d.query_index = p->query_index; d.key_index = p->key_index; d.weights = p->weights;
   d.act_q = p->seq_q; d.act_k = p->seq_k;
@@ -369,13 +374,18 @@ static int dense_lse_launch(const DsaDenseLseParams* p, cudaStream_t st) {
   d.topk = p->s2; d.dtype_w = p->dtype_w; d.lse_only = 1;
   const int64_t rows = (int64_t)p->batch * p->s1;
   if (rows == 0) return DSA_OK;
+  d.di = scratch;
+  if (cudaMemsetAsync(scratch, 0, (size_t)rows * p->s2 * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
   const int stride = p->d_idx + kSliPad;
-  const size_t smem = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T) + (size_t)2 * p->s2 * 4;
+  const size_t smem = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T);
   if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return DSA_ERR_CUDA;
-  sli_teacher_kernel<T><<<(unsigned)rows, kSliThreads, smem, st>>>(d, stride);
+  dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(p->g), 1);
+  sli_teacher_kernel<T><<<grid, kSliThreads, smem, st>>>(d, stride);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
-  count_launch();
+  sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
+  if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+  count_launch(2);
   return DSA_OK;
 }
 
@@ -385,7 +395,7 @@ using namespace dsa;
 
 extern "C" {
 
-int dsa_abi_version(void) { return 6; }
+int dsa_abi_version(void) { return 7; }
 
 unsigned long long dsa_kernel_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -453,12 +463,13 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
   if (p->kernel == DSA_KERNEL_TENSOR && !dsa_sfa_uses_tensor_path(p)) return DSA_ERR_UNSUPPORTED;
   cudaStream_t cs = (cudaStream_t)stream;
-  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
   if (dsa_sfa_uses_tensor_path(p)) {
     SfaDev d = sfa_dev(p);
-    if (d.rows == 0) return DSA_OK;
-    return sfa_sm100_launch(p, d, (int32_t*)workspace, (char*)workspace + kWorkspaceHeader, cs);
+    if (d.rows > 0)   // (the pre-pass kernel clears the header)
+      return sfa_sm100_launch(p, d, (int32_t*)workspace, (char*)workspace + kWorkspaceHeader, cs);
   }
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  if (dsa_sfa_uses_tensor_path(p)) return DSA_OK;   // no rows
   if (p->dtype == DSA_DTYPE_BF16) return sfa_launch_simt<__nv_bfloat16>(p, cs);
   return sfa_launch_simt<__half>(p, cs);
 }
@@ -487,7 +498,7 @@ int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_by
   return sfa_grad_launch<__half>(p, acc, cs);
 }
 
-int dsa_dense_li_lse(const DsaDenseLseParams* p, void* stream) {
+static int dense_lse_validate(const DsaDenseLseParams* p) {
   if (p == nullptr) return DSA_ERR_NULL;
   if (p->struct_size != sizeof(DsaDenseLseParams)) return DSA_ERR_STRUCT;
   if (!p->query_index || !p->key_index || !p->weights || !p->softmax_max_index || !p->softmax_sum_index)
@@ -496,10 +507,29 @@ int dsa_dense_li_lse(const DsaDenseLseParams* p, void* stream) {
   if (p->dtype_w < DSA_DTYPE_BF16 || p->dtype_w > DSA_DTYPE_FP32) return DSA_ERR_VALUE;
   if (p->d_idx != 128 && p->d_idx != 256 && p->d_idx != 512) return DSA_ERR_VALUE;
   if (p->batch < 1 || p->s1 < 0 || p->s2 < 1 || p->g < 1) return DSA_ERR_VALUE;
-  if (p->s2 > 8192) return DSA_ERR_TOO_LARGE;
   if ((int64_t)p->batch * p->s1 > 0x7FFFFFFF) return DSA_ERR_TOO_LARGE;
-  if (p->dtype == DSA_DTYPE_BF16) return dense_lse_launch<__nv_bfloat16>(p, (cudaStream_t)stream);
-  return dense_lse_launch<__half>(p, (cudaStream_t)stream);
+  return DSA_OK;
+}
+
+int dsa_dense_li_lse_workspace_bytes(const DsaDenseLseParams* p, size_t* out_bytes) {
+  int st = dense_lse_validate(p);
+  if (st != DSA_OK) return st;
+  if (!out_bytes) return DSA_ERR_NULL;
+  *out_bytes = kWorkspaceHeader + (size_t)p->batch * p->s1 * p->s2 * 4;
+  return DSA_OK;
+}
+
+int dsa_dense_li_lse(const DsaDenseLseParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = dense_lse_validate(p);
+  if (st != DSA_OK) return st;
+  size_t need = 0;
+  dsa_dense_li_lse_workspace_bytes(p, &need);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0) return DSA_ERR_WORKSPACE;
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
+  float* scratch = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
+  if (p->dtype == DSA_DTYPE_BF16) return dense_lse_launch<__nv_bfloat16>(p, scratch, cs);
+  return dense_lse_launch<__half>(p, scratch, cs);
 }
 
 int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes) {
@@ -507,7 +537,7 @@ int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes) {
   if (st != DSA_OK) return st;
   if (!out_bytes) return DSA_ERR_NULL;
   const size_t rows = (size_t)p->batch * p->s1;
-  *out_bytes = kWorkspaceHeader + align256(rows * (size_t)sli_slots(p) * 4) + align256(rows * 4) +
+  *out_bytes = kWorkspaceHeader + 2 * align256(rows * (size_t)sli_slots(p) * 4) + align256(rows * 4) +
                align256(rows * 8) + (size_t)p->batch * p->s2 * p->d_idx * 4;
   return DSA_OK;
 }

@@ -157,10 +157,14 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __rest
                                                           int32_t* __restrict__ key_list, int32_t split,
                                                           int32_t part_keys, int32_t oob_row,
                                                           int32_t* __restrict__ redo,
-                                                          int32_t* __restrict__ redo_count) {
+                                                          int32_t* __restrict__ redo_count,
+                                                          int32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const int32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (blockIdx.x == 0 && threadIdx.x == 0) *redo_count = 0;
+  // the workspace header (status word of the call) starts at zero: cleared here instead of by a
+  // memset node of its own in front of the operator's launches
+  if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0;
   if (row >= p.rows) return;
   if (lane == 0) redo[row] = 0;
   const RowInfo ri = row_info(p.seq, row);
@@ -1031,7 +1035,7 @@ inline int sfa_sm100_launch(const DsaSfaParams* p, const SfaDev& d, int32_t* sta
   int32_t* redo_list = reinterpret_cast<int32_t*>((char*)scratch + w.redo_list);
   int32_t* redo_count = reinterpret_cast<int32_t*>((char*)scratch + w.redo_count);
   sfa_compact_kernel<<<(d.rows + 3) / 4, 128, 0, st>>>(d, nvalid, key_list, split, part_keys, (int32_t)p->key_rows, redo,
-                                                      redo_count);
+                                                      redo_count, status);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   count_launch();
   SfaSm100Args a;

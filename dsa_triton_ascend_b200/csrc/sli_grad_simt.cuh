@@ -8,11 +8,13 @@
 //     dW[g] = sum_k dI[k] relu[g,k];   ds[g,k] = dI[k] w[g] [relu[g,k] > 0]
 //     dQI[g] = sum_k ds[g,k] ki[idx k];   dKI[idx k] += sum_g ds[g,k] qi[g]
 // The reference runs all stages in one program per row and keeps ReLU values, gathered index keys,
-// p, I and dI in global scratch tensors between them (:385-400).  Here the first kernel produces dI and
-// the row's loss term (p and I live in shared memory); the second, one block per (row, 16 index
-// heads), recomputes the index scores it needs instead of reading a [rows, G, topK] ReLU cache,
-// accumulates dQI / dW in registers and adds dKI into an fp32 accumulator with 16-byte reductions; a
-// third converts the accumulator and sums the loss terms in a fixed order.
+// p, I and dI in global scratch tensors between them (:385-400).  Here: (1) one block per (row, 16
+// heads) of either side keeps its heads in shared memory, walks over the row's keys and adds its
+// share of p[k] or I[k] into fp32 buffers; (2) one block per row turns I and p into dI and the
+// row's loss term; (3) one block per (row, 16 index heads) recomputes the index scores it needs
+// instead of reading a [rows, G, topK] ReLU cache, accumulates dQI / dW in registers and adds dKI
+// into an fp32 accumulator with 16-byte reductions; (4) the accumulator is converted and the loss
+// terms are summed in a fixed order.
 //
 // The same kernels serve the dense operator (dense_loss_backward_triton.py:130-341: every causally
 // visible key 0..n-1 instead of selected ones, attention keys with n2 heads, the student distribution
@@ -44,7 +46,8 @@ struct SliGradDev {
   void* d_weights;          // [rows, g], dtype_w
   void* d_key_index;        // [batch * s2, d_idx]
   float* loss;              // [1]
-  float* di;                // [rows, topk]  scratch
+  float* di;                // [rows, topk]  scratch, zeroed by the caller: index scores, then dI
+  float* p_buf;             // [rows, topk]  scratch, zeroed by the caller: sum over heads of the attention probabilities
   float* loss_parts;        // [rows]        scratch
   float* dki_acc;           // [batch * s2, d_idx] scratch, zeroed by the caller
   int32_t batch, s1, s2, n1, n2, d, d_rope, g, d_idx, topk, dtype_w;
@@ -148,20 +151,103 @@ __device__ __forceinline__ void sli_dots(const T* qs, const T* ks, int stride, i
   *s1 = a1;
 }
 
-// grid = rows; block = 256.  dynamic smem: (16 + 32) * stride elements of T, then 2 * topk floats.
+// Number of 16-head chunks of the attention side (per key head) and of the index side.
+__host__ __device__ inline int sli_att_chunks(int n1, int n2) { return n2 * ((n1 / n2 + kSliHeads - 1) / kSliHeads); }
+__host__ __device__ inline int sli_idx_chunks(int g) { return (g + kSliHeads - 1) / kSliHeads; }
+
+// grid = (rows, attention chunks + index chunks) (index chunks only when lse_only); block = 256.
+// dynamic smem: (16 + 32) * stride elements of T.  A block keeps its 16 heads in shared memory,
+// walks over the row's keys 32 at a time and adds its heads' share of p[k] (attention chunks) or of
+// I[k] (index chunks) into the row's fp32 buffers (zeroed by the caller).
 template <typename T>
 __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, int stride) {
   extern __shared__ __align__(16) unsigned char sli_smem[];
   T* qs = reinterpret_cast<T*>(sli_smem);
   T* ks = qs + kSliHeads * stride;
-  float* p_s = reinterpret_cast<float*>(ks + kSliKeys * stride);
-  float* i_s = p_s + p.topk;
   __shared__ float red_s[kSliThreads / 32][kSliKeys];
-  __shared__ float red8[kSliThreads / 32];
   __shared__ int64_t rows_s[kSliKeys];
   __shared__ float max_s[kSliHeads], inv_s[kSliHeads], w_s[kSliHeads];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t row = blockIdx.x;
+  int32_t b;
+  const int32_t n = sli_row_slots(p, row, &b);
+  if (n == 0) return;
+  const bool dense = p.sparse_indices == nullptr;
+  const int32_t pos = row - b * p.s1;
+  const int32_t* idx_row = dense ? nullptr : p.sparse_indices + (int64_t)row * p.topk;
+  const int grp = p.n1 / p.n2;                    // query heads per attention key head
+  const int att_chunks = p.lse_only ? 0 : sli_att_chunks(p.n1, p.n2);
+  const int c = blockIdx.y;
+  const int phase = c < att_chunks ? 0 : 1;       // 0: attention distribution p, 1: index scores I
+  int kv = 0, h0, h_end;
+  if (phase == 0) {
+    const int cpk = att_chunks / p.n2;
+    kv = c / cpk;
+    h0 = kv * grp + (c - kv * cpk) * kSliHeads;
+    h_end = (kv + 1) * grp;
+  } else {
+    h0 = (c - att_chunks) * kSliHeads;
+    h_end = p.g;
+  }
+  const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
+  float* acc_row = (phase == 0 ? p.p_buf : p.di) + (int64_t)row * p.topk;
+
+  if (phase == 0) {
+    const T* q = (const T*)p.query + (int64_t)row * p.n1 * p.d;
+    const T* qr = p.d_rope ? (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope : nullptr;
+    sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, h_end);
+  } else {
+    sli_stage_heads<T>(qs, stride, (const T*)p.query_index + (int64_t)row * p.g * p.d_idx, p.d_idx, (const T*)nullptr, 0,
+                       h0, h_end);
+  }
+  if (tid < kSliHeads) {
+    const int h = h0 + tid;
+    if (phase == 0) {
+      const int64_t si = (((int64_t)b * p.n2 + kv) * p.s1 + pos) * grp + (h - kv * grp);   // [batch, n2, s1, grp]
+      max_s[tid] = h < h_end ? p.softmax_max[si] : 0.f;
+      inv_s[tid] = h < h_end ? 1.f / (p.softmax_sum[si] + kSliEps) : 0.f;
+    } else {
+      w_s[tid] = h < h_end ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
+    }
+  }
+  for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
+    __syncthreads();   // heads staged; the previous step is done with ks, rows_s and red_s
+    if (tid < kSliKeys) {
+      const int32_t j = j0 + tid;
+      rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
+    }
+    __syncthreads();
+    if (phase == 0)
+      sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
+    else
+      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+    __syncthreads();
+    float s0, s1;
+    sli_dots<T>(qs, ks, stride, w, &s0, &s1);
+    float part;
+    if (phase == 0) {
+      part = (h0 + warp < h_end ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
+             (h0 + warp + 8 < h_end ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
+    } else {
+      part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
+    }
+    red_s[warp][lane] = part;
+    __syncthreads();
+    if (tid < kSliKeys && j0 + tid < n) {
+      float acc = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
+      atomicAdd(&acc_row[j0 + tid], acc);
+    }
+  }
+}
+
+// grid = rows; block = 256.  Student distribution from the row's index scores, dI = student - p and
+// the row's KL term; dI replaces the index scores in place.  With lse_only only the statistics.
+__global__ void __launch_bounds__(kSliThreads) sli_student_kernel(SliGradDev p) {
+  __shared__ float red8[kSliThreads / 32];
+  const int tid = threadIdx.x;
   const int32_t row = blockIdx.x;
   int32_t b;
   const int32_t n = sli_row_slots(p, row, &b);
@@ -173,98 +259,34 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
     }
     return;
   }
-  const int32_t pos = row - b * p.s1;
-  const int32_t* idx_row = dense ? nullptr : p.sparse_indices + (int64_t)row * p.topk;
-  const T* q = (const T*)p.query + (int64_t)row * p.n1 * p.d;
-  const T* qr = p.d_rope ? (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope : nullptr;
-  const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
-  const int grp = p.n1 / p.n2;   // query heads per attention key head
-
-  for (int phase = p.lse_only ? 1 : 0; phase < 2; ++phase) {   // 0: attention distribution p, 1: index scores I
-    const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
-    const int kv_heads = phase == 0 ? p.n2 : 1;
-    const int per_kv = phase == 0 ? grp : p.g;
-    for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
-      __syncthreads();
-      if (tid < kSliKeys) {
-        const int32_t j = j0 + tid;
-        rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
-      }
-      float acc = 0.f;
-      for (int kv = 0; kv < kv_heads; ++kv) {
-        __syncthreads();   // rows_s written; the previous key head's dot products are done with ks
-        if (phase == 0)
-          sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
-        else
-          sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
-        const int h_end = (kv + 1) * per_kv;
-        for (int h0 = kv * per_kv; h0 < h_end; h0 += kSliHeads) {
-          __syncthreads();
-          if (phase == 0) sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, h_end);
-          else sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, h_end);
-          if (tid < kSliHeads) {
-            const int h = h0 + tid;
-            if (phase == 0) {
-              // statistics are [batch, n2, s1, grp]
-              const int64_t si = (((int64_t)b * p.n2 + kv) * p.s1 + pos) * grp + (h - kv * grp);
-              max_s[tid] = h < h_end ? p.softmax_max[si] : 0.f;
-              inv_s[tid] = h < h_end ? 1.f / (p.softmax_sum[si] + kSliEps) : 0.f;
-            } else {
-              w_s[tid] = h < h_end ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
-            }
-          }
-          __syncthreads();
-          float s0, s1;
-          sli_dots<T>(qs, ks, stride, w, &s0, &s1);
-          float part;
-          if (phase == 0) {
-            part = (h0 + warp < h_end ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
-                   (h0 + warp + 8 < h_end ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
-          } else {
-            part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
-          }
-          red_s[warp][lane] = part;
-          __syncthreads();
-          if (tid < kSliKeys) {
-#pragma unroll
-            for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
-          }
-        }
-      }
-      if (tid < kSliKeys && j0 + tid < n) {
-        if (phase == 0) p_s[j0 + tid] = acc * (1.f / (float)p.n1);
-        else i_s[j0 + tid] = acc;
-      }
-    }
-  }
-  __syncthreads();
-
-  // student distribution: softmax of the index scores (:95-103), or, for the dense operator, the
-  // scores normalised with the index statistics (dense_loss_backward_triton.py:300-312)
+  float* di = p.di + (int64_t)row * p.topk;       // holds I[k] on entry
+  // softmax of the index scores (:95-103), or, for the dense operator, the scores normalised with
+  // the index statistics (dense_loss_backward_triton.py:300-312)
   float m, se;
   if (dense && p.stats_given) {
     m = p.index_max[row];
     se = p.index_sum[row];
   } else {
     m = -INFINITY;
-    for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, i_s[k]);
+    for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, di[k]);
     m = sli_block_reduce(m, red8, true);
     se = 0.f;
-    for (int k = tid; k < n; k += kSliThreads) se += expf(i_s[k] - m);
+    for (int k = tid; k < n; k += kSliThreads) se += expf(di[k] - m);
     se = sli_block_reduce(se, red8, false);
     if (dense && tid == 0) { p.index_max[row] = m; p.index_sum[row] = se; }
   }
   if (p.lse_only) return;
-  float* di = p.di + (int64_t)row * p.topk;
   if (dense && !(se > 0.f)) {           // the reference skips such rows: no gradient, no loss
     for (int k = tid; k < n; k += kSliThreads) di[k] = 0.f;
     if (tid == 0) p.loss_parts[row] = 0.f;
     return;
   }
+  const float* pb = p.p_buf + (int64_t)row * p.topk;
   const float inv = dense ? 1.f / fmaxf(se, kSliEps) : 1.f / (se + kSliEps);
+  const float inv_n1 = 1.f / (float)p.n1;
   float kl = 0.f;
   for (int k = tid; k < n; k += kSliThreads) {
-    const float si = expf(i_s[k] - m) * inv, pk = p_s[k];
+    const float si = expf(di[k] - m) * inv, pk = pb[k] * inv_n1;
     di[k] = si - pk;
     const float pc = fmaxf(pk, kSliEps), sc = fmaxf(si, kSliEps);
     kl += pc * (logf(pc) - logf(sc));

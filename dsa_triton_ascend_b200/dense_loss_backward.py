@@ -70,7 +70,13 @@ def npu_dense_lightning_indexer_softmax_lse_triton(query_index, key_index, weigh
     p.dtype_w = dtype_code(weights, (torch.bfloat16, torch.float16, torch.float32), "weights")
     p.batch, p.s1, p.s2, p.g, p.d_idx = B, S1, S2, G, Di
     with torch.cuda.device(dev):
-        _cabi.check(_cabi.lib.dsa_dense_li_lse(ctypes.byref(p), current_stream(dev)), "dense_lightning_indexer_softmax_lse")
+        nbytes = ctypes.c_size_t(0)
+        _cabi.check(_cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)),
+                    "dense_lightning_indexer_softmax_lse")
+        ws = workspace(nbytes.value, dev)
+        _cabi.check(_cabi.lib.dsa_dense_li_lse(ctypes.byref(p), ws.data_ptr(), ws.numel(), current_stream(dev)),
+                    "dense_lightning_indexer_softmax_lse")
+        note_launch("dense_lightning_indexer_softmax_lse", ws, dev)
     return mx, sm
 
 

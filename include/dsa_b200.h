@@ -229,8 +229,8 @@ typedef struct DsaSliGradParams {
   const float* softmax_sum_index;
 } DsaSliGradParams;
 
-/* Workspace: status header + fp32 scratch (dI [rows, topk], one loss term per row, the d_key_index
- * accumulator [batch * s2, d_idx]). */
+/* Workspace: status header + fp32 scratch (index scores / dI and attention probabilities, each
+ * [rows, slots]; one loss term per row; the d_key_index accumulator [batch * s2, d_idx]). */
 int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes);
 int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
@@ -239,7 +239,7 @@ int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_by
  * (dense_loss_backward_triton.py:344-420) behind `npu_dense_lightning_indexer_softmax_lse_triton`
  * (:773-802): per query row the maximum and the sum of exponentials over the causally visible keys
  * of I[k] = sum_g w[g] relu(query_index[g] . key_index[k]); -inf / 0 for rows that see no key.
- * No workspace.
+ * Workspace: status header + the fp32 index scores [batch * s1, s2].
  */
 typedef struct DsaDenseLseParams {
   uint32_t struct_size; /* sizeof(DsaDenseLseParams) */
@@ -254,7 +254,8 @@ typedef struct DsaDenseLseParams {
   int32_t dtype, dtype_w;
   int32_t batch, s1, s2, g, d_idx;
 } DsaDenseLseParams;
-int dsa_dense_li_lse(const DsaDenseLseParams* p, void* stream);
+int dsa_dense_li_lse_workspace_bytes(const DsaDenseLseParams* p, size_t* out_bytes);
+int dsa_dense_li_lse(const DsaDenseLseParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * dsa_li_forward_static - the indexer without a caller workspace and without any allocation.

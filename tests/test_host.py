@@ -200,12 +200,10 @@ def test_sli_grad_guards_and_abi_validation():
         setattr(g, f, 256)
     g.batch, g.s1, g.s2, g.n1, g.d, g.d_rope, g.g, g.d_idx, g.topk = 1, 4, 64, 32, 128, 0, 8, 128, 16
     assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
-    assert n.value == 256 + 256 + 256 + 256 + 64 * 128 * 4
+    assert n.value == 256 + 2 * 256 + 256 + 256 + 64 * 128 * 4
     g.d_rope = 64                                   # rope width given but no rope tensors
     assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -1
-    g.d_rope, g.topk = 0, 10000
-    assert _cabi.lib.dsa_sli_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -8
-    g.topk = 16
+    g.d_rope = 0
     assert _cabi.lib.dsa_sli_grad(ctypes.byref(g), None, 0, None) == -4
 
 
@@ -271,11 +269,14 @@ def test_dense_loss_guards_raise_like_the_reference():
     with pytest.raises(RuntimeError):   # CPU tensors: there is no CPU path
         lse(qi, ki, w)
     p = _cabi.DsaDenseLseParams()
-    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -2
+    n = ctypes.c_size_t(0)
+    assert _cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -2
     p.struct_size = ctypes.sizeof(p)
-    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -1
+    assert _cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -1
     p.query_index = p.key_index = p.weights = p.softmax_max_index = p.softmax_sum_index = 256
-    p.batch, p.s1, p.s2, p.g, p.d_idx = 1, 2, 100000, 32, 128
-    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -8
-    p.s2, p.d_idx = 64, 100
-    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None) == -3
+    p.batch, p.s1, p.s2, p.g, p.d_idx = 1, 2, 64, 32, 100
+    assert _cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == -3
+    p.d_idx = 128
+    assert _cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    assert n.value == 256 + 2 * 64 * 4
+    assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None, 0, None) == -4
