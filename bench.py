@@ -571,7 +571,8 @@ def run_gpu(args):
         "li_topk_share": phase_ms["topk"] / (phase_ms["score"] + phase_ms["topk"]),
         "li_score_tflops": li_score_tf,
         "sfa_ms": sfa_max, "sfa_tflops_per_gpu": sfa_tf_gpu,
-        "timing": {"sfa_ms": pct(sfa_all), "li_ms": pct(li_all), "note": "this rank's steps; value uses the mean"},
+        "timing": {"sfa_ms": pct(sfa_all), "li_ms": pct(li_all), "sfa_ms_steps": [round(x, 3) for x in sfa_all],
+                   "note": "this rank's steps; value uses the mean"},
         "shard_imbalance": {"sfa_max_over_mean": sfa_max / float(np.mean(per_rank["sfa_ms"])),
                             "li_max_over_mean": li_max / float(np.mean(per_rank["li_ms"]))},
         "li_tensor_path": tensor_li,
