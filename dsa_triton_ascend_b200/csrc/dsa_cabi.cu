@@ -311,7 +311,7 @@ static int sli_grad_validate(const DsaSliGradParams* p) {
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <typename T>
-static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st) {
+static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status, cudaStream_t st) {
   SliGradDev d;
   const int64_t rows = (int64_t)p->batch * p->s1;
   const int64_t key_elems = (int64_t)p->batch * p->s2 * p->d_idx;
@@ -348,7 +348,29 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
         cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
             cudaSuccess)
       return DSA_ERR_CUDA;
-    dim3 grid_t((unsigned)rows, (unsigned)(sli_att_chunks(d.n1, d.n2) + sli_idx_chunks(d.g)), 1);
+    // Dense operator: the index scores of all visible keys are the lightning indexer's scores; when
+    // the shape is one the tcgen05 scoring kernel takes, it writes them (row stride = s2) and the
+    // CUDA-core pass below only does the attention side.
+    bool index_done = false;
+    if (p->dense && p->s2 % 4 == 0 && status != nullptr) {
+      DsaLiParams l = {};
+      l.struct_size = sizeof(DsaLiParams);
+      l.kernel = DSA_KERNEL_AUTO;
+      l.query = p->query_index; l.key = p->key_index; l.weights = p->weights;
+      l.seq_q = p->seq_q; l.seq_k = p->seq_k;
+      l.out_indices = (int32_t*)d.loss_parts;   // (not written: the top-k phase does not run)
+      l.layout_q = DSA_LAYOUT_BSND; l.layout_k = DSA_LAYOUT_BSND;
+      l.dtype_qk = p->dtype; l.dtype_w = p->dtype_w;
+      l.batch = p->batch; l.s1 = p->s1; l.s2 = p->s2; l.n1 = p->g; l.n2 = 1; l.d = p->d_idx;
+      l.sparse_count = 1; l.sparse_mode = 3; l.rank_mode = DSA_RANK_IO_DTYPE; l.phases = DSA_PHASE_SCORE;
+      l.key_rows = (int64_t)p->batch * p->s2;
+      if (li_validate(&l) == DSA_OK && li_takes_tensor_path(&l)) {
+        int rc = li_launch<T>(&l, d.di, st, status);
+        if (rc != DSA_OK) return rc;
+        index_done = true;
+      }
+    }
+    dim3 grid_t((unsigned)rows, (unsigned)(sli_att_chunks(d.n1, d.n2) + (index_done ? 0 : sli_idx_chunks(d.g))), 1);
     sli_teacher_kernel<T><<<grid_t, kSliThreads, smem_a, st>>>(d, stride);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
@@ -364,8 +386,25 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, cudaStream_t st)
   count_launch();
   return DSA_OK;
 }
+// The dense index scores are the lightning indexer's scores: the same problem as an indexer call
+// (BSND, rightDownCausal, per-batch lengths) stopped after the scoring phase.
+static DsaLiParams dense_lse_as_li(const DsaDenseLseParams* p) {
+  DsaLiParams l = {};
+  l.struct_size = sizeof(DsaLiParams);
+  l.kernel = DSA_KERNEL_AUTO;
+  l.query = p->query_index; l.key = p->key_index; l.weights = p->weights;
+  l.seq_q = p->seq_q; l.seq_k = p->seq_k;
+  l.out_indices = (int32_t*)p->softmax_max_index;   // (not written: the top-k phase does not run)
+  l.layout_q = DSA_LAYOUT_BSND; l.layout_k = DSA_LAYOUT_BSND;
+  l.dtype_qk = p->dtype; l.dtype_w = p->dtype_w;
+  l.batch = p->batch; l.s1 = p->s1; l.s2 = p->s2; l.n1 = p->g; l.n2 = 1; l.d = p->d_idx;
+  l.sparse_count = 1; l.sparse_mode = 3; l.rank_mode = DSA_RANK_IO_DTYPE; l.phases = DSA_PHASE_SCORE;
+  l.key_rows = (int64_t)p->batch * p->s2;
+  return l;
+}
+
 template <typename T>
-static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, cudaStream_t st) {
+static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, int32_t* status, cudaStream_t st) {
   SliGradDev d = {};
   d.query_index = p->query_index; d.key_index = p->key_index; d.weights = p->weights;
   d.act_q = p->seq_q; d.act_k = p->seq_k;
@@ -374,6 +413,16 @@ static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, cudaStre
   d.topk = p->s2; d.dtype_w = p->dtype_w; d.lse_only = 1;
   const int64_t rows = (int64_t)p->batch * p->s1;
   if (rows == 0) return DSA_OK;
+  const DsaLiParams lp = dense_lse_as_li(p);
+  if (li_validate(&lp) == DSA_OK && li_takes_tensor_path(&lp)) {
+    // tcgen05 scoring kernel, then one reduction per row
+    int rc = li_launch<T>(&lp, scratch, st, status);
+    if (rc != DSA_OK) return rc;
+    sli_lse_rows_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d, scratch, li_score_ld(&lp));
+    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    count_launch();
+    return DSA_OK;
+  }
   d.di = scratch;
   if (cudaMemsetAsync(scratch, 0, (size_t)rows * p->s2 * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
   const int stride = p->d_idx + kSliPad;
@@ -515,7 +564,11 @@ int dsa_dense_li_lse_workspace_bytes(const DsaDenseLseParams* p, size_t* out_byt
   int st = dense_lse_validate(p);
   if (st != DSA_OK) return st;
   if (!out_bytes) return DSA_ERR_NULL;
-  *out_bytes = kWorkspaceHeader + (size_t)p->batch * p->s1 * p->s2 * 4;
+  const DsaLiParams lp = dense_lse_as_li(p);
+  size_t scores = (size_t)p->batch * p->s1 * p->s2 * 4;
+  if (li_validate(&lp) == DSA_OK)
+    scores = std::max(scores, (size_t)round_up(li_rows(&lp) * li_score_ld(&lp) * 4, 256));
+  *out_bytes = kWorkspaceHeader + scores;
   return DSA_OK;
 }
 
@@ -528,8 +581,8 @@ int dsa_dense_li_lse(const DsaDenseLseParams* p, void* workspace, size_t workspa
   cudaStream_t cs = (cudaStream_t)stream;
   if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
   float* scratch = reinterpret_cast<float*>((char*)workspace + kWorkspaceHeader);
-  if (p->dtype == DSA_DTYPE_BF16) return dense_lse_launch<__nv_bfloat16>(p, scratch, cs);
-  return dense_lse_launch<__half>(p, scratch, cs);
+  if (p->dtype == DSA_DTYPE_BF16) return dense_lse_launch<__nv_bfloat16>(p, scratch, (int32_t*)workspace, cs);
+  return dense_lse_launch<__half>(p, scratch, (int32_t*)workspace, cs);
 }
 
 int dsa_sli_grad_workspace_bytes(const DsaSliGradParams* p, size_t* out_bytes) {
@@ -552,8 +605,8 @@ int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_by
   cudaStream_t cs = (cudaStream_t)stream;
   if (cudaMemsetAsync(workspace, 0, kWorkspaceHeader, cs) != cudaSuccess) return DSA_ERR_CUDA;
   char* ws = (char*)workspace + kWorkspaceHeader;
-  if (p->dtype == DSA_DTYPE_BF16) return sli_grad_launch<__nv_bfloat16>(p, ws, cs);
-  return sli_grad_launch<__half>(p, ws, cs);
+  if (p->dtype == DSA_DTYPE_BF16) return sli_grad_launch<__nv_bfloat16>(p, ws, (int32_t*)workspace, cs);
+  return sli_grad_launch<__half>(p, ws, (int32_t*)workspace, cs);
 }
 
 // ---------------------------------------------------------------------------------------------

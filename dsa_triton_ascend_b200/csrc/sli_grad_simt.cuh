@@ -396,6 +396,31 @@ __global__ void __launch_bounds__(kSliThreads) sli_grad_kernel(SliGradDev p) {
   }
 }
 
+// Dense softmax statistics from a row-major fp32 score matrix (leading dimension ld) that holds the
+// index scores of every visible key of a row, as the indexer's scoring kernels leave them:
+// maximum and sum of exponentials over the visible prefix; -inf / 0 for rows that see no key.
+// grid = rows; block = 256.
+__global__ void __launch_bounds__(kSliThreads) sli_lse_rows_kernel(SliGradDev p, const float* __restrict__ scores,
+                                                                   int64_t ld) {
+  __shared__ float red8[kSliThreads / 32];
+  const int tid = threadIdx.x;
+  const int32_t row = blockIdx.x;
+  int32_t b;
+  const int32_t n = sli_row_slots(p, row, &b);
+  if (n == 0) {
+    if (tid == 0) { p.index_max[row] = -INFINITY; p.index_sum[row] = 0.f; }
+    return;
+  }
+  const float* s = scores + (int64_t)row * ld;
+  float m = -INFINITY;
+  for (int k = tid; k < n; k += kSliThreads) m = fmaxf(m, s[k]);
+  m = sli_block_reduce(m, red8, true);
+  float se = 0.f;
+  for (int k = tid; k < n; k += kSliThreads) se += expf(s[k] - m);
+  se = sli_block_reduce(se, red8, false);
+  if (tid == 0) { p.index_max[row] = m; p.index_sum[row] = se; }
+}
+
 // fp32 accumulator -> d_key_index; block 0 also adds up the rows' loss terms in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(256) sli_finalize_kernel(SliGradDev p, int64_t total, int32_t rows) {

@@ -239,7 +239,9 @@ int dsa_sli_grad(const DsaSliGradParams* p, void* workspace, size_t workspace_by
  * (dense_loss_backward_triton.py:344-420) behind `npu_dense_lightning_indexer_softmax_lse_triton`
  * (:773-802): per query row the maximum and the sum of exponentials over the causally visible keys
  * of I[k] = sum_g w[g] relu(query_index[g] . key_index[k]); -inf / 0 for rows that see no key.
- * Workspace: status header + the fp32 index scores [batch * s1, s2].
+ * Workspace: status header + the fp32 index scores [batch * s1, round_up(s2, 4)].  Shapes the
+ * tensor-core scoring kernel of dsa_li_forward takes (16..64 index heads, d_idx 128) run it, followed
+ * by one reduction per row; other shapes run CUDA-core kernels.
  */
 typedef struct DsaDenseLseParams {
   uint32_t struct_size; /* sizeof(DsaDenseLseParams) */
