@@ -110,6 +110,12 @@ static int li_launch(const DsaLiParams* p, float* scores, cudaStream_t st, int32
       }
       else { if (e == 1) DSA_TOPK_FAST(false, 1); else if (e == 2) DSA_TOPK_FAST(false, 2); else DSA_TOPK_FAST(false, 4); }
 #undef DSA_TOPK_FAST
+    } else if (rank16 && p->sparse_count <= kTopkThreads * 4) {
+      // longer rows, io-dtype ranking: the same histogram selection, streaming the row twice
+      const int e = p->sparse_count <= kTopkThreads ? 1 : (p->sparse_count <= 2 * kTopkThreads ? 2 : 4);
+      if (e == 1) li_topk_bins_stream_kernel<T, 1><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+      else if (e == 2) li_topk_bins_stream_kernel<T, 2><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
+      else li_topk_bins_stream_kernel<T, 4><<<(unsigned)rown, kTopkThreads, 0, st>>>(d, scores, ld);
     } else {
       int32_t cap = 1;
       while (cap < p->sparse_count) cap <<= 1;

@@ -771,4 +771,245 @@ __global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, 
   TOPK_PROF();   // 6: emit
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same selection for rows of any length (io-dtype ranking, sparse_count <= 2048): the keys do
+// not fit into registers, so the row is streamed twice from the score scratch (L2-resident at
+// decode sizes) - once to fill the histogram, once to drop the survivors into their bins - and a
+// composite is 64 bits (16-bit key | 32-bit ~position).  Everything else is li_topk_bins_kernel.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+struct BinScale {
+  float hiw, inv_w, gap_scale, pos_scale;
+  // bin of the score rounded to the io dtype, at position pos (monotone in (key desc, position asc))
+  __device__ __forceinline__ int32_t bin(T r, uint32_t pos) const {
+    const float x = to_f32<T>(r);
+    const uint32_t xb = __float_as_uint(x);
+    const float gap = __uint_as_float(xb & 0x7F800000u) * (((xb & 0x807FFFFFu) == 0u) ? 0.5f * gap_scale : gap_scale);
+    const float off = gap >= 2.f ? gap * ((float)pos * pos_scale) : 0.f;
+    return min(max(__float2int_rd(hiw - x * inv_w + off), 0), kBinCount - 1);
+  }
+};
+
+template <typename T, int E>
+__global__ void __launch_bounds__(kTopkThreads, 2) li_topk_bins_stream_kernel(LiDev p, const float* __restrict__ scores,
+                                                                           int64_t ld) {
+  constexpr int P2 = kTopkThreads * E;
+  constexpr int NW = kTopkThreads / 32;
+  __shared__ __align__(16) uint32_t hist[kBinCount];   // counts, then slot cursors
+  __shared__ uint64_t buf[P2];                         // survivors by bin, any order inside a bin
+  __shared__ uint16_t bbin[P2];                        // their bins
+  __shared__ uint64_t side[kBinSide];                  // members of the crossing bin
+  __shared__ uint32_t biglist[kBinBigList];
+  __shared__ float2 part[NW];
+  __shared__ uint32_t warp_tot[NW];
+  __shared__ uint32_t counters[72];
+  __shared__ uint32_t sh_bstar, sh_need, sh_cstar, sh_base, sh_side, sh_big;
+  __shared__ unsigned long long sh_cut;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t rown = blockIdx.x;
+  const int32_t row = rown / p.n2;
+  const RowInfo ri = row_info(p.seq, row);
+  const int32_t n = ri.visible;
+  const int32_t K = p.sparse_count;
+  const int32_t nsel = min(n, K);
+  int32_t* oi = p.out_indices + (int64_t)rown * K;
+  T* ov = (p.return_value && p.out_values != nullptr) ? (T*)p.out_values + (int64_t)rown * K : nullptr;
+  if (nsel == 0) {
+    for (int i = tid; i < K; i += kTopkThreads) {
+      oi[i] = -1;
+      if (ov) ov[i] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  const float* s = scores + (int64_t)rown * ld;
+  auto composite = [](uint32_t key16, uint32_t pos) -> uint64_t {
+    return ((uint64_t)key16 << 32) | (uint64_t)(0xFFFFFFFFu - pos);
+  };
+  // a survivor's final slot is known: position and value go straight to the outputs
+  auto emit = [&](uint32_t slot, uint64_t e) {
+    oi[slot] = (int32_t)(0xFFFFFFFFu - (uint32_t)e);
+    if (ov) ov[slot] = key16_bits<T>((uint32_t)(e >> 32));
+  };
+
+  // ---- 1. scale of the row from a sample of up to 512 scores spread over it
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(hist);
+    h4[2 * tid] = make_uint4(0, 0, 0, 0);
+    h4[2 * tid + 1] = make_uint4(0, 0, 0, 0);
+  }
+  if (tid < 72) counters[tid] = 0;
+  if (tid == 0) { sh_bstar = kBinCount; sh_need = 0; sh_cstar = 0; sh_base = 0; sh_side = 0; sh_big = 0; sh_cut = 0ull; }
+  BinScale<T> sc;
+  {
+    const int ns = min(n, kTopkThreads);
+    const bool in = tid < ns;
+    const int sp = n > kTopkThreads ? (int)(((int64_t)tid * n) >> 9) : tid;
+    const float x = in ? round_io<T>(s[sp]) : 0.f;
+    const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+    const float dv = (in && (tid ^ 1) < ns) ? fabsf(x - other) : 0.f;
+    const float2 tot = block_sum2_f32(x, dv, part);
+    const float mean = tot.x / (float)ns;
+    const float sdev = 0.9f * (tot.y / (float)ns);
+    float hi = mean + 5.f * sdev;
+    float inv_w = sdev > 0.f ? (float)kBinCount / (8.f * sdev) : 0.f;
+    if (!(fabsf(hi) <= 3.0e38f) || !(inv_w <= 3.0e38f)) { hi = 0.f; inv_w = 0.f; }
+    constexpr int kMantBits = std::is_same<T, __half>::value ? 10 : 7;
+    sc.hiw = hi * inv_w;
+    sc.inv_w = inv_w;
+    sc.gap_scale = inv_w * (1.f / (float)(1 << kMantBits));
+    sc.pos_scale = (63.f / 64.f) / (float)n;
+    if (!(fabsf(sc.hiw) <= 3.0e38f)) { sc.hiw = 0.f; sc.inv_w = 0.f; sc.gap_scale = 0.f; }
+  }
+
+  // ---- 2. first pass over the row: histogram (16-byte loads; rows start 16-byte aligned and are
+  // padded to a multiple of 4 scores)
+  for (int32_t pos0 = 4 * tid; pos0 < n; pos0 += 4 * kTopkThreads) {
+    const float4 v = *reinterpret_cast<const float4*>(s + pos0);
+    const float xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (pos0 + u < n) atomicAdd(&hist[sc.bin(from_f32<T>(xs[u]), (uint32_t)(pos0 + u))], 1u);
+  }
+  __syncthreads();
+
+  // ---- 3. slot at which every bin starts; the bin in which the count crosses K
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(hist);
+    uint4 a = h4[2 * tid], c = h4[2 * tid + 1];
+    uint32_t cnt[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+    uint32_t sum = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sum += cnt[q];
+    uint32_t inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    uint32_t run = inc - sum;
+    {
+      const uint32_t wt = warp_tot[lane & (NW - 1)];
+      uint32_t winc = wt;
+#pragma unroll
+      for (int o = 1; o < NW; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, winc, o);
+        if ((lane & (NW - 1)) >= o) winc += t;
+      }
+      run += __shfl_sync(0xffffffffu, winc - wt, warp);
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t c0 = cnt[q];
+      if (run < (uint32_t)K && (uint32_t)K <= run + c0) {
+        sh_bstar = 8 * tid + q; sh_base = run; sh_need = (uint32_t)K - run; sh_cstar = c0;
+      }
+      cnt[q] = run;
+      run += c0;
+    }
+    h4[2 * tid] = make_uint4(cnt[0], cnt[1], cnt[2], cnt[3]);
+    h4[2 * tid + 1] = make_uint4(cnt[4], cnt[5], cnt[6], cnt[7]);
+  }
+  __syncthreads();
+  const uint32_t bstar = sh_bstar, need = sh_need, cstar = sh_cstar, base_star = sh_base;
+  const bool side_cut = cstar <= (uint32_t)kBinSide;
+
+  // ---- 4. a large crossing bin is cut by bisection on the composite (one pass over the row per step)
+  uint64_t cut = 0ull;
+  if (bstar < (uint32_t)kBinCount && !side_cut) {
+    uint64_t lo = 1ull, hi_c = 0xFFFFFFFFFFFFull;
+    int slot = 0;
+#pragma unroll 1
+    for (int it = 0; it < 64 && lo < hi_c; ++it, ++slot) {
+      const uint64_t mid = lo + ((hi_c - lo) >> 1) + ((hi_c - lo) & 1ull);
+      uint32_t c = 0;
+      for (int32_t pos = tid; pos < n; pos += kTopkThreads) {
+        const T r = from_f32<T>(s[pos]);
+        c += (uint32_t)sc.bin(r, (uint32_t)pos) == bstar && composite(rank_key_of<T>(r), (uint32_t)pos) >= mid;
+      }
+      const uint32_t total = block_count(c, &counters[slot]);
+      if (total >= need) lo = mid; else hi_c = mid - 1ull;
+    }
+    cut = lo;
+  }
+
+  // ---- 5. second pass over the row: survivors into their bin's slot range
+  for (int32_t pos0 = 4 * tid; pos0 < n; pos0 += 4 * kTopkThreads) {
+    const float4 v = *reinterpret_cast<const float4*>(s + pos0);
+    const float xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t pos = (uint32_t)(pos0 + u);
+      if ((int32_t)pos >= n) continue;
+      const T r = from_f32<T>(xs[u]);
+      const uint32_t b = (uint32_t)sc.bin(r, pos);
+      if (b > bstar) continue;
+      const uint64_t comp = composite(rank_key_of<T>(r), pos);
+      if (b < bstar || (!side_cut && comp >= cut)) {
+        const uint32_t slot = atomicAdd(&hist[b], 1u);
+        if (slot < (uint32_t)P2) { buf[slot] = comp; bbin[slot] = (uint16_t)b; }
+      } else if (side_cut) {
+        side[atomicAdd(&sh_side, 1u)] = comp;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- 6. order inside each bin
+  {
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+      const int e = r * kTopkThreads + tid;
+      if (e < nsel && (!side_cut || (uint32_t)e < base_star || bstar == (uint32_t)kBinCount)) {
+        const uint64_t mine = buf[e];
+        const uint32_t b = bbin[e];
+        const uint32_t st = b ? hist[b - 1] : 0u;
+        const uint32_t cn = min(hist[b], (uint32_t)nsel) - st;
+        if (cn > (uint32_t)kBinSmall) {
+          if ((uint32_t)e == st) {
+            const uint32_t i = atomicAdd(&sh_big, 1u);
+            if (i < (uint32_t)kBinBigList) biglist[i] = b;
+          }
+        } else {
+          uint32_t rank = 0;
+          for (uint32_t q = st; q < st + cn; ++q) rank += buf[q] > mine;
+          emit(st + rank, mine);
+        }
+      }
+    }
+    if (side_cut && (uint32_t)tid < cstar) {
+      const uint64_t m = side[tid];
+      uint32_t rank = 0;
+      for (uint32_t q = 0; q < cstar; ++q) rank += side[q] > m;
+      if (rank < need) emit(base_star + rank, m);
+    }
+  }
+  __syncthreads();
+  {
+    const uint32_t nbig = min(sh_big, (uint32_t)kBinBigList);
+    for (uint32_t i = 0; i < nbig; ++i) {
+      const uint32_t b = biglist[i];
+      const uint32_t st = b ? hist[b - 1] : 0u;
+      const uint32_t en = min(hist[b], (uint32_t)nsel);
+      const bool shared_bin = en - st > 256u;
+      if (!shared_bin && (i % NW) != (uint32_t)warp) continue;
+      for (uint32_t m0 = st + (shared_bin ? 32u * warp : 0u); m0 < en; m0 += shared_bin ? 32u * NW : 32u) {
+        const uint32_t m = m0 + lane;
+        const uint64_t mine = m < en ? buf[m] : 0ull;
+        uint32_t rank = 0;
+        for (uint32_t q = st; q < en; ++q) rank += buf[q] > mine;
+        if (m < en) emit(st + rank, mine);
+      }
+    }
+  }
+
+  // ---- 7. unused slots
+  for (int i = nsel + tid; i < K; i += kTopkThreads) {
+    oi[i] = -1;
+    if (ov) ov[i] = from_f32<T>(0.f);
+  }
+}
+
 }  // namespace dsa

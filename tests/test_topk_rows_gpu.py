@@ -1,7 +1,8 @@
 """Ordered top-k on rows built to stress the selection: scores are set exactly (one non-zero product
 per head), so the expected order (score descending, position ascending) is known bit for bit.
 
-Covers what random normal data never shows the histogram-based kernel: every score equal, a handful
+Rows of up to 8192 keys run li_topk_bins_kernel, longer ones li_topk_bins_stream_kernel.
+Covers what random normal data never shows the histogram-based kernels: every score equal, a handful
 of distinct values (bins holding hundreds of ties), an outlier that dominates the row's scale,
 sign changes and zeros around the threshold, lengths at and next to sparse_count, fp16."""
 import numpy as np
@@ -50,7 +51,8 @@ def _bf16(x):
 
 
 @pytest.mark.parametrize("S2,K", [(8192, 2048), (8192, 512), (5000, 2048), (2048, 2048), (2049, 2048),
-                                  (2047, 2048), (300, 1024), (1, 64)])
+                                  (2047, 2048), (300, 1024), (1, 64),
+                                  (8193, 2048), (20000, 2048), (70001, 300)])   # longer rows: the streaming kernel
 def test_constructed_rows_select_and_order_exactly(S2, K):
     rng = np.random.RandomState(S2 + K)
     pos = np.arange(S2)
