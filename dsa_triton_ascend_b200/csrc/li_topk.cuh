@@ -456,6 +456,8 @@ __global__ void __launch_bounds__(kTopkThreads) li_topk_fast_kernel(LiDev p, con
 //     passes over all survivors of a radix sort.
 // Rows whose scores pile into few bins (all equal, or a scale dominated by outliers) stay correct:
 // bins of more than kBinSmall members are ordered by whole warps, members x members.
+// Four CTAs per SM (32 registers, a few spilled words): measured faster than three or two - the
+// phases are short dependent chains separated by block barriers, and more resident CTAs hide them.
 // ------------------------------------------------------------------------------------------------
 // Development aid, compiled only with -DDSA_TOPK_PROFILE: cycles per phase of one CTA (the row at
 // three quarters of the grid), read back with dsa_debug_topk_profile().
@@ -512,7 +514,7 @@ __device__ __forceinline__ uint32_t rank_key_of(T r) {
 }
 
 template <typename T, int E>
-__global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, const float* __restrict__ scores,
+__global__ void __launch_bounds__(kTopkThreads, 4) li_topk_bins_kernel(LiDev p, const float* __restrict__ scores,
                                                                     int64_t ld) {
   constexpr int P2 = kTopkThreads * E;
   constexpr int NW = kTopkThreads / 32;
@@ -544,6 +546,10 @@ __global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, 
     return;
   }
   const float* s = scores + (int64_t)rown * ld;
+  // groups of 4 * 512 positions that hold visible keys: the per-key loops below leave at the first
+  // group without one (a branch every thread of the block takes alike - predicated-off instructions
+  // of an unrolled loop still take issue slots, which is what this kernel is short of)
+  const int groups = (n + 4 * kTopkThreads - 1) / (4 * kTopkThreads);
   TOPK_PROF_DECL;
 
   // ---- 1. scale of the row from a sample of up to 512 scores spread over it: centre = their mean,
@@ -586,14 +592,16 @@ __global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, 
   const float tid4 = (float)(4 * tid);
   uint32_t key[kTopkFastKeys];   // key16 | bin << 16; 0 = no key at this position
 #pragma unroll
+  for (int g = 0; g < kTopkFastKeys; ++g) key[g] = 0u;
+#pragma unroll
   for (int g = 0; g < kTopkFastKeys / 4; ++g) {
+    if (g >= groups) break;
     const int pos0 = 4 * (g * kTopkThreads + tid);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (pos0 < n) v = *reinterpret_cast<const float4*>(s + pos0);
     const float xs[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      key[4 * g + u] = 0u;
       if (pos0 + u < n) {
         const T r = from_f32<T>(xs[u]);
         const float x = to_f32<T>(r);
@@ -682,6 +690,7 @@ __global__ void __launch_bounds__(kTopkThreads, 3) li_topk_bins_kernel(LiDev p, 
   // ---- 4. survivors into their bin's slot range (arrival order inside a bin)
 #pragma unroll
   for (int j = 0; j < kTopkFastKeys; ++j) {
+    if ((j >> 2) >= groups) break;
     const uint32_t b = key[j] >> 16;
     const uint32_t pos = 4 * ((j >> 2) * kTopkThreads + tid) + (j & 3);
     const uint32_t comp = (key[j] << 16) | (0xFFFFu - pos);
