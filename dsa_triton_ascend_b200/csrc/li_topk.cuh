@@ -590,9 +590,9 @@ __global__ void __launch_bounds__(kTopkThreads, 4) li_topk_bins_kernel(LiDev p, 
   constexpr int kMantBits = std::is_same<T, __half>::value ? 10 : 7;
   const float gap_scale = inv_w * (1.f / (float)(1 << kMantBits));
   const float tid4 = (float)(4 * tid);
-  uint32_t key[kTopkFastKeys];   // key16 | bin << 16; 0 = no key at this position
+  uint32_t key[kTopkFastKeys];   // key16 | bin << 16; bin 0xFFFF = no key at this position
 #pragma unroll
-  for (int g = 0; g < kTopkFastKeys; ++g) key[g] = 0u;
+  for (int g = 0; g < kTopkFastKeys; ++g) key[g] = 0xFFFF0000u;   // no key: a bin past every real one
 #pragma unroll
   for (int g = 0; g < kTopkFastKeys / 4; ++g) {
     if (g >= groups) break;
@@ -679,7 +679,7 @@ __global__ void __launch_bounds__(kTopkThreads, 4) li_topk_bins_kernel(LiDev p, 
       for (int j = 0; j < kTopkFastKeys; ++j) {
         const uint32_t pos = 4 * ((j >> 2) * kTopkThreads + tid) + (j & 3);
         const uint32_t comp = (key[j] << 16) | (0xFFFFu - pos);
-        c += (key[j] & 0xFFFFu) != 0u && (key[j] >> 16) == bstar && comp >= mid;
+        c += (key[j] >> 16) == bstar && comp >= mid;
       }
       const uint32_t total = block_count(c, &counters[slot]);
       if (total >= need) lo = mid; else hi_c = mid - 1u;
@@ -694,10 +694,11 @@ __global__ void __launch_bounds__(kTopkThreads, 4) li_topk_bins_kernel(LiDev p, 
     const uint32_t b = key[j] >> 16;
     const uint32_t pos = 4 * ((j >> 2) * kTopkThreads + tid) + (j & 3);
     const uint32_t comp = (key[j] << 16) | (0xFFFFu - pos);
-    if ((key[j] & 0xFFFFu) != 0u && b <= bstar) {
+    if (b <= bstar) {
       if (b < bstar || (!side_cut && comp >= cut)) {
         const uint32_t slot = atomicAdd(&hist[b], 1u);
-        if (slot < (uint32_t)P2) { buf[slot] = comp; bbin[slot] = (uint16_t)b; }
+        buf[slot] = comp;
+        bbin[slot] = (uint16_t)b;
       } else if (side_cut) {
         side[atomicAdd(&sh_side, 1u)] = comp;
       }
