@@ -376,15 +376,36 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
         index_done = true;
       }
     }
-    dim3 grid_t((unsigned)rows, (unsigned)(sli_att_chunks(d.n1, d.n2) + (index_done ? 0 : sli_idx_chunks(d.g))), 1);
-    sli_teacher_kernel<T><<<grid_t, kSliThreads, smem_a, st>>>(d, stride);
-    if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+    // Dense operator with fewer than 16 query heads per key head: blocks of 16 (row, head) pairs
+    // share the keys they walk over; the per-row kernel then only does the index side, if any.
+    const int grp = d.n1 / d.n2;
+    const bool pair_blocks = p->dense && grp < kSliHeads && kSliHeads % grp == 0;
+    if (pair_blocks) {
+      if (cudaFuncSetAttribute(sli_dense_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem_a) != cudaSuccess)
+        return DSA_ERR_CUDA;
+      const int rpb = kSliHeads / grp;
+      dim3 grid_d((unsigned)(p->batch * ((p->s1 + rpb - 1) / rpb)), (unsigned)d.n2, 1);
+      sli_dense_teacher_kernel<T><<<grid_d, kSliThreads, smem_a, st>>>(d, stride);
+      if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+      count_launch();
+    }
+    SliGradDev dt = d;
+    if (pair_blocks) dt.lse_only = 1;   // index chunks only
+    const unsigned chunks_t =
+        (unsigned)((pair_blocks ? 0 : sli_att_chunks(d.n1, d.n2)) + (index_done ? 0 : sli_idx_chunks(d.g)));
+    if (chunks_t > 0) {
+      dim3 grid_t((unsigned)rows, chunks_t, 1);
+      sli_teacher_kernel<T><<<grid_t, kSliThreads, smem_a, st>>>(dt, stride);
+      if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
+      count_launch();
+    }
     sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(d.g), 1);
     sli_grad_kernel<T><<<grid, kSliThreads, smem_b, st>>>(d);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
-    count_launch(3);
+    count_launch(2);
   }
   const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>((key_elems + 255) / 256, 148 * 16));
   sli_finalize_kernel<T><<<blocks, 256, 0, st>>>(d, key_elems, (int32_t)rows);

@@ -243,6 +243,71 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
   }
 }
 
+// Attention side of the dense operator when a key head serves fewer than 16 query heads (n1 / n2 in
+// {1, 2, 4, 8}; multi-head attention is 1).  The rows of a batch walk over the same keys, so a block
+// takes 16 / grp consecutive rows times the grp heads of one key head: 16 (row, head) pairs share each
+// staged block of 32 keys, where the per-row kernel above would fill only grp of its 16 head slots.
+// grid = (batch * ceil(s1 / (16 / grp)), n2); block = 256; dynamic smem as above.
+template <typename T>
+__global__ void __launch_bounds__(kSliThreads) sli_dense_teacher_kernel(SliGradDev p, int stride) {
+  extern __shared__ __align__(16) unsigned char sli_smem[];
+  T* qs = reinterpret_cast<T*>(sli_smem);
+  T* ks = qs + kSliHeads * stride;
+  __shared__ int64_t rows_s[kSliKeys];
+  __shared__ float max_s[kSliHeads], inv_s[kSliHeads];
+  __shared__ int32_t n_s[kSliHeads];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int grp = p.n1 / p.n2, rpb = kSliHeads / grp;
+  const int blocks_per_batch = (p.s1 + rpb - 1) / rpb;
+  const int32_t b = blockIdx.x / blocks_per_batch;
+  const int32_t pos0 = (blockIdx.x - b * blocks_per_batch) * rpb;
+  const int kv = blockIdx.y;
+  const int w = p.d + p.d_rope;
+
+  if (tid < kSliHeads) {
+    const int r = tid / grp, hh = tid - r * grp;
+    const int32_t pos = pos0 + r;
+    int32_t n = 0, bb;
+    if (pos < p.s1) n = sli_row_slots(p, b * p.s1 + pos, &bb);
+    n_s[tid] = n;
+    const int64_t si = (((int64_t)b * p.n2 + kv) * p.s1 + min(pos, p.s1 - 1)) * grp + hh;   // [batch, n2, s1, grp]
+    max_s[tid] = n > 0 ? p.softmax_max[si] : 0.f;
+    inv_s[tid] = n > 0 ? 1.f / (p.softmax_sum[si] + kSliEps) : 0.f;
+  }
+  for (int i = tid; i < kSliHeads * w; i += kSliThreads) {
+    const int m = i / w, c = i - m * w;
+    const int r = m / grp, hh = m - r * grp;
+    const int32_t pos = pos0 + r;
+    T v = from_f32<T>(0.f);
+    if (pos < p.s1) {
+      const int64_t qh = ((int64_t)b * p.s1 + pos) * p.n1 + kv * grp + hh;
+      v = c < p.d ? ((const T*)p.query)[qh * p.d + c] : ((const T*)p.query_rope)[qh * p.d_rope + (c - p.d)];
+    }
+    qs[m * stride + c] = v;
+  }
+  __syncthreads();
+  int32_t nmax = 0;
+#pragma unroll
+  for (int m = 0; m < kSliHeads; ++m) nmax = max(nmax, n_s[m]);
+  const int m0 = warp, m1 = warp + 8;
+  const int32_t n0 = n_s[m0], n1 = n_s[m1];
+  float* acc0 = p.p_buf + ((int64_t)b * p.s1 + pos0 + m0 / grp) * p.topk;
+  float* acc1 = p.p_buf + ((int64_t)b * p.s1 + pos0 + m1 / grp) * p.topk;
+  for (int32_t j0 = 0; j0 < nmax; j0 += kSliKeys) {
+    __syncthreads();   // the previous step is done with ks and rows_s
+    if (tid < kSliKeys) rows_s[tid] = j0 + tid < nmax ? (int64_t)b * p.s2 + j0 + tid : -1;
+    __syncthreads();
+    sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
+    __syncthreads();
+    float s0, s1;
+    sli_dots<T>(qs, ks, stride, w, &s0, &s1);
+    const int32_t j = j0 + lane;
+    if (j < n0) atomicAdd(&acc0[j], expf(s0 * p.scale - max_s[m0]) * inv_s[m0]);
+    if (j < n1) atomicAdd(&acc1[j], expf(s1 * p.scale - max_s[m1]) * inv_s[m1]);
+  }
+}
+
 // grid = rows; block = 256.  Student distribution from the row's index scores, dI = student - p and
 // the row's KL term; dI replaces the index scores in place.  With lse_only only the statistics.
 __global__ void __launch_bounds__(kSliThreads) sli_student_kernel(SliGradDev p) {

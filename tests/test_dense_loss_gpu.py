@@ -64,11 +64,15 @@ _CORE = [(1, 2, 64, 32, 32, d, g, di) for d in (128, 256, 512) for g in (32, 64,
 
 @pytest.mark.parametrize("B,S1,S2,N1,N2,D,G,Di", _CORE[::3] + [(1, 3, 96, 32, 32, 128, 32, 128),
                                                               (1, 4, 128, 32, 32, 128, 32, 128),
-                                                              (1, 64, 512, 64, 1, 512, 64, 128)])
+                                                              (1, 64, 512, 64, 1, 512, 64, 128),
+                                                              (2, 5, 80, 32, 16, 128, 32, 128),
+                                                              (1, 7, 64, 16, 4, 128, 32, 128),
+                                                              (1, 40, 256, 32, 32, 128, 32, 128)])
 @pytest.mark.parametrize("dtype", ["bf16", "fp16"])
 def test_dense_operators_against_the_oracle_on_the_reference_configurations(B, S1, S2, N1, N2, D, G, Di, dtype):
     """test_dense_loss_backward_triton.py:20-31 (every third of the 27 core configurations, the two
-    tail configurations) plus an MQA shape with more rows; statistics from the operators themselves,
+    tail configurations) plus an MQA shape with more rows, two grouped-query shapes and a multi-head
+    shape whose rows fill several blocks; statistics from the operators themselves,
     and the path that computes the index statistics internally gives the same result (:462-476)."""
     from dsa_triton_ascend_b200 import dense_lightning_indexer_softmax_lse_triton, dense_loss_backward_triton
     q, k, qr, kr, qi, ki, w = dense_loss_inputs(11, B, S1, S2, N1, N2, D, G, Di, dtype=dtype)
