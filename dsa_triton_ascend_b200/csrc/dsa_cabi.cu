@@ -14,6 +14,7 @@
 #include "sfa_fwd_simt.cuh"
 #include "sfa_fwd_sm100.cuh"
 #include "sfa_bwd_simt.cuh"
+#include "sfa_bwd_mma.cuh"
 #include "sli_grad_simt.cuh"
 
 namespace dsa {
@@ -236,7 +237,9 @@ static int sfa_grad_validate(const DsaSfaGradParams* p) {
   if (p->sparse_count < 1 || p->key_rows < 0) return DSA_ERR_VALUE;
   if (p->layout_q == DSA_LAYOUT_TND && (!p->seq_q || !p->seq_q_cumulative)) return DSA_ERR_VALUE;
   if (p->layout_kv == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
-  if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE) return DSA_ERR_UNSUPPORTED;
+  if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE && p->kernel != DSA_KERNEL_TENSOR)
+    return DSA_ERR_UNSUPPORTED;
+  if (p->kernel == DSA_KERNEL_TENSOR && p->d != kSfaMmaD) return DSA_ERR_UNSUPPORTED;
   return DSA_OK;
 }
 
@@ -261,13 +264,23 @@ static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t s
   d.sparse_count = p->sparse_count; d.sparse_block_size = p->sparse_block_size;
   d.scale = p->scale;
   if (d.rows > 0) {
-    const size_t smem = sfa_grad_smem_bytes(p->d, p->d_rope, sizeof(T));
-    if (cudaFuncSetAttribute(sfa_bwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return DSA_ERR_CUDA;
     const unsigned gy = (unsigned)((p->n1 + kSfaGradHeads - 1) / kSfaGradHeads);
     dim3 grid((unsigned)d.rows, gy, 1);
-    sfa_bwd_simt_kernel<T><<<grid, kSfaGradThreads, smem, st>>>(d);
+    // D = 512: the contractions run on the tensor cores (mma.sync); other widths, or on request, the
+    // CUDA-core kernel
+    if (p->d == kSfaMmaD && p->kernel != DSA_KERNEL_PORTABLE) {
+      const size_t smem = sfa_grad_mma_smem_bytes(sizeof(T));
+      if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess)
+        return DSA_ERR_CUDA;
+      sfa_bwd_mma_kernel<T><<<grid, kSfaGradThreads, smem, st>>>(d);
+    } else {
+      const size_t smem = sfa_grad_smem_bytes(p->d, p->d_rope, sizeof(T));
+      if (cudaFuncSetAttribute(sfa_bwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess)
+        return DSA_ERR_CUDA;
+      sfa_bwd_simt_kernel<T><<<grid, kSfaGradThreads, smem, st>>>(d);
+    }
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     count_launch();
   }

@@ -1,0 +1,359 @@
+// Sparse flash attention backward with the five contractions of a key chunk on the warp-level tensor
+// core instructions (mma.sync m16n8k16, fp32 accumulation), for D = 512, D_rope = 64.  Same math and
+// the same block shape as sfa_bwd_simt_kernel (sparse_flash_attention_grad_triton.py:100-470, golden
+// sparse_flash_attention_grad_numpy.py:96-135): one block per (query row, 16 heads) walks over the
+// row's selected keys 32 at a time,
+//     S  = q . k^T (576 columns)          dP = dO . k_nope^T (512 columns)
+//     P  = exp(S * scale - max) / sum     dS = P * (dP - delta) * scale
+//     dQ += dS . k        dK += dS^T . q        dV += P^T . dO
+// q, k and dO are multiplied as the io dtype they arrive in (exact products, fp32 sums).  P and dS
+// are fp32 values: each is split into a high and a low io-dtype part (x = hi + lo up to 2^-16
+// relative for bf16, 2^-22 for fp16) and every product with them runs twice, so the result carries
+// fp32-like precision where the reference rounds P and dS to the io dtype once.  dK / dV leave the
+// block as 16-byte fp32 reductions into the accumulators that sfa_bwd_finalize_kernel rounds.
+#pragma once
+
+#include "sfa_bwd_simt.cuh"
+
+namespace dsa {
+
+constexpr int kSfaMmaD = 512, kSfaMmaDr = 64, kSfaMmaDq = kSfaMmaD + kSfaMmaDr;
+constexpr int kSfaMmaStride = kSfaMmaDq + kSfaGradPad;    // q / key rows, elements
+constexpr int kSfaMmaDStride = kSfaMmaD + kSfaGradPad;    // dO rows
+constexpr int kSfaMmaPk = kSfaGradKeys + 8;               // [head][key] operand rows (40 elements)
+constexpr int kSfaMmaPh = kSfaGradHeads + 8;              // [key][head] operand rows (24 elements)
+
+inline size_t sfa_grad_mma_smem_bytes(size_t elem) {
+  return ((size_t)(kSfaGradHeads + kSfaGradKeys) * kSfaMmaStride + (size_t)kSfaGradHeads * kSfaMmaDStride) * elem;
+}
+
+template <typename T>
+constexpr bool kIsBf16 = false;
+template <>
+constexpr bool kIsBf16<__nv_bfloat16> = true;
+
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// B fragment (16 x 8, k x n) of a row-major [k][n] tile in shared memory: rows k0 .. k0+15 start at
+// `row0` (16-byte aligned, `stride` elements apart), columns n0 .. n0+7.
+template <typename T>
+__device__ __forceinline__ void ldmatrix_b_trans(uint32_t& b0, uint32_t& b1, const T* row0, int stride) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row0 + (lane & 15) * stride);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+}
+
+// A fragment (16 x 16, row-major rows m0 .. m0+15, columns k0 .. k0+15) by 32-bit loads.
+template <typename T>
+__device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const T* base, int stride, int m0, int k0) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  a[0] = *reinterpret_cast<const uint32_t*>(&base[(m0 + g) * stride + k0 + 2 * c]);
+  a[1] = *reinterpret_cast<const uint32_t*>(&base[(m0 + g + 8) * stride + k0 + 2 * c]);
+  a[2] = *reinterpret_cast<const uint32_t*>(&base[(m0 + g) * stride + k0 + 8 + 2 * c]);
+  a[3] = *reinterpret_cast<const uint32_t*>(&base[(m0 + g + 8) * stride + k0 + 8 + 2 * c]);
+}
+
+// Adds the 16 x 8 accumulator tile (rows -> key rows krow_lo / krow_hi of this lane's two rows,
+// columns col0 .. col0+7 of a row of `width` floats) into `acc`: lanes pair up so that each issues
+// one 16-byte reduction.
+__device__ __forceinline__ void red_tile(float* acc, int width, int64_t krow_lo, int64_t krow_hi, int col0,
+                                         const float (&c)[4]) {
+  const int lane = threadIdx.x & 31, cc = lane & 3;
+  const bool odd = lane & 1;
+  const float s0 = odd ? c[0] : c[2], s1 = odd ? c[1] : c[3];
+  const float r0 = __shfl_xor_sync(0xffffffffu, s0, 1), r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+  const int col = col0 + 2 * (cc & ~1);
+  if (!odd) {
+    if (krow_lo >= 0) red_add_v4(acc + krow_lo * width + col, c[0], c[1], r0, r1);
+  } else {
+    if (krow_hi >= 0) red_add_v4(acc + krow_hi * width + col, r0, r1, c[2], c[3]);
+  }
+}
+
+// grid = (rows, ceil(n1 / 16)); block = 256 threads, two blocks per SM.
+// dynamic smem: q [16][584] | keys [32][584] | dO [16][520], elements of T.
+template <typename T>
+__global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGradDev p) {
+  extern __shared__ __align__(16) unsigned char sfa_grad_smem[];
+  T* qs = reinterpret_cast<T*>(sfa_grad_smem);
+  T* ks = qs + kSfaGradHeads * kSfaMmaStride;
+  T* dos = ks + kSfaGradKeys * kSfaMmaStride;
+  __shared__ float ps_f[kSfaGradHeads][kSfaGradKeys + 1];
+  __shared__ float dp_f[kSfaGradHeads][kSfaGradKeys + 1];
+  __shared__ __align__(16) T ds_hi[kSfaGradHeads * kSfaMmaPk], ds_lo[kSfaGradHeads * kSfaMmaPk];   // [head][key]
+  __shared__ __align__(16) T dst_hi[kSfaGradKeys * kSfaMmaPh], dst_lo[kSfaGradKeys * kSfaMmaPh];   // [key][head]
+  __shared__ __align__(16) T pt_hi[kSfaGradKeys * kSfaMmaPh], pt_lo[kSfaGradKeys * kSfaMmaPh];     // [key][head]
+  __shared__ float delta_s[kSfaGradHeads], max_s[kSfaGradHeads], sum_s[kSfaGradHeads];
+  __shared__ float red_s[kSfaGradThreads / 32];
+  __shared__ int32_t tok_s[kSfaGradKeys];
+  __shared__ int64_t krow_s[kSfaGradKeys];
+
+  constexpr bool kScaled = sizeof(T) == 2 && !kIsBf16<T>;   // fp16: operands of the second products are scaled
+  int dq_exp = 127;                                         // acc holds d_query * 2^dq_exp (fp16 only)
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int32_t row = blockIdx.x;
+  const int32_t h0 = blockIdx.y * kSfaGradHeads;
+  const RowInfo ri = row_info(p.seq, row);
+  const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
+
+  // d_query accumulator: 9 column tiles of 8 per warp (warp w: columns 72 w .. 72 w + 71 of nope|rope)
+  float acc[9][4];
+#pragma unroll
+  for (int t = 0; t < 9; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+
+  if (row_active) {
+    const T* qn = (const T*)p.query + (int64_t)row * p.n1 * kSfaMmaD;
+    const T* qr = (const T*)p.query_rope + (int64_t)row * p.n1 * kSfaMmaDr;
+    const T* dout = (const T*)p.d_out + (int64_t)row * p.n1 * kSfaMmaD;
+    for (int i = tid; i < kSfaGradHeads * (kSfaMmaDq / 8); i += kSfaGradThreads) {
+      const int h = i / (kSfaMmaDq / 8), ch = i - h * (kSfaMmaDq / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h0 + h < p.n1)
+        v = ch < kSfaMmaD / 8 ? reinterpret_cast<const uint4*>(qn + (int64_t)(h0 + h) * kSfaMmaD)[ch]
+                              : reinterpret_cast<const uint4*>(qr + (int64_t)(h0 + h) * kSfaMmaDr)[ch - kSfaMmaD / 8];
+      *reinterpret_cast<uint4*>(&qs[h * kSfaMmaStride + ch * 8]) = v;
+    }
+    for (int i = tid; i < kSfaGradHeads * (kSfaMmaD / 8); i += kSfaGradThreads) {
+      const int h = i / (kSfaMmaD / 8), ch = i - h * (kSfaMmaD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h0 + h < p.n1) v = reinterpret_cast<const uint4*>(dout + (int64_t)(h0 + h) * kSfaMmaD)[ch];
+      *reinterpret_cast<uint4*>(&dos[h * kSfaMmaDStride + ch * 8]) = v;
+    }
+    // delta = dO . O per head (16 threads per head), and the forward statistics
+    {
+      const int ah = tid >> 4;
+      float part = 0.f;
+      if (h0 + ah < p.n1) {
+        const T* o = (const T*)p.out + ((int64_t)row * p.n1 + h0 + ah) * kSfaMmaD;
+        const T* gd = dout + (int64_t)(h0 + ah) * kSfaMmaD;
+        for (int cc = tid & 15; cc < kSfaMmaD; cc += 16) part = fmaf(to_f32<T>(gd[cc]), to_f32<T>(o[cc]), part);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if ((tid & 15) == 0) {
+        const bool hv = h0 + ah < p.n1;
+        delta_s[ah] = part;
+        max_s[ah] = hv ? p.softmax_max[(int64_t)row * p.n1 + h0 + ah] : 0.f;
+        sum_s[ah] = hv ? p.softmax_sum[(int64_t)row * p.n1 + h0 + ah] : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+
+  const int32_t* idx_row = p.sparse_indices + (int64_t)row * p.sparse_count;
+  const int32_t slots = row_active ? p.sparse_count * p.sparse_block_size : 0;
+  const T* kn = (const T*)p.key;
+  const T* kr = (const T*)p.key_rope;
+
+  for (int32_t j0 = 0; j0 < slots; j0 += kSfaGradKeys) {
+    int any = 0;
+    if (tid < kSfaGradKeys) {
+      const int32_t j = j0 + tid;
+      const int32_t tok = j < slots ? sfa_slot_token(p.seq, p.sparse_block_size, ri, idx_row, j) : -1;
+      const int64_t r = tok >= 0 ? key_row(p.seq, ri, tok) : -1;
+      tok_s[tid] = r >= 0 ? tok : -1;
+      krow_s[tid] = r;
+      any = r >= 0;
+    }
+    if (!__syncthreads_or(any)) continue;
+
+    // gather the rows (16-byte chunks), zeros for slots without a key
+    {
+      constexpr int cn = kSfaMmaD / 8, ct = kSfaMmaDq / 8;
+      for (int i = tid; i < kSfaGradKeys * ct; i += kSfaGradThreads) {
+        const int k = i / ct, ch = i - k * ct;
+        const int64_t kr_ = krow_s[k];
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (kr_ >= 0)
+          v = ch < cn ? reinterpret_cast<const uint4*>(kn + kr_ * kSfaMmaD)[ch]
+                      : reinterpret_cast<const uint4*>(kr + kr_ * kSfaMmaDr)[ch - cn];
+        *reinterpret_cast<uint4*>(&ks[k * kSfaMmaStride + ch * 8]) = v;
+      }
+    }
+    __syncthreads();
+
+    // warps 0-3: S tile of keys 8 w .. 8 w + 7 -> P;  warps 4-7: dP tile of keys 8 (w-4) ..
+    {
+      const bool is_s = warp < 4;
+      const int n0 = (warp & 3) * 8;
+      const T* a_base = is_s ? qs : dos;
+      const int a_stride = is_s ? kSfaMmaStride : kSfaMmaDStride;
+      const int ksteps = is_s ? kSfaMmaDq / 16 : kSfaMmaD / 16;
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+      const T* brow = &ks[(n0 + g) * kSfaMmaStride + 2 * c];
+      for (int s = 0; s < ksteps; s += 2) {
+        uint32_t a[4];
+        load_a_frag<T>(a, a_base, a_stride, 0, s * 16);
+        mma_16816<T>(c0, a, *reinterpret_cast<const uint32_t*>(brow + s * 16),
+                     *reinterpret_cast<const uint32_t*>(brow + s * 16 + 8));
+        load_a_frag<T>(a, a_base, a_stride, 0, s * 16 + 16);
+        mma_16816<T>(c1, a, *reinterpret_cast<const uint32_t*>(brow + s * 16 + 16),
+                     *reinterpret_cast<const uint32_t*>(brow + s * 16 + 24));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = g + (e >> 1) * 8, k = n0 + 2 * c + (e & 1);
+        const float v = c0[e] + c1[e];
+        if (is_s) {
+          const float l = sum_s[h];
+          ps_f[h][k] = (tok_s[k] >= 0 && l > 0.f) ? expf(v * p.scale - max_s[h]) / l : 0.f;
+        } else {
+          dp_f[h][k] = v;
+        }
+      }
+    }
+    __syncthreads();
+
+    // dS, and both P and dS as high + low io-dtype parts in the layouts the products below read.
+    // fp16 has a narrow exponent range: P (at most 1) is scaled by 2^13 and dS by a power of two that
+    // brings the chunk's largest |dS| to about 2^13, so that neither part under- or overflows; the
+    // products are scaled back in fp32 (dq_exp / dk_down below).
+    float dk_down = 1.f, p_up = 1.f;
+    {
+      float pv[2], dsv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = tid + u * kSfaGradThreads, h = i >> 5, k = i & 31;
+        pv[u] = ps_f[h][k];
+        dsv[u] = pv[u] * (dp_f[h][k] - delta_s[h]) * p.scale;
+      }
+      float up_k = 1.f, up_q = 1.f;
+      if constexpr (kScaled) {
+        float m = fmaxf(fabsf(dsv[0]), fabsf(dsv[1]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red_s[warp] = m;
+        __syncthreads();
+        m = red_s[0];
+#pragma unroll
+        for (int wv = 1; wv < kSfaGradThreads / 32; ++wv) m = fmaxf(m, red_s[wv]);
+        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : 0;
+        e = max(-100, min(100, e));
+        if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
+          const float f = scalbnf(1.f, e - dq_exp);
+#pragma unroll
+          for (int t = 0; t < 9; ++t)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[t][x] *= f;
+          dq_exp = e;
+        }
+        up_k = scalbnf(1.f, e);
+        up_q = scalbnf(1.f, dq_exp);
+        dk_down = scalbnf(1.f, -e);
+        p_up = 8192.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = tid + u * kSfaGradThreads, h = i >> 5, k = i & 31;
+        const float pp = pv[u] * p_up, dk_ = dsv[u] * up_k, dq_ = dsv[u] * up_q;
+        const T ph = from_f32<T>(pp), kh = from_f32<T>(dk_), qh = from_f32<T>(dq_);
+        pt_hi[k * kSfaMmaPh + h] = ph;
+        pt_lo[k * kSfaMmaPh + h] = from_f32<T>(pp - to_f32<T>(ph));
+        dst_hi[k * kSfaMmaPh + h] = kh;
+        dst_lo[k * kSfaMmaPh + h] = from_f32<T>(dk_ - to_f32<T>(kh));
+        ds_hi[h * kSfaMmaPk + k] = qh;
+        ds_lo[h * kSfaMmaPk + k] = from_f32<T>(dq_ - to_f32<T>(qh));
+      }
+    }
+    __syncthreads();
+
+    // d_query (nope | rope) += dS . k : 16 heads x 72 columns per warp, 32 keys deep
+#pragma unroll
+    for (int k0 = 0; k0 < kSfaGradKeys; k0 += 16) {
+      uint32_t ah[4], al[4];
+      load_a_frag<T>(ah, ds_hi, kSfaMmaPk, 0, k0);
+      load_a_frag<T>(al, ds_lo, kSfaMmaPk, 0, k0);
+#pragma unroll
+      for (int t = 0; t < 9; ++t) {
+        uint32_t b0, b1;
+        ldmatrix_b_trans<T>(b0, b1, &ks[k0 * kSfaMmaStride + (warp * 9 + t) * 8], kSfaMmaStride);
+        mma_16816<T>(acc[t], ah, b0, b1);
+        mma_16816<T>(acc[t], al, b0, b1);
+      }
+    }
+
+    // d_key (nope | rope) += dS^T . q : 32 keys x 72 columns per warp, 16 heads deep
+    {
+      uint32_t ah[2][4], al[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        load_a_frag<T>(ah[mt], dst_hi, kSfaMmaPh, mt * 16, 0);
+        load_a_frag<T>(al[mt], dst_lo, kSfaMmaPh, mt * 16, 0);
+      }
+      for (int t = 0; t < 9; ++t) {
+        const int n0 = (warp * 9 + t) * 8;
+        uint32_t b0, b1;
+        ldmatrix_b_trans<T>(b0, b1, &qs[n0], kSfaMmaStride);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          float cf[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_16816<T>(cf, ah[mt], b0, b1);
+          mma_16816<T>(cf, al[mt], b0, b1);
+          if constexpr (kScaled) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) cf[x] *= dk_down;
+          }
+          red_tile(p.dk_acc, kSfaMmaDq, krow_s[mt * 16 + g], krow_s[mt * 16 + g + 8], n0, cf);
+        }
+      }
+      // d_value += P^T . dO : 32 keys x 64 columns per warp
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        load_a_frag<T>(ah[mt], pt_hi, kSfaMmaPh, mt * 16, 0);
+        load_a_frag<T>(al[mt], pt_lo, kSfaMmaPh, mt * 16, 0);
+      }
+      for (int t = 0; t < 8; ++t) {
+        const int n0 = (warp * 8 + t) * 8;
+        uint32_t b0, b1;
+        ldmatrix_b_trans<T>(b0, b1, &dos[n0], kSfaMmaDStride);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          float cf[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_16816<T>(cf, ah[mt], b0, b1);
+          mma_16816<T>(cf, al[mt], b0, b1);
+          if constexpr (kScaled) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) cf[x] *= (1.f / 8192.f);
+          }
+          red_tile(p.dv_acc, kSfaMmaD, krow_s[mt * 16 + g], krow_s[mt * 16 + g + 8], n0, cf);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // d_query / d_query_rope of this head chunk (zeros for inactive rows)
+  const float dq_down = kScaled ? scalbnf(1.f, -dq_exp) : 1.f;
+#pragma unroll
+  for (int t = 0; t < 9; ++t) {
+    const int col = (warp * 9 + t) * 8 + 2 * c;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int h = g + half * 8;
+      if (h0 + h >= p.n1) continue;
+      const int64_t qh = (int64_t)row * p.n1 + h0 + h;
+      T* dst = col < kSfaMmaD ? (T*)p.d_query + qh * kSfaMmaD + col : (T*)p.d_query_rope + qh * kSfaMmaDr + (col - kSfaMmaD);
+      dst[0] = from_f32<T>(acc[t][2 * half] * dq_down);
+      dst[1] = from_f32<T>(acc[t][2 * half + 1] * dq_down);
+    }
+  }
+}
+
+}  // namespace dsa

@@ -20,6 +20,15 @@ _VALID_D = (128, 256, 512)
 _D_ROPE = 64
 
 
+_kernel = _cabi.KERNEL_AUTO
+
+
+def set_kernel(kind):
+    """"auto", "portable" (CUDA-core kernel) or "tensor" (mma.sync kernel for D = 512, error otherwise)."""
+    global _kernel
+    _kernel = {"auto": _cabi.KERNEL_AUTO, "portable": _cabi.KERNEL_PORTABLE, "tensor": _cabi.KERNEL_TENSOR}[kind]
+
+
 def sparse_flash_attention_grad_triton(
     query,
     key,
@@ -127,7 +136,7 @@ def sparse_flash_attention_grad_triton(
 
     p = _cabi.DsaSfaGradParams()
     p.struct_size = ctypes.sizeof(_cabi.DsaSfaGradParams)
-    p.kernel = _cabi.KERNEL_AUTO
+    p.kernel = _kernel
     p.query, p.query_rope, p.key, p.key_rope = ptr(query), ptr(query_rope), ptr(key), ptr(key_rope)
     p.sparse_indices = ptr(sparse_indices)
     p.d_out, p.out = ptr(d_out), ptr(out)
