@@ -57,6 +57,12 @@ __device__ __forceinline__ void ldmatrix_b_trans(uint32_t& b0, uint32_t& b1, con
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
 // A fragment (16 x 16, row-major rows m0 .. m0+15, columns k0 .. k0+15) by 32-bit loads.
 template <typename T>
 __device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const T* base, int stride, int m0, int k0) {
@@ -99,8 +105,8 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
   __shared__ __align__(16) T pt_hi[kSfaGradKeys * kSfaMmaPh], pt_lo[kSfaGradKeys * kSfaMmaPh];     // [key][head]
   __shared__ float delta_s[kSfaGradHeads], max_s[kSfaGradHeads], sum_s[kSfaGradHeads];
   __shared__ float red_s[kSfaGradThreads / 32];
-  __shared__ int32_t tok_s[kSfaGradKeys];
-  __shared__ int64_t krow_s[kSfaGradKeys];
+  __shared__ int32_t tok_s[2][kSfaGradKeys];
+  __shared__ int64_t krow_s[2][kSfaGradKeys];
 
   constexpr bool kScaled = sizeof(T) == 2 && !kIsBf16<T>;   // fp16: operands of the second products are scaled
   int dq_exp = 127;                                         // acc holds d_query * 2^dq_exp (fp16 only)
@@ -162,31 +168,47 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
   const T* kn = (const T*)p.key;
   const T* kr = (const T*)p.key_rope;
 
-  for (int32_t j0 = 0; j0 < slots; j0 += kSfaGradKeys) {
+  // Slot tables are double-buffered and the keys of the next chunk that holds a key are fetched with
+  // cp.async while the current chunk's d_key / d_value products (which do not read `ks`) run.
+  auto fill_slots = [&](int32_t j0, int buf) -> int {
     int any = 0;
     if (tid < kSfaGradKeys) {
       const int32_t j = j0 + tid;
       const int32_t tok = j < slots ? sfa_slot_token(p.seq, p.sparse_block_size, ri, idx_row, j) : -1;
       const int64_t r = tok >= 0 ? key_row(p.seq, ri, tok) : -1;
-      tok_s[tid] = r >= 0 ? tok : -1;
-      krow_s[tid] = r;
+      tok_s[buf][tid] = r >= 0 ? tok : -1;
+      krow_s[buf][tid] = r;
       any = r >= 0;
     }
-    if (!__syncthreads_or(any)) continue;
-
-    // gather the rows (16-byte chunks), zeros for slots without a key
-    {
-      constexpr int cn = kSfaMmaD / 8, ct = kSfaMmaDq / 8;
-      for (int i = tid; i < kSfaGradKeys * ct; i += kSfaGradThreads) {
-        const int k = i / ct, ch = i - k * ct;
-        const int64_t kr_ = krow_s[k];
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (kr_ >= 0)
-          v = ch < cn ? reinterpret_cast<const uint4*>(kn + kr_ * kSfaMmaD)[ch]
-                      : reinterpret_cast<const uint4*>(kr + kr_ * kSfaMmaDr)[ch - cn];
-        *reinterpret_cast<uint4*>(&ks[k * kSfaMmaStride + ch * 8]) = v;
-      }
+    return any;
+  };
+  // First chunk at or after j0 with a key: its slot table goes to `buf`; returns its start or `slots`.
+  auto next_chunk = [&](int32_t j0, int buf) -> int32_t {
+    while (j0 < slots) {
+      if (__syncthreads_or(fill_slots(j0, buf))) break;
+      j0 += kSfaGradKeys;
     }
+    return j0;
+  };
+  auto gather_async = [&](int buf) {
+    constexpr int cn = kSfaMmaD / 8, ct = kSfaMmaDq / 8;
+    for (int i = tid; i < kSfaGradKeys * ct; i += kSfaGradThreads) {
+      const int k = i / ct, ch = i - k * ct;
+      const int64_t kr_ = krow_s[buf][k];
+      const T* src = kn;
+      if (kr_ >= 0) src = ch < cn ? kn + kr_ * kSfaMmaD + ch * 8 : kr + kr_ * kSfaMmaDr + (ch - cn) * 8;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&ks[k * kSfaMmaStride + ch * 8]);
+      const int bytes = kr_ >= 0 ? 16 : 0;     // 0: the 16 bytes are zero-filled
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int buf = 0;
+  int32_t j0 = next_chunk(0, buf);
+  if (j0 < slots) gather_async(buf);
+  while (j0 < slots) {
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
 
     // warps 0-3: S tile of keys 8 w .. 8 w + 7 -> P;  warps 4-7: dP tile of keys 8 (w-4) ..
@@ -196,24 +218,37 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
       const T* a_base = is_s ? qs : dos;
       const int a_stride = is_s ? kSfaMmaStride : kSfaMmaDStride;
       const int ksteps = is_s ? kSfaMmaDq / 16 : kSfaMmaD / 16;
-      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-      const T* brow = &ks[(n0 + g) * kSfaMmaStride + 2 * c];
-      for (int s = 0; s < ksteps; s += 2) {
-        uint32_t a[4];
-        load_a_frag<T>(a, a_base, a_stride, 0, s * 16);
-        mma_16816<T>(c0, a, *reinterpret_cast<const uint32_t*>(brow + s * 16),
-                     *reinterpret_cast<const uint32_t*>(brow + s * 16 + 8));
-        load_a_frag<T>(a, a_base, a_stride, 0, s * 16 + 16);
-        mma_16816<T>(c1, a, *reinterpret_cast<const uint32_t*>(brow + s * 16 + 16),
-                     *reinterpret_cast<const uint32_t*>(brow + s * 16 + 24));
+      float cs[4][4];     // four independent accumulation chains
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) cs[u][e] = 0.f;
+      // ldmatrix addresses: A = 16 heads x 16 columns per step (four 8x8 blocks: rows 0-7 / 8-15 of
+      // columns k0.. and k0+8..), B = keys n0..n0+7 x 32 columns per two steps
+      const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(
+          a_base + ((lane & 7) + ((lane >> 3) & 1) * 8) * a_stride + (lane >> 4) * 8);
+      const uint32_t b_addr =
+          (uint32_t)__cvta_generic_to_shared(&ks[(n0 + (lane & 7)) * kSfaMmaStride + (lane >> 3) * 8]);
+      for (int s = 0; s < ksteps; s += 4) {
+        uint32_t a[4][4], b[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) ldmatrix_x4(a[u], a_addr + (s + u) * 16 * (int)sizeof(T));
+#pragma unroll
+        for (int u = 0; u < 4; u += 2) {
+          uint32_t r[4];
+          ldmatrix_x4(r, b_addr + (s + u) * 16 * (int)sizeof(T));
+          b[u][0] = r[0]; b[u][1] = r[1]; b[u + 1][0] = r[2]; b[u + 1][1] = r[3];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mma_16816<T>(cs[u], a[u], b[u][0], b[u][1]);
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = g + (e >> 1) * 8, k = n0 + 2 * c + (e & 1);
-        const float v = c0[e] + c1[e];
+        const float v = (cs[0][e] + cs[1][e]) + (cs[2][e] + cs[3][e]);
         if (is_s) {
           const float l = sum_s[h];
-          ps_f[h][k] = (tok_s[k] >= 0 && l > 0.f) ? expf(v * p.scale - max_s[h]) / l : 0.f;
+          ps_f[h][k] = (tok_s[buf][k] >= 0 && l > 0.f) ? expf(v * p.scale - max_s[h]) / l : 0.f;
         } else {
           dp_f[h][k] = v;
         }
@@ -289,6 +324,11 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
       }
     }
 
+    // look for the next chunk and, once every warp is done with `ks` (the barrier inside), start
+    // fetching its keys
+    const int32_t jn = next_chunk(j0 + kSfaGradKeys, buf ^ 1);
+    if (jn < slots) gather_async(buf ^ 1);
+
     // d_key (nope | rope) += dS^T . q : 32 keys x 72 columns per warp, 16 heads deep
     {
       uint32_t ah[2][4], al[2][4];
@@ -310,7 +350,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
 #pragma unroll
             for (int x = 0; x < 4; ++x) cf[x] *= dk_down;
           }
-          red_tile(p.dk_acc, kSfaMmaDq, krow_s[mt * 16 + g], krow_s[mt * 16 + g + 8], n0, cf);
+          red_tile(p.dk_acc, kSfaMmaDq, krow_s[buf][mt * 16 + g], krow_s[buf][mt * 16 + g + 8], n0, cf);
         }
       }
       // d_value += P^T . dO : 32 keys x 64 columns per warp
@@ -332,11 +372,12 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
 #pragma unroll
             for (int x = 0; x < 4; ++x) cf[x] *= (1.f / 8192.f);
           }
-          red_tile(p.dv_acc, kSfaMmaD, krow_s[mt * 16 + g], krow_s[mt * 16 + g + 8], n0, cf);
+          red_tile(p.dv_acc, kSfaMmaD, krow_s[buf][mt * 16 + g], krow_s[buf][mt * 16 + g + 8], n0, cf);
         }
       }
     }
-    __syncthreads();
+    j0 = jn;
+    buf ^= 1;
   }
 
   // d_query / d_query_rope of this head chunk (zeros for inactive rows)
