@@ -269,11 +269,20 @@ static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t s
     // D = 512: the contractions run on the tensor cores (mma.sync); other widths, or on request, the
     // CUDA-core kernel
     if (p->d == kSfaMmaD && p->kernel != DSA_KERNEL_PORTABLE) {
-      const size_t smem = sfa_grad_mma_smem_bytes(sizeof(T));
-      if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-          cudaSuccess)
-        return DSA_ERR_CUDA;
-      sfa_bwd_mma_kernel<T><<<grid, kSfaGradThreads, smem, st>>>(d);
+      if (p->n1 > 16) {   // 32 heads per block: half the scatter-adds per query row
+        const size_t smem = sfa_grad_mma_smem_bytes<2>(sizeof(T));
+        if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+          return DSA_ERR_CUDA;
+        dim3 grid2((unsigned)d.rows, (unsigned)((p->n1 + 31) / 32), 1);
+        sfa_bwd_mma_kernel<T, 2><<<grid2, 512, smem, st>>>(d);
+      } else {
+        const size_t smem = sfa_grad_mma_smem_bytes<1>(sizeof(T));
+        if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+          return DSA_ERR_CUDA;
+        sfa_bwd_mma_kernel<T, 1><<<grid, 256, smem, st>>>(d);
+      }
     } else {
       const size_t smem = sfa_grad_smem_bytes(p->d, p->d_rope, sizeof(T));
       if (cudaFuncSetAttribute(sfa_bwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=

@@ -21,11 +21,6 @@ constexpr int kSfaMmaD = 512, kSfaMmaDr = 64, kSfaMmaDq = kSfaMmaD + kSfaMmaDr;
 constexpr int kSfaMmaStride = kSfaMmaDq + kSfaGradPad;    // q / key rows, elements
 constexpr int kSfaMmaDStride = kSfaMmaD + kSfaGradPad;    // dO rows
 constexpr int kSfaMmaPk = kSfaGradKeys + 8;               // [head][key] operand rows (40 elements)
-constexpr int kSfaMmaPh = kSfaGradHeads + 8;              // [key][head] operand rows (24 elements)
-
-inline size_t sfa_grad_mma_smem_bytes(size_t elem) {
-  return ((size_t)(kSfaGradHeads + kSfaGradKeys) * kSfaMmaStride + (size_t)kSfaGradHeads * kSfaMmaDStride) * elem;
-}
 
 template <typename T>
 constexpr bool kIsBf16 = false;
@@ -90,21 +85,30 @@ __device__ __forceinline__ void red_tile(float* acc, int width, int64_t krow_lo,
   }
 }
 
-// grid = (rows, ceil(n1 / 16)); block = 256 threads, two blocks per SM.
-// dynamic smem: q [16][584] | keys [32][584] | dO [16][520], elements of T.
-template <typename T>
-__global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGradDev p) {
+// MT = 16-head tiles per block (1 or 2): HB = 16 MT heads, 256 MT threads.  Every scatter-add of d_key /
+// d_value covers the block's heads, so two tiles halve the reductions per query row; they cost one
+// block per SM instead of two (with the same number of warps).
+// grid = (rows, ceil(n1 / HB)).  dynamic smem: q [HB][584] | keys [32][584] | dO [HB][520], elements of T.
+template <int MT>
+inline size_t sfa_grad_mma_smem_bytes(size_t elem) {
+  return ((size_t)(16 * MT + kSfaGradKeys) * kSfaMmaStride + (size_t)16 * MT * kSfaMmaDStride) * elem;
+}
+
+template <typename T, int MT>
+__global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(SfaGradDev p) {
+  constexpr int HB = 16 * MT, NT = 256 * MT;
+  constexpr int PH = HB + 8;              // [key][head] operand rows, elements
   extern __shared__ __align__(16) unsigned char sfa_grad_smem[];
   T* qs = reinterpret_cast<T*>(sfa_grad_smem);
-  T* ks = qs + kSfaGradHeads * kSfaMmaStride;
+  T* ks = qs + HB * kSfaMmaStride;
   T* dos = ks + kSfaGradKeys * kSfaMmaStride;
-  __shared__ float ps_f[kSfaGradHeads][kSfaGradKeys + 1];
-  __shared__ float dp_f[kSfaGradHeads][kSfaGradKeys + 1];
-  __shared__ __align__(16) T ds_hi[kSfaGradHeads * kSfaMmaPk], ds_lo[kSfaGradHeads * kSfaMmaPk];   // [head][key]
-  __shared__ __align__(16) T dst_hi[kSfaGradKeys * kSfaMmaPh], dst_lo[kSfaGradKeys * kSfaMmaPh];   // [key][head]
-  __shared__ __align__(16) T pt_hi[kSfaGradKeys * kSfaMmaPh], pt_lo[kSfaGradKeys * kSfaMmaPh];     // [key][head]
-  __shared__ float delta_s[kSfaGradHeads], max_s[kSfaGradHeads], sum_s[kSfaGradHeads];
-  __shared__ float red_s[kSfaGradThreads / 32];
+  __shared__ float ps_f[HB][kSfaGradKeys + 1];
+  __shared__ float dp_f[HB][kSfaGradKeys + 1];
+  __shared__ __align__(16) T ds_hi[HB * kSfaMmaPk], ds_lo[HB * kSfaMmaPk];         // [head][key]
+  __shared__ __align__(16) T dst_hi[kSfaGradKeys * PH], dst_lo[kSfaGradKeys * PH]; // [key][head]
+  __shared__ __align__(16) T pt_hi[kSfaGradKeys * PH], pt_lo[kSfaGradKeys * PH];   // [key][head]
+  __shared__ float delta_s[HB], max_s[HB], sum_s[HB];
+  __shared__ float red_s[NT / 32];
   __shared__ int32_t tok_s[2][kSfaGradKeys];
   __shared__ int64_t krow_s[2][kSfaGradKeys];
 
@@ -113,11 +117,13 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int32_t row = blockIdx.x;
-  const int32_t h0 = blockIdx.y * kSfaGradHeads;
+  const int32_t h0 = blockIdx.y * HB;
   const RowInfo ri = row_info(p.seq, row);
   const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
+  const int qm0 = (warp >> 3) * 16;       // head tile of this warp in the d_query product
+  const int qn0 = (warp & 7) * 72;        // its first column there and in the d_key product
 
-  // d_query accumulator: 9 column tiles of 8 per warp (warp w: columns 72 w .. 72 w + 71 of nope|rope)
+  // d_query accumulator: 16 heads x 72 columns (nine tiles of 8) per warp
   float acc[9][4];
 #pragma unroll
   for (int t = 0; t < 9; ++t)
@@ -128,7 +134,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
     const T* qn = (const T*)p.query + (int64_t)row * p.n1 * kSfaMmaD;
     const T* qr = (const T*)p.query_rope + (int64_t)row * p.n1 * kSfaMmaDr;
     const T* dout = (const T*)p.d_out + (int64_t)row * p.n1 * kSfaMmaD;
-    for (int i = tid; i < kSfaGradHeads * (kSfaMmaDq / 8); i += kSfaGradThreads) {
+    for (int i = tid; i < HB * (kSfaMmaDq / 8); i += NT) {
       const int h = i / (kSfaMmaDq / 8), ch = i - h * (kSfaMmaDq / 8);
       uint4 v = make_uint4(0, 0, 0, 0);
       if (h0 + h < p.n1)
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
                               : reinterpret_cast<const uint4*>(qr + (int64_t)(h0 + h) * kSfaMmaDr)[ch - kSfaMmaD / 8];
       *reinterpret_cast<uint4*>(&qs[h * kSfaMmaStride + ch * 8]) = v;
     }
-    for (int i = tid; i < kSfaGradHeads * (kSfaMmaD / 8); i += kSfaGradThreads) {
+    for (int i = tid; i < HB * (kSfaMmaD / 8); i += NT) {
       const int h = i / (kSfaMmaD / 8), ch = i - h * (kSfaMmaD / 8);
       uint4 v = make_uint4(0, 0, 0, 0);
       if (h0 + h < p.n1) v = reinterpret_cast<const uint4*>(dout + (int64_t)(h0 + h) * kSfaMmaD)[ch];
@@ -192,7 +198,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
   };
   auto gather_async = [&](int buf) {
     constexpr int cn = kSfaMmaD / 8, ct = kSfaMmaDq / 8;
-    for (int i = tid; i < kSfaGradKeys * ct; i += kSfaGradThreads) {
+    for (int i = tid; i < kSfaGradKeys * ct; i += NT) {
       const int k = i / ct, ch = i - k * ct;
       const int64_t kr_ = krow_s[buf][k];
       const T* src = kn;
@@ -211,11 +217,12 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
     asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
 
-    // warps 0-3: S tile of keys 8 w .. 8 w + 7 -> P;  warps 4-7: dP tile of keys 8 (w-4) ..
+    // One 16-head x 8-key tile per warp: the first 4 MT warps compute S -> P, the others dP.
     {
-      const bool is_s = warp < 4;
+      const bool is_s = warp < 4 * MT;
+      const int m0 = ((warp >> 2) % MT) * 16;
       const int n0 = (warp & 3) * 8;
-      const T* a_base = is_s ? qs : dos;
+      const T* a_base = is_s ? qs + m0 * kSfaMmaStride : dos + m0 * kSfaMmaDStride;
       const int a_stride = is_s ? kSfaMmaStride : kSfaMmaDStride;
       const int ksteps = is_s ? kSfaMmaDq / 16 : kSfaMmaD / 16;
       float cs[4][4];     // four independent accumulation chains
@@ -244,7 +251,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int h = g + (e >> 1) * 8, k = n0 + 2 * c + (e & 1);
+        const int h = m0 + g + (e >> 1) * 8, k = n0 + 2 * c + (e & 1);
         const float v = (cs[0][e] + cs[1][e]) + (cs[2][e] + cs[3][e]);
         if (is_s) {
           const float l = sum_s[h];
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
       float pv[2], dsv[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        const int i = tid + u * kSfaGradThreads, h = i >> 5, k = i & 31;
+        const int i = tid + u * NT, h = i >> 5, k = i & 31;
         pv[u] = ps_f[h][k];
         dsv[u] = pv[u] * (dp_f[h][k] - delta_s[h]) * p.scale;
       }
@@ -278,7 +285,7 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
         __syncthreads();
         m = red_s[0];
 #pragma unroll
-        for (int wv = 1; wv < kSfaGradThreads / 32; ++wv) m = fmaxf(m, red_s[wv]);
+        for (int wv = 1; wv < NT / 32; ++wv) m = fmaxf(m, red_s[wv]);
         int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : 0;
         e = max(-100, min(100, e));
         if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
@@ -296,13 +303,13 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        const int i = tid + u * kSfaGradThreads, h = i >> 5, k = i & 31;
+        const int i = tid + u * NT, h = i >> 5, k = i & 31;
         const float pp = pv[u] * p_up, dk_ = dsv[u] * up_k, dq_ = dsv[u] * up_q;
         const T ph = from_f32<T>(pp), kh = from_f32<T>(dk_), qh = from_f32<T>(dq_);
-        pt_hi[k * kSfaMmaPh + h] = ph;
-        pt_lo[k * kSfaMmaPh + h] = from_f32<T>(pp - to_f32<T>(ph));
-        dst_hi[k * kSfaMmaPh + h] = kh;
-        dst_lo[k * kSfaMmaPh + h] = from_f32<T>(dk_ - to_f32<T>(kh));
+        pt_hi[k * PH + h] = ph;
+        pt_lo[k * PH + h] = from_f32<T>(pp - to_f32<T>(ph));
+        dst_hi[k * PH + h] = kh;
+        dst_lo[k * PH + h] = from_f32<T>(dk_ - to_f32<T>(kh));
         ds_hi[h * kSfaMmaPk + k] = qh;
         ds_lo[h * kSfaMmaPk + k] = from_f32<T>(dq_ - to_f32<T>(qh));
       }
@@ -313,12 +320,12 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
 #pragma unroll
     for (int k0 = 0; k0 < kSfaGradKeys; k0 += 16) {
       uint32_t ah[4], al[4];
-      load_a_frag<T>(ah, ds_hi, kSfaMmaPk, 0, k0);
-      load_a_frag<T>(al, ds_lo, kSfaMmaPk, 0, k0);
+      load_a_frag<T>(ah, ds_hi, kSfaMmaPk, qm0, k0);
+      load_a_frag<T>(al, ds_lo, kSfaMmaPk, qm0, k0);
 #pragma unroll
       for (int t = 0; t < 9; ++t) {
         uint32_t b0, b1;
-        ldmatrix_b_trans<T>(b0, b1, &ks[k0 * kSfaMmaStride + (warp * 9 + t) * 8], kSfaMmaStride);
+        ldmatrix_b_trans<T>(b0, b1, &ks[k0 * kSfaMmaStride + qn0 + t * 8], kSfaMmaStride);
         mma_16816<T>(acc[t], ah, b0, b1);
         mma_16816<T>(acc[t], al, b0, b1);
       }
@@ -329,50 +336,67 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
     const int32_t jn = next_chunk(j0 + kSfaGradKeys, buf ^ 1);
     if (jn < slots) gather_async(buf ^ 1);
 
-    // d_key (nope | rope) += dS^T . q : 32 keys x 72 columns per warp, 16 heads deep
+    // d_key (nope | rope) += dS^T . q and d_value += P^T . dO, HB heads deep.  A warp takes 2 / MT
+    // 16-key tiles x 72 columns of d_key and x 64 columns of d_value.
     {
-      uint32_t ah[2][4], al[2][4];
+      constexpr int KT = 2 / MT;             // key tiles per warp
+      const int kt0 = MT == 2 ? (warp >> 3) : 0;
+      const int vn0 = (warp & 7) * 64;
+      uint32_t ah[KT][MT][4], al[KT][MT][4];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        load_a_frag<T>(ah[mt], dst_hi, kSfaMmaPh, mt * 16, 0);
-        load_a_frag<T>(al[mt], dst_lo, kSfaMmaPh, mt * 16, 0);
-      }
+      for (int kt = 0; kt < KT; ++kt)
+#pragma unroll
+        for (int hs = 0; hs < MT; ++hs) {
+          load_a_frag<T>(ah[kt][hs], dst_hi, PH, (kt0 + kt) * 16, hs * 16);
+          load_a_frag<T>(al[kt][hs], dst_lo, PH, (kt0 + kt) * 16, hs * 16);
+        }
       for (int t = 0; t < 9; ++t) {
-        const int n0 = (warp * 9 + t) * 8;
-        uint32_t b0, b1;
-        ldmatrix_b_trans<T>(b0, b1, &qs[n0], kSfaMmaStride);
+        const int n0 = qn0 + t * 8;
+        uint32_t b[MT][2];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int hs = 0; hs < MT; ++hs) ldmatrix_b_trans<T>(b[hs][0], b[hs][1], &qs[hs * 16 * kSfaMmaStride + n0], kSfaMmaStride);
+#pragma unroll
+        for (int kt = 0; kt < KT; ++kt) {
           float cf[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_16816<T>(cf, ah[mt], b0, b1);
-          mma_16816<T>(cf, al[mt], b0, b1);
+#pragma unroll
+          for (int hs = 0; hs < MT; ++hs) {
+            mma_16816<T>(cf, ah[kt][hs], b[hs][0], b[hs][1]);
+            mma_16816<T>(cf, al[kt][hs], b[hs][0], b[hs][1]);
+          }
           if constexpr (kScaled) {
 #pragma unroll
             for (int x = 0; x < 4; ++x) cf[x] *= dk_down;
           }
-          red_tile(p.dk_acc, kSfaMmaDq, krow_s[buf][mt * 16 + g], krow_s[buf][mt * 16 + g + 8], n0, cf);
+          const int kr0 = (kt0 + kt) * 16 + g;
+          red_tile(p.dk_acc, kSfaMmaDq, krow_s[buf][kr0], krow_s[buf][kr0 + 8], n0, cf);
         }
       }
-      // d_value += P^T . dO : 32 keys x 64 columns per warp
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        load_a_frag<T>(ah[mt], pt_hi, kSfaMmaPh, mt * 16, 0);
-        load_a_frag<T>(al[mt], pt_lo, kSfaMmaPh, mt * 16, 0);
-      }
+      for (int kt = 0; kt < KT; ++kt)
+#pragma unroll
+        for (int hs = 0; hs < MT; ++hs) {
+          load_a_frag<T>(ah[kt][hs], pt_hi, PH, (kt0 + kt) * 16, hs * 16);
+          load_a_frag<T>(al[kt][hs], pt_lo, PH, (kt0 + kt) * 16, hs * 16);
+        }
       for (int t = 0; t < 8; ++t) {
-        const int n0 = (warp * 8 + t) * 8;
-        uint32_t b0, b1;
-        ldmatrix_b_trans<T>(b0, b1, &dos[n0], kSfaMmaDStride);
+        const int n0 = vn0 + t * 8;
+        uint32_t b[MT][2];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int hs = 0; hs < MT; ++hs) ldmatrix_b_trans<T>(b[hs][0], b[hs][1], &dos[hs * 16 * kSfaMmaDStride + n0], kSfaMmaDStride);
+#pragma unroll
+        for (int kt = 0; kt < KT; ++kt) {
           float cf[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_16816<T>(cf, ah[mt], b0, b1);
-          mma_16816<T>(cf, al[mt], b0, b1);
+#pragma unroll
+          for (int hs = 0; hs < MT; ++hs) {
+            mma_16816<T>(cf, ah[kt][hs], b[hs][0], b[hs][1]);
+            mma_16816<T>(cf, al[kt][hs], b[hs][0], b[hs][1]);
+          }
           if constexpr (kScaled) {
 #pragma unroll
             for (int x = 0; x < 4; ++x) cf[x] *= (1.f / 8192.f);
           }
-          red_tile(p.dv_acc, kSfaMmaD, krow_s[buf][mt * 16 + g], krow_s[buf][mt * 16 + g + 8], n0, cf);
+          const int kr0 = (kt0 + kt) * 16 + g;
+          red_tile(p.dv_acc, kSfaMmaD, krow_s[buf][kr0], krow_s[buf][kr0 + 8], n0, cf);
         }
       }
     }
@@ -384,10 +408,10 @@ __global__ void __launch_bounds__(kSfaGradThreads, 2) sfa_bwd_mma_kernel(SfaGrad
   const float dq_down = kScaled ? scalbnf(1.f, -dq_exp) : 1.f;
 #pragma unroll
   for (int t = 0; t < 9; ++t) {
-    const int col = (warp * 9 + t) * 8 + 2 * c;
+    const int col = qn0 + t * 8 + 2 * c;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int h = g + half * 8;
+      const int h = qm0 + g + half * 8;
       if (h0 + h >= p.n1) continue;
       const int64_t qh = (int64_t)row * p.n1 + h0 + h;
       T* dst = col < kSfaMmaD ? (T*)p.d_query + qh * kSfaMmaD + col : (T*)p.d_query_rope + qh * kSfaMmaDr + (col - kSfaMmaD);
