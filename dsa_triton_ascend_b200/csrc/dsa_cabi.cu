@@ -369,7 +369,7 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
   if (rows > 0 && cudaMemsetAsync(d.di, 0, 2 * buf_bytes, st) != cudaSuccess) return DSA_ERR_CUDA;
   if (rows > 0) {
     const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
-    const size_t smem_a = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T);
+    const size_t smem_a = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
     const size_t smem_b = (size_t)(kSliHeads + kSliKeys) * (p->d_idx + kSliPad) * sizeof(T);
     if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
@@ -475,7 +475,7 @@ static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, int32_t*
   d.di = scratch;
   if (cudaMemsetAsync(scratch, 0, (size_t)rows * p->s2 * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
   const int stride = p->d_idx + kSliPad;
-  const size_t smem = (size_t)(kSliHeads + kSliKeys) * stride * sizeof(T);
+  const size_t smem = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
   if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return DSA_ERR_CUDA;
   dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(p->g), 1);

@@ -23,7 +23,7 @@
 #pragma once
 
 #include "dsa_common.cuh"
-#include "sfa_bwd_simt.cuh"
+#include "sfa_bwd_mma.cuh"
 
 namespace dsa {
 
@@ -58,6 +58,7 @@ struct SliGradDev {
 
 constexpr int kSliHeads = 16;
 constexpr int kSliKeys = 32;
+constexpr int kSliTeacherKeys = 64;   // keys per step of the tensor-core scoring kernels (one 8-key tile per warp)
 constexpr int kSliThreads = 256;
 constexpr int kSliPad = 8;
 constexpr float kSliEps = 1e-8f;
@@ -112,13 +113,14 @@ __device__ __forceinline__ void sli_stage_heads(T* dst, int stride, const T* a, 
   }
 }
 
-// Gathers the rows idx_s[0..32) (16-byte chunks) of one or two key tensors into shared memory.
+// Gathers the rows rows_s[0..nkeys) (16-byte chunks) of one or two key tensors into shared memory.
 // Row rows_s[k] of a tensor with `nh` heads per position is row rows_s[k] * nh + head.
 template <typename T>
 __device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, int wa, const T* b, int wb,
-                                                const int64_t* rows_s, int nh = 1, int head = 0) {
+                                                const int64_t* rows_s, int nh = 1, int head = 0,
+                                                int nkeys = kSliKeys) {
   const int ca = wa / 8, cb = wb / 8, ct = ca + cb;
-  for (int i = threadIdx.x; i < kSliKeys * ct; i += kSliThreads) {
+  for (int i = threadIdx.x; i < nkeys * ct; i += kSliThreads) {
     const int k = i / ct, c = i - k * ct;
     const int64_t r = rows_s[k] < 0 ? -1 : rows_s[k] * nh + head;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -151,24 +153,56 @@ __device__ __forceinline__ void sli_dots(const T* qs, const T* ks, int stride, i
   *s1 = a1;
 }
 
+// Tensor-core scores (mma.sync m16n8k16, fp32 accumulation) of the 16 staged heads against keys
+// n0 .. n0+7 of `ks` over `w` columns (a multiple of 64): out[0..1] = head lane/4, keys n0 + 2 (lane%4)
+// (+1); out[2..3] = head lane/4 + 8, same keys.  Rows of `stride` elements (16-byte multiples).
+template <typename T>
+__device__ __forceinline__ void sli_tile_scores(const T* qs, const T* ks, int stride, int w, int n0, float (&out)[4]) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t a_addr =
+      (uint32_t)__cvta_generic_to_shared(qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
+  const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(&ks[(n0 + (lane & 7)) * stride + (lane >> 3) * 8]);
+  float cs[4][4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cs[u][e] = 0.f;
+  for (int s = 0; s < w / 16; s += 4) {
+    uint32_t a[4][4], b[4][2];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) ldmatrix_x4(a[u], a_addr + (s + u) * 16 * (int)sizeof(T));
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      uint32_t r[4];
+      ldmatrix_x4(r, b_addr + (s + u) * 16 * (int)sizeof(T));
+      b[u][0] = r[0]; b[u][1] = r[1]; b[u + 1][0] = r[2]; b[u + 1][1] = r[3];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mma_16816<T>(cs[u], a[u], b[u][0], b[u][1]);
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) out[e] = (cs[0][e] + cs[1][e]) + (cs[2][e] + cs[3][e]);
+}
+
 // Number of 16-head chunks of the attention side (per key head) and of the index side.
 __host__ __device__ inline int sli_att_chunks(int n1, int n2) { return n2 * ((n1 / n2 + kSliHeads - 1) / kSliHeads); }
 __host__ __device__ inline int sli_idx_chunks(int g) { return (g + kSliHeads - 1) / kSliHeads; }
 
 // grid = (rows, attention chunks + index chunks) (index chunks only when lse_only); block = 256.
-// dynamic smem: (16 + 32) * stride elements of T.  A block keeps its 16 heads in shared memory,
-// walks over the row's keys 32 at a time and adds its heads' share of p[k] (attention chunks) or of
-// I[k] (index chunks) into the row's fp32 buffers (zeroed by the caller).
+// dynamic smem: (16 + 64) * stride elements of T.  A block keeps its 16 heads in shared memory,
+// walks over the row's keys 64 at a time (each warp scores one tile of 8 keys on the tensor cores)
+// and adds its heads' share of p[k] (attention chunks) or of I[k] (index chunks) into the row's fp32
+// buffers (zeroed by the caller).
 template <typename T>
-__global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, int stride) {
+__global__ void __launch_bounds__(kSliThreads, 2) sli_teacher_kernel(SliGradDev p, int stride) {
   extern __shared__ __align__(16) unsigned char sli_smem[];
   T* qs = reinterpret_cast<T*>(sli_smem);
   T* ks = qs + kSliHeads * stride;
-  __shared__ float red_s[kSliThreads / 32][kSliKeys];
-  __shared__ int64_t rows_s[kSliKeys];
+  __shared__ int64_t rows_s[kSliTeacherKeys];
   __shared__ float max_s[kSliHeads], inv_s[kSliHeads], w_s[kSliHeads];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
   const int32_t row = blockIdx.x;
   int32_t b;
   const int32_t n = sli_row_slots(p, row, &b);
@@ -178,16 +212,16 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
   const int32_t* idx_row = dense ? nullptr : p.sparse_indices + (int64_t)row * p.topk;
   const int grp = p.n1 / p.n2;                    // query heads per attention key head
   const int att_chunks = p.lse_only ? 0 : sli_att_chunks(p.n1, p.n2);
-  const int c = blockIdx.y;
-  const int phase = c < att_chunks ? 0 : 1;       // 0: attention distribution p, 1: index scores I
+  const int ch = blockIdx.y;
+  const int phase = ch < att_chunks ? 0 : 1;      // 0: attention distribution p, 1: index scores I
   int kv = 0, h0, h_end;
   if (phase == 0) {
     const int cpk = att_chunks / p.n2;
-    kv = c / cpk;
-    h0 = kv * grp + (c - kv * cpk) * kSliHeads;
+    kv = ch / cpk;
+    h0 = kv * grp + (ch - kv * cpk) * kSliHeads;
     h_end = (kv + 1) * grp;
   } else {
-    h0 = (c - att_chunks) * kSliHeads;
+    h0 = (ch - att_chunks) * kSliHeads;
     h_end = p.g;
   }
   const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
@@ -211,34 +245,40 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
       w_s[tid] = h < h_end ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h) : 0.f;
     }
   }
-  for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
-    __syncthreads();   // heads staged; the previous step is done with ks, rows_s and red_s
-    if (tid < kSliKeys) {
+  for (int32_t j0 = 0; j0 < n; j0 += kSliTeacherKeys) {
+    __syncthreads();   // heads staged; the previous step is done with ks and rows_s
+    if (tid < kSliTeacherKeys) {
       const int32_t j = j0 + tid;
       rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
     }
     __syncthreads();
     if (phase == 0)
-      sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
+      sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv,
+                         kSliTeacherKeys);
     else
-      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s, 1, 0,
+                         kSliTeacherKeys);
     __syncthreads();
-    float s0, s1;
-    sli_dots<T>(qs, ks, stride, w, &s0, &s1);
-    float part;
+    float sc[4];
+    sli_tile_scores<T>(qs, ks, stride, w, warp * 8, sc);
+    // this thread: heads g and g + 8, keys 2c and 2c + 1 of the warp's tile; sum over the 16 heads
+    float t0, t1;
     if (phase == 0) {
-      part = (h0 + warp < h_end ? expf(s0 * p.scale - max_s[warp]) * inv_s[warp] : 0.f) +
-             (h0 + warp + 8 < h_end ? expf(s1 * p.scale - max_s[warp + 8]) * inv_s[warp + 8] : 0.f);
+      t0 = expf(sc[0] * p.scale - max_s[g]) * inv_s[g] + expf(sc[2] * p.scale - max_s[g + 8]) * inv_s[g + 8];
+      t1 = expf(sc[1] * p.scale - max_s[g]) * inv_s[g] + expf(sc[3] * p.scale - max_s[g + 8]) * inv_s[g + 8];
     } else {
-      part = fmaxf(s0, 0.f) * w_s[warp] + fmaxf(s1, 0.f) * w_s[warp + 8];
+      t0 = fmaxf(sc[0], 0.f) * w_s[g] + fmaxf(sc[2], 0.f) * w_s[g + 8];
+      t1 = fmaxf(sc[1], 0.f) * w_s[g] + fmaxf(sc[3], 0.f) * w_s[g + 8];
     }
-    red_s[warp][lane] = part;
-    __syncthreads();
-    if (tid < kSliKeys && j0 + tid < n) {
-      float acc = 0.f;
 #pragma unroll
-      for (int wv = 0; wv < kSliThreads / 32; ++wv) acc += red_s[wv][tid];
-      atomicAdd(&acc_row[j0 + tid], acc);
+    for (int o = 4; o < 32; o <<= 1) {
+      t0 += __shfl_xor_sync(0xffffffffu, t0, o);
+      t1 += __shfl_xor_sync(0xffffffffu, t1, o);
+    }
+    if (g == 0) {
+      const int32_t j = j0 + warp * 8 + 2 * c;
+      if (j < n) atomicAdd(&acc_row[j], t0);
+      if (j + 1 < n) atomicAdd(&acc_row[j + 1], t1);
     }
   }
 }
@@ -246,14 +286,14 @@ __global__ void __launch_bounds__(kSliThreads) sli_teacher_kernel(SliGradDev p, 
 // Attention side of the dense operator when a key head serves fewer than 16 query heads (n1 / n2 in
 // {1, 2, 4, 8}; multi-head attention is 1).  The rows of a batch walk over the same keys, so a block
 // takes 16 / grp consecutive rows times the grp heads of one key head: 16 (row, head) pairs share each
-// staged block of 32 keys, where the per-row kernel above would fill only grp of its 16 head slots.
+// staged block of 64 keys, where the per-row kernel above would fill only grp of its 16 head slots.
 // grid = (batch * ceil(s1 / (16 / grp)), n2); block = 256; dynamic smem as above.
 template <typename T>
-__global__ void __launch_bounds__(kSliThreads) sli_dense_teacher_kernel(SliGradDev p, int stride) {
+__global__ void __launch_bounds__(kSliThreads, 2) sli_dense_teacher_kernel(SliGradDev p, int stride) {
   extern __shared__ __align__(16) unsigned char sli_smem[];
   T* qs = reinterpret_cast<T*>(sli_smem);
   T* ks = qs + kSliHeads * stride;
-  __shared__ int64_t rows_s[kSliKeys];
+  __shared__ int64_t rows_s[kSliTeacherKeys];
   __shared__ float max_s[kSliHeads], inv_s[kSliHeads];
   __shared__ int32_t n_s[kSliHeads];
 
@@ -290,21 +330,25 @@ __global__ void __launch_bounds__(kSliThreads) sli_dense_teacher_kernel(SliGradD
   int32_t nmax = 0;
 #pragma unroll
   for (int m = 0; m < kSliHeads; ++m) nmax = max(nmax, n_s[m]);
-  const int m0 = warp, m1 = warp + 8;
+  const int g = lane >> 2, c = lane & 3;
+  const int m0 = g, m1 = g + 8;         // this thread's two (row, head) pairs in a score tile
   const int32_t n0 = n_s[m0], n1 = n_s[m1];
   float* acc0 = p.p_buf + ((int64_t)b * p.s1 + pos0 + m0 / grp) * p.topk;
   float* acc1 = p.p_buf + ((int64_t)b * p.s1 + pos0 + m1 / grp) * p.topk;
-  for (int32_t j0 = 0; j0 < nmax; j0 += kSliKeys) {
+  for (int32_t j0 = 0; j0 < nmax; j0 += kSliTeacherKeys) {
     __syncthreads();   // the previous step is done with ks and rows_s
-    if (tid < kSliKeys) rows_s[tid] = j0 + tid < nmax ? (int64_t)b * p.s2 + j0 + tid : -1;
+    if (tid < kSliTeacherKeys) rows_s[tid] = j0 + tid < nmax ? (int64_t)b * p.s2 + j0 + tid : -1;
     __syncthreads();
-    sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv);
+    sli_gather_keys<T>(ks, stride, (const T*)p.key, p.d, (const T*)p.key_rope, p.d_rope, rows_s, p.n2, kv,
+                       kSliTeacherKeys);
     __syncthreads();
-    float s0, s1;
-    sli_dots<T>(qs, ks, stride, w, &s0, &s1);
-    const int32_t j = j0 + lane;
-    if (j < n0) atomicAdd(&acc0[j], expf(s0 * p.scale - max_s[m0]) * inv_s[m0]);
-    if (j < n1) atomicAdd(&acc1[j], expf(s1 * p.scale - max_s[m1]) * inv_s[m1]);
+    float sc[4];
+    sli_tile_scores<T>(qs, ks, stride, w, warp * 8, sc);
+    const int32_t j = j0 + warp * 8 + 2 * c;
+    if (j < n0) atomicAdd(&acc0[j], expf(sc[0] * p.scale - max_s[m0]) * inv_s[m0]);
+    if (j + 1 < n0) atomicAdd(&acc0[j + 1], expf(sc[1] * p.scale - max_s[m0]) * inv_s[m0]);
+    if (j < n1) atomicAdd(&acc1[j], expf(sc[2] * p.scale - max_s[m1]) * inv_s[m1]);
+    if (j + 1 < n1) atomicAdd(&acc1[j + 1], expf(sc[3] * p.scale - max_s[m1]) * inv_s[m1]);
   }
 }
 
