@@ -15,7 +15,7 @@
 #include "sfa_fwd_sm100.cuh"
 #include "sfa_bwd_simt.cuh"
 #include "sfa_bwd_mma.cuh"
-#include "sli_grad_simt.cuh"
+#include "sli_grad.cuh"
 
 namespace dsa {
 
@@ -370,7 +370,7 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
   if (rows > 0) {
     const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
     const size_t smem_a = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
-    const size_t smem_b = (size_t)(kSliHeads + kSliKeys) * (p->d_idx + kSliPad) * sizeof(T);
+    const size_t smem_b = (size_t)(kSliHeads + kSliTeacherKeys) * (p->d_idx + kSliPad) * sizeof(T);
     if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
         cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=

@@ -1,7 +1,6 @@
-// Portable (CUDA-core) backward of the sparse lightning indexer under the KL loss against the
-// attention distribution (sparse_lightning_indexer_grad_kl_loss_triton.py:25-327, golden
-// sli_grad_kl_loss_numpy.py:16-156).  Per query row with n used slots and idx = its sparse
-// indices clipped to [0, S2):
+// Backward of the sparse lightning indexer under the KL loss against the attention distribution
+// (sparse_lightning_indexer_grad_kl_loss_triton.py:25-327, golden sli_grad_kl_loss_numpy.py:16-156).
+// Per query row with n used slots and idx = its sparse indices clipped to [0, S2):
 //     p[k]  = mean_h exp((q[h].k[idx k] + qr[h].kr[idx k]) * scale - max[h]) / (sum[h] + 1e-8)
 //     I[k]  = sum_g w[g] relu(qi[g].ki[idx k]);  sI = softmax_k(I);  dI = sI - p
 //     loss += sum_k max(p,1e-8) (log max(p,1e-8) - log max(sI,1e-8))
@@ -9,12 +8,13 @@
 //     dQI[g] = sum_k ds[g,k] ki[idx k];   dKI[idx k] += sum_g ds[g,k] qi[g]
 // The reference runs all stages in one program per row and keeps ReLU values, gathered index keys,
 // p, I and dI in global scratch tensors between them (:385-400).  Here: (1) one block per (row, 16
-// heads) of either side keeps its heads in shared memory, walks over the row's keys and adds its
-// share of p[k] or I[k] into fp32 buffers; (2) one block per row turns I and p into dI and the
-// row's loss term; (3) one block per (row, 16 index heads) recomputes the index scores it needs
-// instead of reading a [rows, G, topK] ReLU cache, accumulates dQI / dW in registers and adds dKI
-// into an fp32 accumulator with 16-byte reductions; (4) the accumulator is converted and the loss
-// terms are summed in a fixed order.
+// heads) of either side keeps its heads in shared memory, walks over the row's keys 64 at a time,
+// scores them on the tensor cores (mma.sync m16n8k16, fp32 accumulation) and adds its share of p[k]
+// or I[k] into fp32 buffers; (2) one block per row turns I and p into dI and the row's loss term;
+// (3) one block per (row, 16 index heads) recomputes the index scores it needs instead of reading a
+// [rows, G, topK] ReLU cache, accumulates dQI in tensor-core accumulators and dW in registers, and
+// adds its dKI tiles into an fp32 accumulator with 16-byte reductions; (4) the accumulator is
+// converted and the loss terms are summed in a fixed order.
 //
 // The same kernels serve the dense operator (dense_loss_backward_triton.py:130-341: every causally
 // visible key 0..n-1 instead of selected ones, attention keys with n2 heads, the student distribution
@@ -127,30 +127,6 @@ __device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, 
     if (r >= 0) v = c < ca ? reinterpret_cast<const uint4*>(a + r * wa)[c] : reinterpret_cast<const uint4*>(b + r * wb)[c - ca];
     *reinterpret_cast<uint4*>(&dst[k * stride + c * 8]) = v;
   }
-}
-
-// Dot products of key `lane` with heads `warp` and `warp + 8` over `w` columns.
-template <typename T>
-__device__ __forceinline__ void sli_dots(const T* qs, const T* ks, int stride, int w, float* s0, float* s1) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint4* kp = reinterpret_cast<const uint4*>(&ks[lane * stride]);
-  const uint4* q0 = reinterpret_cast<const uint4*>(&qs[warp * stride]);
-  const uint4* q1 = reinterpret_cast<const uint4*>(&qs[(warp + 8) * stride]);
-  float a0 = 0.f, a1 = 0.f;
-  for (int c = 0; c < w / 8; ++c) {
-    const uint4 kv = kp[c], a = q0[c], b = q1[c];
-    const T* kk = reinterpret_cast<const T*>(&kv);
-    const T* aa = reinterpret_cast<const T*>(&a);
-    const T* bb = reinterpret_cast<const T*>(&b);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float kf = to_f32<T>(kk[e]);
-      a0 = fmaf(kf, to_f32<T>(aa[e]), a0);
-      a1 = fmaf(kf, to_f32<T>(bb[e]), a1);
-    }
-  }
-  *s0 = a0;
-  *s1 = a1;
 }
 
 // Tensor-core scores (mma.sync m16n8k16, fp32 accumulation) of the 16 staged heads against keys
@@ -404,28 +380,40 @@ __global__ void __launch_bounds__(kSliThreads) sli_student_kernel(SliGradDev p) 
   if (tid == 0) p.loss_parts[row] = kl;
 }
 
-// grid = (rows, ceil(g / 16)); block = 256.  dynamic smem: (16 + 32) * (d_idx + pad) elements of T.
+// grid = (rows, ceil(g / 16)); block = 256.  dynamic smem: (16 + 64) * (d_idx + pad) elements of T.
+// Per step of 64 keys, all three products run on the tensor cores (mma.sync m16n8k16): the index
+// scores of the block's 16 heads (one 8-key tile per warp), dQI += ds . ki (each warp owns d_idx / 64
+// column tiles, accumulated in registers over the whole row) and dKI += ds^T . qi (a warp takes one
+// 16-key tile and half of the columns; its tiles leave as 16-byte fp32 reductions).  ds is an fp32
+// value: it enters the second and third product as a high and a low io-dtype part, for fp16 scaled
+// by a power of two per step so that neither part leaves the format's range.
 template <typename T>
-__global__ void __launch_bounds__(kSliThreads) sli_grad_kernel(SliGradDev p) {
+__global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) {
   extern __shared__ __align__(16) unsigned char sli_smem[];
+  constexpr int KS = kSliTeacherKeys, PK = KS + 8, PH = kSliHeads + 8;
+  constexpr bool kScaled = sizeof(T) == 2 && !kIsBf16<T>;
   const int stride = p.d_idx + kSliPad;
   T* qs = reinterpret_cast<T*>(sli_smem);
   T* ks = qs + kSliHeads * stride;
-  __shared__ float dss[kSliHeads][kSliKeys + 1];
-  __shared__ float di_s[kSliKeys], w_s[kSliHeads];
-  __shared__ int64_t rows_s[kSliKeys];
+  __shared__ __align__(16) T ds_hi[kSliHeads * PK], ds_lo[kSliHeads * PK];   // [head][key]
+  __shared__ __align__(16) T dst_hi[KS * PH], dst_lo[KS * PH];               // [key][head]
+  __shared__ float di_s[KS], w_s[kSliHeads], red_s[kSliThreads / 32], dw_s[kSliThreads / 32][kSliHeads];
+  __shared__ int64_t rows_s[KS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
   const int32_t row = blockIdx.x;
   const int32_t h0 = blockIdx.y * kSliHeads;
   int32_t b;
   const int32_t n = sli_row_slots(p, row, &b);
-  const int ah = tid >> 4, ac = (tid & 15) * 2;   // dQI accumulator: head ah, columns ac + 32 j (+1)
-  const int nq = p.d_idx / 32;
-  float acc[32];
+  const int ntw = p.d_idx / 64;           // dQI column tiles of this warp: columns 8 (warp * ntw + t) ..
+  float acc[8][4];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-  float dw0 = 0.f, dw1 = 0.f;
+  for (int t = 0; t < 8; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+  float dw0 = 0.f, dw1 = 0.f;             // dW partial sums of heads g and g + 8
+  int dq_exp = 127;                       // acc holds dQI * 2^dq_exp (fp16 only)
 
   if (n > 0) {
     const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
@@ -433,73 +421,133 @@ __global__ void __launch_bounds__(kSliThreads) sli_grad_kernel(SliGradDev p) {
     if (tid < kSliHeads) w_s[tid] = h0 + tid < p.g ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h0 + tid) : 0.f;
     const int32_t* idx_row = p.sparse_indices ? p.sparse_indices + (int64_t)row * p.topk : nullptr;
     const float* di = p.di + (int64_t)row * p.topk;
-    const int gq = p.d_idx / 4;
-    for (int32_t j0 = 0; j0 < n; j0 += kSliKeys) {
+    for (int32_t j0 = 0; j0 < n; j0 += KS) {
       __syncthreads();
-      if (tid < kSliKeys) {
+      if (tid < KS) {
         const int32_t j = j0 + tid;
         rows_s[tid] = j < n ? (int64_t)b * p.s2 + sli_slot_key(p, idx_row, j) : -1;
         di_s[tid] = j < n ? di[j] : 0.f;
       }
       __syncthreads();
-      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s);
+      sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s, 1, 0, KS);
       __syncthreads();
+      float sc[4], dsv[4];
+      sli_tile_scores<T>(qs, ks, stride, p.d_idx, warp * 8, sc);
       {
-        float s0, s1;
-        sli_dots<T>(qs, ks, stride, p.d_idx, &s0, &s1);
-        const float dk = di_s[lane];
-        dw0 = fmaf(dk, fmaxf(s0, 0.f), dw0);
-        dw1 = fmaf(dk, fmaxf(s1, 0.f), dw1);
-        dss[warp][lane] = s0 > 0.f ? dk * w_s[warp] : 0.f;
-        dss[warp + 8][lane] = s1 > 0.f ? dk * w_s[warp + 8] : 0.f;
+        const int k = warp * 8 + 2 * c;
+        const float d0 = di_s[k], d1 = di_s[k + 1];
+        dw0 = fmaf(d0, fmaxf(sc[0], 0.f), fmaf(d1, fmaxf(sc[1], 0.f), dw0));
+        dw1 = fmaf(d0, fmaxf(sc[2], 0.f), fmaf(d1, fmaxf(sc[3], 0.f), dw1));
+        dsv[0] = sc[0] > 0.f ? d0 * w_s[g] : 0.f;
+        dsv[1] = sc[1] > 0.f ? d1 * w_s[g] : 0.f;
+        dsv[2] = sc[2] > 0.f ? d0 * w_s[g + 8] : 0.f;
+        dsv[3] = sc[3] > 0.f ? d1 * w_s[g + 8] : 0.f;
+      }
+      float up_k = 1.f, up_q = 1.f, dk_down = 1.f;
+      if constexpr (kScaled) {
+        float m = fmaxf(fmaxf(fabsf(dsv[0]), fabsf(dsv[1])), fmaxf(fabsf(dsv[2]), fabsf(dsv[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red_s[warp] = m;
+        __syncthreads();
+        m = red_s[0];
+#pragma unroll
+        for (int wv = 1; wv < kSliThreads / 32; ++wv) m = fmaxf(m, red_s[wv]);
+        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : 0;
+        e = max(-100, min(100, e));
+        if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
+          const float f = scalbnf(1.f, e - dq_exp);
+#pragma unroll
+          for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[t][x] *= f;
+          dq_exp = e;
+        }
+        up_k = scalbnf(1.f, e);
+        up_q = scalbnf(1.f, dq_exp);
+        dk_down = scalbnf(1.f, -e);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = g + (e >> 1) * 8, k = warp * 8 + 2 * c + (e & 1);
+        const float dk_ = dsv[e] * up_k, dq_ = dsv[e] * up_q;
+        const T kh = from_f32<T>(dk_), qh = from_f32<T>(dq_);
+        dst_hi[k * PH + h] = kh;
+        dst_lo[k * PH + h] = from_f32<T>(dk_ - to_f32<T>(kh));
+        ds_hi[h * PK + k] = qh;
+        ds_lo[h * PK + k] = from_f32<T>(dq_ - to_f32<T>(qh));
       }
       __syncthreads();
-      for (int k = 0; k < kSliKeys; ++k) {
-        const float w = dss[ah][k];
-        if (w == 0.f) continue;
-        const T* kr_ = &ks[k * stride + ac];
+
+      // dQI += ds . ki : 16 heads x (8 ntw) columns per warp, 64 keys deep
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j < nq) {
-            acc[2 * j] = fmaf(w, to_f32<T>(kr_[32 * j]), acc[2 * j]);
-            acc[2 * j + 1] = fmaf(w, to_f32<T>(kr_[32 * j + 1]), acc[2 * j + 1]);
+      for (int k0 = 0; k0 < KS; k0 += 16) {
+        uint32_t ah[4], al[4];
+        load_a_frag<T>(ah, ds_hi, PK, 0, k0);
+        load_a_frag<T>(al, ds_lo, PK, 0, k0);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          if (t < ntw) {
+            uint32_t b0, b1;
+            ldmatrix_b_trans<T>(b0, b1, &ks[k0 * stride + (warp * ntw + t) * 8], stride);
+            mma_16816<T>(acc[t], ah, b0, b1);
+            mma_16816<T>(acc[t], al, b0, b1);
           }
         }
       }
-      for (int u = tid; u < kSliKeys * gq; u += kSliThreads) {
-        const int k = u / gq, g4 = u - k * gq;
-        const int64_t r = rows_s[k];
-        if (r < 0) continue;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 4
-        for (int h = 0; h < kSliHeads; ++h) {
-          const float w = dss[h][k];
-          const uint2 v = *reinterpret_cast<const uint2*>(&qs[h * stride + 4 * g4]);
-          const T* e = reinterpret_cast<const T*>(&v);
-          a0 = fmaf(w, to_f32<T>(e[0]), a0); a1 = fmaf(w, to_f32<T>(e[1]), a1);
-          a2 = fmaf(w, to_f32<T>(e[2]), a2); a3 = fmaf(w, to_f32<T>(e[3]), a3);
+      // dKI += ds^T . qi : this warp's 16 keys x half of the columns, 16 heads deep
+      {
+        const int mt = warp & 3, nhalf = warp >> 2, nt_half = p.d_idx / 16;
+        uint32_t ah[4], al[4];
+        load_a_frag<T>(ah, dst_hi, PH, mt * 16, 0);
+        load_a_frag<T>(al, dst_lo, PH, mt * 16, 0);
+        const int64_t r_lo = rows_s[mt * 16 + g], r_hi = rows_s[mt * 16 + g + 8];
+        for (int t = 0; t < nt_half; ++t) {
+          const int n0 = (nhalf * nt_half + t) * 8;
+          uint32_t b0, b1;
+          ldmatrix_b_trans<T>(b0, b1, &qs[n0], stride);
+          float cf[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_16816<T>(cf, ah, b0, b1);
+          mma_16816<T>(cf, al, b0, b1);
+          if constexpr (kScaled) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) cf[x] *= dk_down;
+          }
+          red_tile(p.dki_acc, p.d_idx, r_lo, r_hi, n0, cf);
         }
-        red_add_v4(p.dki_acc + r * p.d_idx + 4 * g4, a0, a1, a2, a3);
       }
     }
   }
-  // dW (sum over the keys a lane saw) and dQI of this head chunk; zeros for unused rows
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    dw0 += __shfl_xor_sync(0xffffffffu, dw0, o);
-    dw1 += __shfl_xor_sync(0xffffffffu, dw1, o);
+  // dW: sum over the four lanes that share a head, then over the warps; dQI of this head chunk
+  // (zeros for unused rows)
+  dw0 += __shfl_xor_sync(0xffffffffu, dw0, 1);
+  dw0 += __shfl_xor_sync(0xffffffffu, dw0, 2);
+  dw1 += __shfl_xor_sync(0xffffffffu, dw1, 1);
+  dw1 += __shfl_xor_sync(0xffffffffu, dw1, 2);
+  __syncthreads();
+  if (c == 0) {
+    dw_s[warp][g] = dw0;
+    dw_s[warp][g + 8] = dw1;
   }
-  if (lane == 0) {
-    if (h0 + warp < p.g) store_weight(p.d_weights, p.dtype_w, (int64_t)row * p.g + h0 + warp, dw0);
-    if (h0 + warp + 8 < p.g) store_weight(p.d_weights, p.dtype_w, (int64_t)row * p.g + h0 + warp + 8, dw1);
-  }
-  if (h0 + ah < p.g) {
-    T* dst = (T*)p.d_query_index + ((int64_t)row * p.g + h0 + ah) * p.d_idx + ac;
+  __syncthreads();
+  if (tid < kSliHeads && h0 + tid < p.g) {
+    float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (j < nq) {
-        dst[32 * j] = from_f32<T>(acc[2 * j]);
-        dst[32 * j + 1] = from_f32<T>(acc[2 * j + 1]);
+    for (int wv = 0; wv < kSliThreads / 32; ++wv) sum += dw_s[wv][tid];
+    store_weight(p.d_weights, p.dtype_w, (int64_t)row * p.g + h0 + tid, sum);
+  }
+  const float dq_down = kScaled ? scalbnf(1.f, -dq_exp) : 1.f;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if (t < ntw) {
+      const int col = (warp * ntw + t) * 8 + 2 * c;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int h = g + half * 8;
+        if (h0 + h >= p.g) continue;
+        T* dst = (T*)p.d_query_index + ((int64_t)row * p.g + h0 + h) * p.d_idx + col;
+        dst[0] = from_f32<T>(acc[t][2 * half] * dq_down);
+        dst[1] = from_f32<T>(acc[t][2 * half + 1] * dq_down);
       }
     }
   }
