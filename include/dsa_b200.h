@@ -48,7 +48,8 @@ extern "C" {
 
 #define DSA_KERNEL_AUTO 0     /* tensor-core path when the shape is eligible, else portable */
 #define DSA_KERNEL_PORTABLE 1 /* CUDA-core kernels, any shape                               */
-#define DSA_KERNEL_TENSOR 2   /* tcgen05 path; DSA_ERR_UNSUPPORTED when not eligible        */
+#define DSA_KERNEL_TENSOR 2   /* tensor-core path (tcgen05 forward, mma.sync backward);
+                                 DSA_ERR_UNSUPPORTED when the shape is not eligible         */
 
 #define DSA_PHASE_SCORE 1
 #define DSA_PHASE_TOPK 2
@@ -151,7 +152,7 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
  */
 typedef struct DsaSfaGradParams {
   uint32_t struct_size; /* sizeof(DsaSfaGradParams) */
-  int32_t kernel;       /* DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE */
+  int32_t kernel;       /* DSA_KERNEL_*: the tensor-core kernel takes d = 512 (AUTO uses it there) */
   const void* query;      /* [rows, n1, d]      */
   const void* query_rope; /* [rows, n1, d_rope] */
   const void* key;        /* BSND [batch, s2, 1, d] | TND [T2, 1, d] */
