@@ -113,7 +113,9 @@ __device__ __forceinline__ void sli_stage_heads(T* dst, int stride, const T* a, 
   }
 }
 
-// Gathers the rows rows_s[0..nkeys) (16-byte chunks) of one or two key tensors into shared memory.
+// Gathers the rows rows_s[0..nkeys) (16-byte chunks) of one or two key tensors into shared memory
+// with cp.async (all of a thread's copies are in flight together; zeros for rows_s[k] < 0) and waits
+// for this thread's copies; the caller's barrier makes them visible to the block.
 // Row rows_s[k] of a tensor with `nh` heads per position is row rows_s[k] * nh + head.
 template <typename T>
 __device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, int wa, const T* b, int wb,
@@ -123,10 +125,14 @@ __device__ __forceinline__ void sli_gather_keys(T* dst, int stride, const T* a, 
   for (int i = threadIdx.x; i < nkeys * ct; i += kSliThreads) {
     const int k = i / ct, c = i - k * ct;
     const int64_t r = rows_s[k] < 0 ? -1 : rows_s[k] * nh + head;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r >= 0) v = c < ca ? reinterpret_cast<const uint4*>(a + r * wa)[c] : reinterpret_cast<const uint4*>(b + r * wb)[c - ca];
-    *reinterpret_cast<uint4*>(&dst[k * stride + c * 8]) = v;
+    const T* src = a;
+    if (r >= 0) src = c < ca ? a + r * wa + c * 8 : b + r * wb + (c - ca) * 8;
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(&dst[k * stride + c * 8]);
+    const int bytes = r >= 0 ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 // Tensor-core scores (mma.sync m16n8k16, fp32 accumulation) of the 16 staged heads against keys
