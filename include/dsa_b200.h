@@ -204,7 +204,7 @@ int dsa_sfa_grad(const DsaSfaGradParams* p, void* workspace, size_t workspace_by
  */
 typedef struct DsaSliGradParams {
   uint32_t struct_size; /* sizeof(DsaSliGradParams) */
-  int32_t kernel;       /* DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE */
+  int32_t kernel;       /* DSA_KERNEL_AUTO or DSA_KERNEL_PORTABLE (one implementation: both run it) */
   const void* query;       /* [batch, s1, n1, d]      */
   const void* query_rope;  /* [batch, s1, n1, d_rope] or NULL with d_rope = 0 */
   const void* key;         /* [batch, s2, 1, d]       */
