@@ -1,11 +1,14 @@
-// Portable (CUDA-core) sparse flash attention forward: any head count, D in {128,256,512},
-// all layouts, token-wise and block-wise indices.  Same math as _sfa_kernel's chunked path
+// Any-shape sparse flash attention forward: any head count, D in {128,256,512}, all layouts,
+// token-wise and block-wise indices.  Same math as _sfa_kernel's chunked path
 // (sparse_flash_attention_triton.py:461-604): rows gathered by index, invalid slots masked to
 // -inf, online softmax with fp32 statistics, probabilities rounded to the io dtype before the
-// second product (:520), value = key[..., :D].
+// second product (:520), value = key[..., :D].  One block per (query row, 16 heads) walks over the
+// row's slots 32 at a time; both products of a step run on the warp-level tensor-core instructions
+// (mma.sync m16n8k16, fp32 accumulation), the softmax in fp32 on the CUDA cores.
 #pragma once
 
 #include "dsa_common.cuh"
+#include "mma_sync.cuh"
 
 namespace dsa {
 
@@ -54,22 +57,28 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
   const int32_t stride = dq + kSfaSimtPad;
   T* qs = reinterpret_cast<T*>(sfa_smem);
   T* ks = qs + kSfaSimtHeads * stride;
-  __shared__ float ps[kSfaSimtHeads][kSfaSimtKeys];
+  __shared__ float sp[2][kSfaSimtHeads][kSfaSimtKeys + 1];            // partial scores of the two column halves
+  __shared__ __align__(16) T pt[kSfaSimtHeads * (kSfaSimtKeys + 8)];  // probabilities as the io dtype, [head][key]
   __shared__ float alpha_s[kSfaSimtHeads];
   __shared__ float l_s[kSfaSimtHeads];
   __shared__ float m_s[kSfaSimtHeads];
   __shared__ int32_t tok_s[kSfaSimtKeys];
   __shared__ int64_t krow_s[kSfaSimtKeys];
 
+  constexpr int PK = kSfaSimtKeys + 8;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c4 = lane & 3;
   const RowInfo ri = row_info(p.seq, row);
   const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
 
-  // accumulator mapping: head = tid / 16, columns 2*(tid%16) + 32*j (+1)
-  const int ah = tid >> 4, ac = (tid & 15) * 2;
-  float acc[32];
+  // output accumulator: heads g and g + 8, d / 64 column tiles of 8 per warp (warp w: columns
+  // (d / 8) w .. (d / 8) (w + 1) - 1), in the mma accumulator layout
+  const int ntw = p.d / 64;
+  float acc[8][4];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+  for (int t = 0; t < 8; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
   T* outp = (T*)p.out + ((int64_t)row * p.n1 + h0) * p.d;
   if (!row_active) {
@@ -129,40 +138,50 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
     }
     if (!__syncthreads_or(any)) continue;
 
-    // gather the rows (16-byte chunks; absent paged blocks read as zeros, like the un-paged cache)
+    // gather the rows with cp.async (16-byte chunks, all of a thread's copies in flight together;
+    // slots without a key and absent paged blocks are zero-filled, like the un-paged cache)
     {
       const int cn = p.d / 8, cr = p.d_rope / 8, ct = cn + cr;
       for (int i = tid; i < kSfaSimtKeys * ct; i += kSfaSimtThreads) {
-        int k = i / ct, c = i - k * ct;
-        int64_t kr_ = krow_s[k];
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (kr_ >= 0) {
-          v = c < cn ? reinterpret_cast<const uint4*>(kn + kr_ * p.d)[c]
-                     : reinterpret_cast<const uint4*>(kr + kr_ * p.d_rope)[c - cn];
-        }
-        *reinterpret_cast<uint4*>(&ks[k * stride + c * 8]) = v;
+        const int k = i / ct, c = i - k * ct;
+        const int64_t kr_ = krow_s[k];
+        const T* src = kn;
+        if (kr_ >= 0) src = c < cn ? kn + kr_ * p.d + c * 8 : kr + kr_ * p.d_rope + (c - cn) * 8;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&ks[k * stride + c * 8]);
+        const int bytes = kr_ >= 0 ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_all;" ::: "memory");
     }
     __syncthreads();
 
-    // scores: thread -> key = lane, heads warp and warp + 8
+    // scores on the tensor cores: warp w takes the 8-key tile w % 4 over half w / 4 of the columns
     {
-      float s0 = 0.f, s1 = 0.f;
-      const uint4* kp = reinterpret_cast<const uint4*>(&ks[lane * stride]);
-      const uint4* q0 = reinterpret_cast<const uint4*>(&qs[warp * stride]);
-      const uint4* q1 = reinterpret_cast<const uint4*>(&qs[(warp + 8) * stride]);
-      for (int c = 0; c < dq / 8; ++c) {
-        uint4 kv = kp[c], a = q0[c], b = q1[c];
-        const T* kk = reinterpret_cast<const T*>(&kv);
-        const T* aa = reinterpret_cast<const T*>(&a);
-        const T* bb = reinterpret_cast<const T*>(&b);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float kf = to_f32<T>(kk[e]);
-          s0 = fmaf(kf, to_f32<T>(aa[e]), s0);
-          s1 = fmaf(kf, to_f32<T>(bb[e]), s1);
-        }
+      const int n0 = (warp & 3) * 8, half = warp >> 2, kh = dq / 32;      // kh 16-column steps per half (even)
+      const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(
+          qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
+      const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(&ks[(n0 + (lane & 7)) * stride + (lane >> 3) * 8]);
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int st = half * kh; st < (half + 1) * kh; st += 2) {
+        uint32_t a0[4], a1[4], b[4];
+        ldmatrix_x4(a0, a_addr + st * 16 * (int)sizeof(T));
+        ldmatrix_x4(a1, a_addr + (st + 1) * 16 * (int)sizeof(T));
+        ldmatrix_x4(b, b_addr + st * 16 * (int)sizeof(T));
+        mma_16816<T>(c0, a0, b[0], b[1]);
+        mma_16816<T>(c1, a1, b[2], b[3]);
       }
+      sp[half][g][n0 + 2 * c4] = c0[0] + c1[0];
+      sp[half][g][n0 + 2 * c4 + 1] = c0[1] + c1[1];
+      sp[half][g + 8][n0 + 2 * c4] = c0[2] + c1[2];
+      sp[half][g + 8][n0 + 2 * c4 + 1] = c0[3] + c1[3];
+    }
+    __syncthreads();
+
+    // softmax step: thread -> key = lane, heads warp and warp + 8
+    {
+      float s0 = sp[0][warp][lane] + sp[1][warp][lane];
+      float s1 = sp[0][warp + 8][lane] + sp[1][warp + 8][lane];
       const bool valid = tok_s[lane] >= 0;
       s0 = valid ? s0 * p.scale : -INFINITY;
       s1 = valid ? s1 * p.scale : -INFINITY;
@@ -177,7 +196,7 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
         if (two_pass && pass == 1) {
           const float l = l_s[h];
           const float pv = (valid && l > 0.f) ? expf(sv - m_old) / l : 0.f;
-          ps[h][lane] = round_io<T>(pv);
+          pt[h * PK + lane] = from_f32<T>(pv);
           if (lane == 0) alpha_s[h] = 1.f;
           continue;
         }
@@ -187,7 +206,7 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
         float sum = pv;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        ps[h][lane] = round_io<T>(pv);
+        pt[h * PK + lane] = from_f32<T>(pv);
         __syncwarp();
         if (lane == 0) {
           const float a = m_old == -INFINITY ? 0.f : expf(m_old - m_safe);
@@ -201,21 +220,21 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
 
     // accumulate: acc = acc * alpha + P . V   (skipped in the statistics pass)
     if (!(two_pass && pass == 0)) {
-      const float a = alpha_s[ah];
-      const int nj = p.d / 32;
+      const float a_lo = alpha_s[g], a_hi = alpha_s[g + 8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (j < nj) { acc[2 * j] *= a; acc[2 * j + 1] *= a; }
+      for (int t = 0; t < 8; ++t) {
+        if (t < ntw) { acc[t][0] *= a_lo; acc[t][1] *= a_lo; acc[t][2] *= a_hi; acc[t][3] *= a_hi; }
       }
-      for (int k = 0; k < kSfaSimtKeys; ++k) {
-        const float pk = ps[ah][k];
-        if (pk == 0.f) continue;
-        const T* vr = &ks[k * stride + ac];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j < nj) {
-            acc[2 * j] = fmaf(pk, to_f32<T>(vr[32 * j]), acc[2 * j]);
-            acc[2 * j + 1] = fmaf(pk, to_f32<T>(vr[32 * j + 1]), acc[2 * j + 1]);
+      for (int k0 = 0; k0 < kSfaSimtKeys; k0 += 16) {
+        uint32_t a[4];
+        load_a_frag<T>(a, pt, PK, 0, k0);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          if (t < ntw) {
+            uint32_t b0, b1;
+            ldmatrix_b_trans<T>(b0, b1, &ks[k0 * stride + (warp * ntw + t) * 8], stride);
+            mma_16816<T>(acc[t], a, b0, b1);
           }
         }
       }
@@ -225,16 +244,19 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
 
   // epilogue
   {
-    const float l = l_s[ah];
-    const float inv = two_pass ? 1.f : (l > 0.f ? 1.f / l : 0.f);
-    const int nj = p.d / 32;
-    if (h0 + ah < p.n1) {
-      T* o = outp + (int64_t)ah * p.d + ac;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (j < nj) {
-          o[32 * j] = from_f32<T>(acc[2 * j] * inv);
-          o[32 * j + 1] = from_f32<T>(acc[2 * j + 1] * inv);
+    for (int half = 0; half < 2; ++half) {
+      const int h = g + half * 8;
+      if (h0 + h >= p.n1) continue;
+      const float l = l_s[h];
+      const float inv = two_pass ? 1.f : (l > 0.f ? 1.f / l : 0.f);
+      T* o = outp + (int64_t)h * p.d;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < ntw) {
+          const int col = (warp * ntw + t) * 8 + 2 * c4;
+          o[col] = from_f32<T>(acc[t][2 * half] * inv);
+          o[col + 1] = from_f32<T>(acc[t][2 * half + 1] * inv);
         }
       }
     }
