@@ -11,7 +11,7 @@
 #include "li_score_simt.cuh"
 #include "li_score_sm100.cuh"
 #include "li_topk.cuh"
-#include "sfa_fwd_simt.cuh"
+#include "sfa_fwd_mma.cuh"
 #include "sfa_fwd_sm100.cuh"
 #include "sfa_bwd_simt.cuh"
 #include "sfa_bwd_mma.cuh"
@@ -187,12 +187,12 @@ static int sfa_launch_simt(const DsaSfaParams* p, cudaStream_t st) {
   SfaDev d = sfa_dev(p);
   if (d.rows == 0) return DSA_OK;
   const size_t smem = (size_t)(kSfaSimtHeads + kSfaSimtKeys) * (p->d + p->d_rope + kSfaSimtPad) * sizeof(T);
-  if (cudaFuncSetAttribute(sfa_fwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+  if (cudaFuncSetAttribute(sfa_fwd_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return DSA_ERR_CUDA;
   const unsigned gy = (unsigned)((p->n1 + kSfaSimtHeads - 1) / kSfaSimtHeads);
   dim3 grid((unsigned)d.rows, gy, 1);
-  sfa_fwd_simt_kernel<T><<<grid, kSfaSimtThreads, smem, st>>>(d);
+  sfa_fwd_mma_kernel<T><<<grid, kSfaSimtThreads, smem, st>>>(d);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   count_launch();
   return DSA_OK;

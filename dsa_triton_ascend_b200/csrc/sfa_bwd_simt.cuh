@@ -12,7 +12,7 @@
 #pragma once
 
 #include "dsa_common.cuh"
-#include "sfa_fwd_simt.cuh"
+#include "sfa_fwd_mma.cuh"
 
 namespace dsa {
 

@@ -51,7 +51,7 @@ __device__ __forceinline__ int32_t sfa_slot_token(const SfaDev& p, const RowInfo
 // One query row, 16 heads starting at h0, by one block of 256 threads.
 // dynamic smem: (16 + 32) * (d + d_rope + pad) elements of T.
 template <typename T>
-__device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, int32_t h0) {
+__device__ __forceinline__ void sfa_fwd_mma_row(const SfaDev& p, int32_t row, int32_t h0) {
   extern __shared__ __align__(16) unsigned char sfa_smem[];
   const int32_t dq = p.d + p.d_rope;
   const int32_t stride = dq + kSfaSimtPad;
@@ -270,8 +270,8 @@ __device__ __forceinline__ void sfa_fwd_simt_row(const SfaDev& p, int32_t row, i
 
 // grid = (rows, ceil(n1 / 16)); block = 256 threads.
 template <typename T>
-__global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_simt_kernel(SfaDev p) {
-  sfa_fwd_simt_row<T>(p, (int32_t)blockIdx.x, (int32_t)blockIdx.y * kSfaSimtHeads);
+__global__ void __launch_bounds__(kSfaSimtThreads) sfa_fwd_mma_kernel(SfaDev p) {
+  sfa_fwd_mma_row<T>(p, (int32_t)blockIdx.x, (int32_t)blockIdx.y * kSfaSimtHeads);
 }
 
 // Recomputes the rows listed in redo_list[0 .. *redo_count) (rows whose scores outgrew the
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(kSfaSimtThreads) sfa_redo_kernel(SfaDev p, con
   const int64_t work = (int64_t)min(*redo_count, p.rows) * chunks;
   for (int64_t i = blockIdx.x; i < work; i += gridDim.x) {
     __syncthreads();   // the previous row's shared state is no longer read
-    sfa_fwd_simt_row<T>(p, redo_list[i / chunks], (int32_t)(i % chunks) * kSfaSimtHeads);
+    sfa_fwd_mma_row<T>(p, redo_list[i / chunks], (int32_t)(i % chunks) * kSfaSimtHeads);
   }
 }
 

@@ -57,7 +57,7 @@
 #include <mutex>
 
 #include "ptx_sm100.cuh"
-#include "sfa_fwd_simt.cuh"
+#include "sfa_fwd_mma.cuh"
 
 namespace dsa {
 

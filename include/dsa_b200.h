@@ -47,7 +47,7 @@ extern "C" {
 #define DSA_RANK_FP32 1     /* rank raw fp32 scores (what the reference device path does) */
 
 #define DSA_KERNEL_AUTO 0     /* tensor-core path when the shape is eligible, else portable */
-#define DSA_KERNEL_PORTABLE 1 /* CUDA-core kernels, any shape                               */
+#define DSA_KERNEL_PORTABLE 1 /* any-shape kernels (mma.sync / CUDA cores)                    */
 #define DSA_KERNEL_TENSOR 2   /* tensor-core path (tcgen05 forward, mma.sync backward);
                                  DSA_ERR_UNSUPPORTED when the shape is not eligible         */
 
