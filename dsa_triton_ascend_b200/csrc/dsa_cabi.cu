@@ -239,7 +239,27 @@ static int sfa_grad_validate(const DsaSfaGradParams* p) {
   if (p->layout_kv == DSA_LAYOUT_TND && (!p->seq_k || !p->seq_k_cumulative)) return DSA_ERR_VALUE;
   if (p->kernel != DSA_KERNEL_AUTO && p->kernel != DSA_KERNEL_PORTABLE && p->kernel != DSA_KERNEL_TENSOR)
     return DSA_ERR_UNSUPPORTED;
-  if (p->kernel == DSA_KERNEL_TENSOR && p->d != kSfaMmaD) return DSA_ERR_UNSUPPORTED;
+  return DSA_OK;
+}
+
+// 32 heads per block when there are more than 16 (half the scatter-adds per query row), else 16.
+template <typename T, int D>
+static int sfa_grad_mma_launch(const SfaGradDev& d, int n1, cudaStream_t st) {
+  if (n1 > 16) {
+    const size_t smem = sfa_grad_mma_smem_bytes<2, D>(sizeof(T));
+    if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 2, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DSA_ERR_CUDA;
+    dim3 grid((unsigned)d.rows, (unsigned)((n1 + 31) / 32), 1);
+    sfa_bwd_mma_kernel<T, 2, D><<<grid, 512, smem, st>>>(d);
+  } else {
+    const size_t smem = sfa_grad_mma_smem_bytes<1, D>(sizeof(T));
+    if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 1, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DSA_ERR_CUDA;
+    dim3 grid((unsigned)d.rows, 1, 1);
+    sfa_bwd_mma_kernel<T, 1, D><<<grid, 256, smem, st>>>(d);
+  }
   return DSA_OK;
 }
 
@@ -266,23 +286,13 @@ static int sfa_grad_launch(const DsaSfaGradParams* p, float* acc, cudaStream_t s
   if (d.rows > 0) {
     const unsigned gy = (unsigned)((p->n1 + kSfaGradHeads - 1) / kSfaGradHeads);
     dim3 grid((unsigned)d.rows, gy, 1);
-    // D = 512: the contractions run on the tensor cores (mma.sync); other widths, or on request, the
-    // CUDA-core kernel
-    if (p->d == kSfaMmaD && p->kernel != DSA_KERNEL_PORTABLE) {
-      if (p->n1 > 16) {   // 32 heads per block: half the scatter-adds per query row
-        const size_t smem = sfa_grad_mma_smem_bytes<2>(sizeof(T));
-        if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-            cudaSuccess)
-          return DSA_ERR_CUDA;
-        dim3 grid2((unsigned)d.rows, (unsigned)((p->n1 + 31) / 32), 1);
-        sfa_bwd_mma_kernel<T, 2><<<grid2, 512, smem, st>>>(d);
-      } else {
-        const size_t smem = sfa_grad_mma_smem_bytes<1>(sizeof(T));
-        if (cudaFuncSetAttribute(sfa_bwd_mma_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-            cudaSuccess)
-          return DSA_ERR_CUDA;
-        sfa_bwd_mma_kernel<T, 1><<<grid, 256, smem, st>>>(d);
-      }
+    // the contractions run on the tensor cores (mma.sync); on request the CUDA-core kernel
+    if (p->kernel != DSA_KERNEL_PORTABLE) {
+      int rc;
+      if (p->d == 512) rc = sfa_grad_mma_launch<T, 512>(d, p->n1, st);
+      else if (p->d == 256) rc = sfa_grad_mma_launch<T, 256>(d, p->n1, st);
+      else rc = sfa_grad_mma_launch<T, 128>(d, p->n1, st);
+      if (rc != DSA_OK) return rc;
     } else {
       const size_t smem = sfa_grad_smem_bytes(p->d, p->d_rope, sizeof(T));
       if (cudaFuncSetAttribute(sfa_bwd_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=

@@ -1,9 +1,9 @@
 // Sparse flash attention backward with the five contractions of a key chunk on the warp-level tensor
-// core instructions (mma.sync m16n8k16, fp32 accumulation), for D = 512, D_rope = 64.  Same math and
+// core instructions (mma.sync m16n8k16, fp32 accumulation), for D in {128, 256, 512}, D_rope = 64.  Same math and
 // the same block shape as sfa_bwd_simt_kernel (sparse_flash_attention_grad_triton.py:100-470, golden
 // sparse_flash_attention_grad_numpy.py:96-135): one block per (query row, 16 heads) walks over the
 // row's selected keys 32 at a time,
-//     S  = q . k^T (576 columns)          dP = dO . k_nope^T (512 columns)
+//     S  = q . k^T (D + 64 columns)       dP = dO . k_nope^T (D columns)
 //     P  = exp(S * scale - max) / sum     dS = P * (dP - delta) * scale
 //     dQ += dS . k        dK += dS^T . q        dV += P^T . dO
 // q, k and dO are multiplied as the io dtype they arrive in (exact products, fp32 sums).  P and dS
@@ -18,9 +18,7 @@
 
 namespace dsa {
 
-constexpr int kSfaMmaD = 512, kSfaMmaDr = 64, kSfaMmaDq = kSfaMmaD + kSfaMmaDr;
-constexpr int kSfaMmaStride = kSfaMmaDq + kSfaGradPad;    // q / key rows, elements
-constexpr int kSfaMmaDStride = kSfaMmaD + kSfaGradPad;    // dO rows
+constexpr int kSfaMmaDr = 64;
 constexpr int kSfaMmaPk = kSfaGradKeys + 8;               // [head][key] operand rows (40 elements)
 
 // Adds the 16 x 8 accumulator tile (rows -> key rows krow_lo / krow_hi of this lane's two rows,
@@ -43,14 +41,19 @@ __device__ __forceinline__ void red_tile(float* acc, int width, int64_t krow_lo,
 // MT = 16-head tiles per block (1 or 2): HB = 16 MT heads, 256 MT threads.  Every scatter-add of d_key /
 // d_value covers the block's heads, so two tiles halve the reductions per query row; they cost one
 // block per SM instead of two (with the same number of warps).
-// grid = (rows, ceil(n1 / HB)).  dynamic smem: q [HB][584] | keys [32][584] | dO [HB][520], elements of T.
-template <int MT>
+// grid = (rows, ceil(n1 / HB)).  dynamic smem: q [HB][D+72] | keys [32][D+72] | dO [HB][D+8], elements of T.
+template <int MT, int D>
 inline size_t sfa_grad_mma_smem_bytes(size_t elem) {
-  return ((size_t)(16 * MT + kSfaGradKeys) * kSfaMmaStride + (size_t)16 * MT * kSfaMmaDStride) * elem;
+  return ((size_t)(16 * MT + kSfaGradKeys) * (D + kSfaMmaDr + kSfaGradPad) + (size_t)16 * MT * (D + kSfaGradPad)) * elem;
 }
 
-template <typename T, int MT>
+template <typename T, int MT, int D>
 __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(SfaGradDev p) {
+  constexpr int kSfaMmaD = D, kSfaMmaDq = D + kSfaMmaDr;
+  constexpr int kSfaMmaStride = kSfaMmaDq + kSfaGradPad;    // q / key rows, elements
+  constexpr int kSfaMmaDStride = kSfaMmaD + kSfaGradPad;    // dO rows
+  constexpr int QT = kSfaMmaDq / 64;                        // d_query / d_key column tiles of 8 per warp (9 at D = 512)
+  constexpr int VT = kSfaMmaD / 64;                         // d_value column tiles per warp
   constexpr int HB = 16 * MT, NT = 256 * MT;
   constexpr int PH = HB + 8;              // [key][head] operand rows, elements
   extern __shared__ __align__(16) unsigned char sfa_grad_smem[];
@@ -76,12 +79,12 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
   const RowInfo ri = row_info(p.seq, row);
   const bool row_active = ri.pos < ri.act_q && ri.threshold > 0 && ri.act_k > 0;
   const int qm0 = (warp >> 3) * 16;       // head tile of this warp in the d_query product
-  const int qn0 = (warp & 7) * 72;        // its first column there and in the d_key product
+  const int qn0 = (warp & 7) * (QT * 8);  // its first column there and in the d_key product
 
-  // d_query accumulator: 16 heads x 72 columns (nine tiles of 8) per warp
-  float acc[9][4];
+  // d_query accumulator: 16 heads x 8 QT columns per warp
+  float acc[QT][4];
 #pragma unroll
-  for (int t = 0; t < 9; ++t)
+  for (int t = 0; t < QT; ++t)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
         if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
           const float f = scalbnf(1.f, e - dq_exp);
 #pragma unroll
-          for (int t = 0; t < 9; ++t)
+          for (int t = 0; t < QT; ++t)
 #pragma unroll
             for (int x = 0; x < 4; ++x) acc[t][x] *= f;
           dq_exp = e;
@@ -271,14 +274,14 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
     }
     __syncthreads();
 
-    // d_query (nope | rope) += dS . k : 16 heads x 72 columns per warp, 32 keys deep
+    // d_query (nope | rope) += dS . k : 16 heads x 8 QT columns per warp, 32 keys deep
 #pragma unroll
     for (int k0 = 0; k0 < kSfaGradKeys; k0 += 16) {
       uint32_t ah[4], al[4];
       load_a_frag<T>(ah, ds_hi, kSfaMmaPk, qm0, k0);
       load_a_frag<T>(al, ds_lo, kSfaMmaPk, qm0, k0);
 #pragma unroll
-      for (int t = 0; t < 9; ++t) {
+      for (int t = 0; t < QT; ++t) {
         uint32_t b0, b1;
         ldmatrix_b_trans<T>(b0, b1, &ks[k0 * kSfaMmaStride + qn0 + t * 8], kSfaMmaStride);
         mma_16816<T>(acc[t], ah, b0, b1);
@@ -292,11 +295,11 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
     if (jn < slots) gather_async(buf ^ 1);
 
     // d_key (nope | rope) += dS^T . q and d_value += P^T . dO, HB heads deep.  A warp takes 2 / MT
-    // 16-key tiles x 72 columns of d_key and x 64 columns of d_value.
+    // 16-key tiles x 8 QT columns of d_key and x 8 VT columns of d_value.
     {
       constexpr int KT = 2 / MT;             // key tiles per warp
       const int kt0 = MT == 2 ? (warp >> 3) : 0;
-      const int vn0 = (warp & 7) * 64;
+      const int vn0 = (warp & 7) * (VT * 8);
       uint32_t ah[KT][MT][4], al[KT][MT][4];
 #pragma unroll
       for (int kt = 0; kt < KT; ++kt)
@@ -305,7 +308,7 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
           load_a_frag<T>(ah[kt][hs], dst_hi, PH, (kt0 + kt) * 16, hs * 16);
           load_a_frag<T>(al[kt][hs], dst_lo, PH, (kt0 + kt) * 16, hs * 16);
         }
-      for (int t = 0; t < 9; ++t) {
+      for (int t = 0; t < QT; ++t) {
         const int n0 = qn0 + t * 8;
         uint32_t b[MT][2];
 #pragma unroll
@@ -333,7 +336,7 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
           load_a_frag<T>(ah[kt][hs], pt_hi, PH, (kt0 + kt) * 16, hs * 16);
           load_a_frag<T>(al[kt][hs], pt_lo, PH, (kt0 + kt) * 16, hs * 16);
         }
-      for (int t = 0; t < 8; ++t) {
+      for (int t = 0; t < VT; ++t) {
         const int n0 = vn0 + t * 8;
         uint32_t b[MT][2];
 #pragma unroll
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
   // d_query / d_query_rope of this head chunk (zeros for inactive rows)
   const float dq_down = kScaled ? scalbnf(1.f, -dq_exp) : 1.f;
 #pragma unroll
-  for (int t = 0; t < 9; ++t) {
+  for (int t = 0; t < QT; ++t) {
     const int col = qn0 + t * 8 + 2 * c;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {

@@ -24,7 +24,7 @@ _kernel = _cabi.KERNEL_AUTO
 
 
 def set_kernel(kind):
-    """"auto", "portable" (CUDA-core kernel) or "tensor" (mma.sync kernel for D = 512, error otherwise)."""
+    """"auto" / "tensor" (mma.sync kernel) or "portable" (CUDA-core kernel)."""
     global _kernel
     _kernel = {"auto": _cabi.KERNEL_AUTO, "portable": _cabi.KERNEL_PORTABLE, "tensor": _cabi.KERNEL_TENSOR}[kind]
 

@@ -152,7 +152,7 @@ int dsa_sfa_forward(const DsaSfaParams* p, void* workspace, size_t workspace_byt
  */
 typedef struct DsaSfaGradParams {
   uint32_t struct_size; /* sizeof(DsaSfaGradParams) */
-  int32_t kernel;       /* DSA_KERNEL_*: the tensor-core kernel takes d = 512 (AUTO uses it there) */
+  int32_t kernel;       /* DSA_KERNEL_AUTO / _TENSOR: mma.sync kernel; _PORTABLE: CUDA-core kernel */
   const void* query;      /* [rows, n1, d]      */
   const void* query_rope; /* [rows, n1, d_rope] */
   const void* key;        /* BSND [batch, s2, 1, d] | TND [T2, 1, d] */

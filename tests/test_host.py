@@ -164,10 +164,10 @@ def test_sfa_grad_guards_raise_value_error_like_the_reference():
     assert n.value == 256 + 64 * (2 * 512 + 64) * 4
     g.layout_kv = 2                                   # paged caches are not differentiated
     assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -3
-    g.layout_kv, g.kernel = 0, 2                      # the tensor-core backward takes D = 512 only
+    g.layout_kv, g.kernel = 0, 2                      # tensor-core and CUDA-core kernels take every legal shape
     assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
     g.d = 256
-    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -5
+    assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == 0
     g.kernel = 7
     assert _cabi.lib.dsa_sfa_grad_workspace_bytes(ctypes.byref(g), ctypes.byref(n)) == -5
     g.kernel = 0
