@@ -244,7 +244,9 @@ __global__ void __launch_bounds__(256 * MT, MT == 1 ? 2 : 1) sfa_bwd_mma_kernel(
         m = red_s[0];
 #pragma unroll
         for (int wv = 1; wv < NT / 32; ++wv) m = fmaxf(m, red_s[wv]);
-        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : 0;
+        // (a chunk whose values are all zero must not pin the accumulator's scale: it keeps the
+        // current one, or 2^100 before the first chunk with a non-zero value)
+        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : min(dq_exp, 100);
         e = max(-100, min(100, e));
         if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
           const float f = scalbnf(1.f, e - dq_exp);

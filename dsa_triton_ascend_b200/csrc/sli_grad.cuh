@@ -459,7 +459,9 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
         m = red_s[0];
 #pragma unroll
         for (int wv = 1; wv < kSliThreads / 32; ++wv) m = fmaxf(m, red_s[wv]);
-        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : 0;
+        // (a chunk whose values are all zero must not pin the accumulator's scale: it keeps the
+        // current one, or 2^100 before the first chunk with a non-zero value)
+        int e = (m > 0.f && m < INFINITY) ? 13 - ilogbf(m) : min(dq_exp, 100);
         e = max(-100, min(100, e));
         if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
           const float f = scalbnf(1.f, e - dq_exp);

@@ -109,6 +109,36 @@ def test_grad_both_kernels(kernel, dtype, D):
     _check(got, ref, dtype, S1)
 
 
+def test_grad_fp16_chunk_of_zero_probabilities_before_small_gradients():
+    """fp16 operands of the second products are scaled per 32-key chunk from the chunk's largest |dS|.
+    The first chunk here has probabilities that underflow to exactly zero (dS = 0) and the chunks after
+    it carry gradients around 1e-6: a scale pinned by the all-zero chunk would push them into fp16's
+    subnormal range."""
+    from dsa_triton_ascend_b200 import sparse_flash_attention_grad_triton
+    B, S1, S2, N1, D = 1, 2, 96, 16, 512
+    rng = np.random.RandomState(3)
+    q = np.full((B, S1, N1, D), 2.0, np.float32)
+    qr = np.full((B, S1, N1, 64), 2.0, np.float32)
+    k = np.full((B, S2, 1, D), 2.0, np.float32)
+    kr = np.full((B, S2, 1, 64), 2.0, np.float32)
+    k[:, :32] = -2.0
+    kr[:, :32] = -2.0
+    k[:, 32:] += (rng.randint(-2, 3, size=(B, S2 - 32, 1, D)) / 64.0).astype(np.float32)   # fp16-exact jitter
+    do = (rng.randn(B, S1, N1, D) * 1e-3).astype(np.float16).astype(np.float32)
+    idx = np.tile(np.arange(S2, dtype=np.int32), (B, S1, 1, 1))
+    scale = 1.0 / 24.0
+    out, smax, ssum = sparse_flash_attention_oracle(q, k, idx, qr, kr, scale, [S1], [S2], sparse_mode=0,
+                                                    return_softmax_lse=True, dtype="fp16")
+    ref = sparse_flash_attention_grad_oracle(q, k, idx, do, out, smax, ssum, qr, kr, scale, [S1], [S2],
+                                             sparse_mode=0, dtype="fp16")
+    assert np.abs(ref[0]).max() > 0 and np.abs(ref[0]).max() < 1e-3
+    h = torch.float16
+    got = sparse_flash_attention_grad_triton(dev(q, h), dev(k, h), dev(k, h), dev(idx), dev(do, h), dev(out, h),
+                                             dev(smax), dev(ssum), scale_value=scale, query_rope=dev(qr, h),
+                                             key_rope=dev(kr, h), sparse_mode=0)
+    _check(got, ref, "fp16", S1)
+
+
 def test_grad_tnd_layout_equals_the_padded_bsnd_problem():
     """TND batch with cumulative lengths (sparse_flash_attention_grad_triton.py:566-581 pads it to
     BSND): the token-major gradients equal the oracle's BSND gradients packed back."""
