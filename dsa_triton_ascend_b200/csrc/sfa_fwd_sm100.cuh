@@ -178,37 +178,52 @@ __global__ void __launch_bounds__(128) sfa_compact_kernel(SfaDev p, int2* __rest
     // it plus its own earlier ones)
     const bool wide = p.sparse_block_size == 1 && (p.sparse_count & 3) == 0 &&
                       ((reinterpret_cast<uintptr_t>(p.sparse_indices) & 15) == 0);
-    for (int32_t j0 = 0; wide && j0 < slots; j0 += 128) {
-      const int32_t j = j0 + 4 * lane;
-      int4 v = make_int4(-1, -1, -1, -1);
-      if (j < slots) v = *reinterpret_cast<const int4*>(idx_row + j);
-      const int32_t id[4] = {v.x, v.y, v.z, v.w};
-      int32_t prow[4];
-      uint32_t below = 0, total = 0;
+    // (four steps are resolved together so that their index loads and block-table look-ups are in
+    // flight at the same time: with few rows - decode - the pre-pass is bound by that latency)
+    for (int32_t j0 = 0; wide && j0 < slots; j0 += 512) {
+      int4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int32_t j = j0 + u * 128 + 4 * lane;
+        v[u] = make_int4(-1, -1, -1, -1);
+        if (j < slots) v[u] = *reinterpret_cast<const int4*>(idx_row + j);
+      }
+      int32_t prow[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int32_t id[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int64_t r = -1;
+          const int64_t tok = id[e];
+          if (tok >= 0 && tok < ri.threshold && tok < ri.act_k &&
+              (p.seq.layout_k == DSA_LAYOUT_PA_BSND || tok < p.seq.s2)) {
+            r = key_row(p.seq, ri, (int32_t)tok);
+            if (r < 0 || r >= oob_row) r = oob_row;
+          }
+          prow[u][e] = (int32_t)r;
+        }
+      }
       const uint32_t lt = (1u << lane) - 1u;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int64_t r = -1;
-        const int64_t tok = id[e];
-        if (tok >= 0 && tok < ri.threshold && tok < ri.act_k &&
-            (p.seq.layout_k == DSA_LAYOUT_PA_BSND || tok < p.seq.s2)) {
-          r = key_row(p.seq, ri, (int32_t)tok);
-          if (r < 0 || r >= oob_row) r = oob_row;
-        }
-        prow[e] = (int32_t)r;
-        const uint32_t m = __ballot_sync(0xffffffffu, r >= 0);
-        below += __popc(m & lt);
-        total += __popc(m);
-      }
-      int32_t* o = out + n + below;
-      if (total == 128 && ((n & 3) == 0)) {
-        *reinterpret_cast<int4*>(o) = make_int4(prow[0], prow[1], prow[2], prow[3]);
-      } else {
+      for (int u = 0; u < 4; ++u) {
+        uint32_t below = 0, total = 0;
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (prow[e] >= 0) *o++ = prow[e];
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t m = __ballot_sync(0xffffffffu, prow[u][e] >= 0);
+          below += __popc(m & lt);
+          total += __popc(m);
+        }
+        int32_t* o = out + n + below;
+        if (total == 128 && ((n & 3) == 0)) {
+          *reinterpret_cast<int4*>(o) = make_int4(prow[u][0], prow[u][1], prow[u][2], prow[u][3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (prow[u][e] >= 0) *o++ = prow[u][e];
+        }
+        n += (int32_t)total;
       }
-      n += (int32_t)total;
     }
     for (int32_t j0 = wide ? slots : 0; j0 < slots; j0 += 32) {
       const int32_t j = j0 + lane;
