@@ -47,7 +47,9 @@ constexpr uint32_t kLiKStage = 2 * kLiKBlock;             // 32 KB
 constexpr uint32_t kLiOffK = kLiQBytes;
 constexpr uint32_t kLiOffW = kLiOffK + kLiStages * kLiKStage;
 constexpr uint32_t kLiOffBar = kLiOffW + kLiTok * kLiHeads * 4;
-constexpr uint32_t kLiSmemBytes = kLiOffBar + 256;
+constexpr int kLiDenseGroups = 128;   // most row groups of the dense chunked mode (its table sits behind the barriers)
+constexpr uint32_t kLiOffCum = kLiOffBar + 256;
+constexpr uint32_t kLiSmemBytes = kLiOffCum + (kLiDenseGroups + 2) * 4;
 // Byte offset of key stage s: stages 3 and 4 live in the second half of the Q buffer.
 __host__ __device__ constexpr uint32_t li_stage_off(uint32_t s) {
   return s < (uint32_t)kLiStages ? kLiOffK + s * kLiKStage : 2 * kLiQBlock + (s - kLiStages) * kLiKStage;
@@ -68,6 +70,7 @@ struct LiSm100Args {
   int32_t krow_oob;       // a row coordinate past the key tensor (loads as zeros)
   uint32_t idesc;         // M=128, N=256: four rows per accumulator
   uint32_t idesc_n128;    // M=128, N=128: row groups of at most two rows
+  int32_t dense;          // chunked mode: items are only the chunks that hold keys (see li_dense_setup)
 };
 
 // One work item: up to 8 consecutive query rows of one sequence.
@@ -81,13 +84,9 @@ struct LiItem {
 // Item i -> rows.  BSND: sequences interleaved, later row groups first (under the causal mask they
 // see more keys, so item 0 is the most work).  TND: sequences in order (their group counts are
 // only known on the device), later groups first inside each sequence.
-__device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
+__device__ __forceinline__ LiItem li_group(const LiSm100Args& a, int32_t i) {
   LiItem it;
-  it.row0 = -1; it.nrows = 0; it.krow0 = 0; it.b = 0;
-  // chunk-major: the first chunks exist for every sequence, later ones only for the long sequences,
-  // so work decreases with the item number as the snake order assumes
-  it.chunk = i / a.groups;
-  i -= it.chunk * a.groups;
+  it.row0 = -1; it.nrows = 0; it.krow0 = 0; it.b = 0; it.chunk = 0;
   const SeqDesc& s = a.p.seq;
   int32_t b, pos0, len_q, start_q;
   if (s.layout_q == DSA_LAYOUT_TND) {
@@ -114,14 +113,41 @@ __device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i) {
   it.krow0 = row_info(s, it.row0).key_base;
   return it;
 }
+// `cum` (shared memory, dense mode only): cum[g] = chunks with keys of the row groups before g,
+// cum[groups] = their total, cum[kLiDenseGroups + 1] = key tiles per chunk.
+template <bool kDense>
+__device__ __forceinline__ LiItem li_item(const LiSm100Args& a, int32_t i, const int32_t* cum) {
+  if constexpr (kDense) {
+    if (i >= cum[a.groups]) {
+      LiItem none;
+      none.row0 = -1; none.nrows = 0; none.krow0 = 0; none.b = 0; none.chunk = 0;
+      return none;
+    }
+    int32_t lo = 0, hi = a.groups;          // largest g with cum[g] <= i
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (cum[mid] <= i) lo = mid; else hi = mid;
+    }
+    LiItem it = li_group(a, lo);
+    it.chunk = i - cum[lo];
+    return it;
+  }
+  // chunk-major: the first chunks exist for every sequence, later ones only for the long sequences,
+  // so work decreases with the item number as the snake order assumes
+  const int32_t chunk = i / a.groups;
+  LiItem it = li_group(a, i - chunk * a.groups);
+  it.chunk = chunk;
+  return it;
+}
 // j-th item of CTA c in snake order over a persistent grid of g CTAs (-1 when exhausted).
 __device__ __forceinline__ int32_t li_item_of(int32_t c, int32_t g, int32_t j, int32_t items) {
   const int32_t i = (j & 1) ? (j * g + (g - 1 - c)) : (j * g + c);
   return i < items ? i : -1;
 }
 // Visible key count of each of the item's rows and the item's key tiles [t0, t1); false if none.
+template <bool kDense>
 __device__ __forceinline__ bool li_item_range(const LiSm100Args& a, const LiItem& it, int32_t* vis, int32_t* t0,
-                                              int32_t* t1) {
+                                              int32_t* t1, const int32_t* cum) {
   int32_t mx = 0;
 #pragma unroll
   for (int t = 0; t < kLiTok; ++t) {
@@ -131,11 +157,15 @@ __device__ __forceinline__ bool li_item_range(const LiSm100Args& a, const LiItem
     mx = max(mx, v);
   }
   const int32_t tiles = (mx + kLiKeys - 1) / kLiKeys;
-  *t0 = it.chunk * a.chunk_tiles;
-  *t1 = min(tiles, *t0 + a.chunk_tiles);
+  const int32_t ct = kDense ? cum[kLiDenseGroups + 1] : a.chunk_tiles;
+  *t0 = it.chunk * ct;
+  *t1 = min(tiles, *t0 + ct);
   return *t1 > *t0;
 }
 
+// kDense: chunked mode over the list of chunks that hold keys (decode); compiled apart so that the
+// prefill instantiation carries none of it.
+template <bool kDense>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const LiSm100Args a) {
@@ -152,6 +182,7 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint64_t* wbar = bars + 16;       // epilogue-internal rendezvous around the weight staging
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 18);
+  int32_t* cum_s = reinterpret_cast<int32_t*>(li_smem + kLiOffCum);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t cta = blockIdx.x, grid = gridDim.x;
@@ -179,9 +210,39 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
   }
+  if constexpr (kDense) {
+    // li_dense_setup: key tiles of every row group (every CTA builds the same list)
+    for (int g = threadIdx.x; g < a.groups; g += kLiThreads) {
+      const LiItem it = li_group(a, g);
+      int32_t mx = 0;
+      if (it.row0 >= 0)
+        for (int t = 0; t < it.nrows; ++t) mx = max(mx, row_info(a.p.seq, it.row0 + t).visible);
+      cum_s[g + 1] = (mx + kLiKeys - 1) / kLiKeys;
+    }
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  if constexpr (kDense) {
+    // chunk size: about eight chunks of real work per CTA, at least 8 tiles each; then the running
+    // count of chunks per group.  The static round-robin over this list leaves the CTAs within one
+    // chunk of each other, where the (chunk, group) grid leaves them with whatever mix of full,
+    // partial and empty chunks the sequence lengths produce.
+    if (threadIdx.x == 0) {
+      int64_t total = 0;
+      for (int g = 0; g < a.groups; ++g) total += cum_s[g + 1];
+      int64_t ct = (total + 8ll * grid - 1) / (8ll * grid);
+      if (ct < 8) ct = 8;
+      int32_t acc = 0;
+      cum_s[0] = 0;
+      for (int g = 0; g < a.groups; ++g) {
+        acc += (int32_t)((cum_s[g + 1] + ct - 1) / ct);
+        cum_s[g + 1] = acc;
+      }
+      cum_s[kLiDenseGroups + 1] = (int32_t)ct;
+    }
+    __syncthreads();
+  }
   const uint32_t tmem = *tmem_slot;
   // Q of an item -> shared memory.  64 heads: one 256-row box per half and column block.  Fewer
   // heads (16..63): one box of n1 rows per token into the token's 64-row slot; the slot's other
@@ -226,10 +287,10 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         for (int32_t j = 0; ok; ++j) {
           const int32_t it = li_item_of(cta, grid, j, a.items);
           if (it < 0) break;
-          const LiItem item = li_item(a, it);
+          const LiItem item = li_item<kDense>(a, it, cum_s);
           if (item.row0 < 0) continue;
           int32_t t0, t1;
-          if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+          if (!li_item_range<kDense>(a, item, nullptr, &t0, &t1, cum_s)) continue;
           const int nh = item.nrows > kLiHalf ? 2 : 1;
           ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
           if (!ok) break;
@@ -252,10 +313,10 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int32_t j = 0; ok; ++j) {
       const int32_t it = li_item_of(cta, grid, j, a.items);
       if (it < 0) break;
-      const LiItem item = li_item(a, it);
+      const LiItem item = li_item<kDense>(a, it, cum_s);
       if (item.row0 < 0) continue;
       int32_t t0, t1;
-      if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+      if (!li_item_range<kDense>(a, item, nullptr, &t0, &t1, cum_s)) continue;
       const int nh = item.nrows > kLiHalf ? 2 : 1;
       if (lane == 0) {
         ok = ptx::mbar_wait(qempty, (n_item & 1) ^ 1, abort_flag);
@@ -307,10 +368,10 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       for (int32_t j = 0; ok; ++j) {
         const int32_t it = li_item_of(cta, grid, j, a.items);
         if (it < 0) break;
-        const LiItem item = li_item(a, it);
+        const LiItem item = li_item<kDense>(a, it, cum_s);
         if (item.row0 < 0) continue;
         int32_t t0, t1;
-        if (!li_item_range(a, item, nullptr, &t0, &t1)) continue;
+        if (!li_item_range<kDense>(a, item, nullptr, &t0, &t1, cum_s)) continue;
         const int nh = item.nrows > kLiHalf ? 2 : 1;
         const uint32_t idesc = item.nrows <= 2 ? a.idesc_n128 : a.idesc;
         ok = ptx::mbar_wait(qfull, n_item & 1, abort_flag);
@@ -358,10 +419,10 @@ li_score_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const int32_t it = li_item_of(cta, grid, j, a.items);
       if (it < 0) break;
       int32_t vis[kLiTok];
-      const LiItem item = li_item(a, it);
+      const LiItem item = li_item<kDense>(a, it, cum_s);
       if (item.row0 < 0) continue;
       int32_t t0, t1;
-      if (!li_item_range(a, item, vis, &t0, &t1)) continue;
+      if (!li_item_range<kDense>(a, item, vis, &t0, &t1, cum_s)) continue;
       const int nh = item.nrows > kLiHalf ? 2 : 1;
       const int32_t row0 = item.row0;
       // weights of the item's 8 rows -> shared memory (rows past the sequence end read as zero)
@@ -468,7 +529,9 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
     if (sm_count[dev].load(std::memory_order_relaxed) == 0) {
       int n = 0;
       if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return DSA_ERR_CUDA;
-      if (cudaFuncSetAttribute(li_score_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(li_score_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)kLiSmemBytes) != cudaSuccess ||
+          cudaFuncSetAttribute(li_score_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)kLiSmemBytes) != cudaSuccess)
         return DSA_ERR_CUDA;
       sm_count[dev].store(n, std::memory_order_release);
@@ -515,8 +578,13 @@ inline int li_sm100_launch(const DsaLiParams* p, const LiDev& d, float* scores, 
   a.krow_oob = (int32_t)p->key_rows;
   a.idesc = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 256, 0, 0);
   a.idesc_n128 = ptx::idesc_f16(bf16 ? 1u : 0u, 128, 128, 0, 0);
+  // chunked mode with few enough row groups: the kernel lists the chunks that hold keys itself
+  // (the lengths live on the device) and sizes them so that every CTA gets about eight
+  a.dense = (a.nchunks > 1 && groups <= kLiDenseGroups) ? 1 : 0;
+  if (a.dense) a.items = groups * ((tiles_max + 7) / 8);      // upper bound: chunks are at least 8 tiles
   const int grid = a.items < sms ? a.items : sms;
-  li_score_sm100_kernel<<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
+  if (a.dense) li_score_sm100_kernel<true><<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
+  else li_score_sm100_kernel<false><<<grid, kLiThreads, kLiSmemBytes, st>>>(tq, tk, a);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   count_launch();
   return DSA_OK;
