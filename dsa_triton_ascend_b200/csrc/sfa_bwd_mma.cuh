@@ -1,16 +1,17 @@
-// Sparse flash attention backward with the five contractions of a key chunk on the warp-level tensor
-// core instructions (mma.sync m16n8k16, fp32 accumulation), for D in {128, 256, 512}, D_rope = 64.  Same math and
-// the same block shape as sfa_bwd_simt_kernel (sparse_flash_attention_grad_triton.py:100-470, golden
-// sparse_flash_attention_grad_numpy.py:96-135): one block per (query row, 16 heads) walks over the
-// row's selected keys 32 at a time,
+// Sparse flash attention backward with the five contractions of a key chunk on the warp-level
+// tensor-core instructions (mma.sync m16n8k16, fp32 accumulation), for D in {128, 256, 512} and
+// D_rope = 64.  Same math as sfa_bwd_simt_kernel (sparse_flash_attention_grad_triton.py:100-470, golden
+// sparse_flash_attention_grad_numpy.py:96-135): one block per (query row, 16 or 32 heads) walks over
+// the row's selected keys 32 at a time,
 //     S  = q . k^T (D + 64 columns)       dP = dO . k_nope^T (D columns)
 //     P  = exp(S * scale - max) / sum     dS = P * (dP - delta) * scale
 //     dQ += dS . k        dK += dS^T . q        dV += P^T . dO
 // q, k and dO are multiplied as the io dtype they arrive in (exact products, fp32 sums).  P and dS
 // are fp32 values: each is split into a high and a low io-dtype part (x = hi + lo up to 2^-16
-// relative for bf16, 2^-22 for fp16) and every product with them runs twice, so the result carries
-// fp32-like precision where the reference rounds P and dS to the io dtype once.  dK / dV leave the
-// block as 16-byte fp32 reductions into the accumulators that sfa_bwd_finalize_kernel rounds.
+// relative for bf16, 2^-22 for fp16; fp16 parts are scaled per key chunk, see the kernel) and every
+// product with them runs twice, so the result carries fp32-like precision where the reference
+// rounds P and dS to the io dtype once.  dK / dV leave the block as 16-byte fp32 reductions into the
+// accumulators that sfa_bwd_finalize_kernel rounds.
 #pragma once
 
 #include "mma_sync.cuh"
