@@ -379,9 +379,14 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
   if (rows > 0 && cudaMemsetAsync(d.di, 0, 2 * buf_bytes, st) != cudaSuccess) return DSA_ERR_CUDA;
   if (rows > 0) {
     const int stride = std::max(p->d + p->d_rope, p->d_idx) + kSliPad;
-    const size_t smem_a = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
+    // teacher blocks of 32 heads when a side has more than 16 (half the key gathers per row)
+    const int hb = (d.n1 / d.n2 > kSliHeads || d.g > kSliHeads) ? 2 * kSliHeads : kSliHeads;
+    const size_t smem_a = (size_t)(hb + kSliTeacherKeys) * stride * sizeof(T);
+    const size_t smem_d = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
     const size_t smem_b = (size_t)(kSliHeads + kSliTeacherKeys) * (p->d_idx + kSliPad) * sizeof(T);
-    if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
+    if (cudaFuncSetAttribute(sli_teacher_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(sli_teacher_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
         cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
             cudaSuccess)
@@ -414,21 +419,22 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
     const bool pair_blocks = p->dense && grp < kSliHeads && kSliHeads % grp == 0;
     if (pair_blocks) {
       if (cudaFuncSetAttribute(sli_dense_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)smem_a) != cudaSuccess)
+                               (int)smem_d) != cudaSuccess)
         return DSA_ERR_CUDA;
       const int rpb = kSliHeads / grp;
       dim3 grid_d((unsigned)(p->batch * ((p->s1 + rpb - 1) / rpb)), (unsigned)d.n2, 1);
-      sli_dense_teacher_kernel<T><<<grid_d, kSliThreads, smem_a, st>>>(d, stride);
+      sli_dense_teacher_kernel<T><<<grid_d, kSliThreads, smem_d, st>>>(d, stride);
       if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
       count_launch();
     }
     SliGradDev dt = d;
     if (pair_blocks) dt.lse_only = 1;   // index chunks only
     const unsigned chunks_t =
-        (unsigned)((pair_blocks ? 0 : sli_att_chunks(d.n1, d.n2)) + (index_done ? 0 : sli_idx_chunks(d.g)));
+        (unsigned)((pair_blocks ? 0 : sli_att_chunks(d.n1, d.n2, hb)) + (index_done ? 0 : sli_idx_chunks(d.g, hb)));
     if (chunks_t > 0) {
       dim3 grid_t((unsigned)rows, chunks_t, 1);
-      sli_teacher_kernel<T><<<grid_t, kSliThreads, smem_a, st>>>(dt, stride);
+      if (hb > kSliHeads) sli_teacher_kernel<T, 2><<<grid_t, kSliThreads, smem_a, st>>>(dt, stride);
+      else sli_teacher_kernel<T, 1><<<grid_t, kSliThreads, smem_a, st>>>(dt, stride);
       if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
       count_launch();
     }
@@ -485,11 +491,16 @@ static int dense_lse_launch(const DsaDenseLseParams* p, float* scratch, int32_t*
   d.di = scratch;
   if (cudaMemsetAsync(scratch, 0, (size_t)rows * p->s2 * 4, st) != cudaSuccess) return DSA_ERR_CUDA;
   const int stride = p->d_idx + kSliPad;
-  const size_t smem = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
-  if (cudaFuncSetAttribute(sli_teacher_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  const int hb = p->g > kSliHeads ? 2 * kSliHeads : kSliHeads;
+  const size_t smem = (size_t)(hb + kSliTeacherKeys) * stride * sizeof(T);
+  if (cudaFuncSetAttribute(sli_teacher_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(sli_teacher_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess)
     return DSA_ERR_CUDA;
-  dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(p->g), 1);
-  sli_teacher_kernel<T><<<grid, kSliThreads, smem, st>>>(d, stride);
+  dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(p->g, hb), 1);
+  if (hb > kSliHeads) sli_teacher_kernel<T, 2><<<grid, kSliThreads, smem, st>>>(d, stride);
+  else sli_teacher_kernel<T, 1><<<grid, kSliThreads, smem, st>>>(d, stride);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
   sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
   if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;

@@ -103,9 +103,9 @@ __device__ __forceinline__ float sli_block_reduce(float v, float* red /*[8]*/, b
 // Stages `heads` rows of width `wa` (+ `wb` from a second tensor) into shared memory, zero past `have`.
 template <typename T>
 __device__ __forceinline__ void sli_stage_heads(T* dst, int stride, const T* a, int wa, const T* b, int wb, int h0,
-                                                int have) {
+                                                int have, int heads = kSliHeads) {
   const int w = wa + wb;
-  for (int i = threadIdx.x; i < kSliHeads * w; i += kSliThreads) {
+  for (int i = threadIdx.x; i < heads * w; i += kSliThreads) {
     const int h = i / w, c = i - h * w;
     T v = from_f32<T>(0.f);
     if (h0 + h < have) v = c < wa ? a[(int64_t)(h0 + h) * wa + c] : b[(int64_t)(h0 + h) * wb + (c - wa)];
@@ -166,22 +166,24 @@ __device__ __forceinline__ void sli_tile_scores(const T* qs, const T* ks, int st
   for (int e = 0; e < 4; ++e) out[e] = (cs[0][e] + cs[1][e]) + (cs[2][e] + cs[3][e]);
 }
 
-// Number of 16-head chunks of the attention side (per key head) and of the index side.
-__host__ __device__ inline int sli_att_chunks(int n1, int n2) { return n2 * ((n1 / n2 + kSliHeads - 1) / kSliHeads); }
-__host__ __device__ inline int sli_idx_chunks(int g) { return (g + kSliHeads - 1) / kSliHeads; }
+// Number of head chunks (of hb heads) of the attention side (per key head) and of the index side.
+__host__ __device__ inline int sli_att_chunks(int n1, int n2, int hb = kSliHeads) { return n2 * ((n1 / n2 + hb - 1) / hb); }
+__host__ __device__ inline int sli_idx_chunks(int g, int hb = kSliHeads) { return (g + hb - 1) / hb; }
 
 // grid = (rows, attention chunks + index chunks) (index chunks only when lse_only); block = 256.
-// dynamic smem: (16 + 64) * stride elements of T.  A block keeps its 16 heads in shared memory,
+// MT = 16-head tiles per block (HB = 16 MT heads: two tiles halve the key gathers per row).
+// dynamic smem: (HB + 64) * stride elements of T.  A block keeps its HB heads in shared memory,
 // walks over the row's keys 64 at a time (each warp scores one tile of 8 keys on the tensor cores)
 // and adds its heads' share of p[k] (attention chunks) or of I[k] (index chunks) into the row's fp32
 // buffers (zeroed by the caller).
-template <typename T>
+template <typename T, int MT>
 __global__ void __launch_bounds__(kSliThreads, 2) sli_teacher_kernel(SliGradDev p, int stride) {
+  constexpr int HB = kSliHeads * MT;
   extern __shared__ __align__(16) unsigned char sli_smem[];
   T* qs = reinterpret_cast<T*>(sli_smem);
-  T* ks = qs + kSliHeads * stride;
+  T* ks = qs + HB * stride;
   __shared__ int64_t rows_s[kSliTeacherKeys];
-  __shared__ float max_s[kSliHeads], inv_s[kSliHeads], w_s[kSliHeads];
+  __shared__ float max_s[HB], inv_s[HB], w_s[HB];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -193,17 +195,17 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_teacher_kernel(SliGradDev 
   const int32_t pos = row - b * p.s1;
   const int32_t* idx_row = dense ? nullptr : p.sparse_indices + (int64_t)row * p.topk;
   const int grp = p.n1 / p.n2;                    // query heads per attention key head
-  const int att_chunks = p.lse_only ? 0 : sli_att_chunks(p.n1, p.n2);
+  const int att_chunks = p.lse_only ? 0 : sli_att_chunks(p.n1, p.n2, HB);
   const int ch = blockIdx.y;
   const int phase = ch < att_chunks ? 0 : 1;      // 0: attention distribution p, 1: index scores I
   int kv = 0, h0, h_end;
   if (phase == 0) {
     const int cpk = att_chunks / p.n2;
     kv = ch / cpk;
-    h0 = kv * grp + (ch - kv * cpk) * kSliHeads;
+    h0 = kv * grp + (ch - kv * cpk) * HB;
     h_end = (kv + 1) * grp;
   } else {
-    h0 = (ch - att_chunks) * kSliHeads;
+    h0 = (ch - att_chunks) * HB;
     h_end = p.g;
   }
   const int w = phase == 0 ? p.d + p.d_rope : p.d_idx;
@@ -212,12 +214,12 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_teacher_kernel(SliGradDev 
   if (phase == 0) {
     const T* q = (const T*)p.query + (int64_t)row * p.n1 * p.d;
     const T* qr = p.d_rope ? (const T*)p.query_rope + (int64_t)row * p.n1 * p.d_rope : nullptr;
-    sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, h_end);
+    sli_stage_heads<T>(qs, stride, q, p.d, qr, p.d_rope, h0, h_end, HB);
   } else {
     sli_stage_heads<T>(qs, stride, (const T*)p.query_index + (int64_t)row * p.g * p.d_idx, p.d_idx, (const T*)nullptr, 0,
-                       h0, h_end);
+                       h0, h_end, HB);
   }
-  if (tid < kSliHeads) {
+  if (tid < HB) {
     const int h = h0 + tid;
     if (phase == 0) {
       const int64_t si = (((int64_t)b * p.n2 + kv) * p.s1 + pos) * grp + (h - kv * grp);   // [batch, n2, s1, grp]
@@ -241,16 +243,21 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_teacher_kernel(SliGradDev 
       sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s, 1, 0,
                          kSliTeacherKeys);
     __syncthreads();
-    float sc[4];
-    sli_tile_scores<T>(qs, ks, stride, w, warp * 8, sc);
-    // this thread: heads g and g + 8, keys 2c and 2c + 1 of the warp's tile; sum over the 16 heads
-    float t0, t1;
-    if (phase == 0) {
-      t0 = expf(sc[0] * p.scale - max_s[g]) * inv_s[g] + expf(sc[2] * p.scale - max_s[g + 8]) * inv_s[g + 8];
-      t1 = expf(sc[1] * p.scale - max_s[g]) * inv_s[g] + expf(sc[3] * p.scale - max_s[g + 8]) * inv_s[g + 8];
-    } else {
-      t0 = fmaxf(sc[0], 0.f) * w_s[g] + fmaxf(sc[2], 0.f) * w_s[g + 8];
-      t1 = fmaxf(sc[1], 0.f) * w_s[g] + fmaxf(sc[3], 0.f) * w_s[g + 8];
+    // this thread: heads g and g + 8 of every head tile, keys 2c and 2c + 1 of the warp's key tile;
+    // sum over the block's heads
+    float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float sc[4];
+      sli_tile_scores<T>(qs + mt * kSliHeads * stride, ks, stride, w, warp * 8, sc);
+      const int ha = mt * kSliHeads + g, hb = ha + 8;
+      if (phase == 0) {
+        t0 += expf(sc[0] * p.scale - max_s[ha]) * inv_s[ha] + expf(sc[2] * p.scale - max_s[hb]) * inv_s[hb];
+        t1 += expf(sc[1] * p.scale - max_s[ha]) * inv_s[ha] + expf(sc[3] * p.scale - max_s[hb]) * inv_s[hb];
+      } else {
+        t0 += fmaxf(sc[0], 0.f) * w_s[ha] + fmaxf(sc[2], 0.f) * w_s[hb];
+        t1 += fmaxf(sc[1], 0.f) * w_s[ha] + fmaxf(sc[3], 0.f) * w_s[hb];
+      }
     }
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
