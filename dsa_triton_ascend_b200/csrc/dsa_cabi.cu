@@ -383,12 +383,16 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
     const int hb = (d.n1 / d.n2 > kSliHeads || d.g > kSliHeads) ? 2 * kSliHeads : kSliHeads;
     const size_t smem_a = (size_t)(hb + kSliTeacherKeys) * stride * sizeof(T);
     const size_t smem_d = (size_t)(kSliHeads + kSliTeacherKeys) * stride * sizeof(T);
-    const size_t smem_b = (size_t)(kSliHeads + kSliTeacherKeys) * (p->d_idx + kSliPad) * sizeof(T);
+    // gradient blocks of 32 heads for d_idx = 128 (both head tiles' dQI accumulators fit in registers)
+    const int hg = (d.g > kSliHeads && p->d_idx == 128) ? 2 * kSliHeads : kSliHeads;
+    const size_t smem_b = (size_t)(hg + kSliTeacherKeys) * (p->d_idx + kSliPad) * sizeof(T);
     if (cudaFuncSetAttribute(sli_teacher_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
         cudaFuncSetAttribute(sli_teacher_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(sli_grad_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
+        cudaFuncSetAttribute(sli_grad_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(sli_grad_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b) !=
             cudaSuccess)
       return DSA_ERR_CUDA;
     // Dense operator: the index scores of all visible keys are the lightning indexer's scores; when
@@ -440,8 +444,9 @@ static int sli_grad_launch(const DsaSliGradParams* p, char* ws, int32_t* status,
     }
     sli_student_kernel<<<(unsigned)rows, kSliThreads, 0, st>>>(d);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
-    dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(d.g), 1);
-    sli_grad_kernel<T><<<grid, kSliThreads, smem_b, st>>>(d);
+    dim3 grid((unsigned)rows, (unsigned)sli_idx_chunks(d.g, hg), 1);
+    if (hg > kSliHeads) sli_grad_kernel<T, 2><<<grid, kSliThreads, smem_b, st>>>(d);
+    else sli_grad_kernel<T, 1><<<grid, kSliThreads, smem_b, st>>>(d);
     if (cudaGetLastError() != cudaSuccess) return DSA_ERR_CUDA;
     count_launch(2);
   }

@@ -393,45 +393,54 @@ __global__ void __launch_bounds__(kSliThreads) sli_student_kernel(SliGradDev p) 
   if (tid == 0) p.loss_parts[row] = kl;
 }
 
-// grid = (rows, ceil(g / 16)); block = 256.  dynamic smem: (16 + 64) * (d_idx + pad) elements of T.
+// MT = 16-head tiles per block (HB = 16 MT heads; two tiles only for d_idx = 128, where the dQI
+// accumulators of both fit in registers: half the steps, gathers and dKI reductions per row).
+// grid = (rows, ceil(g / HB)); block = 256.  dynamic smem: (HB + 64) * (d_idx + pad) elements of T.
 // Per step of 64 keys, all three products run on the tensor cores (mma.sync m16n8k16): the index
-// scores of the block's 16 heads (one 8-key tile per warp), dQI += ds . ki (each warp owns d_idx / 64
-// column tiles, accumulated in registers over the whole row) and dKI += ds^T . qi (a warp takes one
-// 16-key tile and half of the columns; its tiles leave as 16-byte fp32 reductions).  ds is an fp32
-// value: it enters the second and third product as a high and a low io-dtype part, for fp16 scaled
-// by a power of two per step so that neither part leaves the format's range.
-template <typename T>
+// scores of the block's heads (one 8-key tile per warp and head tile), dQI += ds . ki (each warp owns
+// d_idx / 64 column tiles of every head tile, accumulated in registers over the whole row) and
+// dKI += ds^T . qi (a warp takes one 16-key tile and half of the columns; its tiles leave as 16-byte
+// fp32 reductions).  ds is an fp32 value: it enters the second and third product as a high and a low
+// io-dtype part, for fp16 scaled by a power of two per step so that neither part leaves the format's
+// range.
+template <typename T, int MT>
 __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) {
   extern __shared__ __align__(16) unsigned char sli_smem[];
-  constexpr int KS = kSliTeacherKeys, PK = KS + 8, PH = kSliHeads + 8;
+  constexpr int HB = kSliHeads * MT;
+  constexpr int NTW = MT == 1 ? 8 : 2;     // most dQI column tiles per warp and head tile
+  constexpr int KS = kSliTeacherKeys, PK = KS + 8, PH = HB + 8;
   constexpr bool kScaled = sizeof(T) == 2 && !kIsBf16<T>;
   const int stride = p.d_idx + kSliPad;
   T* qs = reinterpret_cast<T*>(sli_smem);
-  T* ks = qs + kSliHeads * stride;
-  __shared__ __align__(16) T ds_hi[kSliHeads * PK], ds_lo[kSliHeads * PK];   // [head][key]
-  __shared__ __align__(16) T dst_hi[KS * PH], dst_lo[KS * PH];               // [key][head]
-  __shared__ float di_s[KS], w_s[kSliHeads], red_s[kSliThreads / 32], dw_s[kSliThreads / 32][kSliHeads];
+  T* ks = qs + HB * stride;
+  __shared__ __align__(16) T ds_hi[HB * PK], ds_lo[HB * PK];   // [head][key]
+  __shared__ __align__(16) T dst_hi[KS * PH], dst_lo[KS * PH]; // [key][head]
+  __shared__ float di_s[KS], w_s[HB], red_s[kSliThreads / 32], dw_s[kSliThreads / 32][HB];
   __shared__ int64_t rows_s[KS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int32_t row = blockIdx.x;
-  const int32_t h0 = blockIdx.y * kSliHeads;
+  const int32_t h0 = blockIdx.y * HB;
   int32_t b;
   const int32_t n = sli_row_slots(p, row, &b);
   const int ntw = p.d_idx / 64;           // dQI column tiles of this warp: columns 8 (warp * ntw + t) ..
-  float acc[8][4];
+  float acc[MT][NTW][4];
 #pragma unroll
-  for (int t = 0; t < 8; ++t)
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
-  float dw0 = 0.f, dw1 = 0.f;             // dW partial sums of heads g and g + 8
+    for (int t = 0; t < NTW; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mt][t][e] = 0.f;
+  float dw[MT][2];                        // dW partial sums of heads 16 mt + g and + 8
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) dw[mt][0] = dw[mt][1] = 0.f;
   int dq_exp = 127;                       // acc holds dQI * 2^dq_exp (fp16 only)
 
   if (n > 0) {
     const T* qi = (const T*)p.query_index + (int64_t)row * p.g * p.d_idx;
-    sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, p.g);
-    if (tid < kSliHeads) w_s[tid] = h0 + tid < p.g ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h0 + tid) : 0.f;
+    sli_stage_heads<T>(qs, stride, qi, p.d_idx, (const T*)nullptr, 0, h0, p.g, HB);
+    if (tid < HB) w_s[tid] = h0 + tid < p.g ? load_weight(p.weights, p.dtype_w, (int64_t)row * p.g + h0 + tid) : 0.f;
     const int32_t* idx_row = p.sparse_indices ? p.sparse_indices + (int64_t)row * p.topk : nullptr;
     const float* di = p.di + (int64_t)row * p.topk;
     for (int32_t j0 = 0; j0 < n; j0 += KS) {
@@ -444,21 +453,30 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
       __syncthreads();
       sli_gather_keys<T>(ks, stride, (const T*)p.key_index, p.d_idx, (const T*)nullptr, 0, rows_s, 1, 0, KS);
       __syncthreads();
-      float sc[4], dsv[4];
-      sli_tile_scores<T>(qs, ks, stride, p.d_idx, warp * 8, sc);
+      float dsv[MT][4];
       {
         const int k = warp * 8 + 2 * c;
         const float d0 = di_s[k], d1 = di_s[k + 1];
-        dw0 = fmaf(d0, fmaxf(sc[0], 0.f), fmaf(d1, fmaxf(sc[1], 0.f), dw0));
-        dw1 = fmaf(d0, fmaxf(sc[2], 0.f), fmaf(d1, fmaxf(sc[3], 0.f), dw1));
-        dsv[0] = sc[0] > 0.f ? d0 * w_s[g] : 0.f;
-        dsv[1] = sc[1] > 0.f ? d1 * w_s[g] : 0.f;
-        dsv[2] = sc[2] > 0.f ? d0 * w_s[g + 8] : 0.f;
-        dsv[3] = sc[3] > 0.f ? d1 * w_s[g + 8] : 0.f;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          float sc[4];
+          sli_tile_scores<T>(qs + mt * kSliHeads * stride, ks, stride, p.d_idx, warp * 8, sc);
+          const float wa = w_s[mt * kSliHeads + g], wb = w_s[mt * kSliHeads + g + 8];
+          dw[mt][0] = fmaf(d0, fmaxf(sc[0], 0.f), fmaf(d1, fmaxf(sc[1], 0.f), dw[mt][0]));
+          dw[mt][1] = fmaf(d0, fmaxf(sc[2], 0.f), fmaf(d1, fmaxf(sc[3], 0.f), dw[mt][1]));
+          dsv[mt][0] = sc[0] > 0.f ? d0 * wa : 0.f;
+          dsv[mt][1] = sc[1] > 0.f ? d1 * wa : 0.f;
+          dsv[mt][2] = sc[2] > 0.f ? d0 * wb : 0.f;
+          dsv[mt][3] = sc[3] > 0.f ? d1 * wb : 0.f;
+        }
       }
       float up_k = 1.f, up_q = 1.f, dk_down = 1.f;
       if constexpr (kScaled) {
-        float m = fmaxf(fmaxf(fabsf(dsv[0]), fabsf(dsv[1])), fmaxf(fabsf(dsv[2]), fabsf(dsv[3])));
+        float m = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) m = fmaxf(m, fabsf(dsv[mt][e]));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (lane == 0) red_s[warp] = m;
@@ -473,9 +491,11 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
         if (e < dq_exp) {                 // the accumulator follows the smallest scale seen so far
           const float f = scalbnf(1.f, e - dq_exp);
 #pragma unroll
-          for (int t = 0; t < 8; ++t)
+          for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int x = 0; x < 4; ++x) acc[t][x] *= f;
+            for (int t = 0; t < NTW; ++t)
+#pragma unroll
+              for (int x = 0; x < 4; ++x) acc[mt][t][x] *= f;
           dq_exp = e;
         }
         up_k = scalbnf(1.f, e);
@@ -483,47 +503,61 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
         dk_down = scalbnf(1.f, -e);
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h = g + (e >> 1) * 8, k = warp * 8 + 2 * c + (e & 1);
-        const float dk_ = dsv[e] * up_k, dq_ = dsv[e] * up_q;
-        const T kh = from_f32<T>(dk_), qh = from_f32<T>(dq_);
-        dst_hi[k * PH + h] = kh;
-        dst_lo[k * PH + h] = from_f32<T>(dk_ - to_f32<T>(kh));
-        ds_hi[h * PK + k] = qh;
-        ds_lo[h * PK + k] = from_f32<T>(dq_ - to_f32<T>(qh));
-      }
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = mt * kSliHeads + g + (e >> 1) * 8, k = warp * 8 + 2 * c + (e & 1);
+          const float dk_ = dsv[mt][e] * up_k, dq_ = dsv[mt][e] * up_q;
+          const T kh = from_f32<T>(dk_), qh = from_f32<T>(dq_);
+          dst_hi[k * PH + h] = kh;
+          dst_lo[k * PH + h] = from_f32<T>(dk_ - to_f32<T>(kh));
+          ds_hi[h * PK + k] = qh;
+          ds_lo[h * PK + k] = from_f32<T>(dq_ - to_f32<T>(qh));
+        }
       __syncthreads();
 
-      // dQI += ds . ki : 16 heads x (8 ntw) columns per warp, 64 keys deep
+      // dQI += ds . ki : HB heads x (8 ntw) columns per warp, 64 keys deep
 #pragma unroll
       for (int k0 = 0; k0 < KS; k0 += 16) {
-        uint32_t ah[4], al[4];
-        load_a_frag<T>(ah, ds_hi, PK, 0, k0);
-        load_a_frag<T>(al, ds_lo, PK, 0, k0);
+        uint32_t ah[MT][4], al[MT][4];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
+        for (int mt = 0; mt < MT; ++mt) {
+          load_a_frag<T>(ah[mt], ds_hi, PK, mt * kSliHeads, k0);
+          load_a_frag<T>(al[mt], ds_lo, PK, mt * kSliHeads, k0);
+        }
+#pragma unroll
+        for (int t = 0; t < NTW; ++t) {
           if (t < ntw) {
             uint32_t b0, b1;
             ldmatrix_b_trans<T>(b0, b1, &ks[k0 * stride + (warp * ntw + t) * 8], stride);
-            mma_16816<T>(acc[t], ah, b0, b1);
-            mma_16816<T>(acc[t], al, b0, b1);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_16816<T>(acc[mt][t], ah[mt], b0, b1);
+              mma_16816<T>(acc[mt][t], al[mt], b0, b1);
+            }
           }
         }
       }
-      // dKI += ds^T . qi : this warp's 16 keys x half of the columns, 16 heads deep
+      // dKI += ds^T . qi : this warp's 16 keys x half of the columns, HB heads deep
       {
-        const int mt = warp & 3, nhalf = warp >> 2, nt_half = p.d_idx / 16;
-        uint32_t ah[4], al[4];
-        load_a_frag<T>(ah, dst_hi, PH, mt * 16, 0);
-        load_a_frag<T>(al, dst_lo, PH, mt * 16, 0);
-        const int64_t r_lo = rows_s[mt * 16 + g], r_hi = rows_s[mt * 16 + g + 8];
+        const int kt = warp & 3, nhalf = warp >> 2, nt_half = p.d_idx / 16;
+        uint32_t ah[MT][4], al[MT][4];
+#pragma unroll
+        for (int hs = 0; hs < MT; ++hs) {
+          load_a_frag<T>(ah[hs], dst_hi, PH, kt * 16, hs * 16);
+          load_a_frag<T>(al[hs], dst_lo, PH, kt * 16, hs * 16);
+        }
+        const int64_t r_lo = rows_s[kt * 16 + g], r_hi = rows_s[kt * 16 + g + 8];
         for (int t = 0; t < nt_half; ++t) {
           const int n0 = (nhalf * nt_half + t) * 8;
-          uint32_t b0, b1;
-          ldmatrix_b_trans<T>(b0, b1, &qs[n0], stride);
           float cf[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_16816<T>(cf, ah, b0, b1);
-          mma_16816<T>(cf, al, b0, b1);
+#pragma unroll
+          for (int hs = 0; hs < MT; ++hs) {
+            uint32_t b0, b1;
+            ldmatrix_b_trans<T>(b0, b1, &qs[hs * 16 * stride + n0], stride);
+            mma_16816<T>(cf, ah[hs], b0, b1);
+            mma_16816<T>(cf, al[hs], b0, b1);
+          }
           if constexpr (kScaled) {
 #pragma unroll
             for (int x = 0; x < 4; ++x) cf[x] *= dk_down;
@@ -535,17 +569,23 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
   }
   // dW: sum over the four lanes that share a head, then over the warps; dQI of this head chunk
   // (zeros for unused rows)
-  dw0 += __shfl_xor_sync(0xffffffffu, dw0, 1);
-  dw0 += __shfl_xor_sync(0xffffffffu, dw0, 2);
-  dw1 += __shfl_xor_sync(0xffffffffu, dw1, 1);
-  dw1 += __shfl_xor_sync(0xffffffffu, dw1, 2);
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      dw[mt][u] += __shfl_xor_sync(0xffffffffu, dw[mt][u], 1);
+      dw[mt][u] += __shfl_xor_sync(0xffffffffu, dw[mt][u], 2);
+    }
   __syncthreads();
   if (c == 0) {
-    dw_s[warp][g] = dw0;
-    dw_s[warp][g + 8] = dw1;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      dw_s[warp][mt * kSliHeads + g] = dw[mt][0];
+      dw_s[warp][mt * kSliHeads + g + 8] = dw[mt][1];
+    }
   }
   __syncthreads();
-  if (tid < kSliHeads && h0 + tid < p.g) {
+  if (tid < HB && h0 + tid < p.g) {
     float sum = 0.f;
 #pragma unroll
     for (int wv = 0; wv < kSliThreads / 32; ++wv) sum += dw_s[wv][tid];
@@ -553,19 +593,21 @@ __global__ void __launch_bounds__(kSliThreads, 2) sli_grad_kernel(SliGradDev p) 
   }
   const float dq_down = kScaled ? scalbnf(1.f, -dq_exp) : 1.f;
 #pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    if (t < ntw) {
-      const int col = (warp * ntw + t) * 8 + 2 * c;
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int h = g + half * 8;
-        if (h0 + h >= p.g) continue;
-        T* dst = (T*)p.d_query_index + ((int64_t)row * p.g + h0 + h) * p.d_idx + col;
-        dst[0] = from_f32<T>(acc[t][2 * half] * dq_down);
-        dst[1] = from_f32<T>(acc[t][2 * half + 1] * dq_down);
+    for (int t = 0; t < NTW; ++t) {
+      if (t < ntw) {
+        const int col = (warp * ntw + t) * 8 + 2 * c;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int h = mt * kSliHeads + g + half * 8;
+          if (h0 + h >= p.g) continue;
+          T* dst = (T*)p.d_query_index + ((int64_t)row * p.g + h0 + h) * p.d_idx + col;
+          dst[0] = from_f32<T>(acc[mt][t][2 * half] * dq_down);
+          dst[1] = from_f32<T>(acc[mt][t][2 * half + 1] * dq_down);
+        }
       }
     }
-  }
 }
 
 // Dense softmax statistics from a row-major fp32 score matrix (leading dimension ld) that holds the
