@@ -91,9 +91,14 @@ class ClockSampler:
                         self.mask |= int(get_reasons(h))
                     except Exception:
                         pass
-                    time.sleep(0.004)
+                    time.sleep(0.008)
             self._thread = threading.Thread(target=loop, daemon=True)
             self._thread.start()
+            # the first queries of a process are the slow ones (milliseconds): have them done before
+            # the caller enters its timed region, where a host stall of that size shows at small steps
+            t_end = time.time() + 0.5
+            while not self.sm and time.time() < t_end:
+                time.sleep(0.002)
             return
         except Exception:
             self._thread = None
