@@ -23,6 +23,7 @@ reference goldens under oracle/, run over all host cores) on a bounded sample of
 workload and prints the same JSON line with "impl": "reference".
 """
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -405,6 +406,9 @@ def run_gpu(args):
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
     launches0 = int(_cabi.lib.dsa_kernel_launch_count())
+    # no collector pauses on the host while steps of about a millisecond are being enqueued (N = 8)
+    gc.collect()
+    gc.disable()
     t_wall = time.perf_counter()
     for s in range(args.steps):
         flush.fill_(s & 0xFF)  # evict L2 between timed iterations
@@ -415,6 +419,7 @@ def run_gpu(args):
         ev[s][2].record()
     barrier()
     t_wall = time.perf_counter() - t_wall
+    gc.enable()
     launches = int(_cabi.lib.dsa_kernel_launch_count()) - launches0
     clocks = sampler.stop()
     li_all = [e[0].elapsed_time(e[1]) for e in ev]
