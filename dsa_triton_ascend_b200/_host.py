@@ -32,7 +32,8 @@ def _cached_lengths(values, device):
     operator call); the same lengths (every layer and step of a fixed batch) are uploaded once.
     The tensors are never written; the one-time wait below makes a copy safe to read from any stream."""
     t = torch.tensor(values, dtype=torch.int32, device=device)
-    torch.cuda.current_stream(t.device).synchronize()
+    if t.is_cuda:
+        torch.cuda.current_stream(t.device).synchronize()
     return t
 
 

@@ -284,3 +284,19 @@ def test_dense_loss_guards_raise_like_the_reference():
     assert _cabi.lib.dsa_dense_li_lse_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
     assert n.value == 256 + 2 * 64 * 4
     assert _cabi.lib.dsa_dense_li_lse(ctypes.byref(p), None, 0, None) == -4
+
+
+def test_length_lists_are_uploaded_once():
+    """seq_tensor caches the device copy of a list of lengths (an upload per call stalls the stream);
+    tensors pass through untouched."""
+    import torch
+    from dsa_triton_ascend_b200 import _host
+    a, host_a = _host.seq_tensor([3, 5, 8], "cpu")
+    b, _ = _host.seq_tensor((3, 5, 8), "cpu")
+    c, _ = _host.seq_tensor([3, 5, 9], "cpu")
+    assert a is b and a is not c and host_a == [3, 5, 8]
+    assert a.dtype == torch.int32 and a.tolist() == [3, 5, 8] and c.tolist() == [3, 5, 9]
+    t = torch.tensor([1, 2], dtype=torch.int32)
+    d, host_d = _host.seq_tensor(t, "cpu")
+    assert d.tolist() == [1, 2] and host_d == [1, 2]
+    assert _host.seq_tensor(None, "cpu") == (None, None)
