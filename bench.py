@@ -743,7 +743,7 @@ def cpu_reference(sample_s=12.0, procs=None, lens=SEQ_LENS, topk=TOPK):
     import multiprocessing as mp
     procs = procs or len(os.sched_getaffinity(0))
     L = lens[0]
-    # a short calibration decides how many rows fit the time budget
+    # a short calibration decides how many rows fit the time limit
     t0, p0 = _cpu_sfa_rows((11, [L - 1], L, topk))
     n_sfa = max(procs, int(sample_s * 0.7 / max(t0, 1e-3)) * procs)
     tok = np.unique(np.linspace(0, L - 1, n_sfa).astype(int)).tolist()
